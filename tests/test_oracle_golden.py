@@ -1,0 +1,260 @@
+"""Pins the CPU oracle against the reference's own golden vectors (tests/golden/ref, copied from the reference's
+tests/data) and, where it was built, against the reference's CPU weight codec compiled from its own sources.
+
+Bit-exact wherever the arithmetic is ordered fp32 or integer; where the GPU-generated vectors depend on rsqrtf / tanhf /
+expf / sinf of the GPU (libm differs in the last bit on rare inputs), the gate is ">= 99.9 % identical and never more
+than one step apart", stated in each test.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle_lib as orc
+
+REF = os.path.join(os.path.dirname(__file__), "golden", "ref")
+
+
+def load(*p):
+    return np.load(os.path.join(REF, *p) + ".npy")
+
+
+def bf(a):
+    return (a.astype(np.uint32) << 16).view(np.float32)
+
+
+# ------------------------------------------------------------------ rotation + quantisation (bit-exact)
+
+@pytest.mark.parametrize("name", ["rot3072", "rot8192"])
+def test_rotate_quantize_matches_torch_vectors(name):
+    # tests/unit/test_quant_kernels.cu:384 (RotateQuantizeMatchesTorch)
+    q, s = orc.rotate_quantize(load("quant_kernels", name + "_x"))
+    assert np.array_equal(q, load("quant_kernels", name + "_q"))
+    assert np.array_equal(s.view(np.uint32), load("quant_kernels", name + "_s").view(np.uint32))
+
+
+@pytest.mark.parametrize("rows", [1, 5, 17, 40])
+def test_norm_modulate_rotate_quantize_matches_torch_vectors(rows):
+    # tests/unit/test_quant_kernels.cu:549-571. rsqrtf(GPU) vs 1/sqrt(CPU) may move single values by one step.
+    x = load("quant_kernels", f"norm{rows}_x")
+    q, s = orc.rms_norm_modulate_rotate_quantize(x, load("quant_kernels", "norm_weight"),
+                                                 load("quant_kernels", "norm_mod_scale"),
+                                                 load("quant_kernels", "norm_mod_shift"))
+    want_q, want_s = load("quant_kernels", f"norm{rows}_q"), load("quant_kernels", f"norm{rows}_s")
+    diff = np.abs(q.astype(np.int32) - want_q.astype(np.int32))
+    assert diff.max() <= 1
+    assert (diff == 0).mean() >= 0.999
+    assert np.allclose(s, want_s, rtol=2 ** -7, atol=0)
+    assert (s.view(np.uint32) == want_s.view(np.uint32)).mean() >= 0.8
+
+
+def test_norm_modulate_matches_torch_vectors():
+    # tests/unit/test_kernels_basic.cpp:137-141 (moss_mod_out)
+    y = orc.rms_norm_modulate(load("basic", "moss_norm_x"), load("basic", "moss_norm_w"), load("basic", "moss_mod_scale"),
+                              load("basic", "moss_mod_shift"))
+    want = load("basic", "moss_mod_out")
+    same = (y == want).mean()
+    assert same >= 0.999, same
+    assert np.abs(bf(y) - bf(want)).max() <= np.abs(bf(want)).max() * 2 ** -7
+
+
+@pytest.mark.parametrize("name", ["rot3072", "rot8192"])
+def test_int4_quantizer_matches_torch_vectors(name):
+    # tests/unit/test_quant4_kernels.cu:340-361: the inputs are hash tensors, regenerated here; outputs are eager torch's.
+    from tests import ref_inputs
+    x = ref_inputs.quant4_rot3072_input() if name == "rot3072" else ref_inputs.quant4_rot8192_input()
+    q4, s4 = orc.convrot_quantize_int4(x)
+    assert np.array_equal(q4, load("quant4", name + "_q"))
+    assert np.array_equal(s4.view(np.uint32), load("quant4", name + "_s").view(np.uint32))
+
+
+# ------------------------------------------------------------------ INT8 GEMM + epilogues (bit-exact)
+
+def _gemm_inputs():
+    g = lambda n: load("quant_kernels", "gemm_" + n)
+    return g("xq"), g("xs"), g("wq"), g("ws")
+
+
+def test_gemm_accumulators():
+    xq, xs, wq, ws = _gemm_inputs()
+    assert np.array_equal(orc.int8_gemm_acc(xq, wq), load("quant_kernels", "gemm_acc"))
+
+
+def test_gemm_plain_and_bias():
+    xq, xs, wq, ws = _gemm_inputs()
+    assert np.array_equal(orc.int8_gemm(xq, xs, wq, ws), load("quant_kernels", "gemm_y"))
+    assert np.array_equal(orc.int8_gemm(xq, xs, wq, ws, load("quant_kernels", "gemm_bias")),
+                          load("quant_kernels", "gemm_y_bias"))
+
+
+def test_gemm_gated_residual():
+    xq, xs, wq, ws = _gemm_inputs()
+    got = orc.int8_gemm_gated_residual(xq, xs, wq, ws, load("quant_kernels", "gemm_gate"),
+                                       load("quant_kernels", "gemm_residual"))
+    assert np.array_equal(got, load("quant_kernels", "gemm_res"))
+
+
+def test_gemm_situ_glu():
+    # tanhf / expf of the GPU vs libm: identical except rare last-bit cases.
+    xq, xs, wq, ws = _gemm_inputs()
+    got = orc.int8_gemm_situ_glu(xq, xs, wq, ws)
+    want = load("quant_kernels", "gemm_situ")
+    assert (got == want).mean() >= 0.999
+    assert np.abs(got.astype(np.int32) - want.astype(np.int32)).max() <= 1
+
+
+def test_situ_glu_elementwise():
+    # tests/unit/test_kernels_basic.cpp:198-203
+    got = orc.situ_glu(load("basic", "situ_up_gate"))
+    want = load("basic", "situ_out")
+    assert (got == want).mean() >= 0.999
+    assert np.abs(got.astype(np.int32) - want.astype(np.int32)).max() <= 1
+
+
+def test_int4_gemm_vectors_through_int8_route():
+    # tests/unit/test_quant4_kernels.cu + test_dit_int4.cpp:599: int4 operands sign-extended to int8 give the INT4 GEMM's
+    # results bit for bit.
+    g = lambda n: load("quant4", "gemm_" + n)
+    xq, wq = orc.unpack_int4(g("xq")), orc.unpack_int4(g("wq"))
+    assert np.array_equal(orc.int8_gemm(xq, g("xs"), wq, g("ws")), g("y"))
+    got = orc.int8_gemm_situ_glu(xq, g("xs"), wq, g("ws"))
+    assert (got == g("situ")).mean() >= 0.999
+
+
+def test_up_gate_row_permutation():
+    f = 16
+    rows = [orc.up_gate_row(n, f) for n in range(2 * f)]
+    assert rows[:8] == [0, 1, 2, 3, f, f + 1, f + 2, f + 3]
+    assert sorted(rows) == list(range(2 * f))
+
+
+# ------------------------------------------------------------------ weight codec (bit-exact, + the reference's code)
+
+@pytest.mark.parametrize("name", ["qz_syn_bf16", "qz_sft_l0_o", "qz_sft_l41_upgate", "qz_sft_l7_down", "qz_syn_g16",
+                                  "qz_syn_g64"])
+def test_weight_quantizer_matches_reference_rows(name):
+    # tests/unit/test_quant_format.cpp:161-266 (QuantCodec.*)
+    w, g = load("quant", name + "_w"), int(load("quant", name + "_g")[0])
+    q, s = orc.quantize_convrot_rows_bf16(w, g)
+    assert np.array_equal(q, load("quant", name + "_q"))
+    assert np.array_equal(s.view(np.uint32), load("quant", name + "_s").view(np.uint32))
+
+
+@pytest.mark.parametrize("name", ["w4a8_w4_g16", "w4a8_w4_uniform"])
+def test_grouped_decode_matches_reference(name):
+    packed = load("quant", name + "_packed").view(np.uint8)
+    bits, group = (int(v) for v in load("quant", name + "_meta"))
+    assert bits == 4
+    cb = load("quant", name + "_cb") if os.path.exists(os.path.join(REF, "quant", name + "_cb.npy")) else None
+    got = orc.decode_grouped_int8(packed, load("quant", name + "_srel"), group, cb)
+    assert np.array_equal(got, load("quant", name + "_int8"))
+
+
+def test_int4_unpack_matches_reference():
+    for name in ("w4a4_syn", "w4a4_all"):
+        got = orc.unpack_int4(load("quant", name + "_packed").view(np.uint8))
+        assert np.array_equal(got, load("quant", name + "_int8"))
+
+
+def test_against_reference_codec_sources():
+    ref = orc.ref_codec()
+    if ref is None:
+        pytest.skip("reference tree absent: oracle/_ref not built")
+    import ctypes as C
+    rng = np.random.default_rng(7)
+    w = (rng.standard_normal((24, 1024)).astype(np.float32) * 0.02).view(np.uint32) >> 16
+    w = w.astype(np.uint16)
+    q, s = orc.quantize_convrot_rows_bf16(w, 256)
+    rq, rs = np.empty_like(q), np.empty_like(s)
+    ref.ref_quantize_convrot_rows_bf16(w.ctypes.data_as(C.c_void_p), C.c_int64(24), C.c_int64(1024), C.c_int(256),
+                                       rq.ctypes.data_as(C.c_void_p), rs.ctypes.data_as(C.c_void_p))
+    assert np.array_equal(q, rq) and np.array_equal(s.view(np.uint32), rs.view(np.uint32))
+    packed = rng.integers(0, 256, (16, 256), dtype=np.uint8)
+    srel = rng.integers(0x20, 0x48, (16, 8), dtype=np.uint8)  # positive finite e4m3 values
+    got = orc.decode_grouped_int8(packed, srel, 64)
+    want = np.empty((16, 512), np.int8)
+    rc = ref.ref_decode_grouped_rows(packed.ctypes.data_as(C.c_void_p), srel.ctypes.data_as(C.c_void_p), None,
+                                     C.c_int64(16), C.c_int64(512), C.c_int(4), C.c_int(64),
+                                     want.ctypes.data_as(C.c_void_p))
+    assert rc == 0 and np.array_equal(got, want)
+    # fp16 group scales holding the same values decode identically (every e4m3 value is exact in fp16).
+    vals = np.array([ref.ref_e4m3_to_float(int(b)) for b in srel.ravel()], np.float32).reshape(srel.shape)
+    assert np.array_equal(orc.decode_grouped_int8(packed, vals.astype(np.float16).view(np.uint16), 64), want)
+
+
+# ------------------------------------------------------------------ QK norm + RoPE, RoPE table
+
+def test_rope_bands():
+    assert np.array_equal(orc.MOSS_ROPE_BANDS.view(np.uint32), load("basic", "moss_rope_bands").view(np.uint32))
+
+
+@pytest.mark.parametrize("case", range(4))
+def test_rope_table(case):
+    h, w, t = (int(v) for v in load("basic", f"moss_rope_case{case}_hwt"))
+    tab = orc.moss_rope_table(h, w, t)
+    rows = load("basic", f"moss_rope_case{case}_rows")
+    want = load("basic", f"moss_rope_case{case}_vals")
+    got = tab[rows]
+    # sinf / cosf of the GPU vs libm: last-bit differences on rare phases.
+    assert (got == want).mean() >= 0.995
+    assert np.abs(bf(got) - bf(want)).max() <= 2 ** -7
+
+
+def test_qk_norm_and_rope():
+    # rms_norm_moss on a [32, 24, 128] head view, then moss_rope_apply: the two halves of qk_norm_rope_moss.
+    x = load("basic", "moss_qnorm_x")
+    w = load("basic", "moss_qnorm_w")
+    tokens, heads, _ = x.shape
+    ones_tab = np.zeros((tokens, 128), np.uint16)
+    ones_tab[:, 64:] = 0x3F80  # sin 0, cos 1: RoPE is then the identity
+    qkv = np.concatenate([x.reshape(tokens, -1), x.reshape(tokens, -1)], axis=1)
+    got = orc.qk_norm_rope(qkv, heads, w, w, ones_tab)[:, :heads * 128].reshape(x.shape)
+    want = load("basic", "moss_qnorm_out")
+    assert (got == want).mean() >= 0.999
+    # RoPE alone: a unit norm weight cannot undo the norm, so check rope through its golden input/output directly.
+    q, tab, out = load("basic", "moss_rope_q"), load("basic", "moss_rope_tab"), load("basic", "moss_rope_out")
+    lo, hi = bf(q[..., :64]), bf(q[..., 64:])
+    si, co = bf(tab[:, None, :64]), bf(tab[:, None, 64:])
+    rb = lambda v: bf(_to_bf16(v))
+    new_lo = _to_bf16(rb(lo * co) + rb(-hi * si))
+    new_hi = _to_bf16(rb(hi * co) + rb(lo * si))
+    assert np.array_equal(np.concatenate([new_lo, new_hi], axis=-1), out)
+
+
+def _to_bf16(v):
+    u = np.ascontiguousarray(v, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+# ------------------------------------------------------------------ attention (tolerance: tests/unit/test_attention_q8.cu:281-290)
+
+def _metrics(got, want):
+    got, want = got.astype(np.float64).ravel(), want.astype(np.float64).ravel()
+    cos = float(got @ want / (np.linalg.norm(got) * np.linalg.norm(want)))
+    return cos, float(np.linalg.norm(got - want) / np.linalg.norm(want)), float(np.abs(got - want).max())
+
+
+def test_attention_against_float64_vectors():
+    q, k, v = (load("attention_q8", "oracle_" + n) for n in "qkv")
+    cu = load("attention_q8", "oracle_cu_seqlens")
+    total, heads, _ = q.shape
+    qkv = np.concatenate([a.reshape(total, -1) for a in (q, k, v)], axis=1)
+    scale = float(1.0 / np.sqrt(128.0))
+    out, _ = orc.attention_q8(qkv, cu, heads, int(np.diff(cu).max()), scale)
+    cos, rel, mx = _metrics(bf(out).reshape(total, heads, 128), load("attention_q8", "oracle_out"))
+    assert cos >= 0.998 and rel <= 0.06 and mx <= 0.25, (cos, rel, mx)
+    exact = orc.attention_exact(q, k, v, cu, scale)
+    cos, rel, mx = _metrics(exact, load("attention_q8", "oracle_out"))
+    assert cos >= 0.999999 and mx <= 1e-4, (cos, rel, mx)
+
+
+def test_attention_against_upstream_recording():
+    # tests/unit/test_attention_q8.cu:367-403: cos >= 0.99999, max|diff| <= 0.04 against upstream's int8_fp8_f32acc output.
+    q, k, v = (load("attention_q8", "upstream_" + n) for n in "qkv")
+    total, heads, _ = q.shape
+    qkv = np.concatenate([a.reshape(total, -1) for a in (q, k, v)], axis=1)
+    cu = np.array([0, 160, 320], np.int32)
+    out, _ = orc.attention_q8(qkv, cu, heads, 160, float(1.0 / np.sqrt(128.0)))
+    want = bf(load("attention_q8", "upstream_out_int8_fp8_f32acc"))
+    cos, rel, mx = _metrics(bf(out).reshape(total, heads, 128), want)
+    assert cos >= 0.99999 and mx <= 0.04, (cos, rel, mx)
