@@ -1,0 +1,263 @@
+/* owoinfer_b200 — C ABI of the B200 (sm_100a) implementation of the quantized MOSS-Image DiT block.
+ *
+ * Every entry point replaces one function of the reference engine's quantized-block path and keeps its argument
+ * order, preconditions and error behaviour; the reference symbol is cited above each declaration (paths inside the
+ * reference project). Conventions, mirrored from include/mossinfer/mossinfer.h:5-45,94-113:
+ *   - plain C: pointers, sizes, POD structs; no C++ type or exception crosses the boundary;
+ *   - every function returns a b2_status; on failure b2_last_error_message() holds a thread-local description;
+ *   - all data pointers are DEVICE pointers unless the name says host; row strides are in ELEMENTS;
+ *   - the caller owns all memory and passes the CUDA stream (a cudaStream_t passed as void*; NULL = default stream);
+ *   - no allocation and no host synchronisation on the hot path (the one-time SiTU table fill is the documented
+ *     exception, as in the reference);
+ *   - invalid arguments are rejected before any launch (B2_ERR_INVALID_ARGUMENT; the reference throws
+ *     std::invalid_argument), m == 0 is a no-op.
+ */
+#ifndef OWOINFER_B200_H_
+#define OWOINFER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes: the numeric values of mi_status (include/mossinfer/mossinfer.h:94-108) that this path can return. */
+typedef enum b2_status {
+  B2_OK = 0,
+  B2_ERR_INVALID_ARGUMENT = -1,
+  B2_ERR_NOT_SUPPORTED = -3,
+  B2_ERR_CUDA = -8,
+  B2_ERR_INTERNAL = -9
+} b2_status;
+
+/* mi_last_error_message (include/mossinfer/mossinfer.h:113): thread-local text of the last failure on this thread. */
+const char* b2_last_error_message(void);
+
+/* kInt8NumericsVersion (src/kernels/quant/quant.h:38), kInt4NumericsVersion (src/kernels/quant4/quant4.h:36),
+ * attention_q8::kNumericsVersion (src/kernels/attention_q8/attention_q8.h:78): which = 0, 1, 2. */
+uint32_t b2_numerics_version(int which);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Activation quantisers (bf16 in, int8 / packed int4 + one f32 scale per token out).
+ * ------------------------------------------------------------------------------------------------------------- */
+
+/* quant::rotate_quantize (src/kernels/quant/quant.h:48). x bf16 [m,k] stride ldx; q int8 [m,k] stride ldq; scale f32 [m].
+ * k % 256 == 0, k <= 32768, x and q 16-byte aligned, ldx % 8 == 0, ldq % 16 == 0. */
+int b2_rotate_quantize(const void* x, int64_t ldx, int8_t* q, int64_t ldq, float* scale, int64_t m, int k,
+                       void* stream);
+
+/* quant::rms_norm_modulate_rotate_quantize (src/kernels/quant/quant.h:62). norm_weight, mod_scale, mod_shift bf16 [k],
+ * 16-byte aligned. y (optional, may be NULL): bf16 [m,k] stride ldy receives the norm output. The mean of squares is
+ * summed in the order torch uses for an [m,k] input, which depends on m: call once per tensor the reference normalises. */
+int b2_rms_norm_modulate_rotate_quantize(const void* x, int64_t ldx, const void* norm_weight, const void* mod_scale,
+                                         const void* mod_shift, int8_t* q, int64_t ldq, float* scale, int64_t m, int k,
+                                         void* stream, void* y, int64_t ldy);
+
+/* quant4::convrot_quantize_int4 (src/kernels/quant4/quant4.h:45). q packed int4 [m,k/2] bytes, stride ldq bytes,
+ * even column in the low nibble. ldq % 16 == 0, ldq >= k/2. */
+int b2_convrot_quantize_int4(const void* x, int64_t ldx, uint8_t* q, int64_t ldq, float* scale, int64_t m, int k,
+                             void* stream);
+
+/* quant4::rms_norm_modulate_convrot_quantize_int4 (src/kernels/quant4/quant4.h:51). */
+int b2_rms_norm_modulate_convrot_quantize_int4(const void* x, int64_t ldx, const void* norm_weight,
+                                               const void* mod_scale, const void* mod_shift, uint8_t* q, int64_t ldq,
+                                               float* scale, int64_t m, int k, void* stream);
+
+/* moss_dit::unpack_int4 (src/models/moss_dit/dit_kernels.h:32): packed signed nibbles [rows,k/2] (stride ldp bytes) ->
+ * int8 [rows,k] (stride ldo). k % 32 == 0, 16-byte aligned rows. */
+int b2_unpack_int4(const void* packed, int64_t ldp, int8_t* out, int64_t ldo, int64_t rows, int64_t k, void* stream);
+
+/* quant::decode_grouped_int8 (src/kernels/quant/w4a8_decode.h:39), 4-bit codes only: packed [rows,k/2]; group scales
+ * s_rel [rows,k/group] as e4m3 bytes (scale_kind 0, the reference's format) or fp16 (scale_kind 1); codebook f32 [16]
+ * or NULL (level = code - 8); out int8 [rows,k]. group % 16 == 0, k % group == 0. */
+int b2_decode_grouped_int8(const void* packed, const void* s_rel, int scale_kind, const float* codebook, int64_t rows,
+                           int64_t k, int group, int8_t* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * INT8 x INT8 -> INT32 GEMM with fused epilogues.
+ * ------------------------------------------------------------------------------------------------------------- */
+
+/* quant::Int8Operands (src/kernels/quant/quant.h:82-89). x_q int8 [m,k] stride ldx with x_scale f32 [m]; w int8 [n,k]
+ * contiguous with w_scale f32 [n]. 16-byte aligned x_q, w, w_scale; k % 16 == 0; ldx % 16 == 0; 0 < k <= 131071. */
+typedef struct b2_int8_operands {
+  const int8_t* x_q;
+  int64_t ldx;
+  const float* x_scale;
+  const int8_t* w;
+  const float* w_scale;
+  int64_t m, n, k;
+} b2_int8_operands;
+
+/* quant::Int8Tile (src/kernels/quant/quant.h:77). The tcgen05 kernel has its own tiles; every tile gives the same
+ * bits (the int32 sum is exact). 0 = auto. */
+typedef enum b2_int8_tile { B2_TILE_AUTO = 0, B2_TILE_128x256 = 1, B2_TILE_128x128 = 2, B2_TILE_2CTA_256x256 = 3 } b2_int8_tile;
+
+/* quant::int8_gemm (src/kernels/quant/quant.h:92): out = bf16((acc * x_scale[r]) * w_scale[c] + bias[c]).
+ * bias bf16 [n] or NULL; out bf16 stride ldo, 16-byte aligned, ldo % 8 == 0, n % 8 == 0. */
+int b2_int8_gemm(const b2_int8_operands* op, const void* bias, void* out, int64_t ldo, void* stream, int tile);
+
+/* quant::int8_gemm_gated_residual (src/kernels/quant/quant.h:98): residual += bf16(bf16(y) * gate[c]) in place. */
+int b2_int8_gemm_gated_residual(const b2_int8_operands* op, const void* bias, const void* gate, void* residual,
+                                int64_t ldr, void* stream, int tile);
+
+/* quant::int8_gemm_situ_glu (src/kernels/quant/quant.h:110): w is [2F,k] stored [hidden | gate], op->n = 2F;
+ * out bf16 [m,F] stride ldo, 8-byte aligned, ldo % 4 == 0, F % 4 == 0. The first call on a device outside stream
+ * capture fills two 128 KiB factor tables on `stream` and synchronises it once. */
+int b2_int8_gemm_situ_glu(const b2_int8_operands* op, void* out, int64_t ldo, void* stream, int tile);
+
+/* The raw int32 accumulators of the same GEMM core, acc int32 [m,n] stride ldacc (the scalar oracle kernel of
+ * tests/unit/test_quant_kernels.cu:208-231 computes these; here the tensor-core kernel dumps its own). */
+int b2_int8_gemm_acc(const b2_int8_operands* op, int32_t* acc, int64_t ldacc, void* stream, int tile);
+
+/* W4A8 GEMM: 4-bit grouped weight codes decoded to the INT8 grid (b2_decode_grouped_int8's rule) and multiplied by
+ * INT8 activations; bit-identical to quant::decode_grouped_int8 followed by quant::int8_gemm
+ * (src/kernels/quant/w4a8_decode.h:1-39 + src/kernels/quant/quant.h:92). scratch: device int8 [n,k] for the decoded
+ * weight (caller-owned; may be reused across calls). epilogue: 0 plain (aux = bias or NULL), 1 gated residual
+ * (aux = gate, out = residual in place), 2 SiTU-GLU. */
+typedef struct b2_w4_weight {
+  const void* packed;   /* uint8 [n, k/2] */
+  const void* s_rel;    /* [n, k/group] e4m3 or fp16 */
+  int scale_kind;       /* 0 e4m3, 1 fp16 */
+  int group;
+  const float* codebook; /* f32 [16] or NULL */
+  const float* s_channel; /* f32 [n]: the GEMM's w_scale */
+} b2_w4_weight;
+int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_w4_weight* w, int64_t m, int64_t n,
+                 int64_t k, int epilogue, const void* aux, void* out, int64_t ldo, int8_t* scratch, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * QK-norm + RoPE, RoPE table, 8-bit attention.
+ * ------------------------------------------------------------------------------------------------------------- */
+
+/* kernels::fused::qk_norm_rope_moss (src/kernels/fused/qk_norm_rope.h:17). qkv bf16 [tokens, >= 2*heads*128] stride ld
+ * (q heads then k heads), rewritten in place; q_norm, k_norm bf16 [128]; table bf16 [tokens,128] = [sin64|cos64]. */
+int b2_qk_norm_rope_moss(void* qkv, int64_t ld, int64_t tokens, int heads, const void* q_norm, const void* k_norm,
+                         const void* table, int64_t table_ld, void* stream);
+
+/* kernels::moss_rope_table (src/kernels/basic/rope.h:37): out bf16 [height*width + text_length, 128] stride ld. */
+int b2_moss_rope_table(void* out, int64_t ld, int height, int width, int text_length, void* stream);
+
+/* attention_q8::Variant / Options (src/kernels/attention_q8/attention_q8.h:75-88). Only the e4m3 P·V variant with fp32
+ * accumulation (MI_ATTENTION_Q8_FP8_F32ACC, include/mossinfer/mossinfer.h:269) exists here: tcgen05 accumulates in
+ * fp32. p_range / v_range <= 0 pick 448 / 448. */
+#define B2_ATTENTION_Q8_FP8_F32ACC 3
+typedef struct b2_attention_options {
+  int variant;
+  float p_range;
+  float v_range;
+} b2_attention_options;
+
+/* A bf16 [tokens, heads, 128] view: element strides, head_dim contiguous (core/tensor.h:29-57 restricted to rank 3). */
+typedef struct b2_view3 {
+  void* data;
+  int64_t tokens, heads;
+  int64_t row_stride, head_stride;
+} b2_view3;
+
+/* attention_q8::QkNormRope (src/kernels/attention_q8/attention_q8.h:112-120). */
+typedef struct b2_qk_norm_rope {
+  const void* q_norm;
+  const void* k_norm;
+  const void* table;
+  int64_t table_ld;
+} b2_qk_norm_rope;
+
+/* attention_q8::attention_q8_workspace_bytes (src/kernels/attention_q8/attention_q8.h:98). */
+size_t b2_attention_q8_workspace_bytes(const b2_attention_options* o, int64_t total_q, int64_t total_k, int batch,
+                                       int max_seqlen, int num_heads, int num_kv_heads);
+
+/* attention_q8::attention_q8 (src/kernels/attention_q8/attention_q8.h:122). cu_seqlens_* device int32 [batch+1];
+ * workspace 256-byte aligned; scale finite > 0; norm_rope NULL or the fused QK-norm + RoPE (then k is rewritten in
+ * place and q's values are unspecified afterwards). Self-attention layouts only: num_heads == num_kv_heads. */
+int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
+                    const b2_view3* out, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
+                    int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
+                    const b2_qk_norm_rope* norm_rope);
+
+/* The workspace layout of attention_q8.cu:47-73 as this library carves it (byte offsets from the 256-byte aligned base),
+ * exposed so tests can compare the pre-pass outputs with the oracle: q_i8, k_i8 int8 and v8 e4m3 [total, heads, 128]
+ * (V stays in its natural layout: the tensor core reads it as an MN-major operand, so there is no transposed, padded or
+ * permuted copy); q_scale f32 [batch, heads, q_blocks]; k_scale f32 [batch, heads, k_blocks]; k_mean, v_scale, v_recp f32
+ * [batch, heads, 128]; part_sum, part_amax f32 [batch, heads, chunks, 128]. */
+typedef struct b2_attention_layout {
+  size_t q_i8, k_i8, v8, q_scale, k_scale, k_mean, v_scale, v_recp, part_sum, part_amax, total;
+  int64_t padded_k;
+  int q_blocks, k_blocks, chunks;
+} b2_attention_layout;
+int b2_attention_q8_layout(const b2_attention_options* o, int64_t total_q, int64_t total_k, int batch, int max_seqlen,
+                           int num_heads, int num_kv_heads, b2_attention_layout* out);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * The block and the step.
+ * ------------------------------------------------------------------------------------------------------------- */
+
+/* Int8Linear (src/models/moss_dit/dit_weights.h:75-79): w int8 [n,k] + scale f32 [n]. With tier == B2_TIER_W4A8 the
+ * `w4` member describes the packed weight instead and `w` is unused. */
+typedef struct b2_linear {
+  const int8_t* w;
+  const float* scale;
+  const b2_w4_weight* w4;
+} b2_linear;
+
+/* BlockTensors restricted to the all-quantized block (src/models/moss_dit/dit_weights.h:106-136). */
+typedef struct b2_block_weights {
+  size_t struct_size;
+  const void* norm1;   /* bf16 [D] */
+  const void* norm2;   /* bf16 [D] */
+  const void* q_norm;  /* bf16 [128] */
+  const void* k_norm;  /* bf16 [128] */
+  b2_linear qkv;       /* [3D, D] */
+  b2_linear o;         /* [D, D] */
+  b2_linear up_gate;   /* [2F, D], stored [hidden | gate] */
+  b2_linear down;      /* [D, F] */
+} b2_block_weights;
+
+#define B2_TIER_INT8 0        /* W8A8 ConvRot, the High tier */
+#define B2_TIER_W4A4_VIA_INT8 1 /* int4 weights + int4 activations in INT8 lanes (dit_block_quant.h:107-111) */
+#define B2_TIER_W4A8 2        /* grouped 4-bit weights decoded to INT8, INT8 activations */
+
+/* QuantBlockBuffers + BlockRun (src/models/moss_dit/dit_block_quant.h:77-105, dit_block_fused.h:120-165) for the
+ * all-INT8 route, with an activation layout owned by this library (the reference's `big` layout constants do not fit
+ * F = 12288). All buffers 256-byte aligned. */
+typedef struct b2_block_buffers {
+  size_t struct_size;
+  void* x;            /* bf16 [L, D] residual stream, updated in place */
+  const void* mod;    /* bf16 [6*D]: shift_a, scale_a, gate_a, shift_f, scale_f, gate_f */
+  const void* rope;   /* bf16 [L, 128] */
+  void* workspace;    /* b2_block_quant_workspace_bytes() */
+  size_t workspace_bytes;
+} b2_block_buffers;
+
+typedef struct b2_block_run {
+  size_t struct_size;
+  int64_t tokens;            /* L: rows of x in this run */
+  int D, F, heads;           /* 3072, 8192 | 12288, 24 */
+  const int32_t* cu_seqlens; /* device int32 [batch+1] */
+  int batch;
+  int max_seqlen;
+  int tier;                  /* B2_TIER_* */
+  b2_attention_options attention;
+  int fused_norm_rope;       /* -1 auto (>= 3072 tokens, dit_block_quant.cpp:32-35), 0 separate kernel, 1 in the pre-pass */
+} b2_block_run;
+
+size_t b2_block_quant_workspace_bytes(const b2_block_run* run);
+
+/* moss_dit::run_block_quant (src/models/moss_dit/dit_block_quant.h:145), all-quantized route with 8-bit attention. */
+int b2_run_block_quant(const b2_block_weights* w, const b2_block_buffers* a, const b2_block_run* run, void* stream);
+
+/* The block loop of MossDit::forward (src/models/moss_dit/moss_dit.cpp:1427-1460): blocks[i] applied in order to x,
+ * mods[i] the per-block modulation (the reference shares one vector; pass the same pointer). */
+int b2_dit_step(const b2_block_weights* blocks, int num_blocks, const b2_block_buffers* a, const b2_block_run* run,
+                void* stream);
+
+/* Every mbarrier wait inside the tensor-core kernels is bounded; a CTA whose wait expired raises a device word, drains
+ * and returns instead of hanging. This reads the two words (GEMM, attention): 0 = no wait ever expired on this device.
+ * Synchronises the device; for tests and post-mortems, not for the hot path. No counterpart in the reference (its
+ * kernels have no device-side waits). */
+int b2_kernel_status(int* gemm, int* attention);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OWOINFER_B200_H_ */

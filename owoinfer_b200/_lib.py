@@ -1,0 +1,105 @@
+"""Loads libowoinfer_b200.so and declares its C ABI for ctypes. Fails loudly when the library is missing: there is no
+CPU or PyTorch fallback on the product path."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libowoinfer_b200.so")
+
+# Every symbol include/owoinfer_b200.h declares (tests check that the library exports each of them).
+EXPORTS = [
+    "b2_last_error_message", "b2_numerics_version", "b2_rotate_quantize", "b2_rms_norm_modulate_rotate_quantize",
+    "b2_convrot_quantize_int4", "b2_rms_norm_modulate_convrot_quantize_int4", "b2_unpack_int4", "b2_decode_grouped_int8",
+    "b2_int8_gemm", "b2_int8_gemm_gated_residual", "b2_int8_gemm_situ_glu", "b2_int8_gemm_acc", "b2_w4a8_gemm",
+    "b2_qk_norm_rope_moss", "b2_moss_rope_table", "b2_attention_q8_workspace_bytes", "b2_attention_q8",
+    "b2_attention_q8_layout", "b2_block_quant_workspace_bytes", "b2_run_block_quant", "b2_dit_step",
+    "b2_kernel_status",
+]
+
+
+class Int8Operands(C.Structure):
+    _fields_ = [("x_q", C.c_void_p), ("ldx", C.c_int64), ("x_scale", C.c_void_p), ("w", C.c_void_p),
+                ("w_scale", C.c_void_p), ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64)]
+
+
+class W4Weight(C.Structure):
+    _fields_ = [("packed", C.c_void_p), ("s_rel", C.c_void_p), ("scale_kind", C.c_int), ("group", C.c_int),
+                ("codebook", C.c_void_p), ("s_channel", C.c_void_p)]
+
+
+class AttentionOptions(C.Structure):
+    _fields_ = [("variant", C.c_int), ("p_range", C.c_float), ("v_range", C.c_float)]
+
+
+class View3(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("tokens", C.c_int64), ("heads", C.c_int64), ("row_stride", C.c_int64),
+                ("head_stride", C.c_int64)]
+
+
+class QkNormRope(C.Structure):
+    _fields_ = [("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("table", C.c_void_p), ("table_ld", C.c_int64)]
+
+
+class AttentionLayout(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in ("q_i8", "k_i8", "v8", "q_scale", "k_scale", "k_mean", "v_scale", "v_recp",
+                                          "part_sum", "part_amax", "total")] + \
+               [("padded_k", C.c_int64), ("q_blocks", C.c_int), ("k_blocks", C.c_int), ("chunks", C.c_int)]
+
+
+class Linear(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("scale", C.c_void_p), ("w4", C.POINTER(W4Weight))]
+
+
+class BlockWeights(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("norm1", C.c_void_p), ("norm2", C.c_void_p), ("q_norm", C.c_void_p),
+                ("k_norm", C.c_void_p), ("qkv", Linear), ("o", Linear), ("up_gate", Linear), ("down", Linear)]
+
+
+class BlockBuffers(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("x", C.c_void_p), ("mod", C.c_void_p), ("rope", C.c_void_p),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+class BlockRun(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("tokens", C.c_int64), ("D", C.c_int), ("F", C.c_int), ("heads", C.c_int),
+                ("cu_seqlens", C.c_void_p), ("batch", C.c_int), ("max_seqlen", C.c_int), ("tier", C.c_int),
+                ("attention", AttentionOptions), ("fused_norm_rope", C.c_int)]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m owoinfer_b200.build` "
+                               "(there is no fallback path)")
+        l = C.CDLL(LIB_PATH)
+        l.b2_last_error_message.restype = C.c_char_p
+        l.b2_numerics_version.restype = C.c_uint32
+        l.b2_attention_q8_workspace_bytes.restype = C.c_size_t
+        l.b2_attention_q8_workspace_bytes.argtypes = [C.POINTER(AttentionOptions), C.c_int64, C.c_int64, C.c_int, C.c_int,
+                                                      C.c_int, C.c_int]
+        l.b2_block_quant_workspace_bytes.restype = C.c_size_t
+        l.b2_block_quant_workspace_bytes.argtypes = [C.POINTER(BlockRun)]
+        _lib = l
+    return _lib
+
+
+class B2Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"[{status}] {message}")
+        self.status = status
+
+
+def check(status: int) -> None:
+    """Maps a b2_status to the exception the reference would throw: -1 -> ValueError (std::invalid_argument)."""
+    if status == 0:
+        return
+    msg = lib().b2_last_error_message().decode()
+    if status == -1:
+        raise ValueError(msg)
+    raise B2Error(status, msg)

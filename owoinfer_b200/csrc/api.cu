@@ -1,0 +1,79 @@
+// Host plumbing of the C ABI: thread-local error text, device queries, TMA tensor-map construction.
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace b2 {
+namespace {
+thread_local std::string g_last_error;
+}
+
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+
+int fail_status(int status, const char* op, const std::string& msg) {
+  g_last_error = std::string("owoinfer_b200::") + op + ": " + msg;
+  return status;
+}
+int fail_invalid(const char* op, const std::string& msg) { return fail_status(B2_ERR_INVALID_ARGUMENT, op, msg); }
+int fail_cuda(const char* op, cudaError_t e) {
+  return fail_status(B2_ERR_CUDA, op, std::string("CUDA error: ") + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")");
+}
+
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+bool make_tensor_map_2d(CUtensorMap* map, const void* base, std::uint64_t inner, std::uint64_t rows,
+                        std::uint64_t row_stride, std::uint32_t inner_box, std::uint32_t row_box, const char* op) {
+  static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q{};
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    }
+  });
+  if (encode == nullptr) {
+    fail_status(B2_ERR_CUDA, op, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {row_stride};
+  const cuuint32_t box[2] = {inner_box, row_box};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fail_status(B2_ERR_CUDA, op, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)) +
+                                     " (inner " + std::to_string(inner) + ", rows " + std::to_string(rows) + ", stride " +
+                                     std::to_string(row_stride) + ")");
+    return false;
+  }
+  return true;
+}
+
+}  // namespace b2
+
+extern "C" {
+
+const char* b2_last_error_message(void) { return b2::g_last_error.c_str(); }
+
+uint32_t b2_numerics_version(int which) {
+  (void)which;
+  return 1;
+}
+
+}  // extern "C"

@@ -1,0 +1,906 @@
+// SageAttention-style 8-bit attention for sm_100a, plus the MOSS QK-norm + RoPE and RoPE-table kernels that feed it.
+//
+//   pre-pass (HBM-bound, 128-bit accesses)
+//     stats      per (512-key chunk, head, sequence): partial per-channel K sums and V |max| in a fixed order; with the
+//                fused prologue also RMS-norm + RoPE of q and k (k written back), and Q quantised per (32 tokens, head)
+//     finalize   k_mean = bf16(sum / len); v_scale = amax / v_range; v_recp = v_range / amax
+//     quantise   Q per (32 tokens, head) [when not fused]; K - k_mean per (64 keys, head) -> int8; V * v_recp -> e4m3
+//   attention (tensor-core-bound): one CTA per (128 query rows, head, sequence); 128-key tiles
+//     S = Q8 · K8^T   tcgen05.mma kind::i8, int32 accumulator in TMEM (exact)
+//     softmax         4 warps, one row per thread: S -> fp32 (round toward zero), scaled by
+//                     sm_scale * log2e * q_scale * k_scale[64-key block], running max / denominator in fp32, P = exp2(.)
+//                     shifted so that its maximum is 2^floor3(log2(p_range)), rounded to e4m3 into a swizzled shared tile
+//     O += P8 · V8    tcgen05.mma kind::f8f6f4, fp32 accumulator in TMEM; V is read in its natural [key, channel]
+//                     layout as an MN-major operand, so the pre-pass needs no transpose
+//     out = O / d * v_scale[channel] -> bf16
+// Reference semantics: src/kernels/attention_q8/attention_q8.h:1-127, q8_preprocess.cu:67-385,
+// third_party/sageattention/csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:54-743 (variant kInt8Fp8F32Acc);
+// src/kernels/fused/qk_norm_rope.cu:43-89; src/kernels/basic/rope.cu:30-51.
+#include <algorithm>
+#include <cmath>
+#include <string>
+
+#include "common.cuh"
+
+namespace b2 {
+namespace {
+
+constexpr int kHeadDim = 128;
+constexpr int kStatsChunk = 512;
+constexpr std::size_t kAlign = 256;
+
+__device__ int g_attn_status = 0;
+
+__device__ __forceinline__ std::uint64_t global_ns() {
+  std::uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool wait_bar(std::uint32_t bar, std::uint32_t parity, volatile int* abort_word) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const std::uint64_t t0 = global_ns();
+  for (std::uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 0u) {
+      if (*abort_word != 0) return false;
+      if (global_ns() - t0 > 1000000000ull) {
+        *abort_word = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* x) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const std::uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = __uint_as_float(w[i] << 16);
+    x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* x) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  x[0] = __uint_as_float(raw.x << 16), x[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+  x[2] = __uint_as_float(raw.y << 16), x[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+}
+__device__ __forceinline__ std::uint32_t pack_bf2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const std::uint32_t*>(&h);
+}
+__device__ __forceinline__ std::int32_t f2i8(float v) {
+  std::int32_t r;
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ std::uint32_t pack_i8x4(float a, float b, float c, float d) {
+  return (static_cast<std::uint32_t>(f2i8(a)) & 0xFF) | ((static_cast<std::uint32_t>(f2i8(b)) & 0xFF) << 8) |
+         ((static_cast<std::uint32_t>(f2i8(c)) & 0xFF) << 16) | ((static_cast<std::uint32_t>(f2i8(d)) & 0xFF) << 24);
+}
+// Two floats -> two e4m3 bytes (round to nearest even, saturate to +-448): `lo` in the low byte.
+__device__ __forceinline__ std::uint32_t e4m3x2(float lo, float hi) {
+  std::uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ std::uint32_t e4m3x4(float a, float b, float c, float d) { return e4m3x2(a, b) | (e4m3x2(c, d) << 16); }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// QK-norm + RoPE (standalone) and the RoPE table.
+// ---------------------------------------------------------------------------------------------------------------
+struct NormRopeArgs {
+  __nv_bfloat16* qkv;
+  std::int64_t ld;
+  const __nv_bfloat16* q_norm;
+  const __nv_bfloat16* k_norm;
+  const __nv_bfloat16* table;
+  std::int64_t table_ld;
+  std::int64_t tokens;
+  int heads;
+  float factor;
+};
+
+// One warp per (token, q-or-k head), lane l holding channels 4l..4l+3: the quad sum then the shuffle-down tree are the
+// order of torch's reduce for a 128-wide row. RoPE pairs channel d with d + 64, i.e. lane l with lane l ^ 16.
+__global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeArgs a) {
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const std::int64_t items = a.tokens * 2 * a.heads;
+  const std::int64_t stride = static_cast<std::int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (std::int64_t item = static_cast<std::int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); item < items;
+       item += stride) {
+    const std::int64_t token = item / (2 * a.heads);
+    const int head = static_cast<int>(item % (2 * a.heads));
+    __nv_bfloat16* p = a.qkv + token * a.ld + static_cast<std::int64_t>(head) * kHeadDim + 4 * lane;
+    float x[4], w[4], si[4], co[4];
+    load4(p, x);
+    load4((head < a.heads ? a.q_norm : a.k_norm) + 4 * lane, w);
+    const __nv_bfloat16* tab = a.table + token * a.table_ld + 4 * (lane & 15);
+    load4(tab, si);
+    load4(tab + 64, co);
+    float v = fadd(fadd(fadd(fmul(x[0], x[0]), fmul(x[1], x[1])), fmul(x[2], x[2])), fmul(x[3], x[3]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fadd(v, __shfl_down_sync(0xffffffffu, v, off));
+    const float r = rsqrtf(fadd(fmul(__shfl_sync(0xffffffffu, v, 0), a.factor), 1e-6f));
+    const bool lo_half = lane < 16;
+    float o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float y = rbf(fmul(rbf(fmul(x[i], r)), w[i]));
+      const float other = __shfl_xor_sync(0xffffffffu, y, 16);
+      const float lo = lo_half ? y : other, hi = lo_half ? other : y;
+      o[i] = lo_half ? fadd(rbf(fmul(lo, co[i])), rbf(fmul(-hi, si[i]))) : fadd(rbf(fmul(hi, co[i])), rbf(fmul(lo, si[i])));
+    }
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]));
+  }
+}
+
+struct RopeBands {
+  float v[16];
+};
+// 1 / 1e4^(i/16), i = 0..15, as fp32 (fp32 pow, then fp32 reciprocal).
+constexpr RopeBands kBands = {{1.f, 0.562341332f, 0.316227764f, 0.177827939f, 0.100000001f, 0.0562341288f, 0.0316227786f,
+                               0.0177827943f, 0.00999999978f, 0.00562341325f, 0.00316227786f, 0.00177827943f,
+                               0.00100000005f, 0.000562341302f, 0.000316227786f, 0.00017782794f}};
+
+// One thread per table element: row r, column c; columns 0..63 hold sin, 64..127 cos, over (axis, band) = (c % 64 / 16,
+// c % 16); image tokens (r < height * width) have coordinates (0, text_length, row - (H-1)/2, col - (W-1)/2), text token i
+// has (0, i, 0, 0).
+__global__ void rope_table_kernel(__nv_bfloat16* out, std::int64_t ld, std::int64_t n, int height, int width,
+                                  int text_length, const RopeBands bands) {
+  const std::int64_t hw = static_cast<std::int64_t>(height) * width;
+  const float h_mid = static_cast<float>((height - 1) / 2.0), w_mid = static_cast<float>((width - 1) / 2.0);
+  const std::int64_t total = n * 128;
+  for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<std::int64_t>(gridDim.x) * blockDim.x) {
+    const std::int64_t r = i >> 7;
+    const int c = static_cast<int>(i & 127), pz = c & 63, axis = pz >> 4, band = pz & 15;
+    float coord = 0.f;
+    if (r < hw) {
+      if (axis == 1) coord = static_cast<float>(text_length);
+      if (axis == 2) coord = __fsub_rn(static_cast<float>(r / width), h_mid);
+      if (axis == 3) coord = __fsub_rn(static_cast<float>(r % width), w_mid);
+    } else if (axis == 1) {
+      coord = static_cast<float>(r - hw);
+    }
+    const float phase = fmul(coord, bands.v[band]);
+    out[r * ld + c] = __float2bfloat16_rn(c < 64 ? sinf(phase) : cosf(phase));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Pre-pass.
+// ---------------------------------------------------------------------------------------------------------------
+struct PrepArgs {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  std::int64_t q_row, q_head, k_row, k_head, v_row, v_head;
+  const int* cu;
+  int batch, heads, max_seqlen, chunks, q_blocks, k_blocks;
+  float v_range;
+  // fused prologue
+  const __nv_bfloat16* q_norm;
+  const __nv_bfloat16* k_norm;
+  const __nv_bfloat16* table;
+  std::int64_t table_row;
+  float norm_factor;
+  // outputs
+  std::int8_t* q_i8;
+  std::int8_t* k_i8;
+  std::uint8_t* v8;
+  float* q_scale;
+  float* k_scale;
+  float* k_mean;
+  float* v_scale;
+  float* v_recp;
+  float* part_sum;
+  float* part_amax;
+};
+
+// RMS-norm + RoPE of one (token, head) row held by 16 lanes x 8 channels (two of the 32 quads of the standalone kernel
+// per lane: its shuffle tree 16, 8, 4, 2, 1 becomes 8, 4, 2, 1 per quad and a final add of the two at lane 0).
+__device__ __forceinline__ void norm_rope_row(const float* x, const float* w, const float* si, const float* co,
+                                              float factor, int lane16, float* y) {
+  float quad[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float* e = x + 4 * h;
+    quad[h] = fadd(fadd(fadd(fmul(e[0], e[0]), fmul(e[1], e[1])), fmul(e[2], e[2])), fmul(e[3], e[3]));
+  }
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) quad[h] = fadd(quad[h], __shfl_down_sync(0xffffffffu, quad[h], off, 16));
+  }
+  const float total = __shfl_sync(0xffffffffu, fadd(quad[0], quad[1]), 0, 16);
+  const float r = rsqrtf(fadd(fmul(total, factor), 1e-6f));
+  const bool lo_half = lane16 < 8;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float n = rbf(fmul(rbf(fmul(x[j], r)), w[j]));
+    const float other = __shfl_xor_sync(0xffffffffu, n, 8, 16);
+    const float lo = lo_half ? n : other, hi = lo_half ? other : n;
+    y[j] = lo_half ? rbf(fadd(rbf(fmul(lo, co[j])), rbf(fmul(-hi, si[j])))) : rbf(fadd(rbf(fmul(hi, co[j])), rbf(fmul(lo, si[j]))));
+  }
+}
+
+// CTA = 16 token rows x 16 lanes x 8 channels, one (512-key chunk, head, sequence). Row-thread `row` adds tokens
+// row, row + 16, ... of the chunk in order; the 16 partials are then added in order, and the finalize kernel adds the
+// chunks in order: the K mean is reproducible and independent of the launch shape.
+template <bool kFused>
+__global__ void __launch_bounds__(256) stats_kernel(const PrepArgs p) {
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int lane = static_cast<int>(threadIdx.x) & 15, row = static_cast<int>(threadIdx.x) >> 4, warp = static_cast<int>(threadIdx.x) >> 5;
+  const int start = p.cu[b], len = p.cu[b + 1] - start;
+  float sum[8] = {}, amax[8] = {};
+  __shared__ float s_red[16][kHeadDim];
+  __shared__ float s_wmax[2][8];
+
+  if constexpr (kFused) {
+    float wq[8], wk[8];
+    load8(p.q_norm + lane * 8, wq);
+    load8(p.k_norm + lane * 8, wk);
+    const int pair = (lane & 7) * 8;
+    for (int step0 = 0; step0 < kStatsChunk / 16; step0 += 2) {
+      const int block_start = c * kStatsChunk + step0 * 16;
+      if (block_start >= len) {
+        // Q blocks at or past the sequence end hold no tokens: their scale is the empty block's.
+        if (threadIdx.x == 0) {
+          const int end = min(p.q_blocks, (c + 1) * kStatsChunk / 32);
+          for (int bx = block_start / 32; bx < end; ++bx) {
+            p.q_scale[(static_cast<std::int64_t>(b) * p.heads + h) * p.q_blocks + bx] = 0.0000001f / 127.0f;
+          }
+        }
+        break;
+      }
+      float qy[2][8];
+      float qmax = 0.0000001f;
+      bool valid[2];
+      std::int64_t tok[2];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const int t = block_start + s * 16 + row;
+        valid[s] = t < len;
+        tok[s] = static_cast<std::int64_t>(start) + t;
+        float x[8], si[8], co[8], ky[8];
+        if (valid[s]) {
+          load8(p.table + tok[s] * p.table_row + pair, si);
+          load8(p.table + tok[s] * p.table_row + 64 + pair, co);
+          load8(p.q + tok[s] * p.q_row + h * p.q_head + lane * 8, x);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) x[j] = si[j] = co[j] = 0.f;
+        }
+        norm_rope_row(x, wq, si, co, p.norm_factor, lane, qy[s]);
+        if (valid[s]) {
+          load8(p.k + tok[s] * p.k_row + h * p.k_head + lane * 8, x);
+        }
+        norm_rope_row(x, wk, si, co, p.norm_factor, lane, ky);
+        if (valid[s]) {
+          *reinterpret_cast<uint4*>(p.k + tok[s] * p.k_row + h * p.k_head + lane * 8) =
+              make_uint4(pack_bf2(ky[0], ky[1]), pack_bf2(ky[2], ky[3]), pack_bf2(ky[4], ky[5]), pack_bf2(ky[6], ky[7]));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sum[j] += ky[j];
+          load8(p.v + tok[s] * p.v_row + h * p.v_head + lane * 8, x);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) amax[j] = fmaxf(amax[j], fabsf(x[j]));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qmax = fmaxf(qmax, fabsf(qy[s][j]));
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) qmax = fmaxf(qmax, __shfl_xor_sync(0xffffffffu, qmax, off));
+      const int buf = (step0 >> 1) & 1;
+      if ((threadIdx.x & 31) == 0) s_wmax[buf][warp] = qmax;
+      __syncthreads();
+      float block_max = s_wmax[buf][0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) block_max = fmaxf(block_max, s_wmax[buf][i]);
+      const int bx = block_start / 32;
+      if (threadIdx.x == 0 && bx < p.q_blocks) {
+        p.q_scale[(static_cast<std::int64_t>(b) * p.heads + h) * p.q_blocks + bx] = block_max / 127.0f;
+      }
+      const float qs = 127.0f / block_max;
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        if (!valid[s]) continue;
+        *reinterpret_cast<uint2*>(p.q_i8 + (tok[s] * p.heads + h) * kHeadDim + lane * 8) =
+            make_uint2(pack_i8x4(qy[s][0] * qs, qy[s][1] * qs, qy[s][2] * qs, qy[s][3] * qs),
+                       pack_i8x4(qy[s][4] * qs, qy[s][5] * qs, qy[s][6] * qs, qy[s][7] * qs));
+      }
+    }
+  } else {
+    const int t_end = min(len, (c + 1) * kStatsChunk);
+    for (int t = c * kStatsChunk + row; t < t_end; t += 16) {
+      float x[8];
+      const std::int64_t tok = static_cast<std::int64_t>(start) + t;
+      load8(p.k + tok * p.k_row + h * p.k_head + lane * 8, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum[j] += x[j];
+      load8(p.v + tok * p.v_row + h * p.v_head + lane * 8, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax[j] = fmaxf(amax[j], fabsf(x[j]));
+    }
+  }
+
+  const std::int64_t at = ((static_cast<std::int64_t>(b) * p.heads + h) * p.chunks + c) * kHeadDim + threadIdx.x;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s_red[row][lane * 8 + j] = sum[j];
+  __syncthreads();
+  if (threadIdx.x < kHeadDim) {
+    float s = 0.f;
+    for (int r = 0; r < 16; ++r) s += s_red[r][threadIdx.x];
+    p.part_sum[at] = s;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s_red[row][lane * 8 + j] = amax[j];
+  __syncthreads();
+  if (threadIdx.x < kHeadDim) {
+    float m = 0.f;
+    for (int r = 0; r < 16; ++r) m = fmaxf(m, s_red[r][threadIdx.x]);
+    p.part_amax[at] = m;
+  }
+}
+
+__global__ void __launch_bounds__(kHeadDim) finalize_kernel(const PrepArgs p) {
+  const int h = blockIdx.x, b = blockIdx.y, ch = threadIdx.x;
+  const int len = p.cu[b + 1] - p.cu[b];
+  const std::int64_t base = (static_cast<std::int64_t>(b) * p.heads + h) * p.chunks * kHeadDim + ch;
+  float s = 0.f, a = 0.f;
+  for (int c = 0; c < p.chunks; ++c) {
+    s += p.part_sum[base + static_cast<std::int64_t>(c) * kHeadDim];
+    a = fmaxf(a, p.part_amax[base + static_cast<std::int64_t>(c) * kHeadDim]);
+  }
+  const std::int64_t at = (static_cast<std::int64_t>(b) * p.heads + h) * kHeadDim + ch;
+  p.k_mean[at] = len > 0 ? rbf(s / static_cast<float>(len)) : 0.f;
+  p.v_scale[at] = a > 0.f ? a / p.v_range : 1.f;
+  p.v_recp[at] = a > 0.f ? p.v_range / a : 1.f;
+}
+
+// Q per (32 tokens, head): amax floored at 1e-7, scale = amax / 127, q = rni(x * (127 / amax)). CTA = 32 rows x 16 lanes.
+__global__ void __launch_bounds__(512) quant_q_kernel(const PrepArgs p) {
+  const int bx = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int lane = static_cast<int>(threadIdx.x) & 15, row = static_cast<int>(threadIdx.x) >> 4;
+  const int start = p.cu[b], len = p.cu[b + 1] - start;
+  const int t = bx * 32 + row;
+  const bool valid = t < len;
+  float x[8] = {};
+  const std::int64_t tok = static_cast<std::int64_t>(start) + t;
+  if (valid) load8(p.q + tok * p.q_row + h * p.q_head + lane * 8, x);
+  float amax = 0.0000001f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  __shared__ float s_w[16];
+  if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = s_w[0];
+#pragma unroll
+  for (int i = 1; i < 16; ++i) amax = fmaxf(amax, s_w[i]);
+  if (threadIdx.x == 0) p.q_scale[(static_cast<std::int64_t>(b) * p.heads + h) * p.q_blocks + bx] = amax / 127.0f;
+  if (!valid) return;
+  const float qs = 127.0f / amax;
+  *reinterpret_cast<uint2*>(p.q_i8 + (tok * p.heads + h) * kHeadDim + lane * 8) =
+      make_uint2(pack_i8x4(x[0] * qs, x[1] * qs, x[2] * qs, x[3] * qs), pack_i8x4(x[4] * qs, x[5] * qs, x[6] * qs, x[7] * qs));
+}
+
+// K and V of one (64 keys, head): K - mean -> int8 with one scale; V * v_recp -> e4m3. CTA = 64 rows x 16 lanes (1024).
+__global__ void __launch_bounds__(1024) quant_kv_kernel(const PrepArgs p) {
+  const int bx = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int lane = static_cast<int>(threadIdx.x) & 15, row = static_cast<int>(threadIdx.x) >> 4;
+  const int start = p.cu[b], len = p.cu[b + 1] - start;
+  const int t = bx * 64 + row;
+  const bool valid = t < len;
+  const std::int64_t tok = static_cast<std::int64_t>(start) + t;
+  const std::int64_t stat = (static_cast<std::int64_t>(b) * p.heads + h) * kHeadDim + lane * 8;
+  float x[8] = {};
+  if (valid) {
+    load8(p.k + tok * p.k_row + h * p.k_head + lane * 8, x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] -= p.k_mean[stat + j];
+  }
+  float amax = 0.0000001f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  __shared__ float s_w[32];
+  if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = s_w[0];
+#pragma unroll
+  for (int i = 1; i < 32; ++i) amax = fmaxf(amax, s_w[i]);
+  if (threadIdx.x == 0) p.k_scale[(static_cast<std::int64_t>(b) * p.heads + h) * p.k_blocks + bx] = amax / 127.0f;
+  if (!valid) return;
+  const float ks = 127.0f / amax;
+  const std::int64_t o = (tok * p.heads + h) * kHeadDim + lane * 8;
+  *reinterpret_cast<uint2*>(p.k_i8 + o) =
+      make_uint2(pack_i8x4(x[0] * ks, x[1] * ks, x[2] * ks, x[3] * ks), pack_i8x4(x[4] * ks, x[5] * ks, x[6] * ks, x[7] * ks));
+  float v[8];
+  load8(p.v + tok * p.v_row + h * p.v_head + lane * 8, v);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] *= p.v_recp[stat + j];
+  *reinterpret_cast<uint2*>(p.v8 + o) = make_uint2(e4m3x4(v[0], v[1], v[2], v[3]), e4m3x4(v[4], v[5], v[6], v[7]));
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The attention kernel.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kTileQ = 128, kTileK = 128;
+constexpr int kKvStages = 2;
+constexpr int kTileBytes = 128 * 128;
+constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 1) + 1024;  // Q, K/V stages, P, alignment slack
+constexpr int kAttnThreads = 192;
+constexpr std::uint32_t kTmemCols = 256;  // S: columns [0, 128); O: columns [128, 256)
+
+struct AttnArgs {
+  const float* q_scale;
+  const float* k_scale;
+  const float* v_scale;
+  const int* cu_q;
+  const int* cu_k;
+  __nv_bfloat16* out;
+  std::int64_t out_row, out_head;
+  int heads, q_blocks, k_blocks;
+  float scale_log2;  // sm_scale * log2(e)
+  float p_offset;
+};
+
+__global__ void __launch_bounds__(kAttnThreads)
+attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const AttnArgs a) {
+  const int bq = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q_start = a.cu_q[b], qo_len = a.cu_q[b + 1] - q_start;
+  const int k_start = a.cu_k[b], kv_len = a.cu_k[b + 1] - k_start;
+  const int q0 = bq * kTileQ;
+  if (q0 >= qo_len) return;  // uniform per CTA, before any barrier or allocation
+  const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
+  if (kv_len == 0) {
+    // No keys: zero output rows.
+    const int rows = min(kTileQ, qo_len - q0);
+    for (int i = threadIdx.x; i < rows * 16; i += blockDim.x) {
+      __nv_bfloat16* o = a.out + static_cast<std::int64_t>(q_start + q0 + i / 16) * a.out_row + h * a.out_head + (i % 16) * 8;
+      *reinterpret_cast<uint4*>(o) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+
+  extern __shared__ std::uint8_t smem_raw[];
+  __shared__ __align__(8) std::uint64_t s_q_full, s_k_full[kKvStages], s_k_empty[kKvStages], s_v_full[kKvStages],
+      s_v_empty[kKvStages], s_s_full, s_p_full, s_pv_done;
+  __shared__ std::uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  const std::uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const std::uint32_t q_smem = base;
+  const auto k_smem = [&](int s) { return base + kTileBytes * (1 + s); };
+  const auto v_smem = [&](int s) { return base + kTileBytes * (1 + kKvStages + s); };
+  const std::uint32_t p_smem = base + kTileBytes * (1 + 2 * kKvStages);
+  std::uint8_t* p_generic = smem_raw + (p_smem - smem_u32(smem_raw));
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&s_q_full), 1);
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(smem_u32(&s_k_full[s]), 1);
+      mbar_init(smem_u32(&s_k_empty[s]), 1);
+      mbar_init(smem_u32(&s_v_full[s]), 1);
+      mbar_init(smem_u32(&s_v_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&s_s_full), 1);
+    mbar_init(smem_u32(&s_p_full), 4);
+    mbar_init(smem_u32(&s_pv_done), 1);
+    s_abort = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&s_tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const std::uint32_t tmem_s = s_tmem_base, tmem_o = s_tmem_base + 128;
+  volatile int* abort_word = &s_abort;
+  const int n_tiles = (kv_len + kTileK - 1) / kTileK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&s_q_full), kTileBytes);
+      tma_load_2d(q_smem, &map_q, smem_u32(&s_q_full), h * kHeadDim, q_start + q0);
+      for (int t = 0; t < n_tiles && *abort_word == 0; ++t) {
+        const int s = t % kKvStages;
+        const std::uint32_t ph = (t / kKvStages) & 1u;
+        if (!wait_bar(smem_u32(&s_k_empty[s]), ph ^ 1u, abort_word)) break;
+        mbar_expect_tx(smem_u32(&s_k_full[s]), kTileBytes);
+        tma_load_2d(k_smem(s), &map_k, smem_u32(&s_k_full[s]), h * kHeadDim, k_start + t * kTileK);
+        if (!wait_bar(smem_u32(&s_v_empty[s]), ph ^ 1u, abort_word)) break;
+        mbar_expect_tx(smem_u32(&s_v_full[s]), kTileBytes);
+        tma_load_2d(v_smem(s), &map_v, smem_u32(&s_v_full[s]), h * kHeadDim, k_start + t * kTileK);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr std::uint32_t idesc_qk = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, 128, 128);
+      constexpr std::uint32_t idesc_pv = umma_idesc(/*f32*/ 1, /*e4m3*/ 0, /*e4m3*/ 0, 0, /*B MN-major*/ 1, 128, 128);
+      const auto issue_qk = [&](int t) -> bool {
+        const int s = t % kKvStages;
+        if (!wait_bar(smem_u32(&s_k_full[s]), (t / kKvStages) & 1u, abort_word)) return false;
+        tc_fence_after();
+        const std::uint64_t dq = umma_desc_sw128(q_smem), dk = umma_desc_sw128(k_smem(s));
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) umma_i8(tmem_s, dq + 2u * k4, dk + 2u * k4, idesc_qk, k4 != 0 ? 1u : 0u);
+        tc_commit(smem_u32(&s_k_empty[s]));
+        tc_commit(smem_u32(&s_s_full));
+        return true;
+      };
+      bool ok = wait_bar(smem_u32(&s_q_full), 0, abort_word) && issue_qk(0);
+      for (int t = 0; ok && t < n_tiles; ++t) {
+        const int s = t % kKvStages;
+        if (!wait_bar(smem_u32(&s_p_full), t & 1u, abort_word)) break;  // P(t) written, S(t) consumed
+        if (t + 1 < n_tiles && !issue_qk(t + 1)) break;
+        if (!wait_bar(smem_u32(&s_v_full[s]), (t / kKvStages) & 1u, abort_word)) break;
+        tc_fence_after();
+        const std::uint64_t dp = umma_desc_sw128(p_smem), dv = umma_desc_sw128(v_smem(s));
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          // P: 32 keys = 32 bytes along K inside the swizzle atom (+2); V (MN-major): 32 key rows of 128 bytes (+256).
+          umma_f8(tmem_o, dp + 2u * k4, dv + 256u * k4, idesc_pv, (t | k4) != 0 ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&s_v_empty[s]));
+        tc_commit(smem_u32(&s_pv_done));
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int r_local = quarter * 32 + lane;  // row of the tile == TMEM lane
+    const std::uint32_t lane_off = static_cast<std::uint32_t>(quarter * 32) << 16;
+    const std::int64_t sc_base = static_cast<std::int64_t>(b) * a.heads + h;
+    const float qs = a.q_scale[sc_base * a.q_blocks + (q0 + quarter * 32) / 32] * a.scale_log2;
+    float m_run = -5000000.0f, d_run = 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      if (!wait_bar(smem_u32(&s_s_full), t & 1u, abort_word)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const float c0 = qs * a.k_scale[sc_base * a.k_blocks + 2 * t];
+      const float c1 = (2 * t + 1 < a.k_blocks) ? qs * a.k_scale[sc_base * a.k_blocks + 2 * t + 1] : 0.f;
+      const int valid = min(kTileK, kv_len - t * kTileK);
+      // Pass 1: row maximum of the scaled scores over the valid keys.
+      float mx = -5000000.0f;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        std::uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_off + cc * 32, r);
+        tmem_ld_wait();
+        const float c = cc < 2 ? c0 : c1;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float sv = __int2float_rz(static_cast<int>(r[i])) * c;
+          if (cc * 32 + i < valid) mx = fmaxf(mx, sv);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx - a.p_offset);
+      const float alpha = ex2(m_run - m_new);
+      // O (and the denominator) follow the running maximum. PV(t-1) must have landed before O is touched or P reused.
+      if (t > 0) {
+        if (!wait_bar(smem_u32(&s_pv_done), (t - 1) & 1u, abort_word)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            std::uint32_t r[32];
+            tmem_ld_32x32(tmem_o + lane_off + cc * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(tmem_o + lane_off + cc * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      d_run *= alpha;
+      m_run = m_new;
+      // Pass 2: P = exp2(score - m), denominator from the unrounded P, e4m3 P into the swizzled tile (row = 128 bytes,
+      // 16-byte chunk j of row r stored at chunk j ^ (r % 8)).
+      std::uint8_t* prow = p_generic + r_local * 128;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        std::uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_off + cc * 32, r);
+        tmem_ld_wait();
+        const float c = cc < 2 ? c0 : c1;
+        float pv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float e = ex2(fmaf(__int2float_rz(static_cast<int>(r[i])), c, -m_run));
+          pv[i] = (cc * 32 + i < valid) ? e : 0.f;
+          d_run += pv[i];
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int chunk = (cc * 2 + j) ^ (r_local & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) =
+              make_uint4(e4m3x4(pv[16 * j + 0], pv[16 * j + 1], pv[16 * j + 2], pv[16 * j + 3]),
+                         e4m3x4(pv[16 * j + 4], pv[16 * j + 5], pv[16 * j + 6], pv[16 * j + 7]),
+                         e4m3x4(pv[16 * j + 8], pv[16 * j + 9], pv[16 * j + 10], pv[16 * j + 11]),
+                         e4m3x4(pv[16 * j + 12], pv[16 * j + 13], pv[16 * j + 14], pv[16 * j + 15]));
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_p_full));
+    }
+    if (ok && wait_bar(smem_u32(&s_pv_done), (n_tiles - 1) & 1u, abort_word)) {
+      tc_fence_after();
+      const float inv_d = rcp_approx(d_run);
+      const int row = q0 + r_local;
+      __nv_bfloat16* orow = a.out + static_cast<std::int64_t>(q_start + row) * a.out_row + h * a.out_head;
+      const float* vs = a.v_scale + sc_base * kHeadDim;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        std::uint32_t r[32];
+        tmem_ld_32x32(tmem_o + lane_off + cc * 32, r);
+        tmem_ld_wait();
+        if (row < qo_len) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[8 * v + i]) * inv_d * __ldg(vs + cc * 32 + 8 * v + i);
+            *reinterpret_cast<uint4*>(orow + cc * 32 + 8 * v) =
+                make_uint4(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]), pack_bf2(o[4], o[5]), pack_bf2(o[6], o[7]));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (s_abort != 0) {
+    if (threadIdx.x == 0) atomicExch(&g_attn_status, 1);
+    const std::uint64_t t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(s_tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Host.
+// ---------------------------------------------------------------------------------------------------------------
+std::size_t align_up(std::size_t n) { return (n + kAlign - 1) / kAlign * kAlign; }
+
+b2_attention_layout make_layout(std::int64_t total_q, std::int64_t total_k, int batch, int max_seqlen, int heads, int kv_heads) {
+  b2_attention_layout l{};
+  const auto n = [](std::int64_t v) { return static_cast<std::size_t>(v); };
+  l.padded_k = total_k;
+  l.q_blocks = (max_seqlen + 127) / 128 * 4;
+  l.k_blocks = (max_seqlen + 63) / 64;
+  l.chunks = (max_seqlen + kStatsChunk - 1) / kStatsChunk;
+  std::size_t at = 0;
+  const auto take = [&](std::size_t bytes) {
+    const std::size_t off = at;
+    at += align_up(bytes);
+    return off;
+  };
+  l.q_i8 = take(n(total_q) * n(heads) * kHeadDim);
+  l.k_i8 = take(n(total_k) * n(kv_heads) * kHeadDim);
+  l.v8 = take(n(total_k) * n(kv_heads) * kHeadDim);
+  l.q_scale = take(n(batch) * n(heads) * n(l.q_blocks) * 4);
+  l.k_scale = take(n(batch) * n(kv_heads) * n(l.k_blocks) * 4);
+  l.k_mean = take(n(batch) * n(kv_heads) * kHeadDim * 4);
+  l.v_scale = take(n(batch) * n(kv_heads) * kHeadDim * 4);
+  l.v_recp = take(n(batch) * n(kv_heads) * kHeadDim * 4);
+  l.part_sum = take(n(batch) * n(kv_heads) * n(l.chunks) * kHeadDim * 4);
+  l.part_amax = take(n(batch) * n(kv_heads) * n(l.chunks) * kHeadDim * 4);
+  l.total = at;
+  return l;
+}
+
+int check_view(const char* op, const b2_view3* t, const char* name) {
+  if (t == nullptr || t->tokens < 0 || t->heads <= 0) return fail_invalid(op, std::string(name) + " must be a bf16 [tokens, heads, 128] view");
+  if (t->row_stride % 8 != 0 || t->head_stride % 8 != 0 || !aligned_to(t->data, 16) || (t->tokens > 0 && t->data == nullptr)) {
+    return fail_invalid(op, std::string(name) + " needs a 16-byte aligned base and row/head strides that are multiples of 8");
+  }
+  return B2_OK;
+}
+
+float resolve(float v) { return v > 0 ? v : 448.f; }
+
+}  // namespace
+
+int attn_status_word(int* host_value) {
+  const cudaError_t e = cudaMemcpyFromSymbol(host_value, g_attn_status, sizeof(int));
+  return e == cudaSuccess ? B2_OK : fail_cuda("attention_status", e);
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" {
+
+int b2_qk_norm_rope_moss(void* qkv, int64_t ld, int64_t tokens, int heads, const void* q_norm, const void* k_norm,
+                         const void* table, int64_t table_ld, void* stream) {
+  constexpr const char* op = "qk_norm_rope_moss";
+  if (tokens < 0 || heads < 1 || ld < 2LL * heads * kHeadDim || table_ld < kHeadDim) {
+    return fail_invalid(op, "expected qkv [L, >= 2*heads*128] and table [L, 128]");
+  }
+  if (tokens == 0) return B2_OK;
+  if (qkv == nullptr || table == nullptr || q_norm == nullptr || k_norm == nullptr || !aligned_to(qkv, 16) ||
+      !aligned_to(table, 16) || !aligned_to(q_norm, 16) || !aligned_to(k_norm, 16) || ld % 8 != 0 || table_ld % 8 != 0) {
+    return fail_invalid(op, "needs 16-byte aligned rows and weights");
+  }
+  const std::int64_t rows = tokens * heads;
+  const NormRopeArgs a{static_cast<__nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(q_norm),
+                       static_cast<const __nv_bfloat16*>(k_norm), static_cast<const __nv_bfloat16*>(table), table_ld,
+                       tokens, heads, static_cast<float>(rows) / static_cast<float>(rows * kHeadDim)};
+  const std::int64_t items = tokens * 2 * heads;
+  const unsigned blocks = static_cast<unsigned>(std::min<std::int64_t>((items + 7) / 8, 148 * 64));
+  qk_norm_rope_kernel<<<blocks, 256, 0, as_stream(stream)>>>(a);
+  return check_launch(op);
+}
+
+int b2_moss_rope_table(void* out, int64_t ld, int height, int width, int text_length, void* stream) {
+  constexpr const char* op = "moss_rope_table";
+  if (height < 0 || width < 0 || text_length < 0 || ld < 128) return fail_invalid(op, "negative extent or ld < 128");
+  const std::int64_t n = static_cast<std::int64_t>(height) * width + text_length;
+  if (n == 0) return B2_OK;
+  if (out == nullptr) return fail_invalid(op, "null table");
+  const unsigned blocks = static_cast<unsigned>(std::min<std::int64_t>((n * 128 + 255) / 256, 148 * 32));
+  rope_table_kernel<<<blocks, 256, 0, as_stream(stream)>>>(static_cast<__nv_bfloat16*>(out), ld, n, height, width, text_length, kBands);
+  return check_launch(op);
+}
+
+size_t b2_attention_q8_workspace_bytes(const b2_attention_options* o, int64_t total_q, int64_t total_k, int batch,
+                                       int max_seqlen, int num_heads, int num_kv_heads) {
+  (void)o;
+  return make_layout(total_q, total_k, batch, max_seqlen, num_heads, num_kv_heads).total;
+}
+
+int b2_attention_q8_layout(const b2_attention_options* o, int64_t total_q, int64_t total_k, int batch, int max_seqlen,
+                           int num_heads, int num_kv_heads, b2_attention_layout* out) {
+  (void)o;
+  if (out == nullptr) return fail_invalid("attention_q8_layout", "null output");
+  *out = make_layout(total_q, total_k, batch, max_seqlen, num_heads, num_kv_heads);
+  return B2_OK;
+}
+
+int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
+                    const b2_view3* out, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
+                    int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
+                    const b2_qk_norm_rope* norm_rope) {
+  constexpr const char* op = "attention_q8";
+  if (o == nullptr) return fail_invalid(op, "null options");
+  if (const int rc = check_view(op, q, "q")) return rc;
+  if (const int rc = check_view(op, k, "k")) return rc;
+  if (const int rc = check_view(op, v, "v")) return rc;
+  if (const int rc = check_view(op, out, "out")) return rc;
+  if (o->variant != B2_ATTENTION_Q8_FP8_F32ACC) {
+    return fail_status(B2_ERR_NOT_SUPPORTED, op, "only the e4m3 P·V variant with fp32 accumulation (int8_fp8_f32acc) is built for sm_100a");
+  }
+  const std::int64_t total_q = q->tokens, heads = q->heads, total_k = k->tokens, kv_heads = k->heads;
+  if (v->tokens != total_k || v->heads != kv_heads) return fail_invalid(op, "k and v must both be [total_k, num_kv_heads, 128]");
+  if (out->tokens != total_q || out->heads != heads) return fail_invalid(op, "out must have q's shape");
+  if (kv_heads != heads) return fail_status(B2_ERR_NOT_SUPPORTED, op, "num_heads must equal num_kv_heads (the DiT's joint attention)");
+  if (heads > 65535 || batch > 65535 || batch < 1) return fail_invalid(op, "batch and num_heads must be in [1, 65535]");
+  if (cu_seqlens_q == nullptr || cu_seqlens_k == nullptr) return fail_invalid(op, "null cu_seqlens");
+  if (max_seqlen <= 0) return fail_invalid(op, "max_seqlen must be positive");
+  if (!(std::isfinite(scale) && scale > 0)) return fail_invalid(op, "scale must be finite and positive");
+  const float p_range = resolve(o->p_range), v_range = resolve(o->v_range);
+  if (!(std::isfinite(p_range) && p_range <= 448.f && std::isfinite(v_range) && v_range <= 448.f)) {
+    return fail_invalid(op, "p_range and v_range must be in (0, 448] (e4m3 max)");
+  }
+  if (norm_rope != nullptr) {
+    if (norm_rope->q_norm == nullptr || norm_rope->k_norm == nullptr || norm_rope->table == nullptr ||
+        !aligned_to(norm_rope->q_norm, 16) || !aligned_to(norm_rope->k_norm, 16) || !aligned_to(norm_rope->table, 16) ||
+        norm_rope->table_ld % 8 != 0 || norm_rope->table_ld < kHeadDim) {
+      return fail_invalid(op, "norm_rope: q_norm, k_norm and table must be 16-byte aligned bf16 device tensors");
+    }
+    if (cu_seqlens_k != cu_seqlens_q || k->row_stride != q->row_stride || total_k != total_q) {
+      return fail_invalid(op, "norm_rope needs one cu_seqlens tensor and q and k rows of one stride");
+    }
+  }
+  const b2_attention_layout l = make_layout(total_q, total_k, batch, max_seqlen, static_cast<int>(heads), static_cast<int>(kv_heads));
+  if (total_q * heads * kHeadDim >= (1LL << 32) || total_k * heads * kHeadDim >= (1LL << 32)) return fail_invalid(op, "too many tokens");
+  if (total_q == 0) return B2_OK;
+  if (workspace == nullptr || !aligned_to(workspace, kAlign) || workspace_bytes < l.total) {
+    return fail_invalid(op, "workspace too small or not 256-byte aligned (need " + std::to_string(l.total) + " bytes)");
+  }
+  cudaStream_t st = as_stream(stream);
+  auto* base = static_cast<std::uint8_t*>(workspace);
+  PrepArgs p{};
+  p.q = static_cast<const __nv_bfloat16*>(q->data), p.k = static_cast<__nv_bfloat16*>(k->data);
+  p.v = static_cast<const __nv_bfloat16*>(v->data);
+  p.q_row = q->row_stride, p.q_head = q->head_stride, p.k_row = k->row_stride, p.k_head = k->head_stride;
+  p.v_row = v->row_stride, p.v_head = v->head_stride;
+  p.cu = cu_seqlens_k;
+  p.batch = batch, p.heads = static_cast<int>(heads), p.max_seqlen = max_seqlen;
+  p.chunks = l.chunks, p.q_blocks = l.q_blocks, p.k_blocks = l.k_blocks;
+  p.v_range = v_range;
+  p.q_i8 = reinterpret_cast<std::int8_t*>(base + l.q_i8);
+  p.k_i8 = reinterpret_cast<std::int8_t*>(base + l.k_i8);
+  p.v8 = base + l.v8;
+  p.q_scale = reinterpret_cast<float*>(base + l.q_scale);
+  p.k_scale = reinterpret_cast<float*>(base + l.k_scale);
+  p.k_mean = reinterpret_cast<float*>(base + l.k_mean);
+  p.v_scale = reinterpret_cast<float*>(base + l.v_scale);
+  p.v_recp = reinterpret_cast<float*>(base + l.v_recp);
+  p.part_sum = reinterpret_cast<float*>(base + l.part_sum);
+  p.part_amax = reinterpret_cast<float*>(base + l.part_amax);
+  const dim3 stats_grid(l.chunks, static_cast<unsigned>(heads), batch);
+  if (norm_rope != nullptr) {
+    const std::int64_t rows = total_q * heads;
+    p.q_norm = static_cast<const __nv_bfloat16*>(norm_rope->q_norm);
+    p.k_norm = static_cast<const __nv_bfloat16*>(norm_rope->k_norm);
+    p.table = static_cast<const __nv_bfloat16*>(norm_rope->table);
+    p.table_row = norm_rope->table_ld;
+    p.norm_factor = static_cast<float>(rows) / static_cast<float>(rows * kHeadDim);
+    stats_kernel<true><<<stats_grid, 256, 0, st>>>(p);
+  } else {
+    stats_kernel<false><<<stats_grid, 256, 0, st>>>(p);
+  }
+  if (const int rc = check_launch(op)) return rc;
+  finalize_kernel<<<dim3(static_cast<unsigned>(heads), batch), kHeadDim, 0, st>>>(p);
+  if (const int rc = check_launch(op)) return rc;
+  if (norm_rope == nullptr) {
+    PrepArgs pq = p;
+    pq.cu = cu_seqlens_q;
+    quant_q_kernel<<<dim3(l.q_blocks, static_cast<unsigned>(heads), batch), 512, 0, st>>>(pq);
+    if (const int rc = check_launch(op)) return rc;
+  }
+  quant_kv_kernel<<<dim3(l.k_blocks, static_cast<unsigned>(heads), batch), 1024, 0, st>>>(p);
+  if (const int rc = check_launch(op)) return rc;
+
+  CUtensorMap map_q, map_k, map_v;
+  const std::uint64_t row_bytes = static_cast<std::uint64_t>(heads) * kHeadDim;
+  if (!make_tensor_map_2d(&map_q, p.q_i8, row_bytes, static_cast<std::uint64_t>(total_q), row_bytes, 128, 128, op) ||
+      !make_tensor_map_2d(&map_k, p.k_i8, row_bytes, static_cast<std::uint64_t>(total_k), row_bytes, 128, 128, op) ||
+      !make_tensor_map_2d(&map_v, p.v8, row_bytes, static_cast<std::uint64_t>(total_k), row_bytes, 128, 128, op)) {
+    return B2_ERR_CUDA;
+  }
+  AttnArgs a{};
+  a.q_scale = p.q_scale, a.k_scale = p.k_scale, a.v_scale = p.v_scale;
+  a.cu_q = cu_seqlens_q, a.cu_k = cu_seqlens_k;
+  a.out = static_cast<__nv_bfloat16*>(out->data), a.out_row = out->row_stride, a.out_head = out->head_stride;
+  a.heads = static_cast<int>(heads), a.q_blocks = l.q_blocks, a.k_blocks = l.k_blocks;
+  a.scale_log2 = scale * 1.44269504088896340736f;
+  a.p_offset = static_cast<float>(std::floor(std::log2(static_cast<double>(p_range)) * 1000.0) / 1000.0);
+  if (const cudaError_t e = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+      e != cudaSuccess) {
+    return fail_cuda(op, e);
+  }
+  const dim3 grid((max_seqlen + kTileQ - 1) / kTileQ, static_cast<unsigned>(heads), batch);
+  attention_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(map_q, map_k, map_v, a);
+  return check_launch(op);
+}
+
+}  // extern "C"

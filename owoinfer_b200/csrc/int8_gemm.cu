@@ -1,0 +1,538 @@
+// INT8 x INT8 -> INT32 GEMM for sm_100a with the dequantisation and the following element-wise op fused into the
+// epilogue: out = epilogue(sum_k x_q[r,k] * w[c,k]).
+//
+// Structure (one persistent CTA per SM, 192 threads, warp-specialised):
+//   warp 0  TMA producer: per 128-byte K block, one 128-row box of A and one or two 128-row boxes of B land in a
+//           128-byte-swizzled shared-memory stage (4 to 6 stages), completion on the stage's "full" mbarrier.
+//   warp 1  MMA issuer: one thread issues tcgen05.mma kind::i8 (M 128, N 128 or 256, K 32; four per stage) on
+//           shared-memory descriptors; tcgen05.commit frees the stage ("empty" mbarrier) and, after the last K block,
+//           publishes the accumulator ("tmem_full").
+//   warps 2-5  epilogue: each warp reads its 32 TMEM lanes (one output row per thread) 32 columns at a time, applies the
+//           epilogue and stores. Two accumulators (2 x N TMEM columns) let the epilogue of tile i overlap the main loop
+//           of tile i + 1.
+// The int32 accumulators are exact, so every tile shape gives the same bits. Epilogues (single-rounded fp32, no FMA
+// contraction; reference: src/kernels/quant/int8_gemm_impl.cuh:73-188):
+//   plain           bf16(((float)acc * xs[r]) * ws[c] + bias[c])
+//   gated residual  res = bf16(res + bf16(bf16(y) * gate[c]))
+//   SiTU-GLU        h = bf16(deq(acc_hidden)), g = bf16(deq(acc_gate)); out = bf16(gateF[g] * hiddenF[h]) with the two
+//                   factors tabulated over every bf16 input. The B tile of output columns [128 t, 128 t + 128) is hidden
+//                   rows 128 t.. followed by gate rows F + 128 t.., so one thread finds both halves in its TMEM lane.
+// Every wait on an mbarrier is bounded (one second of %globaltimer); on expiry the CTA raises a status word, drains
+// and frees its TMEM instead of hanging.
+#include <algorithm>
+#include <mutex>
+#include <string>
+
+#include "common.cuh"
+
+namespace b2 {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 128;  // bytes == int8 elements per K block: one 128-byte swizzle atom per row
+constexpr int kThreads = 192;
+constexpr std::int64_t kMaxK = 131071;
+
+enum class Epi : int { kPlain = 0, kGatedResidual = 1, kSituGlu = 2, kAcc = 3 };
+
+struct GemmParams {
+  int m, n, k;        // GEMM rows, GEMM columns (2F for SiTU-GLU), reduction length
+  int m_tiles, n_tiles;
+  int half;           // SiTU-GLU: F
+  const float* xs;
+  const float* ws;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* gate;
+  __nv_bfloat16* out;  // output or residual (in place)
+  std::int64_t ldo;
+  std::int32_t* acc;
+  std::int64_t ldacc;
+  const std::uint16_t* t_gate;
+  const std::uint16_t* t_hidden;
+};
+
+__device__ int g_gemm_status = 0;  // set to 1 by a CTA whose bounded wait expired
+
+__device__ __forceinline__ std::uint64_t global_ns() {
+  std::uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded mbarrier wait on wall time (1 s). Returns false when it gave up or another role already aborted.
+__device__ __forceinline__ bool wait_bar(std::uint32_t bar, std::uint32_t parity, volatile int* abort_word) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const std::uint64_t t0 = global_ns();
+  for (std::uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 0u) {
+      if (*abort_word != 0) return false;
+      if (global_ns() - t0 > 1000000000ull) {
+        *abort_word = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+
+// 8 consecutive bf16 (16 bytes) -> floats.
+__device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
+  const std::uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ std::uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const std::uint32_t*>(&h);
+}
+
+template <int kBN>
+struct Shape {
+  static constexpr int kStages = kBN == 256 ? 4 : 6;
+  static constexpr int kABytes = kBM * kBK;
+  static constexpr int kBBytes = kBN * kBK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+};
+
+template <int kBN, Epi kEpi>
+__global__ void __launch_bounds__(kThreads, 1)
+int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  using S = Shape<kBN>;
+  constexpr int kStages = S::kStages;
+  extern __shared__ std::uint8_t smem_raw[];
+  __shared__ __align__(8) std::uint64_t s_full[kStages], s_empty[kStages], s_tmem_full[2], s_tmem_empty[2];
+  __shared__ std::uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
+  const std::uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const auto a_addr = [&](int s) { return tiles_base + static_cast<std::uint32_t>(s) * S::kStageBytes; };
+  const auto b_addr = [&](int s) { return a_addr(s) + S::kABytes; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&s_full[s]), 1);
+      mbar_init(smem_u32(&s_empty[s]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&s_tmem_full[i]), 1);
+      mbar_init(smem_u32(&s_tmem_empty[i]), 4);
+    }
+    s_abort = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&s_tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const std::uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_word = &s_abort;
+
+  const int k_blocks = (p.k + kBK - 1) / kBK;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      std::uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && *abort_word == 0; tile += gridDim.x) {
+        const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+        const int row_a = mt * kBM;
+        int row_b0, row_b1;
+        if constexpr (kEpi == Epi::kSituGlu) {
+          row_b0 = nt * 128;
+          row_b1 = p.half + nt * 128;
+        } else {
+          row_b0 = nt * kBN;
+          row_b1 = nt * kBN + 128;
+        }
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = static_cast<int>(it % kStages);
+          const std::uint32_t ph = (it / kStages) & 1u;
+          if (!wait_bar(smem_u32(&s_empty[s]), ph ^ 1u, abort_word)) break;
+          const std::uint32_t full = smem_u32(&s_full[s]);
+          mbar_expect_tx(full, S::kStageBytes);
+          tma_load_2d(a_addr(s), &map_a, full, kb * kBK, row_a);
+          tma_load_2d(b_addr(s), &map_b, full, kb * kBK, row_b0);
+          if constexpr (kBN == 256) tma_load_2d(b_addr(s) + 128 * kBK, &map_b, full, kb * kBK, row_b1);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr std::uint32_t idesc = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, kBM, kBN);
+      std::uint32_t it = 0, tile_it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && *abort_word == 0; tile += gridDim.x, ++tile_it) {
+        const std::uint32_t acc = tile_it & 1u, acc_ph = (tile_it >> 1) & 1u;
+        if (!wait_bar(smem_u32(&s_tmem_empty[acc]), acc_ph ^ 1u, abort_word)) break;
+        tc_fence_after();
+        const std::uint32_t d_tmem = tmem_base + acc * kBN;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = static_cast<int>(it % kStages);
+          const std::uint32_t ph = (it / kStages) & 1u;
+          if (!wait_bar(smem_u32(&s_full[s]), ph, abort_word)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const std::uint64_t da = umma_desc_sw128(a_addr(s)), db = umma_desc_sw128(b_addr(s));
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 32; ++k4) {
+            // 32 bytes further along K inside the swizzle atom: +2 in the descriptor's 16-byte address units.
+            umma_i8(d_tmem, da + static_cast<std::uint64_t>(2 * k4), db + static_cast<std::uint64_t>(2 * k4), idesc,
+                    (kb | k4) != 0 ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&s_empty[s]));
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&s_tmem_full[acc]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // Epilogue: warp w may touch TMEM lanes [32 (w % 4), 32 (w % 4) + 32).
+    const int quarter = warp & 3;
+    std::uint32_t tile_it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_it) {
+      const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+      const std::uint32_t acc = tile_it & 1u, acc_ph = (tile_it >> 1) & 1u;
+      if (!wait_bar(smem_u32(&s_tmem_full[acc]), acc_ph, abort_word)) break;
+      tc_fence_after();
+      const int row = mt * kBM + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      const float xs = row_ok ? p.xs[row] : 0.f;
+      const std::uint32_t t_row = tmem_base + acc * kBN + (static_cast<std::uint32_t>(quarter * 32) << 16);
+
+      if constexpr (kEpi == Epi::kSituGlu) {
+        const int col0 = nt * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          std::uint32_t rh[32], rg[32];
+          tmem_ld_32x32(t_row + c0, rh);
+          tmem_ld_32x32(t_row + 128 + c0, rg);
+          tmem_ld_wait();
+          if (row_ok) {
+            __nv_bfloat16* orow = p.out + static_cast<std::int64_t>(row) * p.ldo;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              const int col = col0 + c0 + 4 * v;
+              if (col < p.half) {
+                const float4 wh = ldg4(p.ws + col), wg = ldg4(p.ws + p.half + col);
+                const float whs[4] = {wh.x, wh.y, wh.z, wh.w}, wgs[4] = {wg.x, wg.y, wg.z, wg.w};
+                float o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float h = rbf(fmul(fmul(__int2float_rn(static_cast<int>(rh[4 * v + i])), xs), whs[i]));
+                  const float g = rbf(fmul(fmul(__int2float_rn(static_cast<int>(rg[4 * v + i])), xs), wgs[i]));
+                  const float fg = __uint_as_float(static_cast<std::uint32_t>(__ldg(p.t_gate + (__float_as_uint(g) >> 16))) << 16);
+                  const float fh = __uint_as_float(static_cast<std::uint32_t>(__ldg(p.t_hidden + (__float_as_uint(h) >> 16))) << 16);
+                  o[i] = fmul(fg, fh);
+                }
+                *reinterpret_cast<uint2*>(orow + col) = make_uint2(pack2(o[0], o[1]), pack2(o[2], o[3]));
+              }
+            }
+          }
+        }
+      } else {
+        const int col0 = nt * kBN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN; c0 += 32) {
+          std::uint32_t r[32];
+          tmem_ld_32x32(t_row + c0, r);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          if constexpr (kEpi == Epi::kAcc) {
+            std::int32_t* arow = p.acc + static_cast<std::int64_t>(row) * p.ldacc;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (col0 + c0 + i < p.n) arow[col0 + c0 + i] = static_cast<std::int32_t>(r[i]);
+            }
+          } else {
+            __nv_bfloat16* orow = p.out + static_cast<std::int64_t>(row) * p.ldo;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = col0 + c0 + 8 * v;
+              if (col >= p.n) continue;  // n % 8 == 0: a vector of 8 columns is all in or all out
+              const float4 w0 = ldg4(p.ws + col), w1 = ldg4(p.ws + col + 4);
+              const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+              float bias[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+              if (p.bias != nullptr) unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), bias);
+              float y[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                y[i] = fadd(fmul(fmul(__int2float_rn(static_cast<int>(r[8 * v + i])), xs), ws[i]), bias[i]);
+              }
+              if constexpr (kEpi == Epi::kGatedResidual) {
+                float gate[8], res[8];
+                unpack8(__ldg(reinterpret_cast<const uint4*>(p.gate + col)), gate);
+                unpack8(*reinterpret_cast<const uint4*>(orow + col), res);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[i] = fadd(res[i], rbf(fmul(rbf(y[i]), gate[i])));
+              }
+              *reinterpret_cast<uint4*>(orow + col) =
+                  make_uint4(pack2(y[0], y[1]), pack2(y[2], y[3]), pack2(y[4], y[5]), pack2(y[6], y[7]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_tmem_empty[acc]));
+    }
+  }
+
+  __syncthreads();
+  if (s_abort != 0) {
+    // A wait expired: give in-flight copies and MMAs time to land before the TMEM goes away, then report.
+    if (threadIdx.x == 0) atomicExch(&g_gemm_status, 1);
+    const std::uint64_t t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// SiTU factor tables: for every bf16 input x (index = its 16 bits), the bf16 gate factor
+// bf16(bf16(4 * bf16(tanh(bf16(x / 4)))) * bf16(sigmoid(x))) and hidden factor bf16(25 * bf16(tanh(bf16(x * fp32(1/25))))).
+// Reference: src/kernels/fused/fused_gemm_impl.cuh:58-67, src/kernels/quant/int8_gemm_situ.cu:16-27.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ std::uint16_t g_situ_gate[65536];
+__device__ std::uint16_t g_situ_hidden[65536];
+
+__global__ void fill_situ_tables() {
+  const std::uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  const float x = __uint_as_float(i << 16);
+  const float sig = __fdiv_rn(1.0f, fadd(1.0f, expf(-x)));
+  const float gate = rbf(fmul(rbf(fmul(4.0f, rbf(tanhf(rbf(fmul(x, 0.25f)))))), rbf(sig)));
+  const float hidden = rbf(fmul(25.0f, rbf(tanhf(rbf(fmul(x, 1.0f / 25.0f))))));
+  g_situ_gate[i] = static_cast<std::uint16_t>(float_to_bf_bits(gate));
+  g_situ_hidden[i] = static_cast<std::uint16_t>(float_to_bf_bits(hidden));
+}
+
+struct SituTables {
+  const std::uint16_t* gate = nullptr;
+  const std::uint16_t* hidden = nullptr;
+};
+
+// Filled once per device. Outside stream capture the first call fills on `stream` and synchronises it (the one host
+// synchronisation of this library); inside a capture the fill is enqueued into the graph and the device stays unmarked.
+int situ_tables(cudaStream_t stream, SituTables* out) {
+  constexpr const char* op = "int8_gemm_situ_glu";
+  static std::mutex mu;
+  static bool filled[64] = {};
+  static SituTables ptrs[64];
+  int dev = 0;
+  if (const cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return fail_cuda(op, e);
+  if (dev < 0 || dev >= 64) return fail_status(B2_ERR_INTERNAL, op, "device ordinal out of range");
+  const std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev].gate == nullptr) {
+    void *g = nullptr, *h = nullptr;
+    if (const cudaError_t e = cudaGetSymbolAddress(&g, g_situ_gate); e != cudaSuccess) return fail_cuda(op, e);
+    if (const cudaError_t e = cudaGetSymbolAddress(&h, g_situ_hidden); e != cudaSuccess) return fail_cuda(op, e);
+    ptrs[dev].gate = static_cast<const std::uint16_t*>(g);
+    ptrs[dev].hidden = static_cast<const std::uint16_t*>(h);
+  }
+  if (!filled[dev]) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (const cudaError_t e = cudaStreamIsCapturing(stream, &cap); e != cudaSuccess) return fail_cuda(op, e);
+    fill_situ_tables<<<256, 256, 0, stream>>>();
+    if (const int rc = check_launch(op)) return rc;
+    if (cap == cudaStreamCaptureStatusNone) {
+      if (const cudaError_t e = cudaStreamSynchronize(stream); e != cudaSuccess) return fail_cuda(op, e);
+      filled[dev] = true;
+    }
+  }
+  *out = ptrs[dev];
+  return B2_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Host: validation and launch.
+// ---------------------------------------------------------------------------------------------------------------
+int check_operands(const char* op, const b2_int8_operands* a) {
+  if (a == nullptr) return fail_invalid(op, "null operands");
+  if (a->m < 0 || a->m > 0x7fffffff || a->n <= 0 || a->n > 0x7fffffff || a->k <= 0 || a->k > kMaxK) {
+    return fail_invalid(op, "needs 0 <= m < 2^31, 0 < n < 2^31, 0 < k <= 131071 (m " + std::to_string(a->m) + ", n " +
+                                std::to_string(a->n) + ", k " + std::to_string(a->k) + ")");
+  }
+  if (a->k % 16 != 0 || a->ldx % 16 != 0 || a->ldx < a->k) {
+    return fail_invalid(op, "needs k % 16 == 0 and ldx % 16 == 0, ldx >= k (k " + std::to_string(a->k) + ", ldx " +
+                                std::to_string(a->ldx) + ")");
+  }
+  if (a->w == nullptr || a->w_scale == nullptr || !aligned_to(a->w, 16) || !aligned_to(a->w_scale, 16)) {
+    return fail_invalid(op, "w and w_scale must be 16-byte aligned device pointers");
+  }
+  if (a->m > 0 && (a->x_q == nullptr || a->x_scale == nullptr || !aligned_to(a->x_q, 16))) {
+    return fail_invalid(op, "x_q must be a 16-byte aligned device pointer and x_scale non-null");
+  }
+  return B2_OK;
+}
+
+int check_output(const char* op, const char* name, const void* p, std::int64_t ld, std::int64_t n_out) {
+  if (p == nullptr || !aligned_to(p, 16) || ld < n_out || ld % 8 != 0 || n_out % 8 != 0) {
+    return fail_invalid(op, std::string(name) + " must be 16-byte aligned with a row stride >= n and a multiple of 8, n % 8 == 0 (ld " +
+                                std::to_string(ld) + ", n " + std::to_string(n_out) + ")");
+  }
+  return B2_OK;
+}
+
+template <int kBN, Epi kEpi>
+int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaStream_t stream) {
+  using S = Shape<kBN>;
+  CUtensorMap map_a, map_b;
+  if (!make_tensor_map_2d(&map_a, a->x_q, static_cast<std::uint64_t>(a->k), static_cast<std::uint64_t>(a->m),
+                          static_cast<std::uint64_t>(a->ldx), kBK, 128, op)) {
+    return B2_ERR_CUDA;
+  }
+  if (!make_tensor_map_2d(&map_b, a->w, static_cast<std::uint64_t>(a->k), static_cast<std::uint64_t>(a->n),
+                          static_cast<std::uint64_t>(a->k), kBK, 128, op)) {
+    return B2_ERR_CUDA;
+  }
+  auto kernel = int8_gemm_kernel<kBN, kEpi>;
+  // Opt in to the large dynamic shared-memory size once per device and instantiation.
+  static bool configured[64] = {};
+  int dev = 0;
+  if (const cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return fail_cuda(op, e);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
+        e != cudaSuccess) {
+      return fail_cuda(op, e);
+    }
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  p.m_tiles = (p.m + kBM - 1) / kBM;
+  if constexpr (kEpi == Epi::kSituGlu) p.n_tiles = (p.half + 127) / 128;
+  else p.n_tiles = (p.n + kBN - 1) / kBN;
+  const int total = p.m_tiles * p.n_tiles;
+  const int grid = std::min(total, sm_count());
+  kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_b, p);
+  return check_launch(op);
+}
+
+// Tile choice: 128 x 256 unless the problem then leaves SMs idle that 128 x 128 tiles would fill.
+int pick_bn(int tile, std::int64_t m, std::int64_t n) {
+  if (tile == B2_TILE_128x128) return 128;
+  if (tile == B2_TILE_128x256) return 256;
+  const std::int64_t mt = (m + kBM - 1) / kBM;
+  const std::int64_t big = mt * ((n + 255) / 256);
+  return big >= sm_count() ? 256 : 128;
+}
+
+template <Epi kEpi>
+int dispatch(const char* op, const b2_int8_operands* a, const GemmParams& p, cudaStream_t stream, int tile) {
+  if constexpr (kEpi == Epi::kSituGlu) {
+    return launch_kernel<256, kEpi>(op, a, p, stream);
+  } else {
+    return pick_bn(tile, a->m, a->n) == 256 ? launch_kernel<256, kEpi>(op, a, p, stream)
+                                            : launch_kernel<128, kEpi>(op, a, p, stream);
+  }
+}
+
+GemmParams base_params(const b2_int8_operands* a) {
+  GemmParams p{};
+  p.m = static_cast<int>(a->m), p.n = static_cast<int>(a->n), p.k = static_cast<int>(a->k);
+  p.xs = a->x_scale, p.ws = a->w_scale;
+  return p;
+}
+
+}  // namespace
+
+// Used by the block driver (same translation-unit-independent entry points as the C ABI).
+int gemm_status_word(int* host_value) {
+  const cudaError_t e = cudaMemcpyFromSymbol(host_value, g_gemm_status, sizeof(int));
+  return e == cudaSuccess ? B2_OK : fail_cuda("gemm_status", e);
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" {
+
+int b2_int8_gemm(const b2_int8_operands* op_, const void* bias, void* out, int64_t ldo, void* stream, int tile) {
+  constexpr const char* op = "int8_gemm";
+  if (const int rc = check_operands(op, op_)) return rc;
+  if (const int rc = check_output(op, "out", out, ldo, op_->n)) return rc;
+  if (bias != nullptr && !aligned_to(bias, 16)) return fail_invalid(op, "bias must be 16-byte aligned");
+  if (op_->m == 0) return B2_OK;
+  GemmParams p = base_params(op_);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.out = static_cast<__nv_bfloat16*>(out), p.ldo = ldo;
+  return dispatch<Epi::kPlain>(op, op_, p, as_stream(stream), tile);
+}
+
+int b2_int8_gemm_gated_residual(const b2_int8_operands* op_, const void* bias, const void* gate, void* residual,
+                                int64_t ldr, void* stream, int tile) {
+  constexpr const char* op = "int8_gemm_gated_residual";
+  if (const int rc = check_operands(op, op_)) return rc;
+  if (const int rc = check_output(op, "residual", residual, ldr, op_->n)) return rc;
+  if (bias != nullptr && !aligned_to(bias, 16)) return fail_invalid(op, "bias must be 16-byte aligned");
+  if (gate == nullptr || !aligned_to(gate, 16)) return fail_invalid(op, "gate must be a 16-byte aligned device vector");
+  if (op_->m == 0) return B2_OK;
+  GemmParams p = base_params(op_);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.out = static_cast<__nv_bfloat16*>(residual), p.ldo = ldr;
+  return dispatch<Epi::kGatedResidual>(op, op_, p, as_stream(stream), tile);
+}
+
+int b2_int8_gemm_situ_glu(const b2_int8_operands* op_, void* out, int64_t ldo, void* stream, int tile) {
+  constexpr const char* op = "int8_gemm_situ_glu";
+  if (op_ != nullptr && op_->n % 8 != 0) return fail_invalid(op, "n = 2F needs F % 4 == 0, got n " + std::to_string(op_->n));
+  if (const int rc = check_operands(op, op_)) return rc;
+  const std::int64_t f = op_->n / 2;
+  if (out == nullptr || !aligned_to(out, 8) || ldo < f || ldo % 4 != 0) {
+    return fail_invalid(op, "out must be 8-byte aligned with a row stride >= F and a multiple of 4, got " + std::to_string(ldo));
+  }
+  if (op_->m == 0) return B2_OK;
+  SituTables t;
+  if (const int rc = situ_tables(as_stream(stream), &t)) return rc;
+  GemmParams p = base_params(op_);
+  p.half = static_cast<int>(f);
+  p.out = static_cast<__nv_bfloat16*>(out), p.ldo = ldo;
+  p.t_gate = t.gate, p.t_hidden = t.hidden;
+  return dispatch<Epi::kSituGlu>(op, op_, p, as_stream(stream), tile);
+}
+
+int b2_int8_gemm_acc(const b2_int8_operands* op_, int32_t* acc, int64_t ldacc, void* stream, int tile) {
+  constexpr const char* op = "int8_gemm_acc";
+  if (const int rc = check_operands(op, op_)) return rc;
+  if (acc == nullptr || ldacc < op_->n) return fail_invalid(op, "acc must be non-null with ldacc >= n");
+  if (op_->m == 0) return B2_OK;
+  GemmParams p = base_params(op_);
+  p.acc = acc, p.ldacc = ldacc;
+  return dispatch<Epi::kAcc>(op, op_, p, as_stream(stream), tile);
+}
+
+int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_w4_weight* w, int64_t m, int64_t n,
+                 int64_t k, int epilogue, const void* aux, void* out, int64_t ldo, int8_t* scratch, void* stream) {
+  constexpr const char* op = "w4a8_gemm";
+  if (w == nullptr || scratch == nullptr) return fail_invalid(op, "null weight or scratch");
+  if (epilogue < 0 || epilogue > 2) return fail_invalid(op, "epilogue must be 0 (plain), 1 (gated residual) or 2 (SiTU-GLU)");
+  if (const int rc = b2_decode_grouped_int8(w->packed, w->s_rel, w->scale_kind, w->codebook, n, k, w->group, scratch, stream)) {
+    return rc;
+  }
+  b2_int8_operands a{x_q, ldx, x_scale, scratch, w->s_channel, m, n, k};
+  if (epilogue == 0) return b2_int8_gemm(&a, aux, out, ldo, stream, B2_TILE_AUTO);
+  if (epilogue == 1) return b2_int8_gemm_gated_residual(&a, nullptr, aux, out, ldo, stream, B2_TILE_AUTO);
+  return b2_int8_gemm_situ_glu(&a, out, ldo, stream, B2_TILE_AUTO);
+}
+
+}  // extern "C"

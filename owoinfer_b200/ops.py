@@ -1,0 +1,273 @@
+"""Host-side mirror of the reference's kernel-level interface for the quantized DiT block, over torch CUDA tensors.
+
+Same names, argument meaning and error behaviour as the reference's C++ entry points (kernels::quant::*,
+kernels::quant4::*, attention_q8::attention_q8, kernels::fused::qk_norm_rope_moss, moss_dit::run_block_quant); every
+function calls straight into the C ABI of libowoinfer_b200.so on the current torch stream. torch is used for device
+memory and streams only. Invalid arguments raise ValueError (the reference throws std::invalid_argument).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+TILE_AUTO, TILE_128x256, TILE_128x128 = 0, 1, 2
+TIER_INT8, TIER_W4A4_VIA_INT8, TIER_W4A8 = 0, 1, 2
+ATTENTION_Q8_FP8_F32ACC = 3
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _ld(t) -> int:
+    return t.stride(0) if t.dim() == 2 and t.shape[0] > 1 else t.shape[-1]
+
+
+# ------------------------------------------------------------------------------------------------ quantisers
+
+def rotate_quantize(x, q=None, scale=None):
+    m, k = x.shape
+    q = torch.empty((m, k), dtype=torch.int8, device=x.device) if q is None else q
+    scale = torch.empty(m, dtype=torch.float32, device=x.device) if scale is None else scale
+    check(_lib.lib().b2_rotate_quantize(_ptr(x), C.c_int64(_ld(x)), _ptr(q), C.c_int64(_ld(q)), _ptr(scale), C.c_int64(m),
+                                        C.c_int(k), _stream()))
+    return q, scale
+
+
+def rms_norm_modulate_rotate_quantize(x, norm_weight, mod_scale, mod_shift, q=None, scale=None, y=None):
+    m, k = x.shape
+    q = torch.empty((m, k), dtype=torch.int8, device=x.device) if q is None else q
+    scale = torch.empty(m, dtype=torch.float32, device=x.device) if scale is None else scale
+    check(_lib.lib().b2_rms_norm_modulate_rotate_quantize(
+        _ptr(x), C.c_int64(_ld(x)), _ptr(norm_weight), _ptr(mod_scale), _ptr(mod_shift), _ptr(q), C.c_int64(_ld(q)),
+        _ptr(scale), C.c_int64(m), C.c_int(k), _stream(), _ptr(y), C.c_int64(0 if y is None else _ld(y))))
+    return q, scale
+
+
+def convrot_quantize_int4(x, q=None, scale=None):
+    m, k = x.shape
+    q = torch.empty((m, k // 2), dtype=torch.uint8, device=x.device) if q is None else q
+    scale = torch.empty(m, dtype=torch.float32, device=x.device) if scale is None else scale
+    check(_lib.lib().b2_convrot_quantize_int4(_ptr(x), C.c_int64(_ld(x)), _ptr(q), C.c_int64(_ld(q)), _ptr(scale),
+                                              C.c_int64(m), C.c_int(k), _stream()))
+    return q, scale
+
+
+def rms_norm_modulate_convrot_quantize_int4(x, norm_weight, mod_scale, mod_shift, q=None, scale=None):
+    m, k = x.shape
+    q = torch.empty((m, k // 2), dtype=torch.uint8, device=x.device) if q is None else q
+    scale = torch.empty(m, dtype=torch.float32, device=x.device) if scale is None else scale
+    check(_lib.lib().b2_rms_norm_modulate_convrot_quantize_int4(
+        _ptr(x), C.c_int64(_ld(x)), _ptr(norm_weight), _ptr(mod_scale), _ptr(mod_shift), _ptr(q), C.c_int64(_ld(q)),
+        _ptr(scale), C.c_int64(m), C.c_int(k), _stream()))
+    return q, scale
+
+
+def unpack_int4(packed, out=None):
+    rows, kb = packed.shape
+    out = torch.empty((rows, kb * 2), dtype=torch.int8, device=packed.device) if out is None else out
+    check(_lib.lib().b2_unpack_int4(_ptr(packed), C.c_int64(_ld(packed)), _ptr(out), C.c_int64(_ld(out)), C.c_int64(rows),
+                                    C.c_int64(kb * 2), _stream()))
+    return out
+
+
+def decode_grouped_int8(packed, s_rel, group, codebook=None, out=None):
+    rows, kb = packed.shape
+    k = kb * 2
+    kind = 0 if s_rel.dtype in (torch.uint8, torch.int8) else 1
+    out = torch.empty((rows, k), dtype=torch.int8, device=packed.device) if out is None else out
+    check(_lib.lib().b2_decode_grouped_int8(_ptr(packed), _ptr(s_rel), C.c_int(kind), _ptr(codebook), C.c_int64(rows),
+                                            C.c_int64(k), C.c_int(group), _ptr(out), _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ GEMMs
+
+def _operands(x_q, x_scale, w, w_scale):
+    m, k = x_q.shape
+    return _lib.Int8Operands(x_q.data_ptr(), _ld(x_q), x_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(), m, w.shape[0], k)
+
+
+def int8_gemm(x_q, x_scale, w, w_scale, bias=None, out=None, tile=TILE_AUTO):
+    op = _operands(x_q, x_scale, w, w_scale)
+    out = torch.empty((op.m, op.n), dtype=torch.bfloat16, device=x_q.device) if out is None else out
+    check(_lib.lib().b2_int8_gemm(C.byref(op), _ptr(bias), _ptr(out), C.c_int64(_ld(out)), _stream(), C.c_int(tile)))
+    return out
+
+
+def int8_gemm_gated_residual(x_q, x_scale, w, w_scale, gate, residual, bias=None, tile=TILE_AUTO):
+    op = _operands(x_q, x_scale, w, w_scale)
+    check(_lib.lib().b2_int8_gemm_gated_residual(C.byref(op), _ptr(bias), _ptr(gate), _ptr(residual),
+                                                 C.c_int64(_ld(residual)), _stream(), C.c_int(tile)))
+    return residual
+
+
+def int8_gemm_situ_glu(x_q, x_scale, w, w_scale, out=None, tile=TILE_AUTO):
+    op = _operands(x_q, x_scale, w, w_scale)
+    out = torch.empty((op.m, op.n // 2), dtype=torch.bfloat16, device=x_q.device) if out is None else out
+    check(_lib.lib().b2_int8_gemm_situ_glu(C.byref(op), _ptr(out), C.c_int64(_ld(out)), _stream(), C.c_int(tile)))
+    return out
+
+
+def int8_gemm_acc(x_q, w, tile=TILE_AUTO):
+    m, k = x_q.shape
+    ones = torch.ones(max(m, w.shape[0], 4), dtype=torch.float32, device=x_q.device)
+    op = _operands(x_q, ones, w, ones)
+    acc = torch.empty((m, w.shape[0]), dtype=torch.int32, device=x_q.device)
+    check(_lib.lib().b2_int8_gemm_acc(C.byref(op), _ptr(acc), C.c_int64(w.shape[0]), _stream(), C.c_int(tile)))
+    return acc
+
+
+def make_w4(packed, s_rel, group, s_channel, codebook=None):
+    kind = 0 if s_rel.dtype in (torch.uint8, torch.int8) else 1
+    w = _lib.W4Weight(packed.data_ptr(), s_rel.data_ptr(), kind, group, 0 if codebook is None else codebook.data_ptr(),
+                      s_channel.data_ptr())
+    w._keep = (packed, s_rel, s_channel, codebook)
+    return w
+
+
+def w4a8_gemm(x_q, x_scale, w4, n, epilogue=0, aux=None, out=None, scratch=None):
+    m, k = x_q.shape
+    scratch = torch.empty((n, k), dtype=torch.int8, device=x_q.device) if scratch is None else scratch
+    if out is None:
+        out = torch.empty((m, n // 2 if epilogue == 2 else n), dtype=torch.bfloat16, device=x_q.device)
+    check(_lib.lib().b2_w4a8_gemm(_ptr(x_q), C.c_int64(_ld(x_q)), _ptr(x_scale), C.byref(w4), C.c_int64(m), C.c_int64(n),
+                                  C.c_int64(k), C.c_int(epilogue), _ptr(aux), _ptr(out), C.c_int64(_ld(out)),
+                                  _ptr(scratch), _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ attention side
+
+def qk_norm_rope_moss(qkv, heads, q_norm, k_norm, table):
+    check(_lib.lib().b2_qk_norm_rope_moss(_ptr(qkv), C.c_int64(_ld(qkv)), C.c_int64(qkv.shape[0]), C.c_int(heads),
+                                          _ptr(q_norm), _ptr(k_norm), _ptr(table), C.c_int64(_ld(table)), _stream()))
+    return qkv
+
+
+def moss_rope_table(height, width, text_length, device="cuda"):
+    n = height * width + text_length
+    out = torch.empty((n, 128), dtype=torch.bfloat16, device=device)
+    check(_lib.lib().b2_moss_rope_table(_ptr(out), C.c_int64(128), C.c_int(height), C.c_int(width), C.c_int(text_length),
+                                        _stream()))
+    return out
+
+
+def _view3(t):
+    return _lib.View3(t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), t.stride(1))
+
+
+def attention_options(p_range=0.0, v_range=0.0):
+    return _lib.AttentionOptions(ATTENTION_Q8_FP8_F32ACC, p_range, v_range)
+
+
+def attention_q8_workspace_bytes(total_q, total_k, batch, max_seqlen, heads, kv_heads=None, options=None):
+    o = options or attention_options()
+    return int(_lib.lib().b2_attention_q8_workspace_bytes(C.byref(o), total_q, total_k, batch, max_seqlen, heads,
+                                                          heads if kv_heads is None else kv_heads))
+
+
+def attention_q8_layout(total_q, total_k, batch, max_seqlen, heads, options=None):
+    o = options or attention_options()
+    l = _lib.AttentionLayout()
+    check(_lib.lib().b2_attention_q8_layout(C.byref(o), C.c_int64(total_q), C.c_int64(total_k), C.c_int(batch),
+                                            C.c_int(max_seqlen), C.c_int(heads), C.c_int(heads), C.byref(l)))
+    return l
+
+
+def attention_q8(q, k, v, out, cu_seqlens_q, cu_seqlens_k, max_seqlen, scale, workspace=None, options=None,
+                 norm_rope=None):
+    """q, k, v, out: bf16 [tokens, heads, 128] views (head_dim contiguous). norm_rope: (q_norm, k_norm, table) or None."""
+    o = options or attention_options()
+    batch = cu_seqlens_q.shape[0] - 1
+    if workspace is None:
+        nbytes = attention_q8_workspace_bytes(q.shape[0], k.shape[0], batch, max_seqlen, q.shape[1], k.shape[1], o)
+        workspace = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
+    nr = None
+    if norm_rope is not None:
+        nr = _lib.QkNormRope(norm_rope[0].data_ptr(), norm_rope[1].data_ptr(), norm_rope[2].data_ptr(), _ld(norm_rope[2]))
+    vq, vk, vv, vo = _view3(q), _view3(k), _view3(v), _view3(out)
+    check(_lib.lib().b2_attention_q8(C.byref(o), C.byref(vq), C.byref(vk), C.byref(vv), C.byref(vo), _ptr(cu_seqlens_q),
+                                     _ptr(cu_seqlens_k), C.c_int(batch), C.c_int(max_seqlen), C.c_float(scale),
+                                     _ptr(workspace), C.c_size_t(workspace.numel()), _stream(),
+                                     None if nr is None else C.byref(nr)))
+    return out, workspace
+
+
+def kernel_status():
+    g, a = C.c_int(0), C.c_int(0)
+    check(_lib.lib().b2_kernel_status(C.byref(g), C.byref(a)))
+    return g.value, a.value
+
+
+# ------------------------------------------------------------------------------------------------ block / step
+
+class BlockWeights:
+    """Device weights of one all-quantized block (BlockTensors of the reference, restricted to this route).
+
+    qkv / o / up_gate / down: (int8 weight [n, k], f32 scale [n]) for TIER_INT8; (packed int4 uint8 [n, k/2], f32 scale)
+    for TIER_W4A4_VIA_INT8; a W4Weight from make_w4 for TIER_W4A8.
+    """
+
+    def __init__(self, norm1, norm2, q_norm, k_norm, qkv, o, up_gate, down):
+        self.tensors = (norm1, norm2, q_norm, k_norm, qkv, o, up_gate, down)
+        s = _lib.BlockWeights()
+        s.struct_size = C.sizeof(_lib.BlockWeights)
+        s.norm1, s.norm2, s.q_norm, s.k_norm = (t.data_ptr() for t in (norm1, norm2, q_norm, k_norm))
+        for name, lin in (("qkv", qkv), ("o", o), ("up_gate", up_gate), ("down", down)):
+            l = _lib.Linear()
+            if isinstance(lin, _lib.W4Weight):
+                l.w4 = C.pointer(lin)
+            else:
+                l.w, l.scale = lin[0].data_ptr(), lin[1].data_ptr()
+            setattr(s, name, l)
+        self.struct = s
+
+
+def block_run(tokens, cu_seqlens, max_seqlen, D=3072, F=12288, heads=24, tier=TIER_INT8, p_range=0.0, v_range=0.0,
+              fused_norm_rope=-1):
+    r = _lib.BlockRun()
+    r.struct_size = C.sizeof(_lib.BlockRun)
+    r.tokens, r.D, r.F, r.heads = tokens, D, F, heads
+    r.cu_seqlens = cu_seqlens.data_ptr()
+    r.batch, r.max_seqlen, r.tier = cu_seqlens.shape[0] - 1, max_seqlen, tier
+    r.attention = attention_options(p_range, v_range)
+    r.fused_norm_rope = fused_norm_rope
+    r._keep = cu_seqlens
+    return r
+
+
+def block_quant_workspace_bytes(run) -> int:
+    n = int(_lib.lib().b2_block_quant_workspace_bytes(C.byref(run)))
+    if n == 0:
+        raise ValueError(_lib.lib().b2_last_error_message().decode())
+    return n
+
+
+def block_buffers(x, mod, rope, workspace):
+    b = _lib.BlockBuffers()
+    b.struct_size = C.sizeof(_lib.BlockBuffers)
+    b.x, b.mod, b.rope, b.workspace, b.workspace_bytes = x.data_ptr(), mod.data_ptr(), rope.data_ptr(), workspace.data_ptr(), workspace.numel()
+    b._keep = (x, mod, rope, workspace)
+    return b
+
+
+def run_block_quant(weights: BlockWeights, buffers, run):
+    check(_lib.lib().b2_run_block_quant(C.byref(weights.struct), C.byref(buffers), C.byref(run), _stream()))
+
+
+def dit_step(blocks, buffers, run):
+    arr = (_lib.BlockWeights * len(blocks))(*[b.struct for b in blocks])
+    check(_lib.lib().b2_dit_step(arr, C.c_int(len(blocks)), C.byref(buffers), C.byref(run), _stream()))
+
+
+SM_SCALE = 1.0 / math.sqrt(128.0)
