@@ -1,0 +1,164 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol the header declares, and rejects invalid
+arguments before any launch with the reference's error behaviour (std::invalid_argument -> status -1 -> ValueError).
+No compute call runs here (there is no GPU in this environment)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from owoinfer_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "owoinfer_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b2_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.lib()
+    declared = header_symbols()
+    assert len(declared) >= 20
+    missing = [s for s in declared if not hasattr(lib, s)]
+    assert not missing, missing
+    assert sorted(_lib.EXPORTS) == declared
+
+
+def test_numerics_versions():
+    lib = _lib.lib()
+    assert [lib.b2_numerics_version(i) for i in range(3)] == [1, 1, 1]
+
+
+def _status(rc):
+    return rc, _lib.lib().b2_last_error_message().decode()
+
+
+A16 = C.c_void_p(0x1000)  # a 16-byte aligned fake device address: validation never dereferences it
+A8 = C.c_void_p(0x1008)
+
+
+def test_rotate_quantize_rejects_bad_shapes():
+    lib = _lib.lib()
+    f = lib.b2_rotate_quantize
+    # tests/unit/test_quant_kernels.cu:573-606 (argument rejection)
+    for k in (0, 100, 255, 32768 + 256):
+        rc, msg = _status(f(A16, C.c_int64(max(k, 8)), A16, C.c_int64(max(k, 16)), A16, C.c_int64(4), C.c_int(k), None))
+        assert rc == -1 and "multiple of 256" in msg
+    rc, msg = _status(f(A16, C.c_int64(256), A16, C.c_int64(256), A16, C.c_int64(-1), C.c_int(256), None))
+    assert rc == -1 and "negative" in msg
+    rc, msg = _status(f(None, C.c_int64(256), A16, C.c_int64(256), A16, C.c_int64(1), C.c_int(256), None))
+    assert rc == -1 and "null" in msg
+    rc, msg = _status(f(A8, C.c_int64(256), A16, C.c_int64(256), A16, C.c_int64(1), C.c_int(256), None))
+    assert rc == -1 and "aligned" in msg
+    rc, msg = _status(f(A16, C.c_int64(260), A16, C.c_int64(256), A16, C.c_int64(1), C.c_int(256), None))  # ldx % 8
+    assert rc == -1
+    rc, msg = _status(f(A16, C.c_int64(256), A16, C.c_int64(264), A16, C.c_int64(1), C.c_int(256), None))  # ldq % 16
+    assert rc == -1
+    # m == 0 is a no-op, even with null operands.
+    assert f(None, C.c_int64(256), None, C.c_int64(256), None, C.c_int64(0), C.c_int(256), None) == 0
+
+
+def test_norm_variant_rejects_cross_warp_rows():
+    lib = _lib.lib()
+    f = lib.b2_rms_norm_modulate_rotate_quantize
+    # k = 32768 with one row: torch would split the row across warps (quant.h: "k <= 7680 always works").
+    rc, msg = _status(f(A16, C.c_int64(32768), A16, A16, A16, A16, C.c_int64(32768), A16, C.c_int64(1 << 20), C.c_int(32768),
+                        None, None, C.c_int64(0)))
+    assert rc == -1 and "cross-warp" in msg
+    rc, msg = _status(f(A16, C.c_int64(3072), A8, A16, A16, A16, C.c_int64(3072), A16, C.c_int64(4), C.c_int(3072), None,
+                        None, C.c_int64(0)))
+    assert rc == -1 and "norm_weight" in msg
+    rc, msg = _status(f(A16, C.c_int64(3072), A16, A16, A16, A16, C.c_int64(3072), A16, C.c_int64(4), C.c_int(3072), None,
+                        A16, C.c_int64(100)))
+    assert rc == -1 and "ldy" in msg
+
+
+def _ops(m=4, n=264, k=512, ldx=512, x=A16, w=A16, ws=A16):
+    return _lib.Int8Operands(x.value, ldx, A16.value, w.value, ws.value, m, n, k)
+
+
+def test_gemm_rejects_bad_operands():
+    lib = _lib.lib()
+    # tests/unit/test_quant_kernels.cu:871-901
+    for bad in (_ops(k=0), _ops(k=131072), _ops(k=520, ldx=520), _ops(ldx=500), _ops(n=0), _ops(m=-1), _ops(w=A8),
+                _ops(x=A8)):
+        rc, msg = _status(lib.b2_int8_gemm(C.byref(bad), None, A16, C.c_int64(264), None, 0))
+        assert rc == -1, msg
+    ok = _ops()
+    rc, msg = _status(lib.b2_int8_gemm(C.byref(ok), None, A16, C.c_int64(260), None, 0))  # ldo < n
+    assert rc == -1 and "row stride" in msg
+    rc, msg = _status(lib.b2_int8_gemm(C.byref(_ops(n=260)), None, A16, C.c_int64(264), None, 0))  # n % 8
+    assert rc == -1
+    rc, msg = _status(lib.b2_int8_gemm_gated_residual(C.byref(ok), None, None, A16, C.c_int64(264), None, 0))
+    assert rc == -1 and "gate" in msg
+    rc, msg = _status(lib.b2_int8_gemm_situ_glu(C.byref(_ops(n=268)), A16, C.c_int64(136), None, 0))  # F % 4
+    assert rc == -1 and "F % 4" in msg
+    rc, msg = _status(lib.b2_int8_gemm_situ_glu(C.byref(ok), A16, C.c_int64(130), None, 0))  # ldo < F or % 4
+    assert rc == -1
+    # m == 0: nothing runs.
+    assert lib.b2_int8_gemm(C.byref(_ops(m=0)), None, A16, C.c_int64(264), None, 0) == 0
+
+
+def test_attention_rejects_bad_arguments():
+    lib = _lib.lib()
+    o = _lib.AttentionOptions(3, 0, 0)
+    v = _lib.View3(A16.value, 128, 24, 9216, 128)
+    out = _lib.View3(A16.value, 128, 24, 3072, 128)
+    f = lib.b2_attention_q8
+    args = lambda **kw: [C.byref(kw.get("o", o)), C.byref(kw.get("q", v)), C.byref(kw.get("k", v)), C.byref(kw.get("v", v)),
+                         C.byref(kw.get("out", out)), A16, A16, C.c_int(1), C.c_int(kw.get("max_seqlen", 128)),
+                         C.c_float(kw.get("scale", 0.088)), kw.get("ws", C.c_void_p(0x10000)), C.c_size_t(kw.get("nbytes", 1 << 30)),
+                         None, None]
+    assert _status(f(*args(scale=0.0)))[0] == -1
+    assert _status(f(*args(scale=float("nan"))))[0] == -1
+    assert _status(f(*args(max_seqlen=0)))[0] == -1
+    assert _status(f(*args(o=_lib.AttentionOptions(0, 0, 0))))[0] == -3  # other variants: not built
+    assert _status(f(*args(o=_lib.AttentionOptions(3, 500.0, 0))))[0] == -1  # p_range beyond e4m3
+    assert _status(f(*args(q=_lib.View3(A16.value, 128, 24, 9217, 128))))[0] == -1  # stride not % 8
+    assert _status(f(*args(k=_lib.View3(A16.value, 128, 12, 9216, 128), v=_lib.View3(A16.value, 128, 12, 9216, 128))))[0] == -3
+    rc, msg = _status(f(*args(nbytes=1024)))
+    assert rc == -1 and "workspace" in msg
+    rc, msg = _status(f(*args(ws=C.c_void_p(0x10010))))
+    assert rc == -1 and "workspace" in msg
+    need = lib.b2_attention_q8_workspace_bytes(C.byref(o), 128, 128, 1, 128, 24, 24)
+    lay = _lib.AttentionLayout()
+    assert lib.b2_attention_q8_layout(C.byref(o), C.c_int64(128), C.c_int64(128), 1, 128, 24, 24, C.byref(lay)) == 0
+    assert need == lay.total and lay.q_blocks == 4 and lay.k_blocks == 2 and lay.chunks == 1
+    assert lay.q_i8 % 256 == 0 and lay.k_i8 % 256 == 0 and lay.v8 % 256 == 0
+
+
+def test_block_rejects_mismatched_buffers():
+    lib = _lib.lib()
+    run = _lib.BlockRun()
+    run.struct_size = C.sizeof(_lib.BlockRun)
+    run.tokens, run.D, run.F, run.heads = 1280, 3072, 12288, 24
+    run.cu_seqlens, run.batch, run.max_seqlen, run.tier = A16.value, 1, 1280, 0
+    run.attention = _lib.AttentionOptions(3, 0, 0)
+    need = lib.b2_block_quant_workspace_bytes(C.byref(run))
+    assert need > 1280 * (3 * 3072 * 2 + 12288 * 2)
+    w = _lib.BlockWeights()
+    w.struct_size = C.sizeof(_lib.BlockWeights)
+    b = _lib.BlockBuffers()
+    b.struct_size = C.sizeof(_lib.BlockBuffers)
+    b.x = b.mod = b.rope = b.workspace = 0x10000
+    b.workspace_bytes = need - 1
+    rc, msg = _status(lib.b2_run_block_quant(C.byref(w), C.byref(b), C.byref(run), None))
+    assert rc == -1 and "workspace" in msg  # dit_block_quant.cpp:268-279: refused before any launch
+    b.workspace_bytes = need
+    b.x = 0x10010
+    rc, msg = _status(lib.b2_run_block_quant(C.byref(w), C.byref(b), C.byref(run), None))
+    assert rc == -1 and "256-byte" in msg
+    run.D = 3000
+    assert lib.b2_block_quant_workspace_bytes(C.byref(run)) == 0
+    run.D, run.tier = 3072, 9
+    assert _status(lib.b2_run_block_quant(C.byref(w), C.byref(b), C.byref(run), None))[0] == -1
+
+
+def test_python_layer_fails_loudly_without_library(tmp_path, monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "missing.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.lib()
