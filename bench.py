@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized MOSS-Image DiT denoising step on B200.
+
+python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
+
+Default workload `step1024`: the full INT8 'high'-tier denoising step at 1024^2 (42 blocks of d=3072, 24x128 heads, MLP
+12288, CFG batch 2 = two 8192-token sequences per image), one image per GPU (no collective: weak scaling). One "step" is
+one pass of all blocks over the image's 16384 tokens through the C ABI (b2_dit_step). Other workloads:
+  block1024            one block on one 8192-token sequence (BASELINE configs[1])
+  step1024_cfgsplit    the step with the CFG halves on two GPUs (N = 2, strong scaling against step1024 at N = 1)
+  step2048_ulysses     the 2048^2 step (two 20480-token sequences) with Ulysses sequence parallelism over N GPUs
+  turbo1024            the step with grouped 4-bit weights (W4A8), one image per GPU
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D, HEADS = 3072, 24
+METRIC = "dit_ms_per_step_1024"
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=5)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--workload", default="step1024")
+    p.add_argument("--blocks", type=int, default=42)
+    p.add_argument("--ffn", type=int, default=12288)
+    p.add_argument("--no-profile", action="store_true", help="skip the per-kernel roofline pass and the CPU baseline")
+    return p.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        time.sleep(0.05)
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------------------- CPU arm
+
+def cpu_sample(ffn: int, block_tokens: int, attn_tokens: int, threads: int):
+    """Times the oracle (a CPU port of the reference's arithmetic) on a bounded sample: one block on `block_tokens`
+    tokens (GEMMs and element-wise work, linear in tokens) and the 8-bit attention of one `attn_tokens`-token sequence
+    over 24 heads (quadratic in tokens). Returns (seconds_block, seconds_attention)."""
+    import numpy as np
+    from oracle import oracle_lib as orc
+    orc.set_threads(threads)
+    rng = np.random.default_rng(0)
+
+    def rb(shape, s=1.0, m=0.0):
+        v = (m + rng.standard_normal(shape) * s).astype(np.float32)
+        return ((v.view(np.uint32) + 0x8000) >> 16).astype(np.uint16)
+
+    w = {"norm1": rb(D, 0.1, 1.0), "norm2": rb(D, 0.1, 1.0), "q_norm": rb(128, 0.1, 1.0), "k_norm": rb(128, 0.1, 1.0)}
+    for name, (n, k) in dict(qkv=(3 * D, D), o=(D, D), up=(2 * ffn, D), down=(D, ffn)).items():
+        w[name] = (rng.integers(-127, 128, (n, k), dtype=np.int8), (rng.random(n).astype(np.float32) + 0.5) * 1e-3)
+    x, mod = rb((block_tokens, D)), rb(6 * D, 0.1)
+    rope = orc.moss_rope_table(1, 1, block_tokens - 1)
+    t0 = time.perf_counter()
+    orc.block_quant(x, mod, rope, w, np.array([0, block_tokens], np.int32), block_tokens)
+    t_block = time.perf_counter() - t0
+    qkv = rb((attn_tokens, 3 * HEADS * 128))
+    t0 = time.perf_counter()
+    orc.attention_q8(qkv, np.array([0, attn_tokens], np.int32), HEADS, attn_tokens, 0.08838834764831845)
+    t_attn = time.perf_counter() - t0
+    # The block sample contains a (tiny) attention over block_tokens keys; it is left in: < 0.1 % of the sample.
+    return t_block, t_attn
+
+
+def cpu_extrapolate(t_block, t_attn, block_tokens, attn_tokens, seq_len, seqs, blocks):
+    """ms per step of `blocks` blocks over `seqs` sequences of `seq_len` tokens, from the sample's two rates."""
+    linear = t_block / block_tokens * (seq_len * seqs)
+    quad = t_attn * (seq_len / attn_tokens) ** 2 * seqs
+    return (linear + quad) * blocks * 1e3
+
+
+def workload_shape(name: str, world: int):
+    """(sequence length, sequences per rank-step, tier name) of a workload."""
+    if name == "block1024":
+        return 8192, 1
+    if name in ("step1024", "turbo1024"):
+        return 8192, 2
+    if name == "step1024_cfgsplit":
+        return 8192, 1
+    if name == "step2048_ulysses":
+        return 20480, 2
+    raise SystemExit(f"unknown workload {name}")
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference engine has no CPU implementation of the quantized block and ships no sm_100
+    kernel, so its CPU path for this metric is the oracle port of its arithmetic, run with every host thread on a bounded
+    sample per step and extrapolated to the full step."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    seq_len, seqs = workload_shape(args.workload, 1)
+    blocks = 1 if args.workload == "block1024" else args.blocks
+    bt, at = 128, 1024
+    vals = []
+    for i in range(args.warmup + args.steps):
+        tb, ta = cpu_sample(args.ffn, bt, at, threads)
+        if i >= args.warmup:
+            vals.append(cpu_extrapolate(tb, ta, bt, at, seq_len, seqs, blocks))
+    v = statistics.mean(vals)
+    sample = (f"per step: one block on {bt} tokens + 8-bit attention of one {at}-token sequence x 24 heads, extrapolated "
+              f"(linear part by tokens, attention by tokens^2) to {blocks} blocks x {seqs} x {seq_len} tokens")
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": v, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8", "data": "synthetic",
+            "config": {"workload": args.workload, "blocks": blocks, "ffn": args.ffn, "tokens_per_step": seq_len * seqs,
+                       "note": "CPU port of the reference's arithmetic (the reference has no CPU block path)"},
+            "cpu_baseline": {"value": v, "unit": "ms", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------------------- GPU arm
+
+def gemm_sites(L, F):
+    return [("qkv", 3 * D, D, "plain"), ("o", D, D, "gated"), ("up_gate", 2 * F, D, "situ"), ("down", D, F, "gated")]
+
+
+def profile_kernels(ops, torch, L, F, w, iters=8):
+    """Per-kernel CUDA-event timings of one block's kernels on L tokens, each launch timed alone after an L2 flush."""
+    dev = "cuda"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    xs = torch.rand(L, device=dev) * 1e-2
+    res = torch.randn((L, D), device=dev).to(torch.bfloat16)
+    gate = torch.randn(D, device=dev).to(torch.bfloat16)
+    out = {}
+
+    def timed(fn):
+        ts = []
+        for i in range(iters + 2):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            if i >= 2:
+                ts.append(e0.elapsed_time(e1))
+        return statistics.mean(ts)
+
+    for name, n, k, epi in gemm_sites(L, F):
+        xq = torch.randint(-128, 128, (L, k), dtype=torch.int8, device=dev)
+        wq, ws = w[name]
+        if epi == "plain":
+            o = torch.empty((L, n), dtype=torch.bfloat16, device=dev)
+            ms = timed(lambda: ops.int8_gemm(xq, xs, wq, ws, out=o))
+        elif epi == "gated":
+            ms = timed(lambda: ops.int8_gemm_gated_residual(xq, xs, wq, ws, gate, res))
+        else:
+            o = torch.empty((L, n // 2), dtype=torch.bfloat16, device=dev)
+            ms = timed(lambda: ops.int8_gemm_situ_glu(xq, xs, wq, ws, out=o))
+        out[name] = {"ms": ms, "tops": 2.0 * L * n * k / ms / 1e9}
+        del xq
+    x = torch.randn((L, D), device=dev).to(torch.bfloat16)
+    q = torch.empty((L, D), dtype=torch.int8, device=dev)
+    s = torch.empty(L, dtype=torch.float32, device=dev)
+    v = torch.randn(D, device=dev).to(torch.bfloat16)
+    ms = timed(lambda: ops.rms_norm_modulate_rotate_quantize(x, v, v, v, q=q, scale=s))
+    out["norm_rotate_quantize"] = {"ms": ms, "gbs": 3.0 * L * D / ms / 1e6}
+    ms = timed(lambda: ops.rotate_quantize(x, q=q, scale=s))
+    out["rotate_quantize"] = {"ms": ms, "gbs": 3.0 * L * D / ms / 1e6}
+    return out
+
+
+def main():
+    args = parse()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    from owoinfer_b200 import ops, synth
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.workload == "step2048_ulysses":
+        from owoinfer_b200 import parallel
+        return parallel.bench_ulysses(args, rank, world, local)
+
+    F = args.ffn
+    tier = ops.TIER_W4A8 if args.workload == "turbo1024" else ops.TIER_INT8
+    seq_len, seqs = workload_shape(args.workload, world)
+    if args.workload == "step1024_cfgsplit" and world != 2:
+        raise SystemExit("step1024_cfgsplit runs on exactly 2 GPUs (one CFG half each)")
+    n_blocks = 1 if args.workload == "block1024" else args.blocks
+    L = seq_len * seqs
+    scaling = "strong" if args.workload == "step1024_cfgsplit" else "weak"
+
+    # Weights: every block its own random-init ConvRot weights (~151 MB INT8 per block at F = 12288).
+    seed0 = 3000 + 100000 * (0 if scaling == "strong" else rank)
+    blocks, keep = [], []
+    for b in range(n_blocks):
+        w = synth.block_weights(D, F, seed0 + 100 * b, tier=tier)
+        lin = {}
+        for name in ("qkv", "o", "up_gate", "down"):
+            lin[name] = ops.make_w4(w[name][0], w[name][1], 64, w[name][2]) if tier == ops.TIER_W4A8 else w[name]
+        blocks.append(ops.BlockWeights(w["norm1"], w["norm2"], w["q_norm"], w["k_norm"], lin["qkv"], lin["o"],
+                                       lin["up_gate"], lin["down"]))
+        keep.append((w, lin))
+    cfg_row = rank if scaling == "strong" else 0
+    x0 = synth.activations(L, D, 1001 + rank + cfg_row)
+    mod = synth.modulation(D, 2001)
+    rope_one = ops.moss_rope_table(64, 64, seq_len - 4096)
+    rope = rope_one.repeat(seqs, 1).contiguous()
+    cu = synth.cu_seqlens([seq_len] * seqs)
+    run = ops.block_run(L, cu, seq_len, D=D, F=F, heads=HEADS, tier=tier)
+    ws = torch.empty(ops.block_quant_workspace_bytes(run), dtype=torch.uint8, device="cuda")
+    x = x0.clone()
+    bufs = ops.block_buffers(x, mod, rope, ws)
+    launches_per_block = 12 if tier == ops.TIER_INT8 else 16
+
+    def step():
+        # x keeps evolving across steps (as across denoising steps); re-seed it so values stay in range.
+        x.copy_(x0)
+        ops.dit_step(blocks, bufs, run)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    elapsed = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    ms_step = float(elapsed.item()) / args.steps
+
+    # End to end through the public call with host buffers: H2D of the step's tokens, modulation and RoPE table from
+    # pinned memory, the step, D2H of the result; one stream synchronisation per step.
+    hx = x0.cpu().pin_memory()
+    hmod, hrope = mod.cpu().pin_memory(), rope.cpu().pin_memory()
+    hout = torch.empty_like(hx).pin_memory()
+    h2d = hx.numel() * 2 + hmod.numel() * 2 + hrope.numel() * 2
+    d2h = hout.numel() * 2
+
+    def e2e_step():
+        x.copy_(hx, non_blocking=True)
+        mod.copy_(hmod, non_blocking=True)
+        rope.copy_(hrope, non_blocking=True)
+        ops.dit_step(blocks, bufs, run)
+        hout.copy_(x, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e.item())
+    g_stat = ops.kernel_status()
+
+    # value: ms per image-step aggregated over the job: N images advance per step under weak scaling.
+    units = world if scaling == "weak" else 1
+    line = {"metric": METRIC, "value": ms_step / units, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False, "scaling": scaling,
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": args.workload, "blocks": n_blocks, "d": D, "heads": HEADS, "ffn": F,
+                       "tokens_per_gpu_step": L, "sequences": [seq_len] * seqs, "tier": ["int8", "w4a4_via_int8", "w4a8"][tier],
+                       "attention": "int8_fp8_f32acc", "parallelism": f"image-dp{world}" if scaling == "weak" else "cfg-split2",
+                       "l2": "inputs larger than L2 (block weights stream from HBM every step)"},
+            "e2e": {"value": e2e_ms / units, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches_per_block * n_blocks * args.steps, "kernel_status": list(g_stat)}
+    if rank == 0:
+        line["clocks"] = clocks
+        if not args.no_profile:
+            pk = peaks()
+            prof = profile_kernels(ops, torch, L, F, keep[0][0] if tier == ops.TIER_INT8 else synth.block_weights(D, F, 1, tier=0))
+            total_ops = sum(2.0 * L * n * k for _, n, k, _ in gemm_sites(L, F))
+            total_ms = sum(prof[name]["ms"] for name, *_ in gemm_sites(L, F))
+            achieved = total_ops / total_ms / 1e9
+            peak = 2.0 * pk["bf16"]
+            line["roofline"] = {"bound": "tensor", "kernel": "int8_gemm_kernel (4 sites of one block)", "achieved": achieved,
+                                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                                "peak_source": f"2 x bf16 burst of {pk['source']} peaks (no INT8 figure is measured); nominal dense INT8 4500",
+                                "frac_of_nominal": achieved / 4500.0, "traffic": None, "per_kernel": prof}
+            threads = os.cpu_count() or 1
+            tb, ta = cpu_sample(F, 256, 1536, threads)
+            v = cpu_extrapolate(tb, ta, 256, 1536, seq_len, seqs, n_blocks)
+            line["cpu_baseline"] = {"value": v, "unit": "ms", "cores": threads, "kind": "port",
+                                    "sample": f"one block on 256 tokens ({tb:.2f} s) + attention of one 1536-token sequence x 24 "
+                                              f"heads ({ta:.2f} s), extrapolated to {n_blocks} blocks x {seqs} x {seq_len} tokens"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
