@@ -1,15 +1,16 @@
 // INT8 x INT8 -> INT32 GEMM for sm_100a with the dequantisation and the following element-wise op fused into the
 // epilogue: out = epilogue(sum_k x_q[r,k] * w[c,k]).
 //
-// Structure (one persistent CTA per SM, 192 threads, warp-specialised):
+// Structure (one persistent CTA per SM, 320 threads, warp-specialised):
 //   warp 0  TMA producer: per 128-byte K block, one 128-row box of A and one or two 128-row boxes of B land in a
 //           128-byte-swizzled shared-memory stage (4 to 6 stages), completion on the stage's "full" mbarrier.
 //   warp 1  MMA issuer: one thread issues tcgen05.mma kind::i8 (M 128, N 128 or 256, K 32; four per stage) on
 //           shared-memory descriptors; tcgen05.commit frees the stage ("empty" mbarrier) and, after the last K block,
 //           publishes the accumulator ("tmem_full").
-//   warps 2-5  epilogue: each warp reads its 32 TMEM lanes (one output row per thread) 32 columns at a time, applies the
-//           epilogue and stores. Two accumulators (2 x N TMEM columns) let the epilogue of tile i overlap the main loop
-//           of tile i + 1.
+//   warps 2-9  epilogue: each warp reads its 32 TMEM lanes (one output row per thread) and half of the tile's columns,
+//           64 columns per TMEM round trip, applies the epilogue and stores; the tile's per-column vectors (w_scale,
+//           bias, gate) are staged once in shared memory. Two accumulators (2 x N TMEM columns) let the epilogue of tile
+//           i overlap the main loop of tile i + 1.
 // The int32 accumulators are exact, so every tile shape gives the same bits. Epilogues (single-rounded fp32, no FMA
 // contraction; reference: src/kernels/quant/int8_gemm_impl.cuh:73-188):
 //   plain           bf16(((float)acc * xs[r]) * ws[c] + bias[c])
@@ -30,10 +31,12 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBK = 128;  // bytes == int8 elements per K block: one 128-byte swizzle atom per row
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr std::int64_t kMaxK = 131071;
 
 enum class Epi : int { kPlain = 0, kGatedResidual = 1, kSituGlu = 2, kAcc = 3 };
+constexpr int kMiniTable = 4096;  // 2 signs x 16 exponents x 128 mantissas
+constexpr std::uint32_t kMiniExpLo = 117;
 
 struct GemmParams {
   int m, n, k;        // GEMM rows, GEMM columns (2F for SiTU-GLU), reduction length
@@ -91,6 +94,17 @@ __device__ __forceinline__ std::uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<const std::uint32_t*>(&h);
 }
 
+// One SiTU factor of the bf16 value v: from the shared-memory slice when its exponent is inside the slice, else from the
+// full table in global memory (same entries, so the same bits either way).
+__device__ __forceinline__ float situ_factor(const std::uint16_t* mini, const std::uint16_t* full, float v) {
+  const std::uint32_t bits = __float_as_uint(v) >> 16;
+  const std::uint32_t e = ((bits >> 7) & 0xFFu) - kMiniExpLo;
+  std::uint32_t entry;
+  if (e < 16u) entry = mini[((bits >> 15) << 11) | (e << 7) | (bits & 127u)];
+  else entry = __ldg(full + bits);
+  return __uint_as_float(entry << 16);
+}
+
 template <int kBN>
 struct Shape {
   static constexpr int kStages = kBN == 256 ? 4 : 6;
@@ -109,6 +123,10 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __shared__ __align__(8) std::uint64_t s_full[kStages], s_empty[kStages], s_tmem_full[2], s_tmem_empty[2];
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ __align__(16) float s_vec[8][384];  // per epilogue warp: w_scale, bias, gate of its 128 columns
+  // SiTU-GLU: the slice of the two factor tables for inputs with 2^-10 <= |x| < 2^6 (bf16 exponent field 117..132), where
+  // almost every pre-activation falls: [sign][exponent - 117][mantissa], gate factors then hidden factors.
+  __shared__ std::uint16_t s_tab[kEpi == Epi::kSituGlu ? 2 * kMiniTable : 1];
 
   const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
   const std::uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -122,7 +140,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&s_tmem_full[i]), 1);
-      mbar_init(smem_u32(&s_tmem_empty[i]), 4);
+      mbar_init(smem_u32(&s_tmem_empty[i]), 8);
     }
     s_abort = 0;
     fence_mbar_init();
@@ -132,6 +150,13 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 1) {
     tmem_alloc(smem_u32(&s_tmem_base), 512);
     tmem_relinquish();
+  }
+  if constexpr (kEpi == Epi::kSituGlu) {
+    for (int i = threadIdx.x; i < 2 * kMiniTable; i += blockDim.x) {
+      const int j = i & (kMiniTable - 1);
+      const std::uint32_t bits = (static_cast<std::uint32_t>(j >> 11) << 15) | ((((j >> 7) & 15u) + kMiniExpLo) << 7) | (j & 127u);
+      s_tab[i] = __ldg((i < kMiniTable ? p.t_gate : p.t_hidden) + bits);
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -202,12 +227,54 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     __syncwarp();
   } else {
-    // Epilogue: warp w may touch TMEM lanes [32 (w % 4), 32 (w % 4) + 32).
-    const int quarter = warp & 3;
+    // Epilogue: 8 warps. Warp w may touch TMEM lanes [32 (w % 4), 32 (w % 4) + 32); warps 2..5 take the first half of the
+    // tile's columns, warps 6..9 the second half (SiTU-GLU: output columns, each needing its hidden and gate accumulator).
+    const int quarter = warp & 3, col_half = (warp - 2) >> 2;
     std::uint32_t tile_it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_it) {
       const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
       const std::uint32_t acc = tile_it & 1u, acc_ph = (tile_it >> 1) & 1u;
+      // This warp's per-column vectors (w_scale, bias, gate of its half of the tile's columns) -> its own slice of shared
+      // memory, four columns per lane; only the warp itself reads them back, so a warp-level sync is enough.
+      float* vec = s_vec[warp - 2];
+      __syncwarp();
+      {
+        constexpr int kHalfCols = (kEpi == Epi::kSituGlu) ? 64 : kBN / 2;
+        for (int j = lane * 4; j < 128; j += 128) {
+          int col;
+          bool ok;
+          if constexpr (kEpi == Epi::kSituGlu) {
+            const int oc = nt * 128 + col_half * 64 + (j & 63);   // output column; j < 64 hidden, j >= 64 gate
+            col = (j < 64 ? 0 : p.half) + oc;
+            ok = oc < p.half;
+          } else {
+            col = nt * kBN + col_half * kHalfCols + j;
+            ok = j < kHalfCols && col < p.n;
+          }
+          float4 w = make_float4(0.f, 0.f, 0.f, 0.f), b = w, g = w;
+          if (ok) {
+            w = ldg4(p.ws + col);
+            if constexpr (kEpi == Epi::kPlain || kEpi == Epi::kGatedResidual) {
+              if (p.bias != nullptr) {
+                float t[4];
+                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.bias + col));
+                t[0] = __uint_as_float(raw.x << 16), t[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+                t[2] = __uint_as_float(raw.y << 16), t[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+                b = make_float4(t[0], t[1], t[2], t[3]);
+              }
+            }
+            if constexpr (kEpi == Epi::kGatedResidual) {
+              const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.gate + col));
+              g = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                              __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u));
+            }
+          }
+          *reinterpret_cast<float4*>(vec + j) = w;
+          *reinterpret_cast<float4*>(vec + 128 + j) = b;
+          *reinterpret_cast<float4*>(vec + 256 + j) = g;
+        }
+      }
+      __syncwarp();
       if (!wait_bar(smem_u32(&s_tmem_full[acc]), acc_ph, abort_word)) break;
       tc_fence_after();
       const int row = mt * kBM + quarter * 32 + lane;
@@ -218,7 +285,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if constexpr (kEpi == Epi::kSituGlu) {
         const int col0 = nt * 128;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 32) {
+        for (int c0 = col_half * 64; c0 < col_half * 64 + 64; c0 += 32) {
           std::uint32_t rh[32], rg[32];
           tmem_ld_32x32(t_row + c0, rh);
           tmem_ld_32x32(t_row + 128 + c0, rg);
@@ -229,16 +296,15 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int v = 0; v < 8; ++v) {
               const int col = col0 + c0 + 4 * v;
               if (col < p.half) {
-                const float4 wh = ldg4(p.ws + col), wg = ldg4(p.ws + p.half + col);
+                const float4 wh = *reinterpret_cast<const float4*>(vec + (c0 - col_half * 64) + 4 * v);
+                const float4 wg = *reinterpret_cast<const float4*>(vec + 64 + (c0 - col_half * 64) + 4 * v);
                 const float whs[4] = {wh.x, wh.y, wh.z, wh.w}, wgs[4] = {wg.x, wg.y, wg.z, wg.w};
                 float o[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const float h = rbf(fmul(fmul(__int2float_rn(static_cast<int>(rh[4 * v + i])), xs), whs[i]));
                   const float g = rbf(fmul(fmul(__int2float_rn(static_cast<int>(rg[4 * v + i])), xs), wgs[i]));
-                  const float fg = __uint_as_float(static_cast<std::uint32_t>(__ldg(p.t_gate + (__float_as_uint(g) >> 16))) << 16);
-                  const float fh = __uint_as_float(static_cast<std::uint32_t>(__ldg(p.t_hidden + (__float_as_uint(h) >> 16))) << 16);
-                  o[i] = fmul(fg, fh);
+                  o[i] = fmul(situ_factor(s_tab, p.t_gate, g), situ_factor(s_tab + kMiniTable, p.t_hidden, h));
                 }
                 *reinterpret_cast<uint2*>(orow + col) = make_uint2(pack2(o[0], o[1]), pack2(o[2], o[3]));
               }
@@ -247,37 +313,51 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
       } else {
         const int col0 = nt * kBN;
+        constexpr int kHalfCols = kBN / 2;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBN; c0 += 32) {
-          std::uint32_t r[32];
-          tmem_ld_32x32(t_row + c0, r);
+        for (int c0 = col_half * kHalfCols; c0 < (col_half + 1) * kHalfCols; c0 += 64) {
+          std::uint32_t r[64];
+          tmem_ld_32x32(t_row + c0, *reinterpret_cast<std::uint32_t(*)[32]>(&r[0]));
+          tmem_ld_32x32(t_row + c0 + 32, *reinterpret_cast<std::uint32_t(*)[32]>(&r[32]));
           tmem_ld_wait();
           if (!row_ok) continue;
           if constexpr (kEpi == Epi::kAcc) {
             std::int32_t* arow = p.acc + static_cast<std::int64_t>(row) * p.ldacc;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < 64; ++i) {
               if (col0 + c0 + i < p.n) arow[col0 + c0 + i] = static_cast<std::int32_t>(r[i]);
             }
           } else {
             __nv_bfloat16* orow = p.out + static_cast<std::int64_t>(row) * p.ldo;
+            uint4 resv[8];
+            if constexpr (kEpi == Epi::kGatedResidual) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
+              for (int v = 0; v < 8; ++v) {
+                if (col0 + c0 + 8 * v < p.n) resv[v] = *reinterpret_cast<const uint4*>(orow + col0 + c0 + 8 * v);
+              }
+            }
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
               const int col = col0 + c0 + 8 * v;
               if (col >= p.n) continue;  // n % 8 == 0: a vector of 8 columns is all in or all out
-              const float4 w0 = ldg4(p.ws + col), w1 = ldg4(p.ws + col + 4);
+              const int lc = c0 - col_half * kHalfCols + 8 * v;  // column inside this warp's half
+              const float4 w0 = *reinterpret_cast<const float4*>(vec + lc);
+              const float4 w1 = *reinterpret_cast<const float4*>(vec + lc + 4);
+              const float4 b0 = *reinterpret_cast<const float4*>(vec + 128 + lc);
+              const float4 b1 = *reinterpret_cast<const float4*>(vec + 128 + lc + 4);
               const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-              float bias[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-              if (p.bias != nullptr) unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), bias);
+              const float bias[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
               float y[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 y[i] = fadd(fmul(fmul(__int2float_rn(static_cast<int>(r[8 * v + i])), xs), ws[i]), bias[i]);
               }
               if constexpr (kEpi == Epi::kGatedResidual) {
-                float gate[8], res[8];
-                unpack8(__ldg(reinterpret_cast<const uint4*>(p.gate + col)), gate);
-                unpack8(*reinterpret_cast<const uint4*>(orow + col), res);
+                const float4 g0 = *reinterpret_cast<const float4*>(vec + 256 + lc);
+                const float4 g1 = *reinterpret_cast<const float4*>(vec + 256 + lc + 4);
+                const float gate[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                float res[8];
+                unpack8(resv[v], res);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) y[i] = fadd(res[i], rbf(fmul(rbf(y[i]), gate[i])));
               }
