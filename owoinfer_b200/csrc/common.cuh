@@ -172,6 +172,59 @@ __device__ __forceinline__ void umma_f8(std::uint32_t d_tmem, std::uint64_t a_de
       : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster share one MMA; CTA rank 0 of the pair issues it. -------------------
+__device__ __forceinline__ std::uint32_t cluster_ctarank() {
+  std::uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The shared::cluster address of `smem_addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ std::uint32_t map_to_cta(std::uint32_t smem_addr, std::uint32_t rank) {
+  std::uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on an mbarrier given by its shared::cluster address (own or peer CTA).
+__device__ __forceinline__ void mbar_arrive_cluster(std::uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion bytes go to an mbarrier that may live in the peer CTA of the pair (shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(std::uint32_t dst, const CUtensorMap* map, std::uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<std::uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(std::uint32_t dst_smem, std::uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(std::uint32_t addr, std::uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns) : "memory");
+}
+// Commit of the pair's MMAs: arrives on the mbarrier at this shared-memory offset in every CTA of `cta_mask`.
+__device__ __forceinline__ void tc_commit_pair(std::uint32_t bar, std::uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(cta_mask)
+               : "memory");
+}
+// D[tmem of both CTAs] (+)= A[smem, 128 rows per CTA] * B[smem, N/2 rows per CTA]; issued by the pair's leader only.
+__device__ __forceinline__ void umma_i8_pair(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
+                                             std::uint32_t idesc, std::uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // TMEM -> registers: this warp's 32 lanes x 32 consecutive 32-bit columns (lane i of the warp gets TMEM lane
 // lane_base + i). taddr = (lane << 16) | column.
 __device__ __forceinline__ void tmem_ld_32x32(std::uint32_t taddr, std::uint32_t (&r)[32]) {

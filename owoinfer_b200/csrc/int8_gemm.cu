@@ -105,19 +105,24 @@ __device__ __forceinline__ float situ_factor(const std::uint16_t* mini, const st
   return __uint_as_float(entry << 16);
 }
 
-template <int kBN>
+// kCtas == 2: a CTA pair shares one 256 x 256 tile; each CTA stages its 128 rows of A and 128 of the 256 rows of B.
+template <int kBN, int kCtas>
 struct Shape {
-  static constexpr int kStages = kBN == 256 ? 4 : 6;
+  static constexpr int kStages = (kBN == 256 && kCtas == 1) ? 4 : 6;
   static constexpr int kABytes = kBM * kBK;
-  static constexpr int kBBytes = kBN * kBK;
+  static constexpr int kBBytes = (kBN / kCtas) * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
 };
 
-template <int kBN, Epi kEpi>
+template <int kBN, Epi kEpi, int kCtas>
 __global__ void __launch_bounds__(kThreads, 1)
 int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
-  using S = Shape<kBN>;
+  static_assert(kCtas == 1 || kBN == 256, "CTA pairs run 256 x 256 tiles");
+  using S = Shape<kBN, kCtas>;
+  const std::uint32_t rank = kCtas == 2 ? cluster_ctarank() : 0u;   // CTA of the pair; rank 0 issues the MMAs
+  const int tile0 = kCtas == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int tile_step = kCtas == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   constexpr int kStages = S::kStages;
   extern __shared__ std::uint8_t smem_raw[];
   __shared__ __align__(8) std::uint64_t s_full[kStages], s_empty[kStages], s_tmem_full[2], s_tmem_empty[2];
@@ -140,7 +145,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&s_tmem_full[i]), 1);
-      mbar_init(smem_u32(&s_tmem_empty[i]), 8);
+      mbar_init(smem_u32(&s_tmem_empty[i]), 8 * kCtas);
     }
     s_abort = 0;
     fence_mbar_init();
@@ -148,8 +153,13 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     prefetch_tensormap(&map_b);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&s_tmem_base), 512);
-    tmem_relinquish();
+    if constexpr (kCtas == 2) {
+      tmem_alloc_pair(smem_u32(&s_tmem_base), 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&s_tmem_base), 512);
+      tmem_relinquish();
+    }
   }
   if constexpr (kEpi == Epi::kSituGlu) {
     for (int i = threadIdx.x; i < 2 * kMiniTable; i += blockDim.x) {
@@ -160,6 +170,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (kCtas == 2) cluster_sync_all();  // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const std::uint32_t tmem_base = s_tmem_base;
   volatile int* abort_word = &s_abort;
@@ -170,9 +181,9 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 0) {
     if (lane == 0) {
       std::uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && *abort_word == 0; tile += gridDim.x) {
+      for (int tile = tile0; tile < total_tiles && *abort_word == 0; tile += tile_step) {
         const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
-        const int row_a = mt * kBM;
+        const int row_a = mt * (kBM * kCtas) + static_cast<int>(rank) * kBM;
         int row_b0, row_b1;
         if constexpr (kEpi == Epi::kSituGlu) {
           row_b0 = nt * 128;
@@ -181,24 +192,33 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           row_b0 = nt * kBN;
           row_b1 = nt * kBN + 128;
         }
+        if (kCtas == 2 && rank == 1) row_b0 = row_b1;  // the pair's second CTA stages the second 128 rows of B
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = static_cast<int>(it % kStages);
           const std::uint32_t ph = (it / kStages) & 1u;
           if (!wait_bar(smem_u32(&s_empty[s]), ph ^ 1u, abort_word)) break;
           const std::uint32_t full = smem_u32(&s_full[s]);
-          mbar_expect_tx(full, S::kStageBytes);
-          tma_load_2d(a_addr(s), &map_a, full, kb * kBK, row_a);
-          tma_load_2d(b_addr(s), &map_b, full, kb * kBK, row_b0);
-          if constexpr (kBN == 256) tma_load_2d(b_addr(s) + 128 * kBK, &map_b, full, kb * kBK, row_b1);
+          if constexpr (kCtas == 2) {
+            // Both CTAs' copies complete on the leader's barrier, which expects the bytes of the whole pair.
+            if (rank == 0) mbar_expect_tx(full, 2 * S::kStageBytes);
+            const std::uint32_t full_leader = map_to_cta(full, 0);
+            tma_load_2d_pair(a_addr(s), &map_a, full_leader, kb * kBK, row_a);
+            tma_load_2d_pair(b_addr(s), &map_b, full_leader, kb * kBK, row_b0);
+          } else {
+            mbar_expect_tx(full, S::kStageBytes);
+            tma_load_2d(a_addr(s), &map_a, full, kb * kBK, row_a);
+            tma_load_2d(b_addr(s), &map_b, full, kb * kBK, row_b0);
+            if constexpr (kBN == 256) tma_load_2d(b_addr(s) + 128 * kBK, &map_b, full, kb * kBK, row_b1);
+          }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr std::uint32_t idesc = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, kBM, kBN);
+    if (lane == 0 && rank == 0) {
+      constexpr std::uint32_t idesc = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, kBM * kCtas, kBN);
       std::uint32_t it = 0, tile_it = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && *abort_word == 0; tile += gridDim.x, ++tile_it) {
+      for (int tile = tile0; tile < total_tiles && *abort_word == 0; tile += tile_step, ++tile_it) {
         const std::uint32_t acc = tile_it & 1u, acc_ph = (tile_it >> 1) & 1u;
         if (!wait_bar(smem_u32(&s_tmem_empty[acc]), acc_ph ^ 1u, abort_word)) break;
         tc_fence_after();
@@ -216,13 +236,20 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
           for (int k4 = 0; k4 < kBK / 32; ++k4) {
             // 32 bytes further along K inside the swizzle atom: +2 in the descriptor's 16-byte address units.
-            umma_i8(d_tmem, da + static_cast<std::uint64_t>(2 * k4), db + static_cast<std::uint64_t>(2 * k4), idesc,
-                    (kb | k4) != 0 ? 1u : 0u);
+            if constexpr (kCtas == 2) {
+              umma_i8_pair(d_tmem, da + static_cast<std::uint64_t>(2 * k4), db + static_cast<std::uint64_t>(2 * k4), idesc,
+                           (kb | k4) != 0 ? 1u : 0u);
+            } else {
+              umma_i8(d_tmem, da + static_cast<std::uint64_t>(2 * k4), db + static_cast<std::uint64_t>(2 * k4), idesc,
+                      (kb | k4) != 0 ? 1u : 0u);
+            }
           }
-          tc_commit(smem_u32(&s_empty[s]));
+          if constexpr (kCtas == 2) tc_commit_pair(smem_u32(&s_empty[s]), 3);
+          else tc_commit(smem_u32(&s_empty[s]));
         }
         if (!ok) break;
-        tc_commit(smem_u32(&s_tmem_full[acc]));
+        if constexpr (kCtas == 2) tc_commit_pair(smem_u32(&s_tmem_full[acc]), 3);
+        else tc_commit(smem_u32(&s_tmem_full[acc]));
       }
     }
     __syncwarp();
@@ -231,7 +258,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // tile's columns, warps 6..9 the second half (SiTU-GLU: output columns, each needing its hidden and gate accumulator).
     const int quarter = warp & 3, col_half = (warp - 2) >> 2;
     std::uint32_t tile_it = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_it) {
+    for (int tile = tile0; tile < total_tiles; tile += tile_step, ++tile_it) {
       const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
       const std::uint32_t acc = tile_it & 1u, acc_ph = (tile_it >> 1) & 1u;
       // This warp's per-column vectors (w_scale, bias, gate of its half of the tile's columns) -> its own slice of shared
@@ -277,7 +304,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       __syncwarp();
       if (!wait_bar(smem_u32(&s_tmem_full[acc]), acc_ph, abort_word)) break;
       tc_fence_after();
-      const int row = mt * kBM + quarter * 32 + lane;
+      const int row = mt * (kBM * kCtas) + static_cast<int>(rank) * kBM + quarter * 32 + lane;
       const bool row_ok = row < p.m;
       const float xs = row_ok ? p.xs[row] : 0.f;
       const std::uint32_t t_row = tmem_base + acc * kBN + (static_cast<std::uint32_t>(quarter * 32) << 16);
@@ -369,7 +396,10 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_tmem_empty[acc]));
+      if (lane == 0) {
+        if constexpr (kCtas == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&s_tmem_empty[acc]), 0));
+        else mbar_arrive(smem_u32(&s_tmem_empty[acc]));
+      }
     }
   }
 
@@ -382,9 +412,11 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     __syncthreads();
   }
+  if constexpr (kCtas == 2) cluster_sync_all();  // nothing of the pair is in flight towards this CTA any more
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if constexpr (kCtas == 2) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -473,9 +505,9 @@ int check_output(const char* op, const char* name, const void* p, std::int64_t l
   return B2_OK;
 }
 
-template <int kBN, Epi kEpi>
+template <int kBN, Epi kEpi, int kCtas>
 int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaStream_t stream) {
-  using S = Shape<kBN>;
+  using S = Shape<kBN, kCtas>;
   CUtensorMap map_a, map_b;
   if (!make_tensor_map_2d(&map_a, a->x_q, static_cast<std::uint64_t>(a->k), static_cast<std::uint64_t>(a->m),
                           static_cast<std::uint64_t>(a->ldx), kBK, 128, op)) {
@@ -485,7 +517,7 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
                           static_cast<std::uint64_t>(a->k), kBK, 128, op)) {
     return B2_ERR_CUDA;
   }
-  auto kernel = int8_gemm_kernel<kBN, kEpi>;
+  auto kernel = int8_gemm_kernel<kBN, kEpi, kCtas>;
   // Opt in to the large dynamic shared-memory size once per device and instantiation.
   static bool configured[64] = {};
   int dev = 0;
@@ -497,31 +529,48 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
     }
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  p.m_tiles = (p.m + kBM - 1) / kBM;
+  p.m_tiles = (p.m + kBM * kCtas - 1) / (kBM * kCtas);
   if constexpr (kEpi == Epi::kSituGlu) p.n_tiles = (p.half + 127) / 128;
   else p.n_tiles = (p.n + kBN - 1) / kBN;
   const int total = p.m_tiles * p.n_tiles;
-  const int grid = std::min(total, sm_count());
-  kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_b, p);
-  return check_launch(op);
+  if constexpr (kCtas == 2) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * std::min(total, sm_count() / 2)));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = S::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr, cfg.numAttrs = 1;
+    if (const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, p); e != cudaSuccess) return fail_cuda(op, e);
+    return check_launch(op);
+  } else {
+    const int grid = std::min(total, sm_count());
+    kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_b, p);
+    return check_launch(op);
+  }
 }
 
-// Tile choice: 128 x 256 unless the problem then leaves SMs idle that 128 x 128 tiles would fill.
-int pick_bn(int tile, std::int64_t m, std::int64_t n) {
-  if (tile == B2_TILE_128x128) return 128;
-  if (tile == B2_TILE_128x256) return 256;
-  const std::int64_t mt = (m + kBM - 1) / kBM;
-  const std::int64_t big = mt * ((n + 255) / 256);
-  return big >= sm_count() ? 256 : 128;
+// Tile choice: CTA pairs on 256 x 256 tiles when there are enough of them to fill the GPU; else one CTA per 128 x 256
+// tile, or 128 x 128 when even those leave SMs idle.
+int pick_tile(int tile, std::int64_t m, std::int64_t n_tiles_256) {
+  if (tile != B2_TILE_AUTO) return tile;
+  const std::int64_t pairs = ((m + 255) / 256) * n_tiles_256;
+  if (pairs >= sm_count() / 2) return B2_TILE_2CTA_256x256;
+  const std::int64_t big = ((m + kBM - 1) / kBM) * n_tiles_256;
+  return big >= sm_count() ? B2_TILE_128x256 : B2_TILE_128x128;
 }
 
 template <Epi kEpi>
 int dispatch(const char* op, const b2_int8_operands* a, const GemmParams& p, cudaStream_t stream, int tile) {
   if constexpr (kEpi == Epi::kSituGlu) {
-    return launch_kernel<256, kEpi>(op, a, p, stream);
+    const int t = pick_tile(tile, a->m, (p.half + 127) / 128);
+    return t == B2_TILE_2CTA_256x256 ? launch_kernel<256, kEpi, 2>(op, a, p, stream) : launch_kernel<256, kEpi, 1>(op, a, p, stream);
   } else {
-    return pick_bn(tile, a->m, a->n) == 256 ? launch_kernel<256, kEpi>(op, a, p, stream)
-                                            : launch_kernel<128, kEpi>(op, a, p, stream);
+    const int t = pick_tile(tile, a->m, (a->n + 255) / 256);
+    if (t == B2_TILE_2CTA_256x256) return launch_kernel<256, kEpi, 2>(op, a, p, stream);
+    return t == B2_TILE_128x256 ? launch_kernel<256, kEpi, 1>(op, a, p, stream) : launch_kernel<128, kEpi, 1>(op, a, p, stream);
   }
 }
 

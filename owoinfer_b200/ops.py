@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import check
 
-TILE_AUTO, TILE_128x256, TILE_128x128 = 0, 1, 2
+TILE_AUTO, TILE_128x256, TILE_128x128, TILE_2CTA_256x256 = 0, 1, 2, 3
 TIER_INT8, TIER_W4A4_VIA_INT8, TIER_W4A8 = 0, 1, 2
 ATTENTION_Q8_FP8_F32ACC = 3
 
