@@ -7,9 +7,10 @@
 //     quantise   Q per (32 tokens, head) [when not fused]; K - k_mean per (64 keys, head) -> int8; V * v_recp -> e4m3
 //   attention (tensor-core-bound): one CTA per (128 query rows, head, sequence); 128-key tiles
 //     S = Q8 · K8^T   tcgen05.mma kind::i8, int32 accumulator in TMEM (exact)
-//     softmax         4 warps, one row per thread: S -> fp32 (round toward zero), scaled by
+//     softmax         4 warps, one row per thread: S -> fp32 (exact: |S| < 2^22), scaled by
 //                     sm_scale * log2e * q_scale * k_scale[64-key block], running max / denominator in fp32, P = exp2(.)
-//                     shifted so that its maximum is 2^floor3(log2(p_range)), rounded to e4m3 into a swizzled shared tile
+//                     shifted so that its maximum stays within [p_range / 2, p_range] (the reference maximum may lag the
+//                     true one by one binade, which makes rescaling O rare), rounded to e4m3 into a swizzled shared tile
 //     O += P8 · V8    tcgen05.mma kind::f8f6f4, fp32 accumulator in TMEM; V is read in its natural [key, channel]
 //                     layout as an MN-major operand, so the pre-pass needs no transpose
 //     out = O / d * v_scale[channel] -> bf16
@@ -17,6 +18,7 @@
 // third_party/sageattention/csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:54-743 (variant kInt8Fp8F32Acc);
 // src/kernels/fused/qk_norm_rope.cu:43-89; src/kernels/basic/rope.cu:30-51.
 #include <algorithm>
+#include <climits>
 #include <cmath>
 #include <string>
 
@@ -445,6 +447,7 @@ constexpr int kTileBytes = 128 * 128;
 constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 1) + 1024;  // Q, K/V stages, P, alignment slack
 constexpr int kAttnThreads = 192;
 constexpr std::uint32_t kTmemCols = 256;  // S: columns [0, 128); O: columns [128, 256)
+constexpr float kLazy = 1.0f;              // how far (log2 units) the softmax reference maximum may lag the true one
 
 struct AttnArgs {
   const float* q_scale;
@@ -584,30 +587,48 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const float c0 = qs * a.k_scale[sc_base * a.k_blocks + 2 * t];
       const float c1 = (2 * t + 1 < a.k_blocks) ? qs * a.k_scale[sc_base * a.k_blocks + 2 * t + 1] : 0.f;
       const int valid = min(kTileK, kv_len - t * kTileK);
-      // Pass 1: row maximum of the scaled scores over the valid keys.
-      float mx = -5000000.0f;
+      const bool full_tile = valid == kTileK;
+      // Pass 1: row maximum. The scales are positive, so the maximum of the scaled scores of a 64-key block is the
+      // scaled integer maximum: integer max per block, two multiplies per row.
+      int imax0 = INT_MIN, imax1 = INT_MIN;
 #pragma unroll 1
       for (int cc = 0; cc < 4; ++cc) {
         std::uint32_t r[32];
         tmem_ld_32x32(tmem_s + lane_off + cc * 32, r);
         tmem_ld_wait();
-        const float c = cc < 2 ? c0 : c1;
+        int mloc = INT_MIN;
+        if (full_tile) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float sv = __int2float_rz(static_cast<int>(r[i])) * c;
-          if (cc * 32 + i < valid) mx = fmaxf(mx, sv);
+          for (int i = 0; i < 32; ++i) mloc = max(mloc, static_cast<int>(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mloc = (cc * 32 + i < valid) ? max(mloc, static_cast<int>(r[i])) : mloc;
         }
+        if (cc < 2) imax0 = max(imax0, mloc);
+        else imax1 = max(imax1, mloc);
       }
-      const float m_new = fmaxf(m_run, mx - a.p_offset);
-      const float alpha = ex2(m_run - m_new);
-      // O (and the denominator) follow the running maximum. PV(t-1) must have landed before O is touched or P reused.
+      float mx = -5000000.0f;
+      if (imax0 != INT_MIN) mx = fmaxf(mx, static_cast<float>(imax0) * c0);
+      if (imax1 != INT_MIN) mx = fmaxf(mx, static_cast<float>(imax1) * c1);
+      // The reference maximum m_run may lag the true running maximum by up to kLazy (in log2 units): P is scaled so that
+      // its largest value is 2^(p_offset - kLazy) against an exact maximum, hence at most 2^p_offset <= p_range against
+      // a lagging one. O and the denominator are rescaled only when some row of the warp exceeds the lag.
+      const float m_tile = mx - (a.p_offset - kLazy);
+      const bool grow = __any_sync(0xffffffffu, m_tile > m_run + kLazy);
+      float alpha = 1.0f;
+      if (grow) {
+        const float m_new = fmaxf(m_run, m_tile);
+        alpha = ex2(m_run - m_new);
+        m_run = m_new;
+      }
+      // PV(t-1) must have landed before O is touched or the P tile reused.
       if (t > 0) {
         if (!wait_bar(smem_u32(&s_pv_done), (t - 1) & 1u, abort_word)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+        if (grow) {
 #pragma unroll 1
           for (int cc = 0; cc < 4; ++cc) {
             std::uint32_t r[32];
@@ -621,22 +642,32 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
       }
       d_run *= alpha;
-      m_run = m_new;
-      // Pass 2: P = exp2(score - m), denominator from the unrounded P, e4m3 P into the swizzled tile (row = 128 bytes,
-      // 16-byte chunk j of row r stored at chunk j ^ (r % 8)).
+      // Pass 2: P = exp2(S * c - m). |S| < 2^22, so S + 0x4B400000 reinterpreted as fp32 is exactly 12582912 + S: one
+      // integer add and one FMA (with the constant folded into the addend) replace the conversion, multiply and subtract.
+      // Denominator from the unrounded P; e4m3 P into the swizzled tile (row = 128 bytes, 16-byte chunk j of row r
+      // stored at chunk j ^ (r % 8)).
       std::uint8_t* prow = p_generic + r_local * 128;
+      const float bias0 = -fmaf(12582912.0f, c0, m_run), bias1 = -fmaf(12582912.0f, c1, m_run);
+      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll 1
       for (int cc = 0; cc < 4; ++cc) {
         std::uint32_t r[32];
         tmem_ld_32x32(tmem_s + lane_off + cc * 32, r);
         tmem_ld_wait();
-        const float c = cc < 2 ? c0 : c1;
+        const float c = cc < 2 ? c0 : c1, bias = cc < 2 ? bias0 : bias1;
         float pv[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float e = ex2(fmaf(__int2float_rz(static_cast<int>(r[i])), c, -m_run));
-          pv[i] = (cc * 32 + i < valid) ? e : 0.f;
-          d_run += pv[i];
+        for (int i = 0; i < 32; ++i) pv[i] = ex2(fmaf(__uint_as_float(r[i] + 0x4B400000u), c, bias));
+        if (!full_tile) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pv[i] = (cc * 32 + i < valid) ? pv[i] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          d0 += pv[i];
+          d1 += pv[i + 1];
+          d2 += pv[i + 2];
+          d3 += pv[i + 3];
         }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -648,6 +679,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                          e4m3x4(pv[16 * j + 12], pv[16 * j + 13], pv[16 * j + 14], pv[16 * j + 15]));
         }
       }
+      d_run += (d0 + d1) + (d2 + d3);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
