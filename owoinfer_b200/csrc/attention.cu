@@ -7,7 +7,7 @@
 //     quantise   Q per (32 tokens, head) [when not fused]; K - k_mean per (64 keys, head) -> int8; V * v_recp -> e4m3
 //   attention (tensor-core-bound): one CTA per (128 query rows, head, sequence); 128-key tiles
 //     S = Q8 · K8^T   tcgen05.mma kind::i8, int32 accumulator in TMEM (exact)
-//     softmax         4 warps, one row per thread: S -> fp32 (exact: |S| < 2^22), scaled by
+//     softmax         8 warps, two threads per row (one 64-key block each): S -> fp32 (exact: |S| < 2^22), scaled by
 //                     sm_scale * log2e * q_scale * k_scale[64-key block], running max / denominator in fp32, P = exp2(.)
 //                     shifted so that its maximum stays within [p_range / 2, p_range] (the reference maximum may lag the
 //                     true one by one binade, which makes rescaling O rare), rounded to e4m3 into a swizzled shared tile
@@ -445,7 +445,7 @@ constexpr int kTileQ = 128, kTileK = 128;
 constexpr int kKvStages = 2;
 constexpr int kTileBytes = 128 * 128;
 constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 1) + 1024;  // Q, K/V stages, P, alignment slack
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;  // TMA warp, MMA warp, 8 softmax warps
 constexpr std::uint32_t kTmemCols = 256;  // S: columns [0, 128); O: columns [128, 256)
 constexpr float kLazy = 1.0f;              // how far (log2 units) the softmax reference maximum may lag the true one
 
@@ -462,7 +462,7 @@ struct AttnArgs {
   float p_offset;
 };
 
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(kAttnThreads, 2)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const AttnArgs a) {
   const int bq = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -486,6 +486,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       s_v_empty[kKvStages], s_s_full, s_p_full, s_pv_done;
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ float s_mx[2][2][kTileQ];  // [tile parity][key half][row]: block maxima exchanged by a row's two threads
+  __shared__ float s_den[2][kTileQ];    // [key half][row]: the two partial denominators of a row
   const std::uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const std::uint32_t q_smem = base;
   const auto k_smem = [&](int s) { return base + kTileBytes * (1 + s); };
@@ -502,7 +504,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(smem_u32(&s_v_empty[s]), 1);
     }
     mbar_init(smem_u32(&s_s_full), 1);
-    mbar_init(smem_u32(&s_p_full), 4);
+    mbar_init(smem_u32(&s_p_full), 8);
     mbar_init(smem_u32(&s_pv_done), 1);
     s_abort = 0;
     fence_mbar_init();
@@ -571,48 +573,51 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     __syncwarp();
   } else {
-    const int quarter = warp & 3;
+    // Softmax: 8 warps, two threads per query row. Warp w may touch TMEM lanes [32 (w % 4), +32); warps 2..5 take keys
+    // 0..63 of a tile (one K scale block), warps 6..9 keys 64..127. The two threads of a row exchange their block
+    // maxima through shared memory once per tile (and their denominators once at the end).
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r_local = quarter * 32 + lane;  // row of the tile == TMEM lane
     const std::uint32_t lane_off = static_cast<std::uint32_t>(quarter * 32) << 16;
+    const std::uint32_t col_off = static_cast<std::uint32_t>(half * 64);
     const std::int64_t sc_base = static_cast<std::int64_t>(b) * a.heads + h;
     const float qs = a.q_scale[sc_base * a.q_blocks + (q0 + quarter * 32) / 32] * a.scale_log2;
     float m_run = -5000000.0f, d_run = 0.f;
-    bool ok = true;
+    // A warp whose bounded wait expired keeps walking the loop so that it still meets the others at the named
+    // barriers, but touches nothing.
+    bool dead = false;
     for (int t = 0; t < n_tiles; ++t) {
-      if (!wait_bar(smem_u32(&s_s_full), t & 1u, abort_word)) {
-        ok = false;
-        break;
-      }
+      if (!dead && !wait_bar(smem_u32(&s_s_full), t & 1u, abort_word)) dead = true;
       tc_fence_after();
-      const float c0 = qs * a.k_scale[sc_base * a.k_blocks + 2 * t];
-      const float c1 = (2 * t + 1 < a.k_blocks) ? qs * a.k_scale[sc_base * a.k_blocks + 2 * t + 1] : 0.f;
-      const int valid = min(kTileK, kv_len - t * kTileK);
-      const bool full_tile = valid == kTileK;
-      // Pass 1: row maximum. The scales are positive, so the maximum of the scaled scores of a 64-key block is the
-      // scaled integer maximum: integer max per block, two multiplies per row.
-      int imax0 = INT_MIN, imax1 = INT_MIN;
+      const int kblock = 2 * t + half;
+      const float c = (!dead && kblock < a.k_blocks) ? qs * a.k_scale[sc_base * a.k_blocks + kblock] : 0.f;
+      const int valid = min(64, kv_len - t * kTileK - half * 64);  // valid keys of this thread's block (may be <= 0)
+      const bool full_tile = valid == 64;
+      // Pass 1: block maximum. The scale is positive, so the maximum scaled score is the scaled integer maximum.
+      int imax = INT_MIN;
+      if (!dead) {
 #pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        std::uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_off + cc * 32, r);
-        tmem_ld_wait();
-        int mloc = INT_MIN;
-        if (full_tile) {
+        for (int cc = 0; cc < 2; ++cc) {
+          std::uint32_t r[32];
+          tmem_ld_32x32(tmem_s + lane_off + col_off + cc * 32, r);
+          tmem_ld_wait();
+          if (full_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mloc = max(mloc, static_cast<int>(r[i]));
-        } else {
+            for (int i = 0; i < 32; ++i) imax = max(imax, static_cast<int>(r[i]));
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mloc = (cc * 32 + i < valid) ? max(mloc, static_cast<int>(r[i])) : mloc;
+            for (int i = 0; i < 32; ++i) imax = (cc * 32 + i < valid) ? max(imax, static_cast<int>(r[i])) : imax;
+          }
         }
-        if (cc < 2) imax0 = max(imax0, mloc);
-        else imax1 = max(imax1, mloc);
       }
-      float mx = -5000000.0f;
-      if (imax0 != INT_MIN) mx = fmaxf(mx, static_cast<float>(imax0) * c0);
-      if (imax1 != INT_MIN) mx = fmaxf(mx, static_cast<float>(imax1) * c1);
+      const float mx_own = imax != INT_MIN ? static_cast<float>(imax) * c : -5000000.0f;
+      s_mx[t & 1][half][r_local] = mx_own;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const float mx = fmaxf(mx_own, s_mx[t & 1][half ^ 1][r_local]);
       // The reference maximum m_run may lag the true running maximum by up to kLazy (in log2 units): P is scaled so that
       // its largest value is 2^(p_offset - kLazy) against an exact maximum, hence at most 2^p_offset <= p_range against
-      // a lagging one. O and the denominator are rescaled only when some row of the warp exceeds the lag.
+      // a lagging one. O and the denominator are rescaled only when some row of the warp exceeds the lag. Both threads
+      // of a row see the same values, so both warps take the same decision.
       const float m_tile = mx - (a.p_offset - kLazy);
       const bool grow = __any_sync(0xffffffffu, m_tile > m_run + kLazy);
       float alpha = 1.0f;
@@ -622,39 +627,36 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         m_run = m_new;
       }
       // PV(t-1) must have landed before O is touched or the P tile reused.
-      if (t > 0) {
-        if (!wait_bar(smem_u32(&s_pv_done), (t - 1) & 1u, abort_word)) {
-          ok = false;
-          break;
-        }
+      if (t > 0 && !dead) {
+        if (!wait_bar(smem_u32(&s_pv_done), (t - 1) & 1u, abort_word)) dead = true;
         tc_fence_after();
-        if (grow) {
+        if (grow && !dead) {
 #pragma unroll 1
-          for (int cc = 0; cc < 4; ++cc) {
+          for (int cc = 0; cc < 2; ++cc) {
             std::uint32_t r[32];
-            tmem_ld_32x32(tmem_o + lane_off + cc * 32, r);
+            tmem_ld_32x32(tmem_o + lane_off + col_off + cc * 32, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_off + cc * 32, r);
+            tmem_st_32x32(tmem_o + lane_off + col_off + cc * 32, r);
           }
           tmem_st_wait();
         }
       }
       d_run *= alpha;
+      if (dead) continue;
       // Pass 2: P = exp2(S * c - m). |S| < 2^22, so S + 0x4B400000 reinterpreted as fp32 is exactly 12582912 + S: one
       // integer add and one FMA (with the constant folded into the addend) replace the conversion, multiply and subtract.
       // Denominator from the unrounded P; e4m3 P into the swizzled tile (row = 128 bytes, 16-byte chunk j of row r
       // stored at chunk j ^ (r % 8)).
       std::uint8_t* prow = p_generic + r_local * 128;
-      const float bias0 = -fmaf(12582912.0f, c0, m_run), bias1 = -fmaf(12582912.0f, c1, m_run);
+      const float bias = -fmaf(12582912.0f, c, m_run);
       float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         std::uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_off + cc * 32, r);
+        tmem_ld_32x32(tmem_s + lane_off + col_off + cc * 32, r);
         tmem_ld_wait();
-        const float c = cc < 2 ? c0 : c1, bias = cc < 2 ? bias0 : bias1;
         float pv[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) pv[i] = ex2(fmaf(__uint_as_float(r[i] + 0x4B400000u), c, bias));
@@ -671,7 +673,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          const int chunk = (cc * 2 + j) ^ (r_local & 7);
+          const int chunk = (half * 4 + cc * 2 + j) ^ (r_local & 7);
           *reinterpret_cast<uint4*>(prow + chunk * 16) =
               make_uint4(e4m3x4(pv[16 * j + 0], pv[16 * j + 1], pv[16 * j + 2], pv[16 * j + 3]),
                          e4m3x4(pv[16 * j + 4], pv[16 * j + 5], pv[16 * j + 6], pv[16 * j + 7]),
@@ -685,16 +687,20 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_p_full));
     }
-    if (ok && wait_bar(smem_u32(&s_pv_done), (n_tiles - 1) & 1u, abort_word)) {
+    // Row denominator = the two threads' sums.
+    s_den[half][r_local] = d_run;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const float d_row = d_run + s_den[half ^ 1][r_local];
+    if (!dead && wait_bar(smem_u32(&s_pv_done), (n_tiles - 1) & 1u, abort_word)) {
       tc_fence_after();
-      const float inv_d = rcp_approx(d_run);
+      const float inv_d = rcp_approx(d_row);
       const int row = q0 + r_local;
-      __nv_bfloat16* orow = a.out + static_cast<std::int64_t>(q_start + row) * a.out_row + h * a.out_head;
-      const float* vs = a.v_scale + sc_base * kHeadDim;
+      __nv_bfloat16* orow = a.out + static_cast<std::int64_t>(q_start + row) * a.out_row + h * a.out_head + half * 64;
+      const float* vs = a.v_scale + sc_base * kHeadDim + half * 64;
 #pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         std::uint32_t r[32];
-        tmem_ld_32x32(tmem_o + lane_off + cc * 32, r);
+        tmem_ld_32x32(tmem_o + lane_off + col_off + cc * 32, r);
         tmem_ld_wait();
         if (row < qo_len) {
 #pragma unroll
