@@ -126,6 +126,20 @@ typedef struct b2_w4_weight {
 int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_w4_weight* w, int64_t m, int64_t n,
                  int64_t k, int epilogue, const void* aux, void* out, int64_t ldo, int8_t* scratch, void* stream);
 
+/* b2_w4a8_gemm without a scratch argument, for hosts that cannot give this call any device memory of their own and
+ * are not allowed to allocate: a plug-in running on a step path where the CUDA allocator is off limits (an allocation
+ * can synchronise the device or fail in the middle of a step), or an embedding whose arena was sized before the W4A8
+ * tier was chosen. The decoded INT8 weight is written to a 16 MiB array inside the library's own device image, so
+ * n * k must not exceed 16 MiB (16777216); larger weights are refused with B2_ERR_INVALID_ARGUMENT and need
+ * b2_w4a8_gemm. Nothing is allocated or freed, by this call or by anything it calls. Every GPU that loads the library
+ * carries the array until the process ends. The first call on a device looks up the array's device address (the device
+ * must be current); make that first call before capturing a stream. All calls on a device share the one array and it
+ * keeps what the last call decoded: two calls whose kernels can overlap on the GPU (different streams) race on it, so
+ * serialise them. Nothing in it needs clearing: each call overwrites the n * k bytes it then reads.
+ * No counterpart in the reference, whose callers always own their buffers. */
+int b2_w4a8_gemm_noalloc(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_w4_weight* w, int64_t m, int64_t n,
+                         int64_t k, int epilogue, const void* aux, void* out, int64_t ldo, void* stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * QK-norm + RoPE, RoPE table, 8-bit attention.
  * ------------------------------------------------------------------------------------------------------------- */

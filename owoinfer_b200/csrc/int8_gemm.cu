@@ -476,6 +476,33 @@ int situ_tables(cudaStream_t stream, SituTables* out) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// Built-in scratch of b2_w4a8_gemm_noalloc: part of the library's device image, so every GPU that loads the library
+// holds these 16 MiB until the process exits. The name below is only a host-side handle; the device address is asked
+// from the runtime once per device (with that device current) and that address is what the kernels receive.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr std::size_t kStaticScratchBytes = std::size_t{16} << 20;
+static __device__ __align__(256) std::int8_t g_w4_scratch[kStaticScratchBytes];
+
+int static_scratch(std::int8_t** out) {
+  constexpr const char* op = "w4a8_gemm_noalloc";
+  static std::mutex mu;
+  static std::int8_t* ptrs[64] = {};
+  int dev = 0;
+  if (const cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return fail_cuda(op, e);
+  if (dev < 0 || dev >= 64) return fail_status(B2_ERR_INTERNAL, op, "device ordinal out of range");
+  const std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    std::int8_t* p = nullptr;
+    if (const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_w4_scratch); e != cudaSuccess) {
+      return fail_cuda(op, e);
+    }
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return B2_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // Host: validation and launch.
 // ---------------------------------------------------------------------------------------------------------------
 int check_operands(const char* op, const b2_int8_operands* a) {
@@ -663,5 +690,22 @@ int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_
   if (epilogue == 1) return b2_int8_gemm_gated_residual(&a, nullptr, aux, out, ldo, stream, B2_TILE_AUTO);
   return b2_int8_gemm_situ_glu(&a, out, ldo, stream, B2_TILE_AUTO);
 }
+
+/* b2_w4a8_gemm for callers that have no device memory to lend as scratch and may not allocate any: the decoded INT8
+ * weight goes to a fixed 16 MiB array that lives in this library's device image instead of a caller buffer. See the
+ * header for the rules (size limit, first call, overlapping calls). */
+int b2_w4a8_gemm_noalloc(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_w4_weight* w, int64_t m, int64_t n,
+                         int64_t k, int epilogue, const void* aux, void* out, int64_t ldo, void* stream) {
+  constexpr const char* op = "w4a8_gemm_noalloc";
+  if (n <= 0 || k <= 0 || static_cast<std::uint64_t>(n) * static_cast<std::uint64_t>(k) > kStaticScratchBytes) {
+    return fail_invalid(op, "the decoded weight (n * k = " + std::to_string(n) + " * " + std::to_string(k) +
+                                " bytes) does not fit the built-in scratch of " + std::to_string(kStaticScratchBytes) +
+                                " bytes; use b2_w4a8_gemm with a caller-owned scratch buffer");
+  }
+  std::int8_t* scratch = nullptr;
+  if (const int rc = static_scratch(&scratch)) return rc;
+  return b2_w4a8_gemm(x_q, ldx, x_scale, w, m, n, k, epilogue, aux, out, ldo, scratch, stream);
+}
+
 
 }  // extern "C"
