@@ -213,6 +213,23 @@ def profile_kernels(ops, torch, L, F, w, iters=8):
     out["norm_rotate_quantize"] = {"ms": ms, "gbs": 3.0 * L * D / ms / 1e6}
     ms = timed(lambda: ops.rotate_quantize(x, q=q, scale=s))
     out["rotate_quantize"] = {"ms": ms, "gbs": 3.0 * L * D / ms / 1e6}
+    xf = torch.randn((L, F), device=dev).to(torch.bfloat16)
+    qf = torch.empty((L, F), dtype=torch.int8, device=dev)
+    ms = timed(lambda: ops.rotate_quantize(xf, q=qf, scale=s))
+    out["rotate_quantize_ffn"] = {"ms": ms, "gbs": 3.0 * L * F / ms / 1e6}
+    del xf, qf
+    # 8-bit attention of the step's sequences (pre-pass with fused QK-norm + RoPE, then the attention kernel).
+    qkv = torch.randn((L, 3 * D), device=dev).to(torch.bfloat16)
+    views = [qkv.as_strided((L, HEADS, 128), (3 * D, 128, 1), i * D) for i in range(3)]
+    o = torch.empty((L, HEADS, 128), dtype=torch.bfloat16, device=dev)
+    seqs = max(1, L // 8192)
+    sl = L // seqs
+    cu = torch.tensor([i * sl for i in range(seqs + 1)], dtype=torch.int32, device=dev)
+    rope = ops.moss_rope_table(64, 64, sl - 4096).repeat(seqs, 1).contiguous() if sl >= 4096 else ops.moss_rope_table(1, 1, sl - 1).repeat(seqs, 1).contiguous()
+    qn = torch.ones(128, device=dev).to(torch.bfloat16)
+    _, wsa = ops.attention_q8(*views, o, cu, cu, sl, ops.SM_SCALE, norm_rope=(qn, qn, rope))
+    ms = timed(lambda: ops.attention_q8(*views, o, cu, cu, sl, ops.SM_SCALE, workspace=wsa, norm_rope=(qn, qn, rope)))
+    out["attention_q8"] = {"ms": ms, "tops": 4.0 * seqs * sl * sl * D / ms / 1e9}
     return out
 
 

@@ -5,9 +5,10 @@
 //                fused prologue also RMS-norm + RoPE of q and k (k written back), and Q quantised per (32 tokens, head)
 //     finalize   k_mean = bf16(sum / len); v_scale = amax / v_range; v_recp = v_range / amax
 //     quantise   Q per (32 tokens, head) [when not fused]; K - k_mean per (64 keys, head) -> int8; V * v_recp -> e4m3
-//   attention (tensor-core-bound): one CTA per (128 query rows, head, sequence); 128-key tiles
+//   attention (tensor-core-bound): one CTA per (128 query rows, head, sequence), one CTA per SM; 128-key tiles; S is
+//   double-buffered in TMEM so the MMA warp runs a tile ahead of the softmax warps
 //     S = Q8 · K8^T   tcgen05.mma kind::i8, int32 accumulator in TMEM (exact)
-//     softmax         8 warps, two threads per row (one 64-key block each): S -> fp32 (exact: |S| < 2^22), scaled by
+//     softmax         16 warps, four threads per row (32 keys each): S -> fp32 (exact: |S| < 2^22), scaled by
 //                     sm_scale * log2e * q_scale * k_scale[64-key block], running max / denominator in fp32, P = exp2(.)
 //                     shifted so that its maximum stays within [p_range / 2, p_range] (the reference maximum may lag the
 //                     true one by one binade, which makes rescaling O rare), rounded to e4m3 into a swizzled shared tile
@@ -229,11 +230,21 @@ __device__ __forceinline__ void norm_rope_row(const float* x, const float* w, co
   const float r = rsqrtf(fadd(fmul(total, factor), 1e-6f));
   const bool lo_half = lane16 < 8;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float n = rbf(fmul(rbf(fmul(x[j], r)), w[j]));
-    const float other = __shfl_xor_sync(0xffffffffu, n, 8, 16);
-    const float lo = lo_half ? n : other, hi = lo_half ? other : n;
-    y[j] = lo_half ? rbf(fadd(rbf(fmul(lo, co[j])), rbf(fmul(-hi, si[j])))) : rbf(fadd(rbf(fmul(hi, co[j])), rbf(fmul(lo, si[j]))));
+  for (int j = 0; j < 8; j += 2) {
+    // Two channels per packed bf16 conversion.
+    float n0 = fmul(x[j], r), n1 = fmul(x[j + 1], r);
+    rbf2(n0, n1);
+    n0 = fmul(n0, w[j]), n1 = fmul(n1, w[j + 1]);
+    rbf2(n0, n1);
+    const float o0 = __shfl_xor_sync(0xffffffffu, n0, 8, 16), o1 = __shfl_xor_sync(0xffffffffu, n1, 8, 16);
+    // lo' = bf16(lo*cos) + bf16(-hi*sin); hi' = bf16(hi*cos) + bf16(lo*sin): own * cos, then the partner term.
+    float a0 = fmul(n0, co[j]), a1 = fmul(n1, co[j + 1]);
+    float b0 = fmul(lo_half ? -o0 : o0, si[j]), b1 = fmul(lo_half ? -o1 : o1, si[j + 1]);
+    rbf2(a0, a1);
+    rbf2(b0, b1);
+    float s0 = fadd(a0, b0), s1 = fadd(a1, b1);
+    rbf2(s0, s1);
+    y[j] = s0, y[j + 1] = s1;
   }
 }
 
@@ -442,12 +453,13 @@ __global__ void __launch_bounds__(1024) quant_kv_kernel(const PrepArgs p) {
 // The attention kernel.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kTileQ = 128, kTileK = 128;
-constexpr int kKvStages = 2;
+constexpr int kKvStages = 3;
 constexpr int kTileBytes = 128 * 128;
-constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 1) + 1024;  // Q, K/V stages, P, alignment slack
-constexpr int kAttnThreads = 320;  // TMA warp, MMA warp, 8 softmax warps
-constexpr std::uint32_t kTmemCols = 256;  // S: columns [0, 128); O: columns [128, 256)
-constexpr float kLazy = 1.0f;              // how far (log2 units) the softmax reference maximum may lag the true one
+constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 2) + 1024;  // Q, K/V stages, two P tiles, alignment slack
+constexpr int kSoftmaxWarps = 16;
+constexpr int kAttnThreads = 64 + 32 * kSoftmaxWarps;  // TMA warp, MMA warp, 16 softmax warps
+constexpr std::uint32_t kTmemCols = 512;  // S[0]: columns [0, 128); S[1]: [128, 256); O: [256, 384)
+constexpr float kLazy = 1.0f;             // how far (log2 units) the softmax reference maximum may lag the true one
 
 struct AttnArgs {
   const float* q_scale;
@@ -462,7 +474,10 @@ struct AttnArgs {
   float p_offset;
 };
 
-__global__ void __launch_bounds__(kAttnThreads, 2)
+// One CTA per SM (its shared memory and its 512 TMEM columns fill the SM). The score tile S is double-buffered in TMEM:
+// the MMA warp runs one key tile ahead of the softmax warps, so the tensor pipe works on Q·K^T of tile t + 1 and P·V of
+// tile t - 1 while the sixteen softmax warps turn S(t) into P(t).
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const AttnArgs a) {
   const int bq = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -483,17 +498,17 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
   extern __shared__ std::uint8_t smem_raw[];
   __shared__ __align__(8) std::uint64_t s_q_full, s_k_full[kKvStages], s_k_empty[kKvStages], s_v_full[kKvStages],
-      s_v_empty[kKvStages], s_s_full, s_p_full, s_pv_done;
+      s_v_empty[kKvStages], s_s_full[2], s_p_full[2], s_pv_done;
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ float s_mx[2][2][kTileQ];  // [tile parity][key half][row]: block maxima exchanged by a row's two threads
-  __shared__ float s_den[2][kTileQ];    // [key half][row]: the two partial denominators of a row
+  __shared__ float s_mx[2][4][kTileQ];  // [tile parity][key quarter][row]: block maxima exchanged by a row's four threads
+  __shared__ float s_den[4][kTileQ];    // [key quarter][row]: the four partial denominators of a row
   const std::uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const std::uint32_t q_smem = base;
   const auto k_smem = [&](int s) { return base + kTileBytes * (1 + s); };
   const auto v_smem = [&](int s) { return base + kTileBytes * (1 + kKvStages + s); };
-  const std::uint32_t p_smem = base + kTileBytes * (1 + 2 * kKvStages);
-  std::uint8_t* p_generic = smem_raw + (p_smem - smem_u32(smem_raw));
+  const auto p_smem = [&](int i) { return base + kTileBytes * (1 + 2 * kKvStages + i); };
+  std::uint8_t* p_generic = smem_raw + (p_smem(0) - smem_u32(smem_raw));
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&s_q_full), 1);
@@ -503,8 +518,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(smem_u32(&s_v_full[s]), 1);
       mbar_init(smem_u32(&s_v_empty[s]), 1);
     }
-    mbar_init(smem_u32(&s_s_full), 1);
-    mbar_init(smem_u32(&s_p_full), 8);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&s_s_full[i]), 1);
+      mbar_init(smem_u32(&s_p_full[i]), kSoftmaxWarps);
+    }
     mbar_init(smem_u32(&s_pv_done), 1);
     s_abort = 0;
     fence_mbar_init();
@@ -519,7 +536,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const std::uint32_t tmem_s = s_tmem_base, tmem_o = s_tmem_base + 128;
+  const std::uint32_t tmem_s = s_tmem_base, tmem_o = s_tmem_base + 256;
   volatile int* abort_word = &s_abort;
   const int n_tiles = (kv_len + kTileK - 1) / kTileK;
 
@@ -543,25 +560,28 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (lane == 0) {
       constexpr std::uint32_t idesc_qk = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, 128, 128);
       constexpr std::uint32_t idesc_pv = umma_idesc(/*f32*/ 1, /*e4m3*/ 0, /*e4m3*/ 0, 0, /*B MN-major*/ 1, 128, 128);
+      // S(t) = Q · K(t)^T into TMEM buffer t % 2.
       const auto issue_qk = [&](int t) -> bool {
         const int s = t % kKvStages;
         if (!wait_bar(smem_u32(&s_k_full[s]), (t / kKvStages) & 1u, abort_word)) return false;
         tc_fence_after();
         const std::uint64_t dq = umma_desc_sw128(q_smem), dk = umma_desc_sw128(k_smem(s));
+        const std::uint32_t d = tmem_s + static_cast<std::uint32_t>(t & 1) * 128u;
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) umma_i8(tmem_s, dq + 2u * k4, dk + 2u * k4, idesc_qk, k4 != 0 ? 1u : 0u);
+        for (int k4 = 0; k4 < 4; ++k4) umma_i8(d, dq + 2u * k4, dk + 2u * k4, idesc_qk, k4 != 0 ? 1u : 0u);
         tc_commit(smem_u32(&s_k_empty[s]));
-        tc_commit(smem_u32(&s_s_full));
+        tc_commit(smem_u32(&s_s_full[t & 1]));
         return true;
       };
       bool ok = wait_bar(smem_u32(&s_q_full), 0, abort_word) && issue_qk(0);
+      if (ok && n_tiles > 1) ok = issue_qk(1);
       for (int t = 0; ok && t < n_tiles; ++t) {
         const int s = t % kKvStages;
-        if (!wait_bar(smem_u32(&s_p_full), t & 1u, abort_word)) break;  // P(t) written, S(t) consumed
-        if (t + 1 < n_tiles && !issue_qk(t + 1)) break;
+        // P(t) is written and S(t) consumed (the softmax warps keep S in registers after their first pass).
+        if (!wait_bar(smem_u32(&s_p_full[t & 1]), (t >> 1) & 1u, abort_word)) break;
         if (!wait_bar(smem_u32(&s_v_full[s]), (t / kKvStages) & 1u, abort_word)) break;
         tc_fence_after();
-        const std::uint64_t dp = umma_desc_sw128(p_smem), dv = umma_desc_sw128(v_smem(s));
+        const std::uint64_t dp = umma_desc_sw128(p_smem(t & 1)), dv = umma_desc_sw128(v_smem(s));
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
           // P: 32 keys = 32 bytes along K inside the swizzle atom (+2); V (MN-major): 32 key rows of 128 bytes (+256).
@@ -569,55 +589,56 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         tc_commit(smem_u32(&s_v_empty[s]));
         tc_commit(smem_u32(&s_pv_done));
+        if (t + 2 < n_tiles && !issue_qk(t + 2)) break;
       }
     }
     __syncwarp();
   } else {
-    // Softmax: 8 warps, two threads per query row. Warp w may touch TMEM lanes [32 (w % 4), +32); warps 2..5 take keys
-    // 0..63 of a tile (one K scale block), warps 6..9 keys 64..127. The two threads of a row exchange their block
-    // maxima through shared memory once per tile (and their denominators once at the end).
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    // Softmax: 16 warps, four threads per query row. Warp w may touch TMEM lanes [32 (w % 4), +32); the four warps that
+    // share a lane quarter each take 32 of a tile's 128 keys (key quarters 0, 1 belong to one K scale block, 2, 3 to
+    // the next). A thread reads its 32 scores once, keeps them in registers for both passes, and exchanges its block
+    // maximum with the row's other three threads through shared memory (one 128-thread named barrier per lane quarter).
+    const int quarter = warp & 3, cq = (warp - 2) >> 2;
     const int r_local = quarter * 32 + lane;  // row of the tile == TMEM lane
     const std::uint32_t lane_off = static_cast<std::uint32_t>(quarter * 32) << 16;
-    const std::uint32_t col_off = static_cast<std::uint32_t>(half * 64);
+    const std::uint32_t col_off = static_cast<std::uint32_t>(cq * 32);
     const std::int64_t sc_base = static_cast<std::int64_t>(b) * a.heads + h;
     const float qs = a.q_scale[sc_base * a.q_blocks + (q0 + quarter * 32) / 32] * a.scale_log2;
+    const int bar_id = 1 + quarter;
     float m_run = -5000000.0f, d_run = 0.f;
     // A warp whose bounded wait expired keeps walking the loop so that it still meets the others at the named
     // barriers, but touches nothing.
     bool dead = false;
     for (int t = 0; t < n_tiles; ++t) {
-      if (!dead && !wait_bar(smem_u32(&s_s_full), t & 1u, abort_word)) dead = true;
+      if (!dead && !wait_bar(smem_u32(&s_s_full[t & 1]), (t >> 1) & 1u, abort_word)) dead = true;
       tc_fence_after();
-      const int kblock = 2 * t + half;
+      const int kblock = 2 * t + (cq >> 1);
       const float c = (!dead && kblock < a.k_blocks) ? qs * a.k_scale[sc_base * a.k_blocks + kblock] : 0.f;
-      const int valid = min(64, kv_len - t * kTileK - half * 64);  // valid keys of this thread's block (may be <= 0)
-      const bool full_tile = valid == 64;
-      // Pass 1: block maximum. The scale is positive, so the maximum scaled score is the scaled integer maximum.
+      const int valid = min(32, kv_len - t * kTileK - cq * 32);  // valid keys among this thread's 32 (may be <= 0)
+      const bool full_tile = valid == 32;
+      std::uint32_t sreg[32];
       int imax = INT_MIN;
       if (!dead) {
-#pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
-          std::uint32_t r[32];
-          tmem_ld_32x32(tmem_s + lane_off + col_off + cc * 32, r);
-          tmem_ld_wait();
-          if (full_tile) {
+        tmem_ld_32x32(tmem_s + static_cast<std::uint32_t>(t & 1) * 128u + lane_off + col_off, sreg);
+        tmem_ld_wait();
+        // Pass 1: block maximum. The scale is positive, so the maximum scaled score is the scaled integer maximum.
+        if (full_tile) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) imax = max(imax, static_cast<int>(r[i]));
-          } else {
+          for (int i = 0; i < 32; ++i) imax = max(imax, static_cast<int>(sreg[i]));
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) imax = (cc * 32 + i < valid) ? max(imax, static_cast<int>(r[i])) : imax;
-          }
+          for (int i = 0; i < 32; ++i) imax = (i < valid) ? max(imax, static_cast<int>(sreg[i])) : imax;
         }
       }
       const float mx_own = imax != INT_MIN ? static_cast<float>(imax) * c : -5000000.0f;
-      s_mx[t & 1][half][r_local] = mx_own;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      const float mx = fmaxf(mx_own, s_mx[t & 1][half ^ 1][r_local]);
+      s_mx[t & 1][cq][r_local] = mx_own;
+      asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+      const float mx = fmaxf(fmaxf(s_mx[t & 1][0][r_local], s_mx[t & 1][1][r_local]),
+                             fmaxf(s_mx[t & 1][2][r_local], s_mx[t & 1][3][r_local]));
       // The reference maximum m_run may lag the true running maximum by up to kLazy (in log2 units): P is scaled so that
       // its largest value is 2^(p_offset - kLazy) against an exact maximum, hence at most 2^p_offset <= p_range against
-      // a lagging one. O and the denominator are rescaled only when some row of the warp exceeds the lag. Both threads
-      // of a row see the same values, so both warps take the same decision.
+      // a lagging one. O and the denominator are rescaled only when some row of the warp exceeds the lag. The four
+      // threads of a row see the same values, so their warps take the same decision.
       const float m_tile = mx - (a.p_offset - kLazy);
       const bool grow = __any_sync(0xffffffffu, m_tile > m_run + kLazy);
       float alpha = 1.0f;
@@ -625,92 +646,78 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const float m_new = fmaxf(m_run, m_tile);
         alpha = ex2(m_run - m_new);
         m_run = m_new;
-      }
-      // PV(t-1) must have landed before O is touched or the P tile reused.
-      if (t > 0 && !dead) {
-        if (!wait_bar(smem_u32(&s_pv_done), (t - 1) & 1u, abort_word)) dead = true;
-        tc_fence_after();
-        if (grow && !dead) {
-#pragma unroll 1
-          for (int cc = 0; cc < 2; ++cc) {
+        // O is rescaled in place; P·V of the previous tile must have landed first.
+        if (t > 0 && !dead) {
+          if (!wait_bar(smem_u32(&s_pv_done), (t - 1) & 1u, abort_word)) dead = true;
+          tc_fence_after();
+          if (!dead) {
             std::uint32_t r[32];
-            tmem_ld_32x32(tmem_o + lane_off + col_off + cc * 32, r);
+            tmem_ld_32x32(tmem_o + lane_off + col_off, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_off + col_off + cc * 32, r);
+            tmem_st_32x32(tmem_o + lane_off + col_off, r);
+            tmem_st_wait();
           }
-          tmem_st_wait();
         }
       }
       d_run *= alpha;
       if (dead) continue;
       // Pass 2: P = exp2(S * c - m). |S| < 2^22, so S + 0x4B400000 reinterpreted as fp32 is exactly 12582912 + S: one
       // integer add and one FMA (with the constant folded into the addend) replace the conversion, multiply and subtract.
-      // Denominator from the unrounded P; e4m3 P into the swizzled tile (row = 128 bytes, 16-byte chunk j of row r
+      // Denominator from the unrounded P; e4m3 P into the swizzled tile t % 2 (row = 128 bytes, 16-byte chunk j of row r
       // stored at chunk j ^ (r % 8)).
-      std::uint8_t* prow = p_generic + r_local * 128;
+      std::uint8_t* prow = p_generic + (t & 1) * kTileBytes + r_local * 128;
       const float bias = -fmaf(12582912.0f, c, m_run);
       float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        std::uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_off + col_off + cc * 32, r);
-        tmem_ld_wait();
-        float pv[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) pv[i] = ex2(fmaf(__uint_as_float(r[i] + 0x4B400000u), c, bias));
+      for (int g = 0; g < 2; ++g) {
+        float pv[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pv[i] = ex2(fmaf(__uint_as_float(sreg[16 * g + i] + 0x4B400000u), c, bias));
         if (!full_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pv[i] = (cc * 32 + i < valid) ? pv[i] : 0.f;
+          for (int i = 0; i < 16; ++i) pv[i] = (16 * g + i < valid) ? pv[i] : 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
+        for (int i = 0; i < 16; i += 4) {
           d0 += pv[i];
           d1 += pv[i + 1];
           d2 += pv[i + 2];
           d3 += pv[i + 3];
         }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int chunk = (half * 4 + cc * 2 + j) ^ (r_local & 7);
-          *reinterpret_cast<uint4*>(prow + chunk * 16) =
-              make_uint4(e4m3x4(pv[16 * j + 0], pv[16 * j + 1], pv[16 * j + 2], pv[16 * j + 3]),
-                         e4m3x4(pv[16 * j + 4], pv[16 * j + 5], pv[16 * j + 6], pv[16 * j + 7]),
-                         e4m3x4(pv[16 * j + 8], pv[16 * j + 9], pv[16 * j + 10], pv[16 * j + 11]),
-                         e4m3x4(pv[16 * j + 12], pv[16 * j + 13], pv[16 * j + 14], pv[16 * j + 15]));
-        }
+        const int chunk = (cq * 2 + g) ^ (r_local & 7);
+        *reinterpret_cast<uint4*>(prow + chunk * 16) =
+            make_uint4(e4m3x4(pv[0], pv[1], pv[2], pv[3]), e4m3x4(pv[4], pv[5], pv[6], pv[7]),
+                       e4m3x4(pv[8], pv[9], pv[10], pv[11]), e4m3x4(pv[12], pv[13], pv[14], pv[15]));
       }
       d_run += (d0 + d1) + (d2 + d3);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_p_full));
+      if (lane == 0) mbar_arrive(smem_u32(&s_p_full[t & 1]));
     }
-    // Row denominator = the two threads' sums.
-    s_den[half][r_local] = d_run;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    const float d_row = d_run + s_den[half ^ 1][r_local];
+    // Row denominator = the four threads' sums.
+    s_den[cq][r_local] = d_run;
+    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+    const float d_row = (s_den[0][r_local] + s_den[1][r_local]) + (s_den[2][r_local] + s_den[3][r_local]);
     if (!dead && wait_bar(smem_u32(&s_pv_done), (n_tiles - 1) & 1u, abort_word)) {
       tc_fence_after();
       const float inv_d = rcp_approx(d_row);
       const int row = q0 + r_local;
-      __nv_bfloat16* orow = a.out + static_cast<std::int64_t>(q_start + row) * a.out_row + h * a.out_head + half * 64;
-      const float* vs = a.v_scale + sc_base * kHeadDim + half * 64;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        std::uint32_t r[32];
-        tmem_ld_32x32(tmem_o + lane_off + col_off + cc * 32, r);
-        tmem_ld_wait();
-        if (row < qo_len) {
+      __nv_bfloat16* orow = a.out + static_cast<std::int64_t>(q_start + row) * a.out_row + h * a.out_head + cq * 32;
+      const float* vs = a.v_scale + sc_base * kHeadDim + cq * 32;
+      std::uint32_t r[32];
+      tmem_ld_32x32(tmem_o + lane_off + col_off, r);
+      tmem_ld_wait();
+      if (row < qo_len) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            float o[8];
+        for (int v = 0; v < 4; ++v) {
+          float o[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[8 * v + i]) * inv_d * __ldg(vs + cc * 32 + 8 * v + i);
-            *reinterpret_cast<uint4*>(orow + cc * 32 + 8 * v) =
-                make_uint4(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]), pack_bf2(o[4], o[5]), pack_bf2(o[6], o[7]));
-          }
+          for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[8 * v + i]) * inv_d * __ldg(vs + 8 * v + i);
+          *reinterpret_cast<uint4*>(orow + 8 * v) =
+              make_uint4(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]), pack_bf2(o[4], o[5]), pack_bf2(o[6], o[7]));
         }
       }
     }

@@ -50,6 +50,13 @@ __device__ __forceinline__ float fmul(float a, float b) { return __fmul_rn(a, b)
 __device__ __forceinline__ float fadd(float a, float b) { return __fadd_rn(a, b); }
 __device__ __forceinline__ float rbf(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float bf_bits_to_float(std::uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+// Two values rounded to bf16 with one packed conversion (half the conversion-unit work of two rbf calls).
+__device__ __forceinline__ void rbf2(float& a, float& b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  const std::uint32_t u = *reinterpret_cast<const std::uint32_t*>(&h);
+  a = __uint_as_float(u << 16);
+  b = __uint_as_float(u & 0xFFFF0000u);
+}
 __device__ __forceinline__ std::uint32_t float_to_bf_bits(float v) {
   return static_cast<std::uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(v)));
 }

@@ -41,6 +41,7 @@ constexpr std::uint32_t kMiniExpLo = 117;
 struct GemmParams {
   int m, n, k;        // GEMM rows, GEMM columns (2F for SiTU-GLU), reduction length
   int m_tiles, n_tiles;
+  int band_m;         // M tiles per band of the tile order (see tile_coords)
   int half;           // SiTU-GLU: F
   const float* xs;
   const float* ws;
@@ -92,6 +93,17 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
 __device__ __forceinline__ std::uint32_t pack2(float lo, float hi) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const std::uint32_t*>(&h);
+}
+
+// Order of the output tiles over the persistent CTAs: bands of band_m M tiles; inside a band the M tile index runs
+// fastest. The CTAs working at the same time then share a few activation row blocks and sweep the weight, so both stay
+// in L2 (with M fastest over the whole problem a long-K activation matrix is re-read from DRAM once per wave).
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int* mt, int* nt) {
+  const int per_band = p.band_m * p.n_tiles;
+  const int band = tile / per_band, r = tile - band * per_band;
+  const int rows = min(p.band_m, p.m_tiles - band * p.band_m);
+  *mt = band * p.band_m + r % rows;
+  *nt = r / rows;
 }
 
 // One SiTU factor of the bf16 value v: from the shared-memory slice when its exponent is inside the slice, else from the
@@ -182,7 +194,8 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (lane == 0) {
       std::uint32_t it = 0;
       for (int tile = tile0; tile < total_tiles && *abort_word == 0; tile += tile_step) {
-        const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+        int mt, nt;
+        tile_coords(p, tile, &mt, &nt);
         const int row_a = mt * (kBM * kCtas) + static_cast<int>(rank) * kBM;
         int row_b0, row_b1;
         if constexpr (kEpi == Epi::kSituGlu) {
@@ -259,7 +272,8 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int quarter = warp & 3, col_half = (warp - 2) >> 2;
     std::uint32_t tile_it = 0;
     for (int tile = tile0; tile < total_tiles; tile += tile_step, ++tile_it) {
-      const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+      int mt, nt;
+      tile_coords(p, tile, &mt, &nt);
       const std::uint32_t acc = tile_it & 1u, acc_ph = (tile_it >> 1) & 1u;
       // This warp's per-column vectors (w_scale, bias, gate of its half of the tile's columns) -> its own slice of shared
       // memory, four columns per lane; only the warp itself reads them back, so a warp-level sync is enough.
@@ -560,6 +574,8 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
   if constexpr (kEpi == Epi::kSituGlu) p.n_tiles = (p.half + 127) / 128;
   else p.n_tiles = (p.n + kBN - 1) / kBN;
   const int total = p.m_tiles * p.n_tiles;
+  // Tiles in flight at once / N tiles = M tiles that fit one wave.
+  p.band_m = std::max(1, (sm_count() / kCtas) / std::max(1, p.n_tiles));
   if constexpr (kCtas == 2) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * std::min(total, sm_count() / 2)));

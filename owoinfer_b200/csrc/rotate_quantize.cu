@@ -157,10 +157,19 @@ __global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
       load16_bf16(a.mod_scale + c0, sc);
       load16_bf16(a.mod_shift + c0, sh);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float t = fmul(rbf(fmul(v[s][j], r)), w[j]);
-        const float one_plus = rbf(fadd(1.0f, sc[j]));
-        v[s][j] = rbf(fadd(rbf(fmul(rbf(t), one_plus)), sh[j]));
+      for (int j = 0; j < 16; j += 2) {
+        // bf16(bf16(bf16(bf16(x*r)*w) * bf16(1+scale)) + shift), two elements per packed conversion.
+        float a = fmul(v[s][j], r), b = fmul(v[s][j + 1], r);
+        rbf2(a, b);
+        a = fmul(a, w[j]), b = fmul(b, w[j + 1]);
+        rbf2(a, b);
+        float pa = fadd(1.0f, sc[j]), pb = fadd(1.0f, sc[j + 1]);
+        rbf2(pa, pb);
+        a = fmul(a, pa), b = fmul(b, pb);
+        rbf2(a, b);
+        a = fadd(a, sh[j]), b = fadd(b, sh[j + 1]);
+        rbf2(a, b);
+        v[s][j] = a, v[s][j + 1] = b;
       }
       if (a.y != nullptr) store16_bf16(a.y + row * a.ldy + c0, v[s]);
     }
@@ -181,9 +190,9 @@ __global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
     stages_on_registers(v[s]);
     if (half_id + s * halves < groups) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        v[s][j] = rbf(v[s][j]);
-        amax = fmaxf(amax, fabsf(v[s][j]));
+      for (int j = 0; j < 16; j += 2) {
+        rbf2(v[s][j], v[s][j + 1]);
+        amax = fmaxf(amax, fmaxf(fabsf(v[s][j]), fabsf(v[s][j + 1])));
       }
     }
   }
@@ -211,10 +220,16 @@ __global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
   for (int s = 0; s < kSlots; ++s) {
     if ((half_id & ~1) + s * halves >= groups) continue;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      // rne, then clamp; fmaxf sends NaN to the lower bound, infinities saturate.
-      const float qv = fminf(kHi, fmaxf(kLo, rintf(rbf(fmul(v[s][j], inv_s)))));
-      qtile[h + 16 * j] = static_cast<std::uint8_t>(static_cast<std::int8_t>(static_cast<int>(qv)));
+    for (int j = 0; j < 16; j += 2) {
+      // Clamp, then round to nearest even: the bounds are integers, so this equals rounding first. fmaxf sends NaN to
+      // the lower bound, infinities saturate. Adding 1.5 * 2^23 rounds to an integer (ties to even) and leaves its two's
+      // complement in the low mantissa bits, whose low byte is the int8 code.
+      float a = fmul(v[s][j], inv_s), b = fmul(v[s][j + 1], inv_s);
+      rbf2(a, b);
+      a = fadd(fminf(kHi, fmaxf(kLo, a)), 12582912.0f);
+      b = fadd(fminf(kHi, fmaxf(kLo, b)), 12582912.0f);
+      qtile[h + 16 * j] = static_cast<std::uint8_t>(__float_as_uint(a));
+      qtile[h + 16 * (j + 1)] = static_cast<std::uint8_t>(__float_as_uint(b));
     }
     __syncwarp();
     const uint4 bytes = *reinterpret_cast<const uint4*>(qtile + 16 * h);
