@@ -5,10 +5,9 @@
 //                fused prologue also RMS-norm + RoPE of q and k (k written back), and Q quantised per (32 tokens, head)
 //     finalize   k_mean = bf16(sum / len); v_scale = amax / v_range; v_recp = v_range / amax
 //     quantise   Q per (32 tokens, head) [when not fused]; K - k_mean per (64 keys, head) -> int8; V * v_recp -> e4m3
-//   attention (tensor-core-bound): one CTA per (128 query rows, head, sequence), one CTA per SM; 128-key tiles; S is
-//   double-buffered in TMEM so the MMA warp runs a tile ahead of the softmax warps
+//   attention (tensor-core-bound): one CTA per (128 query rows, head, sequence), two CTAs per SM; 128-key tiles
 //     S = Q8 · K8^T   tcgen05.mma kind::i8, int32 accumulator in TMEM (exact)
-//     softmax         16 warps, four threads per row (32 keys each): S -> fp32 (exact: |S| < 2^22), scaled by
+//     softmax         8 warps, two threads per row (one 64-key block each): S -> fp32 (exact: |S| < 2^22), scaled by
 //                     sm_scale * log2e * q_scale * k_scale[64-key block], running max / denominator in fp32, P = exp2(.)
 //                     shifted so that its maximum stays within [p_range / 2, p_range] (the reference maximum may lag the
 //                     true one by one binade, which makes rescaling O rare), rounded to e4m3 into a swizzled shared tile
@@ -33,6 +32,12 @@ constexpr int kStatsChunk = 512;
 constexpr std::size_t kAlign = 256;
 
 __device__ int g_attn_status = 0;
+#ifdef B2_ATTN_TRACE
+__device__ long long g_attn_trace[4096];
+#define TRACE(slot) do { if (tracing) a.trace[t * 8 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ std::uint64_t global_ns() {
   std::uint64_t t;
@@ -87,12 +92,31 @@ __device__ __forceinline__ std::uint32_t e4m3x2(float lo, float hi) {
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
   return r;
 }
-__device__ __forceinline__ std::uint32_t e4m3x4(float a, float b, float c, float d) { return e4m3x2(a, b) | (e4m3x2(c, d) << 16); }
+__device__ __forceinline__ std::uint32_t e4m3x4(float a, float b, float c, float d) {
+  return __byte_perm(e4m3x2(a, b), e4m3x2(c, d), 0x5410);
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for x <= ~9 on the FMA and integer pipes (no special-function unit): x = n + f with n = round(x), |f| <= 1/2;
+// 2^f by a cubic (relative error < 7e-4, far below e4m3's 2^-4 steps), 2^n by adding n to the exponent field.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float z = x + 12582912.0f;          // low mantissa bits of z hold n (two's complement)
+  const float f = x - (z - 12582912.0f);
+  const float p = fmaf(fmaf(fmaf(0.0555041087f, f, 0.240226507f), f, 0.693147181f), f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(z) << 23));
+}
+#ifndef B2_EXP_POLY_MASK
+#define B2_EXP_POLY_MASK 0  // bit (i & 3) set: score i uses ex2_poly. Measured on B200: 0 (all on the special-function unit) is fastest
+#endif
 __device__ __forceinline__ float rcp_approx(float x) {
   float y;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -453,13 +477,12 @@ __global__ void __launch_bounds__(1024) quant_kv_kernel(const PrepArgs p) {
 // The attention kernel.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kTileQ = 128, kTileK = 128;
-constexpr int kKvStages = 3;
+constexpr int kKvStages = 2;
 constexpr int kTileBytes = 128 * 128;
-constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 2) + 1024;  // Q, K/V stages, two P tiles, alignment slack
-constexpr int kSoftmaxWarps = 16;
-constexpr int kAttnThreads = 64 + 32 * kSoftmaxWarps;  // TMA warp, MMA warp, 16 softmax warps
-constexpr std::uint32_t kTmemCols = 512;  // S[0]: columns [0, 128); S[1]: [128, 256); O: [256, 384)
-constexpr float kLazy = 1.0f;             // how far (log2 units) the softmax reference maximum may lag the true one
+constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 1) + 1024;  // Q, K/V stages, P, alignment slack
+constexpr int kAttnThreads = 320;  // TMA warp, MMA warp, 8 softmax warps
+constexpr std::uint32_t kTmemCols = 256;  // S: columns [0, 128); O: columns [128, 256)
+constexpr float kLazy = 1.0f;              // how far (log2 units) the softmax reference maximum may lag the true one
 
 struct AttnArgs {
   const float* q_scale;
@@ -472,12 +495,12 @@ struct AttnArgs {
   int heads, q_blocks, k_blocks;
   float scale_log2;  // sm_scale * log2(e)
   float p_offset;
+#ifdef B2_ATTN_TRACE
+  long long* trace;  // [tile][8] clock64 stamps of CTA (0,0,0), softmax warp 2 lane 0 and the MMA thread
+#endif
 };
 
-// One CTA per SM (its shared memory and its 512 TMEM columns fill the SM). The score tile S is double-buffered in TMEM:
-// the MMA warp runs one key tile ahead of the softmax warps, so the tensor pipe works on Q·K^T of tile t + 1 and P·V of
-// tile t - 1 while the sixteen softmax warps turn S(t) into P(t).
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kAttnThreads, 2)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const AttnArgs a) {
   const int bq = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -498,17 +521,17 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
   extern __shared__ std::uint8_t smem_raw[];
   __shared__ __align__(8) std::uint64_t s_q_full, s_k_full[kKvStages], s_k_empty[kKvStages], s_v_full[kKvStages],
-      s_v_empty[kKvStages], s_s_full[2], s_p_full[2], s_pv_done;
+      s_v_empty[kKvStages], s_s_full, s_s_free, s_p_full, s_pv_done;
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ float s_mx[2][4][kTileQ];  // [tile parity][key quarter][row]: block maxima exchanged by a row's four threads
-  __shared__ float s_den[4][kTileQ];    // [key quarter][row]: the four partial denominators of a row
+  __shared__ float s_mx[2][2][kTileQ];  // [tile parity][key half][row]: block maxima exchanged by a row's two threads
+  __shared__ float s_den[2][kTileQ];    // [key half][row]: the two partial denominators of a row
   const std::uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const std::uint32_t q_smem = base;
   const auto k_smem = [&](int s) { return base + kTileBytes * (1 + s); };
   const auto v_smem = [&](int s) { return base + kTileBytes * (1 + kKvStages + s); };
-  const auto p_smem = [&](int i) { return base + kTileBytes * (1 + 2 * kKvStages + i); };
-  std::uint8_t* p_generic = smem_raw + (p_smem(0) - smem_u32(smem_raw));
+  const std::uint32_t p_smem = base + kTileBytes * (1 + 2 * kKvStages);
+  std::uint8_t* p_generic = smem_raw + (p_smem - smem_u32(smem_raw));
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&s_q_full), 1);
@@ -518,11 +541,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(smem_u32(&s_v_full[s]), 1);
       mbar_init(smem_u32(&s_v_empty[s]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&s_s_full[i]), 1);
-      mbar_init(smem_u32(&s_p_full[i]), kSoftmaxWarps);
-    }
+    mbar_init(smem_u32(&s_s_full), 1);
+    mbar_init(smem_u32(&s_p_full), 8);
     mbar_init(smem_u32(&s_pv_done), 1);
+    mbar_init(smem_u32(&s_s_free), 8);
     s_abort = 0;
     fence_mbar_init();
     prefetch_tensormap(&map_q);
@@ -536,7 +558,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const std::uint32_t tmem_s = s_tmem_base, tmem_o = s_tmem_base + 256;
+  const std::uint32_t tmem_s = s_tmem_base, tmem_o = s_tmem_base + 128;
   volatile int* abort_word = &s_abort;
   const int n_tiles = (kv_len + kTileK - 1) / kTileK;
 
@@ -558,30 +580,41 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
+#ifdef B2_ATTN_TRACE
+      const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#endif
       constexpr std::uint32_t idesc_qk = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, 128, 128);
       constexpr std::uint32_t idesc_pv = umma_idesc(/*f32*/ 1, /*e4m3*/ 0, /*e4m3*/ 0, 0, /*B MN-major*/ 1, 128, 128);
-      // S(t) = Q · K(t)^T into TMEM buffer t % 2.
       const auto issue_qk = [&](int t) -> bool {
         const int s = t % kKvStages;
         if (!wait_bar(smem_u32(&s_k_full[s]), (t / kKvStages) & 1u, abort_word)) return false;
         tc_fence_after();
         const std::uint64_t dq = umma_desc_sw128(q_smem), dk = umma_desc_sw128(k_smem(s));
-        const std::uint32_t d = tmem_s + static_cast<std::uint32_t>(t & 1) * 128u;
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) umma_i8(d, dq + 2u * k4, dk + 2u * k4, idesc_qk, k4 != 0 ? 1u : 0u);
+        // S was pre-filled with the integer 0x4B400000 by the softmax warps: accumulate onto it (see the softmax pass).
+        for (int k4 = 0; k4 < 4; ++k4) umma_i8(tmem_s, dq + 2u * k4, dk + 2u * k4, idesc_qk, 1u);
         tc_commit(smem_u32(&s_k_empty[s]));
-        tc_commit(smem_u32(&s_s_full[t & 1]));
+        tc_commit(smem_u32(&s_s_full));
         return true;
       };
-      bool ok = wait_bar(smem_u32(&s_q_full), 0, abort_word) && issue_qk(0);
-      if (ok && n_tiles > 1) ok = issue_qk(1);
+      // s_s_free phase i: S is pre-filled and free for Q·K^T of tile i (phase 0 comes from the start-up pre-fill).
+      bool ok = wait_bar(smem_u32(&s_s_free), 0, abort_word) && wait_bar(smem_u32(&s_q_full), 0, abort_word);
+      tc_fence_after();
+      ok = ok && issue_qk(0);
       for (int t = 0; ok && t < n_tiles; ++t) {
         const int s = t % kKvStages;
-        // P(t) is written and S(t) consumed (the softmax warps keep S in registers after their first pass).
-        if (!wait_bar(smem_u32(&s_p_full[t & 1]), (t >> 1) & 1u, abort_word)) break;
+        // Q·K^T of the next tile as soon as the softmax warps have read S(t) (half way through their second pass).
+        if (t + 1 < n_tiles) {
+          if (!wait_bar(smem_u32(&s_s_free), (t + 1) & 1u, abort_word)) break;
+          tc_fence_after();
+          TRACE(5);
+          if (!issue_qk(t + 1)) break;
+        }
+        TRACE(6);
+        if (!wait_bar(smem_u32(&s_p_full), t & 1u, abort_word)) break;  // P(t) written
         if (!wait_bar(smem_u32(&s_v_full[s]), (t / kKvStages) & 1u, abort_word)) break;
         tc_fence_after();
-        const std::uint64_t dp = umma_desc_sw128(p_smem(t & 1)), dv = umma_desc_sw128(v_smem(s));
+        const std::uint64_t dp = umma_desc_sw128(p_smem), dv = umma_desc_sw128(v_smem(s));
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
           // P: 32 keys = 32 bytes along K inside the swizzle atom (+2); V (MN-major): 32 key rows of 128 bytes (+256).
@@ -589,56 +622,71 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         tc_commit(smem_u32(&s_v_empty[s]));
         tc_commit(smem_u32(&s_pv_done));
-        if (t + 2 < n_tiles && !issue_qk(t + 2)) break;
+        TRACE(7);
       }
     }
     __syncwarp();
   } else {
-    // Softmax: 16 warps, four threads per query row. Warp w may touch TMEM lanes [32 (w % 4), +32); the four warps that
-    // share a lane quarter each take 32 of a tile's 128 keys (key quarters 0, 1 belong to one K scale block, 2, 3 to
-    // the next). A thread reads its 32 scores once, keeps them in registers for both passes, and exchanges its block
-    // maximum with the row's other three threads through shared memory (one 128-thread named barrier per lane quarter).
-    const int quarter = warp & 3, cq = (warp - 2) >> 2;
+    // Softmax: 8 warps, two threads per query row. Warp w may touch TMEM lanes [32 (w % 4), +32); warps 2..5 take keys
+    // 0..63 of a tile (one K scale block), warps 6..9 keys 64..127. The two threads of a row exchange their block
+    // maxima through shared memory once per tile (and their denominators once at the end).
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r_local = quarter * 32 + lane;  // row of the tile == TMEM lane
     const std::uint32_t lane_off = static_cast<std::uint32_t>(quarter * 32) << 16;
-    const std::uint32_t col_off = static_cast<std::uint32_t>(cq * 32);
+    const std::uint32_t col_off = static_cast<std::uint32_t>(half * 64);
     const std::int64_t sc_base = static_cast<std::int64_t>(b) * a.heads + h;
     const float qs = a.q_scale[sc_base * a.q_blocks + (q0 + quarter * 32) / 32] * a.scale_log2;
-    const int bar_id = 1 + quarter;
+#ifdef B2_ATTN_TRACE
+    const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 2 && lane == 0;
+#endif
     float m_run = -5000000.0f, d_run = 0.f;
+    // The score accumulator is pre-filled with the integer 0x4B400000 before every Q·K^T, so a column read back holds the
+    // bit pattern of the fp32 number 12582912 + S (exact, |S| < 2^22): the scores arrive as floats with no conversion,
+    // their order is the integers' order, and the constant folds into the addend of the exponent's FMA.
+    const auto prefill_s = [&](int cc) { tmem_fill_32x32(tmem_s + lane_off + col_off + cc * 32, 0x4B400000u); };
+    prefill_s(0);
+    prefill_s(1);
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&s_s_free));
     // A warp whose bounded wait expired keeps walking the loop so that it still meets the others at the named
     // barriers, but touches nothing.
     bool dead = false;
     for (int t = 0; t < n_tiles; ++t) {
-      if (!dead && !wait_bar(smem_u32(&s_s_full[t & 1]), (t >> 1) & 1u, abort_word)) dead = true;
+      if (!dead && !wait_bar(smem_u32(&s_s_full), t & 1u, abort_word)) dead = true;
       tc_fence_after();
-      const int kblock = 2 * t + (cq >> 1);
+      TRACE(0);
+      const int kblock = 2 * t + half;
       const float c = (!dead && kblock < a.k_blocks) ? qs * a.k_scale[sc_base * a.k_blocks + kblock] : 0.f;
-      const int valid = min(32, kv_len - t * kTileK - cq * 32);  // valid keys among this thread's 32 (may be <= 0)
-      const bool full_tile = valid == 32;
-      std::uint32_t sreg[32];
-      int imax = INT_MIN;
+      const int valid = min(64, kv_len - t * kTileK - half * 64);  // valid keys of this thread's block (may be <= 0)
+      const bool full_tile = valid == 64;
+      // Pass 1: block maximum of the biased scores (three-input float max: monotone in S).
+      float bmax = 0.f;  // below every biased score (those are >= 2^22)
       if (!dead) {
-        tmem_ld_32x32(tmem_s + static_cast<std::uint32_t>(t & 1) * 128u + lane_off + col_off, sreg);
-        tmem_ld_wait();
-        // Pass 1: block maximum. The scale is positive, so the maximum scaled score is the scaled integer maximum.
-        if (full_tile) {
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          std::uint32_t r[32];
+          tmem_ld_32x32(tmem_s + lane_off + col_off + cc * 32, r);
+          tmem_ld_wait();
+          if (full_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) imax = max(imax, static_cast<int>(sreg[i]));
-        } else {
+            for (int i = 0; i < 32; i += 2) bmax = fmax3(bmax, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) imax = (i < valid) ? max(imax, static_cast<int>(sreg[i])) : imax;
+            for (int i = 0; i < 32; ++i) bmax = (cc * 32 + i < valid) ? fmaxf(bmax, __uint_as_float(r[i])) : bmax;
+          }
         }
       }
-      const float mx_own = imax != INT_MIN ? static_cast<float>(imax) * c : -5000000.0f;
-      s_mx[t & 1][cq][r_local] = mx_own;
-      asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-      const float mx = fmaxf(fmaxf(s_mx[t & 1][0][r_local], s_mx[t & 1][1][r_local]),
-                             fmaxf(s_mx[t & 1][2][r_local], s_mx[t & 1][3][r_local]));
+      const float mx_own = bmax != 0.f ? (bmax - 12582912.0f) * c : -5000000.0f;
+      TRACE(1);
+      s_mx[t & 1][half][r_local] = mx_own;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const float mx = fmaxf(mx_own, s_mx[t & 1][half ^ 1][r_local]);
       // The reference maximum m_run may lag the true running maximum by up to kLazy (in log2 units): P is scaled so that
       // its largest value is 2^(p_offset - kLazy) against an exact maximum, hence at most 2^p_offset <= p_range against
-      // a lagging one. O and the denominator are rescaled only when some row of the warp exceeds the lag. The four
-      // threads of a row see the same values, so their warps take the same decision.
+      // a lagging one. O and the denominator are rescaled only when some row of the warp exceeds the lag. Both threads
+      // of a row see the same values, so both warps take the same decision.
       const float m_tile = mx - (a.p_offset - kLazy);
       const bool grow = __any_sync(0xffffffffu, m_tile > m_run + kLazy);
       float alpha = 1.0f;
@@ -646,78 +694,105 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const float m_new = fmaxf(m_run, m_tile);
         alpha = ex2(m_run - m_new);
         m_run = m_new;
-        // O is rescaled in place; P·V of the previous tile must have landed first.
-        if (t > 0 && !dead) {
-          if (!wait_bar(smem_u32(&s_pv_done), (t - 1) & 1u, abort_word)) dead = true;
-          tc_fence_after();
-          if (!dead) {
+      }
+      // PV(t-1) must have landed before O is touched or the P tile reused.
+      if (t > 0 && !dead) {
+        if (!wait_bar(smem_u32(&s_pv_done), (t - 1) & 1u, abort_word)) dead = true;
+        tc_fence_after();
+        if (grow && !dead) {
+#pragma unroll 1
+          for (int cc = 0; cc < 2; ++cc) {
             std::uint32_t r[32];
-            tmem_ld_32x32(tmem_o + lane_off + col_off, r);
+            tmem_ld_32x32(tmem_o + lane_off + col_off + cc * 32, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_off + col_off, r);
-            tmem_st_wait();
+            tmem_st_32x32(tmem_o + lane_off + col_off + cc * 32, r);
           }
+          tmem_st_wait();
         }
       }
       d_run *= alpha;
+      TRACE(2);
       if (dead) continue;
-      // Pass 2: P = exp2(S * c - m). |S| < 2^22, so S + 0x4B400000 reinterpreted as fp32 is exactly 12582912 + S: one
-      // integer add and one FMA (with the constant folded into the addend) replace the conversion, multiply and subtract.
-      // Denominator from the unrounded P; e4m3 P into the swizzled tile t % 2 (row = 128 bytes, 16-byte chunk j of row r
-      // stored at chunk j ^ (r % 8)).
-      std::uint8_t* prow = p_generic + (t & 1) * kTileBytes + r_local * 128;
+      // Pass 2: P = exp2(S * c - m) = exp2((12582912 + S) * c + bias) with bias = -(12582912 * c + m): one FMA and one
+      // ex2 per score. Denominator from the unrounded P; e4m3 P into the swizzled tile (row = 128 bytes, 16-byte chunk j
+      // of row r stored at chunk j ^ (r % 8)).
+      std::uint8_t* prow = p_generic + r_local * 128;
       const float bias = -fmaf(12582912.0f, c, m_run);
       float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        float pv[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) pv[i] = ex2(fmaf(__uint_as_float(sreg[16 * g + i] + 0x4B400000u), c, bias));
-        if (!full_tile) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) pv[i] = (16 * g + i < valid) ? pv[i] : 0.f;
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        std::uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_off + col_off + cc * 32, r);
+        tmem_ld_wait();
+        // These columns are consumed: refill them with the bias; after the second chunk S goes back to the MMA warp, so
+        // Q·K^T of the next tile runs under the exponentials of this chunk.
+        prefill_s(cc);
+        if (cc == 1) {
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&s_s_free));
         }
 #pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-          d0 += pv[i];
-          d1 += pv[i + 1];
-          d2 += pv[i + 2];
-          d3 += pv[i + 3];
+        for (int j = 0; j < 2; ++j) {  // 16 keys = one 16-byte chunk of the P row at a time
+          float pv[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // The exponentials are split between the special-function unit and the FMA pipe, which would otherwise idle.
+            const float e = fmaf(__uint_as_float(r[16 * j + i]), c, bias);
+            pv[i] = ((B2_EXP_POLY_MASK >> (i & 3)) & 1) ? ex2_poly(e) : ex2(e);
+          }
+          if (!full_tile) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pv[i] = (cc * 32 + 16 * j + i < valid) ? pv[i] : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            d0 += pv[i];
+            d1 += pv[i + 1];
+            d2 += pv[i + 2];
+            d3 += pv[i + 3];
+          }
+          const int chunk = (half * 4 + cc * 2 + j) ^ (r_local & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) =
+              make_uint4(e4m3x4(pv[0], pv[1], pv[2], pv[3]), e4m3x4(pv[4], pv[5], pv[6], pv[7]),
+                         e4m3x4(pv[8], pv[9], pv[10], pv[11]), e4m3x4(pv[12], pv[13], pv[14], pv[15]));
         }
-        const int chunk = (cq * 2 + g) ^ (r_local & 7);
-        *reinterpret_cast<uint4*>(prow + chunk * 16) =
-            make_uint4(e4m3x4(pv[0], pv[1], pv[2], pv[3]), e4m3x4(pv[4], pv[5], pv[6], pv[7]),
-                       e4m3x4(pv[8], pv[9], pv[10], pv[11]), e4m3x4(pv[12], pv[13], pv[14], pv[15]));
       }
       d_run += (d0 + d1) + (d2 + d3);
+      TRACE(3);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_p_full[t & 1]));
+      if (lane == 0) mbar_arrive(smem_u32(&s_p_full));
+      TRACE(4);
     }
-    // Row denominator = the four threads' sums.
-    s_den[cq][r_local] = d_run;
-    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-    const float d_row = (s_den[0][r_local] + s_den[1][r_local]) + (s_den[2][r_local] + s_den[3][r_local]);
+    // Row denominator = the two threads' sums.
+    s_den[half][r_local] = d_run;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const float d_row = d_run + s_den[half ^ 1][r_local];
     if (!dead && wait_bar(smem_u32(&s_pv_done), (n_tiles - 1) & 1u, abort_word)) {
       tc_fence_after();
       const float inv_d = rcp_approx(d_row);
       const int row = q0 + r_local;
-      __nv_bfloat16* orow = a.out + static_cast<std::int64_t>(q_start + row) * a.out_row + h * a.out_head + cq * 32;
-      const float* vs = a.v_scale + sc_base * kHeadDim + cq * 32;
-      std::uint32_t r[32];
-      tmem_ld_32x32(tmem_o + lane_off + col_off, r);
-      tmem_ld_wait();
-      if (row < qo_len) {
+      __nv_bfloat16* orow = a.out + static_cast<std::int64_t>(q_start + row) * a.out_row + h * a.out_head + half * 64;
+      const float* vs = a.v_scale + sc_base * kHeadDim + half * 64;
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        std::uint32_t r[32];
+        tmem_ld_32x32(tmem_o + lane_off + col_off + cc * 32, r);
+        tmem_ld_wait();
+        if (row < qo_len) {
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          float o[8];
+          for (int v = 0; v < 4; ++v) {
+            float o[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[8 * v + i]) * inv_d * __ldg(vs + 8 * v + i);
-          *reinterpret_cast<uint4*>(orow + 8 * v) =
-              make_uint4(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]), pack_bf2(o[4], o[5]), pack_bf2(o[6], o[7]));
+            for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[8 * v + i]) * inv_d * __ldg(vs + cc * 32 + 8 * v + i);
+            *reinterpret_cast<uint4*>(orow + cc * 32 + 8 * v) =
+                make_uint4(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]), pack_bf2(o[4], o[5]), pack_bf2(o[6], o[7]));
+          }
         }
       }
     }
@@ -939,6 +1014,13 @@ int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_v
   a.heads = static_cast<int>(heads), a.q_blocks = l.q_blocks, a.k_blocks = l.k_blocks;
   a.scale_log2 = scale * 1.44269504088896340736f;
   a.p_offset = static_cast<float>(std::floor(std::log2(static_cast<double>(p_range)) * 1000.0) / 1000.0);
+#ifdef B2_ATTN_TRACE
+  {
+    void* tp = nullptr;
+    cudaGetSymbolAddress(&tp, g_attn_trace);
+    a.trace = static_cast<long long*>(tp);
+  }
+#endif
   if (const cudaError_t e = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
       e != cudaSuccess) {
     return fail_cuda(op, e);
@@ -947,5 +1029,11 @@ int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_v
   attention_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(map_q, map_k, map_v, a);
   return check_launch(op);
 }
+
+#ifdef B2_ATTN_TRACE
+int b2_attention_trace(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(long long) * n) == cudaSuccess ? 0 : -8;
+}
+#endif
 
 }  // extern "C"

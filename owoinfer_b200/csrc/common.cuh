@@ -259,6 +259,15 @@ __device__ __forceinline__ void tmem_st_32x32(std::uint32_t taddr, const std::ui
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
       : "memory");
 }
+// The same 32-bit value into this warp's 32 lanes x 32 consecutive columns.
+__device__ __forceinline__ void tmem_fill_32x32(std::uint32_t taddr, std::uint32_t v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
+      "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+      ::"r"(taddr), "r"(v)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 #endif  // __CUDACC__
 
