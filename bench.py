@@ -40,6 +40,7 @@ def parse():
     p.add_argument("--blocks", type=int, default=42)
     p.add_argument("--ffn", type=int, default=12288)
     p.add_argument("--no-profile", action="store_true", help="skip the per-kernel roofline pass and the CPU baseline")
+    p.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own CUDA kernels on this GPU")
     return p.parse_args()
 
 
@@ -165,6 +166,33 @@ def run_reference(args, rank, world):
 
 
 # ----------------------------------------------------------------------------------------------------------- GPU arm
+
+def reference_kernels_on_this_gpu(torch, ops, keep, x, x0, mod, rope, cu, seq_len, L, F):
+    """The same step over the reference's own CUDA kernels (its mma.sync INT8 GEMMs and attention, compiled for sm_100a
+    into oracle/_ref/libref_cuda.so), sequenced as its run_block_quant does, on this GPU with the same weights and
+    inputs: what the reference would do here. Reported beside the CPU baseline; None where that build is absent."""
+    from oracle import ref_cuda_lib as refk
+    if not refk.available():
+        return None
+    rb = refk.RefBlock(L, cu, seq_len, D, F, HEADS)
+
+    def ref_step():
+        x.copy_(x0)
+        for w, _ in keep:
+            rb.run(x, mod, rope, w, ops.SM_SCALE)
+
+    ref_step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 2
+    e0.record()
+    for _ in range(n):
+        ref_step()
+    e1.record()
+    torch.cuda.synchronize()
+    return {"value": e0.elapsed_time(e1) / n, "unit": "ms", "kind": "reference CUDA kernels built for sm_100a, device-timed",
+            "steps": n, "blocks": len(keep)}
+
 
 def gemm_sites(L, F):
     return [("qkv", 3 * D, D, "plain"), ("o", D, D, "gated"), ("up_gate", 2 * F, D, "situ"), ("down", D, F, "gated")]
@@ -371,6 +399,8 @@ def main():
             line["cpu_baseline"] = {"value": v, "unit": "ms", "cores": threads, "kind": "port",
                                     "sample": f"one block on 256 tokens ({tb:.2f} s) + attention of one 1536-token sequence x 24 "
                                               f"heads ({ta:.2f} s), extrapolated to {n_blocks} blocks x {seqs} x {seq_len} tokens"}
+            if world == 1 and tier == ops.TIER_INT8 and not args.no_ref_gpu:
+                line["reference_gpu"] = reference_kernels_on_this_gpu(torch, ops, keep, x, x0, mod, rope, cu, seq_len, L, F)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

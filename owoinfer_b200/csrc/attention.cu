@@ -1,8 +1,9 @@
 // SageAttention-style 8-bit attention for sm_100a, plus the MOSS QK-norm + RoPE and RoPE-table kernels that feed it.
 //
 //   pre-pass (HBM-bound, 128-bit accesses)
-//     stats      per (512-key chunk, head, sequence): partial per-channel K sums and V |max| in a fixed order; with the
-//                fused prologue also RMS-norm + RoPE of q and k (k written back), and Q quantised per (32 tokens, head)
+//     prologue   (fused QK-norm + RoPE only) per (32 tokens, head): RMS-norm + RoPE of q and k, k written back,
+//                Q quantised
+//     stats      per (512-key chunk, head, sequence): partial per-channel K sums and V |max| in a fixed order
 //     finalize   k_mean = bf16(sum / len); v_scale = amax / v_range; v_recp = v_range / amax
 //     quantise   Q per (32 tokens, head) [when not fused]; K - k_mean per (64 keys, head) -> int8; V * v_recp -> e4m3
 //   attention (tensor-core-bound): one CTA per (128 query rows, head, sequence), two CTAs per SM; 128-key tiles
@@ -272,102 +273,94 @@ __device__ __forceinline__ void norm_rope_row(const float* x, const float* w, co
   }
 }
 
-// CTA = 16 token rows x 16 lanes x 8 channels, one (512-key chunk, head, sequence). Row-thread `row` adds tokens
-// row, row + 16, ... of the chunk in order; the 16 partials are then added in order, and the finalize kernel adds the
-// chunks in order: the K mean is reproducible and independent of the launch shape.
-template <bool kFused>
+// Fused prologue, one CTA per (32-token Q block, head, sequence): 32 token rows x 16 lanes x 8 channels. RMS-norm + RoPE
+// of q and k; Q quantised with the block's scale; k written back in place for the statistics and K/V quantisation
+// passes. Every load of a row is issued before the first use.
+__global__ void __launch_bounds__(512, 2) norm_rope_quant_q_kernel(const PrepArgs p) {
+  const int bx = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int lane = static_cast<int>(threadIdx.x) & 15, row = static_cast<int>(threadIdx.x) >> 4;
+  const int start = p.cu[b], len = p.cu[b + 1] - start;
+  const std::int64_t scale_at = (static_cast<std::int64_t>(b) * p.heads + h) * p.q_blocks + bx;
+  if (bx * 32 >= len) {
+    // A block at or past the sequence end holds no tokens: its scale is the empty block's.
+    if (threadIdx.x == 0) p.q_scale[scale_at] = 0.0000001f / 127.0f;
+    return;
+  }
+  const int t = bx * 32 + row;
+  const bool valid = t < len;
+  const std::int64_t tok = static_cast<std::int64_t>(start) + t;
+  const int pair = (lane & 7) * 8;
+  float x[8] = {}, kx[8] = {}, si[8] = {}, co[8] = {}, w[8], qy[8], ky[8];
+  __nv_bfloat16* k_at = p.k + tok * p.k_row + h * p.k_head + lane * 8;
+  if (valid) {
+    load8(p.q + tok * p.q_row + h * p.q_head + lane * 8, x);
+    load8(k_at, kx);
+    load8(p.table + tok * p.table_row + pair, si);
+    load8(p.table + tok * p.table_row + 64 + pair, co);
+  }
+  load8(p.q_norm + lane * 8, w);
+  norm_rope_row(x, w, si, co, p.norm_factor, lane, qy);
+  load8(p.k_norm + lane * 8, w);
+  norm_rope_row(kx, w, si, co, p.norm_factor, lane, ky);
+  if (valid) {
+    *reinterpret_cast<uint4*>(k_at) =
+        make_uint4(pack_bf2(ky[0], ky[1]), pack_bf2(ky[2], ky[3]), pack_bf2(ky[4], ky[5]), pack_bf2(ky[6], ky[7]));
+  }
+  float qmax = 0.0000001f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) qmax = fmaxf(qmax, fabsf(qy[j]));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) qmax = fmaxf(qmax, __shfl_xor_sync(0xffffffffu, qmax, off));
+  __shared__ float s_w[16];
+  if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = qmax;
+  __syncthreads();
+  qmax = s_w[0];
+#pragma unroll
+  for (int i = 1; i < 16; ++i) qmax = fmaxf(qmax, s_w[i]);
+  if (threadIdx.x == 0) p.q_scale[scale_at] = qmax / 127.0f;
+  if (!valid) return;
+  const float qs = 127.0f / qmax;
+  *reinterpret_cast<uint2*>(p.q_i8 + (tok * p.heads + h) * kHeadDim + lane * 8) =
+      make_uint2(pack_i8x4(qy[0] * qs, qy[1] * qs, qy[2] * qs, qy[3] * qs),
+                 pack_i8x4(qy[4] * qs, qy[5] * qs, qy[6] * qs, qy[7] * qs));
+}
+
+// Statistics, one CTA per (512-key chunk, head, sequence): 16 token rows x 16 lanes x 8 channels. Row-thread `row` adds
+// tokens row, row + 16, ... of the chunk in order; the 16 partials are then added in order, and the finalize kernel adds
+// the chunks in order: the K mean is reproducible and independent of the launch shape. Loads run four tokens ahead.
 __global__ void __launch_bounds__(256) stats_kernel(const PrepArgs p) {
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int lane = static_cast<int>(threadIdx.x) & 15, row = static_cast<int>(threadIdx.x) >> 4, warp = static_cast<int>(threadIdx.x) >> 5;
+  const int lane = static_cast<int>(threadIdx.x) & 15, row = static_cast<int>(threadIdx.x) >> 4;
   const int start = p.cu[b], len = p.cu[b + 1] - start;
   float sum[8] = {}, amax[8] = {};
   __shared__ float s_red[16][kHeadDim];
-  __shared__ float s_wmax[2][8];
 
-  if constexpr (kFused) {
-    float wq[8], wk[8];
-    load8(p.q_norm + lane * 8, wq);
-    load8(p.k_norm + lane * 8, wk);
-    const int pair = (lane & 7) * 8;
-    for (int step0 = 0; step0 < kStatsChunk / 16; step0 += 2) {
-      const int block_start = c * kStatsChunk + step0 * 16;
-      if (block_start >= len) {
-        // Q blocks at or past the sequence end hold no tokens: their scale is the empty block's.
-        if (threadIdx.x == 0) {
-          const int end = min(p.q_blocks, (c + 1) * kStatsChunk / 32);
-          for (int bx = block_start / 32; bx < end; ++bx) {
-            p.q_scale[(static_cast<std::int64_t>(b) * p.heads + h) * p.q_blocks + bx] = 0.0000001f / 127.0f;
-          }
-        }
-        break;
-      }
-      float qy[2][8];
-      float qmax = 0.0000001f;
-      bool valid[2];
-      std::int64_t tok[2];
+  const int t_end = min(len, (c + 1) * kStatsChunk);
+  constexpr int kAhead = 4;
+  for (int t0 = c * kStatsChunk + row; t0 < t_end; t0 += 16 * kAhead) {
+    uint4 kr[kAhead], vr[kAhead];
 #pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const int t = block_start + s * 16 + row;
-        valid[s] = t < len;
-        tok[s] = static_cast<std::int64_t>(start) + t;
-        float x[8], si[8], co[8], ky[8];
-        if (valid[s]) {
-          load8(p.table + tok[s] * p.table_row + pair, si);
-          load8(p.table + tok[s] * p.table_row + 64 + pair, co);
-          load8(p.q + tok[s] * p.q_row + h * p.q_head + lane * 8, x);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) x[j] = si[j] = co[j] = 0.f;
-        }
-        norm_rope_row(x, wq, si, co, p.norm_factor, lane, qy[s]);
-        if (valid[s]) {
-          load8(p.k + tok[s] * p.k_row + h * p.k_head + lane * 8, x);
-        }
-        norm_rope_row(x, wk, si, co, p.norm_factor, lane, ky);
-        if (valid[s]) {
-          *reinterpret_cast<uint4*>(p.k + tok[s] * p.k_row + h * p.k_head + lane * 8) =
-              make_uint4(pack_bf2(ky[0], ky[1]), pack_bf2(ky[2], ky[3]), pack_bf2(ky[4], ky[5]), pack_bf2(ky[6], ky[7]));
-#pragma unroll
-          for (int j = 0; j < 8; ++j) sum[j] += ky[j];
-          load8(p.v + tok[s] * p.v_row + h * p.v_head + lane * 8, x);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) amax[j] = fmaxf(amax[j], fabsf(x[j]));
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) qmax = fmaxf(qmax, fabsf(qy[s][j]));
-      }
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) qmax = fmaxf(qmax, __shfl_xor_sync(0xffffffffu, qmax, off));
-      const int buf = (step0 >> 1) & 1;
-      if ((threadIdx.x & 31) == 0) s_wmax[buf][warp] = qmax;
-      __syncthreads();
-      float block_max = s_wmax[buf][0];
-#pragma unroll
-      for (int i = 1; i < 8; ++i) block_max = fmaxf(block_max, s_wmax[buf][i]);
-      const int bx = block_start / 32;
-      if (threadIdx.x == 0 && bx < p.q_blocks) {
-        p.q_scale[(static_cast<std::int64_t>(b) * p.heads + h) * p.q_blocks + bx] = block_max / 127.0f;
-      }
-      const float qs = 127.0f / block_max;
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        if (!valid[s]) continue;
-        *reinterpret_cast<uint2*>(p.q_i8 + (tok[s] * p.heads + h) * kHeadDim + lane * 8) =
-            make_uint2(pack_i8x4(qy[s][0] * qs, qy[s][1] * qs, qy[s][2] * qs, qy[s][3] * qs),
-                       pack_i8x4(qy[s][4] * qs, qy[s][5] * qs, qy[s][6] * qs, qy[s][7] * qs));
+    for (int u = 0; u < kAhead; ++u) {
+      const int t = t0 + 16 * u;
+      const std::int64_t tok = static_cast<std::int64_t>(start) + t;
+      if (t < t_end) {
+        kr[u] = *reinterpret_cast<const uint4*>(p.k + tok * p.k_row + h * p.k_head + lane * 8);
+        vr[u] = *reinterpret_cast<const uint4*>(p.v + tok * p.v_row + h * p.v_head + lane * 8);
+      } else {
+        kr[u] = vr[u] = make_uint4(0, 0, 0, 0);  // +0 leaves the sum and the maximum as they are
       }
     }
-  } else {
-    const int t_end = min(len, (c + 1) * kStatsChunk);
-    for (int t = c * kStatsChunk + row; t < t_end; t += 16) {
-      float x[8];
-      const std::int64_t tok = static_cast<std::int64_t>(start) + t;
-      load8(p.k + tok * p.k_row + h * p.k_head + lane * 8, x);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) sum[j] += x[j];
-      load8(p.v + tok * p.v_row + h * p.v_head + lane * 8, x);
+    for (int u = 0; u < kAhead; ++u) {
+      if (t0 + 16 * u >= t_end) break;
+      const std::uint32_t kw[4] = {kr[u].x, kr[u].y, kr[u].z, kr[u].w}, vw[4] = {vr[u].x, vr[u].y, vr[u].z, vr[u].w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) amax[j] = fmaxf(amax[j], fabsf(x[j]));
+      for (int i = 0; i < 4; ++i) {
+        sum[2 * i] += __uint_as_float(kw[i] << 16);
+        sum[2 * i + 1] += __uint_as_float(kw[i] & 0xFFFF0000u);
+        amax[2 * i] = fmaxf(amax[2 * i], fabsf(__uint_as_float(vw[i] << 16)));
+        amax[2 * i + 1] = fmaxf(amax[2 * i + 1], fabsf(__uint_as_float(vw[i] & 0xFFFF0000u)));
+      }
     }
   }
 
@@ -443,9 +436,10 @@ __global__ void __launch_bounds__(1024) quant_kv_kernel(const PrepArgs p) {
   const bool valid = t < len;
   const std::int64_t tok = static_cast<std::int64_t>(start) + t;
   const std::int64_t stat = (static_cast<std::int64_t>(b) * p.heads + h) * kHeadDim + lane * 8;
-  float x[8] = {};
+  float x[8] = {}, v[8] = {};
   if (valid) {
     load8(p.k + tok * p.k_row + h * p.k_head + lane * 8, x);
+    load8(p.v + tok * p.v_row + h * p.v_head + lane * 8, v);  // in flight across the block reduction
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] -= p.k_mean[stat + j];
   }
@@ -466,8 +460,6 @@ __global__ void __launch_bounds__(1024) quant_kv_kernel(const PrepArgs p) {
   const std::int64_t o = (tok * p.heads + h) * kHeadDim + lane * 8;
   *reinterpret_cast<uint2*>(p.k_i8 + o) =
       make_uint2(pack_i8x4(x[0] * ks, x[1] * ks, x[2] * ks, x[3] * ks), pack_i8x4(x[4] * ks, x[5] * ks, x[6] * ks, x[7] * ks));
-  float v[8];
-  load8(p.v + tok * p.v_row + h * p.v_head + lane * 8, v);
 #pragma unroll
   for (int j = 0; j < 8; ++j) v[j] *= p.v_recp[stat + j];
   *reinterpret_cast<uint2*>(p.v8 + o) = make_uint2(e4m3x4(v[0], v[1], v[2], v[3]), e4m3x4(v[4], v[5], v[6], v[7]));
@@ -984,10 +976,10 @@ int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_v
     p.table = static_cast<const __nv_bfloat16*>(norm_rope->table);
     p.table_row = norm_rope->table_ld;
     p.norm_factor = static_cast<float>(rows) / static_cast<float>(rows * kHeadDim);
-    stats_kernel<true><<<stats_grid, 256, 0, st>>>(p);
-  } else {
-    stats_kernel<false><<<stats_grid, 256, 0, st>>>(p);
+    norm_rope_quant_q_kernel<<<dim3(l.q_blocks, static_cast<unsigned>(heads), batch), 512, 0, st>>>(p);
+    if (const int rc = check_launch(op)) return rc;
   }
+  stats_kernel<<<stats_grid, 256, 0, st>>>(p);
   if (const int rc = check_launch(op)) return rc;
   finalize_kernel<<<dim3(static_cast<unsigned>(heads), batch), kHeadDim, 0, st>>>(p);
   if (const int rc = check_launch(op)) return rc;

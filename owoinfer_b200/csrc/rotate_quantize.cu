@@ -141,7 +141,39 @@ __global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
   }
 
   if constexpr (kNorm) {
-    if (warp == 0) {
+    if constexpr (kSlots == 1) {
+      // The squares go through shared memory (the transpose tiles, not yet in use, hold a whole row when every half-warp
+      // has one group), so that torch's 4 * bw accumulator chains run on as many threads instead of on one warp.
+      float* sq = smem_f;
+      if (half_id < groups) {
+        float4* dst = reinterpret_cast<float4*>(sq + half_id * kGroup + 16 * h);
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          dst[j >> 2] = make_float4(fmul(v[0][j], v[0][j]), fmul(v[0][j + 1], v[0][j + 1]), fmul(v[0][j + 2], v[0][j + 2]),
+                                    fmul(v[0][j + 3], v[0][j + 3]));
+        }
+      }
+      __syncthreads();
+      // Chain (t, c) = torch thread t's accumulator c: elements 4 * (t + bw * i) + c, i = 0, 1, ... in order.
+      for (int ct = tid; ct < 4 * a.bw; ct += static_cast<int>(blockDim.x)) {
+        float acc = 0.f;
+        for (int e = ct; e < a.k; e += 4 * a.bw) acc = fadd(acc, sq[e]);
+        const float a1 = __shfl_down_sync(0xffffffffu, acc, 1), a2 = __shfl_down_sync(0xffffffffu, acc, 2);
+        const float a3 = __shfl_down_sync(0xffffffffu, acc, 3);
+        if ((ct & 3) == 0) s_part[ct >> 2] = fadd(fadd(fadd(acc, a1), a2), a3);
+      }
+      __syncthreads();
+      if (warp == 0) {
+        for (int off = a.bw / 2; off >= 32; off >>= 1) {
+          for (int t = lane; t < off; t += 32) s_part[t] = fadd(s_part[t], s_part[t + off]);
+          __syncwarp();
+        }
+        float ss = s_part[lane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss = fadd(ss, __shfl_down_sync(0xffffffffu, ss, off));
+        if (lane == 0) s_inv_rms = rsqrtf(fadd(fmul(ss, a.factor), 1e-6f));
+      }
+    } else if (warp == 0) {
       const float ss = torch_order_sum_squares(xr, a.k, a.bw, s_part, lane);
       if (lane == 0) s_inv_rms = rsqrtf(fadd(fmul(ss, a.factor), 1e-6f));
     }
