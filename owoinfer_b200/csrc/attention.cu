@@ -35,7 +35,7 @@ constexpr std::size_t kAlign = 256;
 __device__ int g_attn_status = 0;
 #ifdef B2_ATTN_TRACE
 __device__ long long g_attn_trace[4096];
-#define TRACE(slot) do { if (tracing) a.trace[t * 8 + (slot)] = clock64(); } while (0)
+#define TRACE(slot) do { if (tracing) a.trace[u * 8 + (slot)] = clock64(); } while (0)
 #else
 #define TRACE(slot) do { } while (0)
 #endif
@@ -48,14 +48,36 @@ __device__ __forceinline__ std::uint64_t global_ns() {
 __device__ __forceinline__ bool wait_bar(std::uint32_t bar, std::uint32_t parity, volatile int* abort_word) {
   if (mbar_try_wait(bar, parity)) return true;
   const std::uint64_t t0 = global_ns();
-  for (std::uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 0u) {
-      if (*abort_word != 0) return false;
-      if (global_ns() - t0 > 1000000000ull) {
-        *abort_word = 1;
-        return false;
-      }
+  for (;;) {
+    // A tight inner loop (test, branch); the abort word and the clock are looked at once per 256 tests.
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+      if (mbar_try_wait_hint(bar, parity)) return true;
+    }
+    if (*abort_word != 0) return false;
+    if (global_ns() - t0 > 1000000000ull) {
+      *abort_word = 1;
+      return false;
+    }
+  }
+}
+
+// The same for a role with slack (the TMA and MMA warps share their scheduler with softmax warps): sleeps between tests so
+// that waiting costs next to no issue slots.
+template <int kSleepNs>
+__device__ __forceinline__ bool wait_bar_relaxed(std::uint32_t bar, std::uint32_t parity, volatile int* abort_word) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const std::uint64_t t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      __nanosleep(kSleepNs);
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_word != 0) return false;
+    if (global_ns() - t0 > 1000000000ull) {
+      *abort_word = 1;
+      return false;
     }
   }
 }
@@ -94,7 +116,33 @@ __device__ __forceinline__ std::uint32_t e4m3x2(float lo, float hi) {
   return r;
 }
 __device__ __forceinline__ std::uint32_t e4m3x4(float a, float b, float c, float d) {
-  return __byte_perm(e4m3x2(a, b), e4m3x2(c, d), 0x5410);
+  std::uint32_t w;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}"
+      : "=r"(w)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return w;
+}
+// Packed fp32 pairs (one instruction for two lanes of work): d = a * b + c and d = a + b on (x, y) pairs.
+__device__ __forceinline__ std::uint64_t pack2(float x, float y) {
+  std::uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+  return r;
+}
+__device__ __forceinline__ void unpack2(std::uint64_t v, float& x, float& y) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
+}
+__device__ __forceinline__ std::uint64_t fma2(std::uint64_t a, std::uint64_t b, std::uint64_t c) {
+  std::uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ std::uint64_t add2(std::uint64_t a, std::uint64_t b) {
+  std::uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
@@ -115,6 +163,12 @@ __device__ __forceinline__ float ex2_poly(float x) {
   const float p = fmaf(fmaf(fmaf(0.0555041087f, f, 0.240226507f), f, 0.693147181f), f, 1.0f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(z) << 23));
 }
+#ifndef B2_TRACE_WARP
+#define B2_TRACE_WARP 2
+#endif
+#ifndef B2_MMA_SLEEP_NS
+#define B2_MMA_SLEEP_NS 100
+#endif
 #ifndef B2_EXP_POLY_MASK
 #define B2_EXP_POLY_MASK 0  // bit (i & 3) set: score i uses ex2_poly. Measured on B200: 0 (all on the special-function unit) is fastest
 #endif
@@ -468,13 +522,72 @@ __global__ void __launch_bounds__(1024) quant_kv_kernel(const PrepArgs p) {
 // ---------------------------------------------------------------------------------------------------------------
 // The attention kernel.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kTileQ = 128, kTileK = 128;
+// One softmax pass of one thread over its row's 64 scores of a sub-tile. The score accumulator was pre-filled with the
+// integer 0x4B400000 before Q·K^T, so a column read back is the bit pattern of the fp32 number 12582912 + S (exact:
+// |S| < 2^22): the scores arrive as floats with no conversion, their order is the integers' order, and the constant
+// is folded into `bias`. P = exp2(f * c + bias) with packed fp32 pairs for the FMA and the denominator; e4m3 P goes
+// into the swizzled P tile (row = 128 bytes, 16-byte chunk n of row r stored at chunk n ^ (r % 8); this sub-tile owns
+// chunks chunk0 .. chunk0 + 3). Returns the largest biased score (0 if none) and the sum of the unrounded P.
+template <bool kFull>
+__device__ __forceinline__ void softmax_pass(std::uint32_t s_cols, float c, float bias, int valid, std::uint8_t* prow,
+                                             int chunk0, int row_xor, float& bmax_out, float& sum_out) {
+  const std::uint64_t c2 = pack2(c, c), bias2 = pack2(bias, bias);
+  std::uint64_t dA = pack2(0.f, 0.f), dB = dA;
+  float bmax = 0.f;
+  const auto chunk = [&](const std::uint32_t (&r)[16], int n) {  // keys 16 n .. 16 n + 15 = one 16-byte chunk of the P row
+    float pv[16];
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const float f0 = __uint_as_float(r[i]), f1 = __uint_as_float(r[i + 1]);
+      float e0, e1;
+      unpack2(fma2(pack2(f0, f1), c2, bias2), e0, e1);
+      pv[i] = ex2(e0);
+      pv[i + 1] = ex2(e1);
+      if constexpr (kFull) {
+        bmax = fmax3(bmax, f0, f1);
+      } else {
+        const bool in0 = 16 * n + i < valid, in1 = 16 * n + i + 1 < valid;
+        bmax = fmax3(bmax, in0 ? f0 : 0.f, in1 ? f1 : 0.f);
+        pv[i] = in0 ? pv[i] : 0.f;
+        pv[i + 1] = in1 ? pv[i + 1] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+      dA = add2(dA, pack2(pv[i], pv[i + 1]));
+      dB = add2(dB, pack2(pv[i + 2], pv[i + 3]));
+    }
+    *reinterpret_cast<uint4*>(prow + ((chunk0 + n) ^ row_xor) * 16) =
+        make_uint4(e4m3x4(pv[0], pv[1], pv[2], pv[3]), e4m3x4(pv[4], pv[5], pv[6], pv[7]),
+                   e4m3x4(pv[8], pv[9], pv[10], pv[11]), e4m3x4(pv[12], pv[13], pv[14], pv[15]));
+  };
+  std::uint32_t ra[16], rb[16], rc[16], rd[16];
+  tmem_ld_32x16(s_cols, ra);
+  tmem_ld_32x16(s_cols + 16, rb);
+  tmem_ld_32x16(s_cols + 32, rc);
+  tmem_ld_32x16(s_cols + 48, rd);
+  tmem_ld_wait();
+  chunk(ra, 0);
+  chunk(rb, 1);
+  chunk(rc, 2);
+  chunk(rd, 3);
+  float d0, d1, d2, d3;
+  unpack2(dA, d0, d1);
+  unpack2(dB, d2, d3);
+  bmax_out = bmax;
+  sum_out = (d0 + d1) + (d2 + d3);
+}
+
+constexpr int kTileQ = 128, kTileK = 128, kSubK = 64;
 constexpr int kKvStages = 2;
 constexpr int kTileBytes = 128 * 128;
 constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 1) + 1024;  // Q, K/V stages, P, alignment slack
-constexpr int kAttnThreads = 320;  // TMA warp, MMA warp, 8 softmax warps
-constexpr std::uint32_t kTmemCols = 256;  // S: columns [0, 128); O: columns [128, 256)
-constexpr float kLazy = 1.0f;              // how far (log2 units) the softmax reference maximum may lag the true one
+constexpr int kAttnThreads = 192;  // TMA warp, MMA warp, 4 softmax warps
+constexpr std::uint32_t kTmemCols = 256;  // S(u % 2): columns [64 (u % 2), +64); O: columns [128, 256)
+// Softmax reference maximum: set kHeadroom binades above what the largest P needs, raised again once fewer than kRaise
+// binades are left. e4m3 keeps full relative precision over 14 binades below p_range, so three binades of headroom cost
+// nothing measurable.
+constexpr float kHeadroom = 3.0f, kRaise = 1.0f;
 
 struct AttnArgs {
   const float* q_scale;
@@ -488,10 +601,17 @@ struct AttnArgs {
   float scale_log2;  // sm_scale * log2(e)
   float p_offset;
 #ifdef B2_ATTN_TRACE
-  long long* trace;  // [tile][8] clock64 stamps of CTA (0,0,0), softmax warp 2 lane 0 and the MMA thread
+  long long* trace;  // [sub-tile][8] clock64 stamps of CTA (0,0,0), softmax warp 2 lane 0 and the MMA warp
 #endif
 };
 
+// One CTA per (128 query rows, head, sequence), two CTAs per SM. K and V arrive in 128-key tiles; the tensor work runs in
+// 64-key sub-tiles u = 0, 1, ... (one K scale block each) with the score accumulator double-buffered in TMEM, so the MMA
+// warp computes S(u + 1) while the softmax warps turn S(u) into P(u):
+//   MMA warp      S(u % 2) = Q · K(u)^T (N = 64), O += P(u % 2) · V(u) (K = 64)
+//   softmax warps one thread per query row (TMEM lane), 64 scores per sub-tile: no exchange between threads
+//   P             e4m3, the two buffers interleaved in one swizzled [128 x 128 B] tile: buffer i = bytes [64 i, +64) of
+//                 each row
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const AttnArgs a) {
@@ -513,11 +633,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
   extern __shared__ std::uint8_t smem_raw[];
   __shared__ __align__(8) std::uint64_t s_q_full, s_k_full[kKvStages], s_k_empty[kKvStages], s_v_full[kKvStages],
-      s_v_empty[kKvStages], s_s_full, s_s_free, s_p_full, s_pv_done;
+      s_v_empty[kKvStages], s_s_full[2], s_p_full[2], s_pv_done[2], s_s_ready;
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ float s_mx[2][2][kTileQ];  // [tile parity][key half][row]: block maxima exchanged by a row's two threads
-  __shared__ float s_den[2][kTileQ];    // [key half][row]: the two partial denominators of a row
   const std::uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const std::uint32_t q_smem = base;
   const auto k_smem = [&](int s) { return base + kTileBytes * (1 + s); };
@@ -533,10 +651,12 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(smem_u32(&s_v_full[s]), 1);
       mbar_init(smem_u32(&s_v_empty[s]), 1);
     }
-    mbar_init(smem_u32(&s_s_full), 1);
-    mbar_init(smem_u32(&s_p_full), 8);
-    mbar_init(smem_u32(&s_pv_done), 1);
-    mbar_init(smem_u32(&s_s_free), 8);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&s_s_full[i]), 1);
+      mbar_init(smem_u32(&s_p_full[i]), 4);
+      mbar_init(smem_u32(&s_pv_done[i]), 1);
+    }
+    mbar_init(smem_u32(&s_s_ready), 4);
     s_abort = 0;
     fence_mbar_init();
     prefetch_tensormap(&map_q);
@@ -552,7 +672,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   tc_fence_after();
   const std::uint32_t tmem_s = s_tmem_base, tmem_o = s_tmem_base + 128;
   volatile int* abort_word = &s_abort;
-  const int n_tiles = (kv_len + kTileK - 1) / kTileK;
+  const int n_tiles = (kv_len + kTileK - 1) / kTileK;  // 128-key K/V tiles
+  const int n_sub = (kv_len + kSubK - 1) / kSubK;      // 64-key sub-tiles
 
   if (warp == 0) {
     if (lane == 0) {
@@ -561,220 +682,221 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       for (int t = 0; t < n_tiles && *abort_word == 0; ++t) {
         const int s = t % kKvStages;
         const std::uint32_t ph = (t / kKvStages) & 1u;
-        if (!wait_bar(smem_u32(&s_k_empty[s]), ph ^ 1u, abort_word)) break;
+        if (!wait_bar_relaxed<400>(smem_u32(&s_k_empty[s]), ph ^ 1u, abort_word)) break;
         mbar_expect_tx(smem_u32(&s_k_full[s]), kTileBytes);
         tma_load_2d(k_smem(s), &map_k, smem_u32(&s_k_full[s]), h * kHeadDim, k_start + t * kTileK);
-        if (!wait_bar(smem_u32(&s_v_empty[s]), ph ^ 1u, abort_word)) break;
+        if (!wait_bar_relaxed<400>(smem_u32(&s_v_empty[s]), ph ^ 1u, abort_word)) break;
         mbar_expect_tx(smem_u32(&s_v_full[s]), kTileBytes);
         tma_load_2d(v_smem(s), &map_v, smem_u32(&s_v_full[s]), h * kHeadDim, k_start + t * kTileK);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
+    // The whole warp walks the loop (uniform control flow, every lane takes the waits); one elected lane issues.
 #ifdef B2_ATTN_TRACE
-      const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
 #endif
-      constexpr std::uint32_t idesc_qk = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, 128, 128);
-      constexpr std::uint32_t idesc_pv = umma_idesc(/*f32*/ 1, /*e4m3*/ 0, /*e4m3*/ 0, 0, /*B MN-major*/ 1, 128, 128);
-      const auto issue_qk = [&](int t) -> bool {
-        const int s = t % kKvStages;
-        if (!wait_bar(smem_u32(&s_k_full[s]), (t / kKvStages) & 1u, abort_word)) return false;
-        tc_fence_after();
-        const std::uint64_t dq = umma_desc_sw128(q_smem), dk = umma_desc_sw128(k_smem(s));
-#pragma unroll
-        // S was pre-filled with the integer 0x4B400000 by the softmax warps: accumulate onto it (see the softmax pass).
-        for (int k4 = 0; k4 < 4; ++k4) umma_i8(tmem_s, dq + 2u * k4, dk + 2u * k4, idesc_qk, 1u);
-        tc_commit(smem_u32(&s_k_empty[s]));
-        tc_commit(smem_u32(&s_s_full));
-        return true;
-      };
-      // s_s_free phase i: S is pre-filled and free for Q·K^T of tile i (phase 0 comes from the start-up pre-fill).
-      bool ok = wait_bar(smem_u32(&s_s_free), 0, abort_word) && wait_bar(smem_u32(&s_q_full), 0, abort_word);
+    constexpr std::uint32_t idesc_qk = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, 128, kSubK);
+    constexpr std::uint32_t idesc_pv = umma_idesc(/*f32*/ 1, /*e4m3*/ 0, /*e4m3*/ 0, 0, /*B MN-major*/ 1, 128, 128);
+    const std::uint64_t dq = umma_desc_sw128(q_smem), dp = umma_desc_sw128(p_smem);
+    static_assert(kKvStages == 2, "the descriptors below are selected, not indexed");
+    const std::uint64_t dk0 = umma_desc_sw128(k_smem(0)), dk1 = umma_desc_sw128(k_smem(1));
+    const std::uint64_t dv0 = umma_desc_sw128(v_smem(0)), dv1 = umma_desc_sw128(v_smem(1));
+    // 64 keys = 64 rows of 128 bytes of a K or V tile: 8192 bytes, 512 in the descriptors' 16-byte units.
+    constexpr std::uint32_t kHalfTile = 64 * 128 / 16;
+    // S(u % 2) = Q · K(u)^T. The K tile goes back to the TMA warp after its second half.
+    const auto issue_qk = [&](int u) -> bool {
+      const int s = (u >> 1) % kKvStages;
+      bool got = true;
+      if ((u & 1) == 0) got = wait_bar(smem_u32(&s_k_full[s]), ((u >> 1) / kKvStages) & 1u, abort_word);
+      if (__any_sync(0xffffffffu, !got)) return false;
       tc_fence_after();
-      ok = ok && issue_qk(0);
-      for (int t = 0; ok && t < n_tiles; ++t) {
-        const int s = t % kKvStages;
-        // Q·K^T of the next tile as soon as the softmax warps have read S(t) (half way through their second pass).
-        if (t + 1 < n_tiles) {
-          if (!wait_bar(smem_u32(&s_s_free), (t + 1) & 1u, abort_word)) break;
-          tc_fence_after();
-          TRACE(5);
-          if (!issue_qk(t + 1)) break;
-        }
-        TRACE(6);
-        if (!wait_bar(smem_u32(&s_p_full), t & 1u, abort_word)) break;  // P(t) written
-        if (!wait_bar(smem_u32(&s_v_full[s]), (t / kKvStages) & 1u, abort_word)) break;
-        tc_fence_after();
-        const std::uint64_t dp = umma_desc_sw128(p_smem), dv = umma_desc_sw128(v_smem(s));
+      if (elect_one()) {
+        const std::uint64_t d = (s != 0 ? dk1 : dk0) + (u & 1) * kHalfTile;
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
-          // P: 32 keys = 32 bytes along K inside the swizzle atom (+2); V (MN-major): 32 key rows of 128 bytes (+256).
-          umma_f8(tmem_o, dp + 2u * k4, dv + 256u * k4, idesc_pv, (t | k4) != 0 ? 1u : 0u);
+          umma_i8(tmem_s + static_cast<std::uint32_t>(u & 1) * kSubK, dq + 2u * k4, d + 2u * k4, idesc_qk, 1u);  // onto the pre-fill
         }
-        tc_commit(smem_u32(&s_v_empty[s]));
-        tc_commit(smem_u32(&s_pv_done));
-        TRACE(7);
+        if ((u & 1) != 0 || u + 1 >= n_sub) tc_commit(smem_u32(&s_k_empty[s]));
+        tc_commit(smem_u32(&s_s_full[u & 1]));
       }
+      __syncwarp();
+      return true;
+    };
+    bool ok = wait_bar(smem_u32(&s_q_full), 0, abort_word) && wait_bar(smem_u32(&s_s_ready), 0, abort_word);
+    ok = !__any_sync(0xffffffffu, !ok);
+    tc_fence_after();
+    ok = ok && issue_qk(0);
+    if (ok && n_sub > 1) ok = issue_qk(1);
+    for (int u = 0; ok && u < n_sub; ++u) {
+      const int s = (u >> 1) % kKvStages;
+      bool got = true;
+      if ((u & 1) == 0) got = wait_bar(smem_u32(&s_v_full[s]), ((u >> 1) / kKvStages) & 1u, abort_word);
+      // The softmax warps have consumed S(u) and written P(u).
+      got = got && wait_bar_relaxed<B2_MMA_SLEEP_NS>(smem_u32(&s_p_full[u & 1]), (u >> 1) & 1u, abort_word);
+      if (__any_sync(0xffffffffu, !got)) break;
+      tc_fence_after();
+      TRACE(5);
+      if (elect_one()) {
+#pragma unroll
+        for (int k2 = 0; k2 < 2; ++k2) {
+          // P buffer u % 2: bytes [64 (u % 2), +64) of each row, 32 keys = 32 bytes along K inside the swizzle atom (+2);
+          // V (MN-major): 32 key rows of 128 bytes (+256 per step), second half of the tile at +kHalfTile.
+          umma_f8(tmem_o, dp + 2u * (2 * (u & 1) + k2), (s != 0 ? dv1 : dv0) + (u & 1) * kHalfTile + 256u * k2, idesc_pv,
+                  (u | k2) != 0 ? 1u : 0u);
+        }
+        if ((u & 1) != 0 || u + 1 >= n_sub) tc_commit(smem_u32(&s_v_empty[s]));
+        tc_commit(smem_u32(&s_pv_done[u & 1]));
+      }
+      __syncwarp();
+      TRACE(6);
+      if (u + 2 < n_sub && !issue_qk(u + 2)) break;
+      TRACE(7);
     }
-    __syncwarp();
   } else {
-    // Softmax: 8 warps, two threads per query row. Warp w may touch TMEM lanes [32 (w % 4), +32); warps 2..5 take keys
-    // 0..63 of a tile (one K scale block), warps 6..9 keys 64..127. The two threads of a row exchange their block
-    // maxima through shared memory once per tile (and their denominators once at the end).
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    // Softmax: 4 warps, one thread per query row; warp w may touch TMEM lanes [32 (w % 4), +32). One pass per sub-tile:
+    // P = exp2(S * c - m) against the reference maximum m carried over from the earlier sub-tiles, while the sub-tile's
+    // own maximum is tracked on the side. m is kept kHeadroom binades above what the largest P would need, so scores
+    // above everything seen so far still fit; when they do not (P would pass p_range), the warp raises m for those
+    // rows, rescales O and the denominator and runs the pass again on the same S. Sub-tile 0 has no carried maximum
+    // and reads its scores once more, for the maximum only.
+    const int quarter = warp & 3;
     const int r_local = quarter * 32 + lane;  // row of the tile == TMEM lane
     const std::uint32_t lane_off = static_cast<std::uint32_t>(quarter * 32) << 16;
-    const std::uint32_t col_off = static_cast<std::uint32_t>(half * 64);
     const std::int64_t sc_base = static_cast<std::int64_t>(b) * a.heads + h;
     const float qs = a.q_scale[sc_base * a.q_blocks + (q0 + quarter * 32) / 32] * a.scale_log2;
+    const float* k_scale = a.k_scale + sc_base * a.k_blocks;
 #ifdef B2_ATTN_TRACE
-    const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 2 && lane == 0;
+    const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == B2_TRACE_WARP && lane == 0;
 #endif
-    float m_run = -5000000.0f, d_run = 0.f;
-    // The score accumulator is pre-filled with the integer 0x4B400000 before every Q·K^T, so a column read back holds the
-    // bit pattern of the fp32 number 12582912 + S (exact, |S| < 2^22): the scores arrive as floats with no conversion,
-    // their order is the integers' order, and the constant folds into the addend of the exponent's FMA.
-    const auto prefill_s = [&](int cc) { tmem_fill_32x32(tmem_s + lane_off + col_off + cc * 32, 0x4B400000u); };
-    prefill_s(0);
-    prefill_s(1);
+    constexpr float kNone = -5000000.0f;  // "no score": below every scaled score
+    float m_run = kNone, d_run = 0.f;
+    float o_scale = 1.0f;  // factor O still has to be multiplied by (applied once the P·V before it have landed)
+    // Bounded wait with one answer for the whole warp (the TMEM accesses that follow are warp-wide).
+    const auto warp_wait = [&](std::uint32_t bar, std::uint32_t parity) {
+      const bool ok = wait_bar(bar, parity, abort_word);
+      return !__any_sync(0xffffffffu, !ok);
+    };
+    // O (this thread's row, 128 channels) times `factor`, in place.
+    const auto rescale_o = [&](float factor) {
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        std::uint32_t r[32];
+        tmem_ld_32x32(tmem_o + lane_off + cc * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+        tmem_st_32x32(tmem_o + lane_off + cc * 32, r);
+      }
+      tmem_st_wait();
+    };
+    // Both score buffers start out pre-filled (see softmax_pass); the MMA warp waits for that once.
+    const auto prefill_s = [&](std::uint32_t cols) {
+      tmem_fill_32x32(cols, 0x4B400000u);
+      tmem_fill_32x32(cols + 32, 0x4B400000u);
+    };
+    prefill_s(tmem_s + lane_off);
+    prefill_s(tmem_s + lane_off + kSubK);
     tmem_st_wait();
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(smem_u32(&s_s_free));
-    // A warp whose bounded wait expired keeps walking the loop so that it still meets the others at the named
-    // barriers, but touches nothing.
-    bool dead = false;
-    for (int t = 0; t < n_tiles; ++t) {
-      if (!dead && !wait_bar(smem_u32(&s_s_full), t & 1u, abort_word)) dead = true;
+    if (lane == 0) mbar_arrive(smem_u32(&s_s_ready));
+    std::uint8_t* prow = p_generic + r_local * 128;
+    bool dead = false;  // a bounded wait expired: leave without touching anything else
+    for (int u = 0; u < n_sub; ++u) {
+      const std::uint32_t s_cols = tmem_s + lane_off + static_cast<std::uint32_t>(u & 1) * kSubK;
+      TRACE(4);
+      // S(u) computed; P·V(u - 2), which read this sub-tile's P buffer, landed.
+      if (!warp_wait(smem_u32(&s_s_full[u & 1]), (u >> 1) & 1u) ||
+          (u >= 2 && !warp_wait(smem_u32(&s_pv_done[u & 1]), ((u >> 1) - 1) & 1u))) {
+        dead = true;
+        break;
+      }
       tc_fence_after();
       TRACE(0);
-      const int kblock = 2 * t + half;
-      const float c = (!dead && kblock < a.k_blocks) ? qs * a.k_scale[sc_base * a.k_blocks + kblock] : 0.f;
-      const int valid = min(64, kv_len - t * kTileK - half * 64);  // valid keys of this thread's block (may be <= 0)
-      const bool full_tile = valid == 64;
-      // Pass 1: block maximum of the biased scores (three-input float max: monotone in S).
-      float bmax = 0.f;  // below every biased score (those are >= 2^22)
-      if (!dead) {
+      const float c = (u < a.k_blocks) ? qs * k_scale[u] : 0.f;
+      const int valid = min(kSubK, kv_len - u * kSubK);  // valid keys of this sub-tile (>= 1)
+      if (u == 0) {
+        float bmax = 0.f;  // below every biased score (those are >= 2^22)
 #pragma unroll 1
         for (int cc = 0; cc < 2; ++cc) {
           std::uint32_t r[32];
-          tmem_ld_32x32(tmem_s + lane_off + col_off + cc * 32, r);
+          tmem_ld_32x32(s_cols + cc * 32, r);
           tmem_ld_wait();
-          if (full_tile) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) bmax = fmax3(bmax, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) bmax = (cc * 32 + i < valid) ? fmaxf(bmax, __uint_as_float(r[i])) : bmax;
-          }
+          for (int i = 0; i < 32; ++i) bmax = fmaxf(bmax, (cc * 32 + i < valid) ? __uint_as_float(r[i]) : 0.f);
         }
+        m_run = (bmax - 12582912.0f) * c - (a.p_offset - kHeadroom);
       }
-      const float mx_own = bmax != 0.f ? (bmax - 12582912.0f) * c : -5000000.0f;
-      TRACE(1);
-      s_mx[t & 1][half][r_local] = mx_own;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      const float mx = fmaxf(mx_own, s_mx[t & 1][half ^ 1][r_local]);
-      // The reference maximum m_run may lag the true running maximum by up to kLazy (in log2 units): P is scaled so that
-      // its largest value is 2^(p_offset - kLazy) against an exact maximum, hence at most 2^p_offset <= p_range against
-      // a lagging one. O and the denominator are rescaled only when some row of the warp exceeds the lag. Both threads
-      // of a row see the same values, so both warps take the same decision.
-      const float m_tile = mx - (a.p_offset - kLazy);
-      const bool grow = __any_sync(0xffffffffu, m_tile > m_run + kLazy);
-      float alpha = 1.0f;
-      if (grow) {
-        const float m_new = fmaxf(m_run, m_tile);
-        alpha = ex2(m_run - m_new);
-        m_run = m_new;
-      }
-      // PV(t-1) must have landed before O is touched or the P tile reused.
-      if (t > 0 && !dead) {
-        if (!wait_bar(smem_u32(&s_pv_done), (t - 1) & 1u, abort_word)) dead = true;
-        tc_fence_after();
-        if (grow && !dead) {
-#pragma unroll 1
-          for (int cc = 0; cc < 2; ++cc) {
-            std::uint32_t r[32];
-            tmem_ld_32x32(tmem_o + lane_off + col_off + cc * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_off + col_off + cc * 32, r);
-          }
-          tmem_st_wait();
+      bool o_idle = u < 1;  // every P·V up to u - 1 has to land before O is rescaled
+      float mx, d_tile;
+      for (;;) {
+        const float bias = -fmaf(12582912.0f, c, m_run);
+        float bmax;
+        if (valid == kSubK) {
+          softmax_pass<true>(s_cols, c, bias, valid, prow, 4 * (u & 1), r_local & 7, bmax, d_tile);
+        } else {
+          softmax_pass<false>(s_cols, c, bias, valid, prow, 4 * (u & 1), r_local & 7, bmax, d_tile);
         }
+        TRACE(1);
+        mx = bmax != 0.f ? (bmax - 12582912.0f) * c : kNone;
+        const bool over = mx - m_run > a.p_offset;  // some P of this row passed p_range: the pass has to run again
+        const bool any_over = __any_sync(0xffffffffu, over);
+        if (!any_over && !__any_sync(0xffffffffu, o_scale != 1.0f)) break;
+        // O is about to be rescaled: every P·V issued so far (the last one is u - 1) has to have landed.
+        if (!o_idle) {
+          o_idle = true;
+          if (!warp_wait(smem_u32(&s_pv_done[(u - 1) & 1]), ((u - 1) >> 1) & 1u)) {
+            dead = true;
+            break;
+          }
+          tc_fence_after();
+        }
+        float alpha = o_scale;
+        o_scale = 1.0f;
+        if (over) {
+          const float m_new = mx - (a.p_offset - kHeadroom);
+          const float grow = ex2(m_run - m_new);
+          m_run = m_new;
+          d_run *= grow;
+          alpha *= grow;
+        }
+        if (u > 0) rescale_o(alpha);
+        if (!any_over) break;
       }
-      d_run *= alpha;
+      if (dead) break;
+      d_run += d_tile;
       TRACE(2);
-      if (dead) continue;
-      // Pass 2: P = exp2(S * c - m) = exp2((12582912 + S) * c + bias) with bias = -(12582912 * c + m): one FMA and one
-      // ex2 per score. Denominator from the unrounded P; e4m3 P into the swizzled tile (row = 128 bytes, 16-byte chunk j
-      // of row r stored at chunk j ^ (r % 8)).
-      std::uint8_t* prow = p_generic + r_local * 128;
-      const float bias = -fmaf(12582912.0f, c, m_run);
-      float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        std::uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_off + col_off + cc * 32, r);
-        tmem_ld_wait();
-        // These columns are consumed: refill them with the bias; after the second chunk S goes back to the MMA warp, so
-        // Q·K^T of the next tile runs under the exponentials of this chunk.
-        prefill_s(cc);
-        if (cc == 1) {
-          tmem_st_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&s_s_free));
-        }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {  // 16 keys = one 16-byte chunk of the P row at a time
-          float pv[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            // The exponentials are split between the special-function unit and the FMA pipe, which would otherwise idle.
-            const float e = fmaf(__uint_as_float(r[16 * j + i]), c, bias);
-            pv[i] = ((B2_EXP_POLY_MASK >> (i & 3)) & 1) ? ex2_poly(e) : ex2(e);
-          }
-          if (!full_tile) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) pv[i] = (cc * 32 + 16 * j + i < valid) ? pv[i] : 0.f;
-          }
-#pragma unroll
-          for (int i = 0; i < 16; i += 4) {
-            d0 += pv[i];
-            d1 += pv[i + 1];
-            d2 += pv[i + 2];
-            d3 += pv[i + 3];
-          }
-          const int chunk = (half * 4 + cc * 2 + j) ^ (r_local & 7);
-          *reinterpret_cast<uint4*>(prow + chunk * 16) =
-              make_uint4(e4m3x4(pv[0], pv[1], pv[2], pv[3]), e4m3x4(pv[4], pv[5], pv[6], pv[7]),
-                         e4m3x4(pv[8], pv[9], pv[10], pv[11]), e4m3x4(pv[12], pv[13], pv[14], pv[15]));
-        }
+      // S is consumed (pre-fill it for Q·K^T of sub-tile u + 2) and P written: both go to the MMA warp.
+      if (u + 2 < n_sub) {
+        prefill_s(s_cols);
+        tmem_st_wait();
       }
-      d_run += (d0 + d1) + (d2 + d3);
-      TRACE(3);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_p_full));
-      TRACE(4);
+      if (lane == 0) mbar_arrive(smem_u32(&s_p_full[u & 1]));
+      TRACE(3);
+      // Less than kRaise binades of headroom left: raise the reference for the sub-tiles to come. P·V of this one was
+      // computed against the old reference, so O is rescaled after it lands (at the end of the next pass).
+      if (u + 1 < n_sub && mx - m_run > a.p_offset - kRaise) {
+        const float m_new = mx - (a.p_offset - kHeadroom);
+        const float grow = ex2(m_run - m_new);
+        m_run = m_new;
+        d_run *= grow;
+        o_scale = grow;
+      }
     }
-    // Row denominator = the two threads' sums.
-    s_den[half][r_local] = d_run;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    const float d_row = d_run + s_den[half ^ 1][r_local];
-    if (!dead && wait_bar(smem_u32(&s_pv_done), (n_tiles - 1) & 1u, abort_word)) {
+    if (!dead && warp_wait(smem_u32(&s_pv_done[(n_sub - 1) & 1]), ((n_sub - 1) >> 1) & 1u)) {
       tc_fence_after();
-      const float inv_d = rcp_approx(d_row);
+      const float inv_d = rcp_approx(d_run);
       const int row = q0 + r_local;
-      __nv_bfloat16* orow = a.out + static_cast<std::int64_t>(q_start + row) * a.out_row + h * a.out_head + half * 64;
-      const float* vs = a.v_scale + sc_base * kHeadDim + half * 64;
+      __nv_bfloat16* orow = a.out + static_cast<std::int64_t>(q_start + row) * a.out_row + h * a.out_head;
+      const float* vs = a.v_scale + sc_base * kHeadDim;
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
+      for (int cc = 0; cc < 4; ++cc) {
         std::uint32_t r[32];
-        tmem_ld_32x32(tmem_o + lane_off + col_off + cc * 32, r);
+        tmem_ld_32x32(tmem_o + lane_off + cc * 32, r);
         tmem_ld_wait();
         if (row < qo_len) {
 #pragma unroll

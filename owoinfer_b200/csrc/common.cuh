@@ -91,6 +91,22 @@ __device__ __forceinline__ bool mbar_try_wait(std::uint32_t bar, std::uint32_t p
       : "memory");
   return ok != 0;
 }
+// The same test, letting the hardware keep the thread suspended for up to `hint_ns` while the phase is incomplete (it
+// resumes when the phase completes): a waiting warp then issues next to no instructions.
+#ifndef B2_WAIT_HINT_NS
+#define B2_WAIT_HINT_NS 20000
+#endif
+__device__ __forceinline__ bool mbar_try_wait_hint(std::uint32_t bar, std::uint32_t parity) {
+  std::uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(static_cast<std::uint32_t>(B2_WAIT_HINT_NS))
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: spins at most kSpinLimit polls, also giving up early once another thread of the CTA has raised the
 // abort word. Returns false on give-up (and raises the abort word), so the caller can unwind instead of hanging.
 constexpr std::uint32_t kSpinLimit = 1u << 24;
@@ -243,6 +259,26 @@ __device__ __forceinline__ void tmem_ld_32x32(std::uint32_t taddr, std::uint32_t
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// True in exactly one lane of a converged warp (the others skip the guarded instruction; control flow stays uniform).
+__device__ __forceinline__ bool elect_one() {
+  std::uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+// The same for 16 consecutive columns.
+__device__ __forceinline__ void tmem_ld_32x16(std::uint32_t taddr, std::uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }

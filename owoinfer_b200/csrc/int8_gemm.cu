@@ -67,14 +67,12 @@ __device__ __forceinline__ std::uint64_t global_ns() {
 __device__ __forceinline__ bool wait_bar(std::uint32_t bar, std::uint32_t parity, volatile int* abort_word) {
   if (mbar_try_wait(bar, parity)) return true;
   const std::uint64_t t0 = global_ns();
-  for (std::uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 0u) {
-      if (*abort_word != 0) return false;
-      if (global_ns() - t0 > 1000000000ull) {
-        *abort_word = 1;
-        return false;
-      }
+  for (;;) {
+    if (mbar_try_wait_hint(bar, parity)) return true;
+    if (*abort_word != 0) return false;
+    if (global_ns() - t0 > 1000000000ull) {
+      *abort_word = 1;
+      return false;
     }
   }
 }

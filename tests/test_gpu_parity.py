@@ -395,8 +395,11 @@ def test_attention_prepass_bits_and_output(ops, lens, fused):
     got = bf(u16(out)).reshape(total, heads * 128)
     assert np.isfinite(got).all()
     cos, rel, mxe = metrics(got, bf(want))
-    # Same quantised operands, same algorithm; the GPU uses ex2.approx / rcp.approx and 128-key tiles.
-    assert cos >= 0.9995 and rel <= 0.03, (cos, rel, mxe)
+    # Same quantised operands and statistics. P is rounded to e4m3 (3 mantissa bits) after a shift by a reference
+    # maximum; the oracle shifts by the exact running maximum of each 64-key step, the GPU by a maximum that is only
+    # raised when the headroom runs out, so single P values round differently and the two outputs differ by about the sum
+    # of their own e4m3 errors (~3 % of the output norm on flat random scores, where every key contributes).
+    assert cos >= 0.9993 and rel <= 0.036, (cos, rel, mxe)
     exact = orc.attention_exact(*(normed_h[:, i * heads * 128:(i + 1) * heads * 128].reshape(total, heads, 128) for i in range(3)),
                                 cu, ops.SM_SCALE)
     cos, rel, mxe = metrics(got, exact.reshape(total, -1))
