@@ -31,12 +31,27 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBK = 128;  // bytes == int8 elements per K block: one 128-byte swizzle atom per row
-constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr std::int64_t kMaxK = 131071;
 
 enum class Epi : int { kPlain = 0, kGatedResidual = 1, kSituGlu = 2, kAcc = 3 };
-constexpr int kMiniTable = 4096;  // 2 signs x 16 exponents x 128 mantissas
-constexpr std::uint32_t kMiniExpLo = 117;
+// Producer warp, MMA warp, then the epilogue warps: 8 (two per TMEM lane quarter), or 16 for the SiTU-GLU epilogue, whose
+// table look-ups are latency-bound and want more warps in flight.
+#ifndef B2_EPI_WARPS_GATED
+#define B2_EPI_WARPS_GATED 8
+#endif
+#ifndef B2_EPI_WARPS_PLAIN
+#define B2_EPI_WARPS_PLAIN 8
+#endif
+__host__ __device__ constexpr int epi_warps(Epi e, int bn) {
+  return e == Epi::kSituGlu ? 16 : bn != 256 ? 8 : e == Epi::kGatedResidual ? B2_EPI_WARPS_GATED : e == Epi::kPlain ? B2_EPI_WARPS_PLAIN : 8;
+}
+__host__ __device__ constexpr int threads_of(Epi e, int bn) { return 64 + 32 * epi_warps(e, bn); }
+// Shared-memory slice of the SiTU factor tables: inputs with 2^-26 <= |x| < 2^6 (bf16 exponent field 101..132), where all
+// but a vanishing share of the pre-activations fall. Gate factors: [sign][exponent - 101][mantissa]; hidden factors: the
+// positive half only (25 tanh(h / 25) is odd and every rounding in it is sign-symmetric, so the factor of -h is the
+// factor of h with the sign bit set).
+constexpr std::uint32_t kMiniExpLo = 101;
+constexpr int kMiniGate = 2 * 32 * 128, kMiniHidden = 32 * 128;
 
 struct GemmParams {
   int m, n, k;        // GEMM rows, GEMM columns (2F for SiTU-GLU), reduction length
@@ -104,15 +119,10 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int* 
   *nt = r / rows;
 }
 
-// One SiTU factor of the bf16 value v: from the shared-memory slice when its exponent is inside the slice, else from the
-// full table in global memory (same entries, so the same bits either way).
-__device__ __forceinline__ float situ_factor(const std::uint16_t* mini, const std::uint16_t* full, float v) {
-  const std::uint32_t bits = __float_as_uint(v) >> 16;
-  const std::uint32_t e = ((bits >> 7) & 0xFFu) - kMiniExpLo;
-  std::uint32_t entry;
-  if (e < 16u) entry = mini[((bits >> 15) << 11) | (e << 7) | (bits & 127u)];
-  else entry = __ldg(full + bits);
-  return __uint_as_float(entry << 16);
+// One SiTU factor of the bf16 value with these bits from the full table in global memory (the slow path for a value
+// outside the shared-memory slice; same entries, so the same bits either way).
+__device__ __forceinline__ float situ_factor_full(const std::uint16_t* full, std::uint32_t bits) {
+  return __uint_as_float(static_cast<std::uint32_t>(__ldg(full + bits)) << 16);
 }
 
 // kCtas == 2: a CTA pair shares one 256 x 256 tile; each CTA stages its 128 rows of A and 128 of the 256 rows of B.
@@ -126,7 +136,7 @@ struct Shape {
 };
 
 template <int kBN, Epi kEpi, int kCtas>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_of(kEpi, kBN), 1)
 int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   static_assert(kCtas == 1 || kBN == 256, "CTA pairs run 256 x 256 tiles");
   using S = Shape<kBN, kCtas>;
@@ -138,10 +148,11 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __shared__ __align__(8) std::uint64_t s_full[kStages], s_empty[kStages], s_tmem_full[2], s_tmem_empty[2];
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ __align__(16) float s_vec[8][384];  // per epilogue warp: w_scale, bias, gate of its 128 columns
-  // SiTU-GLU: the slice of the two factor tables for inputs with 2^-10 <= |x| < 2^6 (bf16 exponent field 117..132), where
-  // almost every pre-activation falls: [sign][exponent - 117][mantissa], gate factors then hidden factors.
-  __shared__ std::uint16_t s_tab[kEpi == Epi::kSituGlu ? 2 * kMiniTable : 1];
+  // Per epilogue warp: w_scale, bias, gate of its 128 columns (SiTU-GLU: w_scale of its 32 hidden and 32 gate columns).
+  constexpr int kEpiWarps = epi_warps(kEpi, kBN), kVecFloats = kEpi == Epi::kSituGlu ? 64 : 384;
+  __shared__ __align__(16) float s_vec[kEpiWarps][kVecFloats];
+  // SiTU-GLU: the slices of the two factor tables, gate factors then hidden factors.
+  __shared__ std::uint16_t s_tab[kEpi == Epi::kSituGlu ? kMiniGate + kMiniHidden : 1];
 
   const int warp = static_cast<int>(threadIdx.x) >> 5, lane = static_cast<int>(threadIdx.x) & 31;
   const std::uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -155,7 +166,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&s_tmem_full[i]), 1);
-      mbar_init(smem_u32(&s_tmem_empty[i]), 8 * kCtas);
+      mbar_init(smem_u32(&s_tmem_empty[i]), kEpiWarps * kCtas);
     }
     s_abort = 0;
     fence_mbar_init();
@@ -172,10 +183,11 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   }
   if constexpr (kEpi == Epi::kSituGlu) {
-    for (int i = threadIdx.x; i < 2 * kMiniTable; i += blockDim.x) {
-      const int j = i & (kMiniTable - 1);
-      const std::uint32_t bits = (static_cast<std::uint32_t>(j >> 11) << 15) | ((((j >> 7) & 15u) + kMiniExpLo) << 7) | (j & 127u);
-      s_tab[i] = __ldg((i < kMiniTable ? p.t_gate : p.t_hidden) + bits);
+    for (int i = threadIdx.x; i < kMiniGate + kMiniHidden; i += blockDim.x) {
+      const bool gate = i < kMiniGate;
+      const std::uint32_t j = gate ? i : i - kMiniGate;  // [sign (gate only)][exponent][mantissa]
+      const std::uint32_t bits = ((j >> 12) << 15) | ((((j >> 7) & 31u) + kMiniExpLo) << 7) | (j & 127u);
+      s_tab[i] = __ldg((gate ? p.t_gate : p.t_hidden) + bits);
     }
   }
   tc_fence_before();
@@ -226,48 +238,58 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    // The whole warp of the issuing CTA walks the loop (uniform control flow, so descriptors and loop state stay in
+    // uniform registers; every lane takes the waits); one elected lane issues the MMAs and commits.
+    if (rank == 0) {
       constexpr std::uint32_t idesc = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, kBM * kCtas, kBN);
-      std::uint32_t it = 0, tile_it = 0;
-      for (int tile = tile0; tile < total_tiles && *abort_word == 0; tile += tile_step, ++tile_it) {
+      constexpr std::uint32_t kStageUnits = S::kStageBytes >> 4;  // descriptor address units are 16 bytes
+      const std::uint64_t da0 = umma_desc_sw128(a_addr(0)), db0 = umma_desc_sw128(b_addr(0));
+      std::uint32_t s = 0, ph = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = tile0; ok && tile < total_tiles; tile += tile_step, ++tile_it) {
         const std::uint32_t acc = tile_it & 1u, acc_ph = (tile_it >> 1) & 1u;
-        if (!wait_bar(smem_u32(&s_tmem_empty[acc]), acc_ph ^ 1u, abort_word)) break;
+        ok = wait_bar(smem_u32(&s_tmem_empty[acc]), acc_ph ^ 1u, abort_word);
+        ok = !__any_sync(0xffffffffu, !ok);
+        if (!ok) break;
         tc_fence_after();
         const std::uint32_t d_tmem = tmem_base + acc * kBN;
-        bool ok = true;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = static_cast<int>(it % kStages);
-          const std::uint32_t ph = (it / kStages) & 1u;
-          if (!wait_bar(smem_u32(&s_full[s]), ph, abort_word)) {
-            ok = false;
-            break;
-          }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = wait_bar(smem_u32(&s_full[s]), ph, abort_word);
+          ok = !__any_sync(0xffffffffu, !ok);
+          if (!ok) break;
           tc_fence_after();
-          const std::uint64_t da = umma_desc_sw128(a_addr(s)), db = umma_desc_sw128(b_addr(s));
+          if (elect_one()) {
+            const std::uint64_t da = da0 + s * kStageUnits, db = db0 + s * kStageUnits;
 #pragma unroll
-          for (int k4 = 0; k4 < kBK / 32; ++k4) {
-            // 32 bytes further along K inside the swizzle atom: +2 in the descriptor's 16-byte address units.
-            if constexpr (kCtas == 2) {
-              umma_i8_pair(d_tmem, da + static_cast<std::uint64_t>(2 * k4), db + static_cast<std::uint64_t>(2 * k4), idesc,
-                           (kb | k4) != 0 ? 1u : 0u);
-            } else {
-              umma_i8(d_tmem, da + static_cast<std::uint64_t>(2 * k4), db + static_cast<std::uint64_t>(2 * k4), idesc,
-                      (kb | k4) != 0 ? 1u : 0u);
+            for (int k4 = 0; k4 < kBK / 32; ++k4) {
+              // 32 bytes further along K inside the swizzle atom: +2 in the descriptor's 16-byte address units.
+              if constexpr (kCtas == 2) {
+                umma_i8_pair(d_tmem, da + static_cast<std::uint64_t>(2 * k4), db + static_cast<std::uint64_t>(2 * k4), idesc,
+                             (kb | k4) != 0 ? 1u : 0u);
+              } else {
+                umma_i8(d_tmem, da + static_cast<std::uint64_t>(2 * k4), db + static_cast<std::uint64_t>(2 * k4), idesc,
+                        (kb | k4) != 0 ? 1u : 0u);
+              }
             }
+            if constexpr (kCtas == 2) tc_commit_pair(smem_u32(&s_empty[s]), 3);
+            else tc_commit(smem_u32(&s_empty[s]));
           }
-          if constexpr (kCtas == 2) tc_commit_pair(smem_u32(&s_empty[s]), 3);
-          else tc_commit(smem_u32(&s_empty[s]));
+          __syncwarp();
+          if (++s == kStages) s = 0, ph ^= 1u;
         }
         if (!ok) break;
-        if constexpr (kCtas == 2) tc_commit_pair(smem_u32(&s_tmem_full[acc]), 3);
-        else tc_commit(smem_u32(&s_tmem_full[acc]));
+        if (elect_one()) {
+          if constexpr (kCtas == 2) tc_commit_pair(smem_u32(&s_tmem_full[acc]), 3);
+          else tc_commit(smem_u32(&s_tmem_full[acc]));
+        }
+        __syncwarp();
       }
     }
     __syncwarp();
   } else {
     // Epilogue: 8 warps. Warp w may touch TMEM lanes [32 (w % 4), 32 (w % 4) + 32); warps 2..5 take the first half of the
     // tile's columns, warps 6..9 the second half (SiTU-GLU: output columns, each needing its hidden and gate accumulator).
-    const int quarter = warp & 3, col_half = (warp - 2) >> 2;
+    const int quarter = warp & 3, col_half = (warp - 2) >> 2;  // SiTU-GLU: one of four 32-column parts
     std::uint32_t tile_it = 0;
     for (int tile = tile0; tile < total_tiles; tile += tile_step, ++tile_it) {
       int mt, nt;
@@ -278,13 +300,13 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       float* vec = s_vec[warp - 2];
       __syncwarp();
       {
-        constexpr int kHalfCols = (kEpi == Epi::kSituGlu) ? 64 : kBN / 2;
-        for (int j = lane * 4; j < 128; j += 128) {
+        constexpr int kHalfCols = kBN / (kEpiWarps / 4);  // columns of one warp's part of the tile
+        for (int j = lane * 4; j < (kEpi == Epi::kSituGlu ? 64 : 128); j += 128) {
           int col;
           bool ok;
           if constexpr (kEpi == Epi::kSituGlu) {
-            const int oc = nt * 128 + col_half * 64 + (j & 63);   // output column; j < 64 hidden, j >= 64 gate
-            col = (j < 64 ? 0 : p.half) + oc;
+            const int oc = nt * 128 + col_half * 32 + (j & 31);   // output column; j < 32 hidden, j >= 32 gate
+            col = (j < 32 ? 0 : p.half) + oc;
             ok = oc < p.half;
           } else {
             col = nt * kBN + col_half * kHalfCols + j;
@@ -309,8 +331,10 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
           *reinterpret_cast<float4*>(vec + j) = w;
-          *reinterpret_cast<float4*>(vec + 128 + j) = b;
-          *reinterpret_cast<float4*>(vec + 256 + j) = g;
+          if constexpr (kEpi != Epi::kSituGlu) {
+            *reinterpret_cast<float4*>(vec + 128 + j) = b;
+            *reinterpret_cast<float4*>(vec + 256 + j) = g;
+          }
         }
       }
       __syncwarp();
@@ -323,8 +347,8 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
       if constexpr (kEpi == Epi::kSituGlu) {
         const int col0 = nt * 128;
-#pragma unroll 1
-        for (int c0 = col_half * 64; c0 < col_half * 64 + 64; c0 += 32) {
+        {
+          const int c0 = col_half * 32;
           std::uint32_t rh[32], rg[32];
           tmem_ld_32x32(t_row + c0, rh);
           tmem_ld_32x32(t_row + 128 + c0, rg);
@@ -335,15 +359,33 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int v = 0; v < 8; ++v) {
               const int col = col0 + c0 + 4 * v;
               if (col < p.half) {
-                const float4 wh = *reinterpret_cast<const float4*>(vec + (c0 - col_half * 64) + 4 * v);
-                const float4 wg = *reinterpret_cast<const float4*>(vec + 64 + (c0 - col_half * 64) + 4 * v);
+                const float4 wh = *reinterpret_cast<const float4*>(vec + 4 * v);
+                const float4 wg = *reinterpret_cast<const float4*>(vec + 32 + 4 * v);
                 const float whs[4] = {wh.x, wh.y, wh.z, wh.w}, wgs[4] = {wg.x, wg.y, wg.z, wg.w};
+                // Both pre-activations of an output are rounded to bf16 by one packed conversion: hidden bits in the low
+                // half, gate bits in the high half. One subtraction rebases both exponents onto the shared-memory slice
+                // of the tables; the look-up runs unconditionally (its index is masked into the slice) and the rare
+                // output with a value outside the slice is redone from the full tables afterwards. (A borrow out of the
+                // low half only happens when that half is outside the slice, which sends both halves to the redo.)
                 float o[4];
+                std::uint32_t both[4], outside = 0u;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                  const float h = rbf(fmul(fmul(__int2float_rn(static_cast<int>(rh[4 * v + i])), xs), whs[i]));
-                  const float g = rbf(fmul(fmul(__int2float_rn(static_cast<int>(rg[4 * v + i])), xs), wgs[i]));
-                  o[i] = fmul(situ_factor(s_tab, p.t_gate, g), situ_factor(s_tab + kMiniTable, p.t_hidden, h));
+                  const float h = fmul(fmul(__int2float_rn(static_cast<int>(rh[4 * v + i])), xs), whs[i]);
+                  const float g = fmul(fmul(__int2float_rn(static_cast<int>(rg[4 * v + i])), xs), wgs[i]);
+                  both[i] = pack2(h, g);
+                  const std::uint32_t u = both[i] - ((kMiniExpLo << 7) * 0x10001u);
+                  outside |= u;
+                  const std::uint32_t ih = u & 0xFFFu;
+                  const std::uint32_t ig = ((u >> 16) & 0xFFFu) + ((u >> 19) & 0x1000u);
+                  const std::uint32_t hb = static_cast<std::uint32_t>(s_tab[kMiniGate + ih]) | (both[i] & 0x8000u);
+                  o[i] = fmul(__uint_as_float(static_cast<std::uint32_t>(s_tab[ig]) << 16), __uint_as_float(hb << 16));
+                }
+                if ((outside & 0x70007000u) != 0u) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    o[i] = fmul(situ_factor_full(p.t_gate, both[i] >> 16), situ_factor_full(p.t_hidden, both[i] & 0xFFFFu));
+                  }
                 }
                 *reinterpret_cast<uint2*>(orow + col) = make_uint2(pack2(o[0], o[1]), pack2(o[2], o[3]));
               }
@@ -352,7 +394,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
       } else {
         const int col0 = nt * kBN;
-        constexpr int kHalfCols = kBN / 2;
+        constexpr int kHalfCols = kBN / (kEpiWarps / 4);
 #pragma unroll 1
         for (int c0 = col_half * kHalfCols; c0 < (col_half + 1) * kHalfCols; c0 += 64) {
           std::uint32_t r[64];
@@ -577,7 +619,7 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
   if constexpr (kCtas == 2) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * std::min(total, sm_count() / 2)));
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(threads_of(kEpi, kBN));
     cfg.dynamicSmemBytes = S::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr{};
@@ -588,7 +630,7 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
     return check_launch(op);
   } else {
     const int grid = std::min(total, sm_count());
-    kernel<<<grid, kThreads, S::kSmemBytes, stream>>>(map_a, map_b, p);
+    kernel<<<grid, threads_of(kEpi, kBN), S::kSmemBytes, stream>>>(map_a, map_b, p);
     return check_launch(op);
   }
 }

@@ -70,8 +70,7 @@ def exchange_tokens_to_heads(qkv_local: torch.Tensor, local_lens, heads: int, gr
     """All-to-all #1. qkv_local: [sum(local_lens), 3 * heads * 128] (this rank's tokens of every sequence, all heads).
     Returns one tensor per sequence of shape [world * local_len, 3, heads / world, 128]: the FULL sequence, q / k / v of
     this rank's heads (tokens in sequence order: rank 0's slice, rank 1's slice, ...)."""
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
     hp = heads // world
     out, start = [], 0
     for c in local_lens:
@@ -84,14 +83,13 @@ def exchange_tokens_to_heads(qkv_local: torch.Tensor, local_lens, heads: int, gr
             recv = send
         out.append(recv.view(world * c, 3, hp, 128))
         start += c
-    del rank
     return out
 
 
 def exchange_heads_to_tokens(attn_full, local_lens, heads: int, group=None) -> torch.Tensor:
     """All-to-all #2. attn_full: per sequence [world * local_len, heads / world, 128] (full sequence, this rank's heads).
     Returns [sum(local_lens), heads * 128]: this rank's tokens of every sequence, all heads."""
-    world = dist.get_world_size(group)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
     hp = heads // world
     parts = []
     for o, c in zip(attn_full, local_lens):
