@@ -387,7 +387,8 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     o[i] = fmul(situ_factor_full(p.t_gate, both[i] >> 16), situ_factor_full(p.t_hidden, both[i] & 0xFFFFu));
                   }
                 }
-                *reinterpret_cast<uint2*>(orow + col) = make_uint2(pack2(o[0], o[1]), pack2(o[2], o[3]));
+                // Streaming store: the output (4 x the weight's size) must not push the weight out of L2.
+                __stcs(reinterpret_cast<uint2*>(orow + col), make_uint2(pack2(o[0], o[1]), pack2(o[2], o[3])));
               }
             }
           }
@@ -442,8 +443,9 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                 for (int i = 0; i < 8; ++i) y[i] = fadd(res[i], rbf(fmul(rbf(y[i]), gate[i])));
               }
-              *reinterpret_cast<uint4*>(orow + col) =
-                  make_uint4(pack2(y[0], y[1]), pack2(y[2], y[3]), pack2(y[4], y[5]), pack2(y[6], y[7]));
+              const uint4 packed = make_uint4(pack2(y[0], y[1]), pack2(y[2], y[3]), pack2(y[4], y[5]), pack2(y[6], y[7]));
+              if constexpr (kEpi == Epi::kPlain) __stcs(reinterpret_cast<uint4*>(orow + col), packed);  // streaming, as above
+              else *reinterpret_cast<uint4*>(orow + col) = packed;
             }
           }
         }
@@ -614,8 +616,17 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
   if constexpr (kEpi == Epi::kSituGlu) p.n_tiles = (p.half + 127) / 128;
   else p.n_tiles = (p.n + kBN - 1) / kBN;
   const int total = p.m_tiles * p.n_tiles;
-  // Tiles in flight at once / N tiles = M tiles that fit one wave.
-  p.band_m = std::max(1, (sm_count() / kCtas) / std::max(1, p.n_tiles));
+  // M tiles per band: what one wave covers across all N tiles. A weight too large to stay in L2 beside the activations
+  // (above 32 MB) instead streams past a band of activation rows held to a fifth of L2 (band_m x tile rows x K bytes):
+  // it is then read from HBM once per band rather than once per M tile.
+  {
+    p.band_m = std::max(1, (sm_count() / kCtas) / std::max(1, p.n_tiles));
+    const std::int64_t a_tile_bytes = static_cast<std::int64_t>(kBM * kCtas) * p.k;
+    if (static_cast<std::int64_t>(p.n) * p.k > (32 << 20)) {
+      const std::int64_t resident = std::min<std::int64_t>(p.m_tiles, (25 << 20) / std::max<std::int64_t>(1, a_tile_bytes));
+      p.band_m = std::max(p.band_m, static_cast<int>(resident));
+    }
+  }
   if constexpr (kCtas == 2) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * std::min(total, sm_count() / 2)));
