@@ -41,6 +41,7 @@ def parse():
     p.add_argument("--ffn", type=int, default=12288)
     p.add_argument("--no-profile", action="store_true", help="skip the per-kernel roofline pass and the CPU baseline")
     p.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own CUDA kernels on this GPU")
+    p.add_argument("--no-graph", action="store_true", help="enqueue the step's kernels directly instead of replaying a CUDA graph")
     return p.parse_args()
 
 
@@ -191,15 +192,16 @@ def reference_kernels_on_this_gpu(torch, ops, keep, x, x0, mod, rope, cu, seq_le
     e1.record()
     torch.cuda.synchronize()
     return {"value": e0.elapsed_time(e1) / n, "unit": "ms", "kind": "reference CUDA kernels built for sm_100a, device-timed",
-            "steps": n, "blocks": len(keep)}
+            "steps": n, "blocks": len(keep), "per_kernel": profile_kernels(ops, torch, L, F, keep[0][0], iters=4, ref=refk)}
 
 
 def gemm_sites(L, F):
     return [("qkv", 3 * D, D, "plain"), ("o", D, D, "gated"), ("up_gate", 2 * F, D, "situ"), ("down", D, F, "gated")]
 
 
-def profile_kernels(ops, torch, L, F, w, iters=8):
-    """Per-kernel CUDA-event timings of one block's kernels on L tokens, each launch timed alone after an L2 flush."""
+def profile_kernels(ops, torch, L, F, w, iters=8, ref=None):
+    """Per-kernel CUDA-event timings of one block's kernels on L tokens, each launch timed alone after an L2 flush.
+    With `ref` (oracle/ref_cuda_lib) the same launches go to the reference's own CUDA kernels instead."""
     dev = "cuda"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     xs = torch.rand(L, device=dev) * 1e-2
@@ -225,25 +227,28 @@ def profile_kernels(ops, torch, L, F, w, iters=8):
         wq, ws = w[name]
         if epi == "plain":
             o = torch.empty((L, n), dtype=torch.bfloat16, device=dev)
-            ms = timed(lambda: ops.int8_gemm(xq, xs, wq, ws, out=o))
+            ms = timed((lambda: ref.int8_gemm(xq, xs, wq, ws, o)) if ref else (lambda: ops.int8_gemm(xq, xs, wq, ws, out=o)))
         elif epi == "gated":
-            ms = timed(lambda: ops.int8_gemm_gated_residual(xq, xs, wq, ws, gate, res))
+            ms = timed((lambda: ref.int8_gemm_gated_residual(xq, xs, wq, ws, gate, res)) if ref
+                       else (lambda: ops.int8_gemm_gated_residual(xq, xs, wq, ws, gate, res)))
         else:
             o = torch.empty((L, n // 2), dtype=torch.bfloat16, device=dev)
-            ms = timed(lambda: ops.int8_gemm_situ_glu(xq, xs, wq, ws, out=o))
+            ms = timed((lambda: ref.int8_gemm_situ_glu(xq, xs, wq, ws, o)) if ref
+                       else (lambda: ops.int8_gemm_situ_glu(xq, xs, wq, ws, out=o)))
         out[name] = {"ms": ms, "tops": 2.0 * L * n * k / ms / 1e9}
         del xq
     x = torch.randn((L, D), device=dev).to(torch.bfloat16)
     q = torch.empty((L, D), dtype=torch.int8, device=dev)
     s = torch.empty(L, dtype=torch.float32, device=dev)
     v = torch.randn(D, device=dev).to(torch.bfloat16)
-    ms = timed(lambda: ops.rms_norm_modulate_rotate_quantize(x, v, v, v, q=q, scale=s))
+    ms = timed((lambda: ref.rms_norm_modulate_rotate_quantize(x, v, v, v, q, s)) if ref
+               else (lambda: ops.rms_norm_modulate_rotate_quantize(x, v, v, v, q=q, scale=s)))
     out["norm_rotate_quantize"] = {"ms": ms, "gbs": 3.0 * L * D / ms / 1e6}
-    ms = timed(lambda: ops.rotate_quantize(x, q=q, scale=s))
+    ms = timed((lambda: ref.rotate_quantize(x, q, s)) if ref else (lambda: ops.rotate_quantize(x, q=q, scale=s)))
     out["rotate_quantize"] = {"ms": ms, "gbs": 3.0 * L * D / ms / 1e6}
     xf = torch.randn((L, F), device=dev).to(torch.bfloat16)
     qf = torch.empty((L, F), dtype=torch.int8, device=dev)
-    ms = timed(lambda: ops.rotate_quantize(xf, q=qf, scale=s))
+    ms = timed((lambda: ref.rotate_quantize(xf, qf, s)) if ref else (lambda: ops.rotate_quantize(xf, q=qf, scale=s)))
     out["rotate_quantize_ffn"] = {"ms": ms, "gbs": 3.0 * L * F / ms / 1e6}
     del xf, qf
     # 8-bit attention of the step's sequences (pre-pass with fused QK-norm + RoPE, then the attention kernel).
@@ -255,8 +260,13 @@ def profile_kernels(ops, torch, L, F, w, iters=8):
     cu = torch.tensor([i * sl for i in range(seqs + 1)], dtype=torch.int32, device=dev)
     rope = ops.moss_rope_table(64, 64, sl - 4096).repeat(seqs, 1).contiguous() if sl >= 4096 else ops.moss_rope_table(1, 1, sl - 1).repeat(seqs, 1).contiguous()
     qn = torch.ones(128, device=dev).to(torch.bfloat16)
-    _, wsa = ops.attention_q8(*views, o, cu, cu, sl, ops.SM_SCALE, norm_rope=(qn, qn, rope))
-    ms = timed(lambda: ops.attention_q8(*views, o, cu, cu, sl, ops.SM_SCALE, workspace=wsa, norm_rope=(qn, qn, rope)))
+    if ref:
+        o2 = o.view(L, D)
+        wsa = torch.empty(max(256, ref.attention_workspace_bytes(L, seqs, sl, HEADS)), dtype=torch.uint8, device=dev)
+        ms = timed(lambda: ref.attention_q8(qkv, HEADS, o2, cu, sl, ops.SM_SCALE, wsa, (qn, qn, rope)))
+    else:
+        _, wsa = ops.attention_q8(*views, o, cu, cu, sl, ops.SM_SCALE, norm_rope=(qn, qn, rope))
+        ms = timed(lambda: ops.attention_q8(*views, o, cu, cu, sl, ops.SM_SCALE, workspace=wsa, norm_rope=(qn, qn, rope)))
     out["attention_q8"] = {"ms": ms, "tops": 4.0 * seqs * sl * sl * D / ms / 1e9}
     return out
 
@@ -312,10 +322,26 @@ def main():
     bufs = ops.block_buffers(x, mod, rope, ws)
     launches_per_block = 12 if tier == ops.TIER_INT8 else 16
 
+    # The step (504 launches) is captured once into a CUDA graph and replayed, as the reference's engine does with its step
+    # graphs; the first SiTU-GLU call fills its tables outside any capture, hence the eager call first.
+    graph = None
+    if not args.no_graph:
+        ops.dit_step(blocks, bufs, run)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            ops.dit_step(blocks, bufs, run)
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            ops.dit_step(blocks, bufs, run)
+
     def step():
         # x keeps evolving across steps (as across denoising steps); re-seed it so values stay in range.
         x.copy_(x0)
-        ops.dit_step(blocks, bufs, run)
+        run_step()
 
     def barrier():
         if world > 1:
@@ -352,7 +378,7 @@ def main():
         x.copy_(hx, non_blocking=True)
         mod.copy_(hmod, non_blocking=True)
         rope.copy_(hrope, non_blocking=True)
-        ops.dit_step(blocks, bufs, run)
+        run_step()
         hout.copy_(x, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -377,7 +403,8 @@ def main():
             "config": {"workload": args.workload, "blocks": n_blocks, "d": D, "heads": HEADS, "ffn": F,
                        "tokens_per_gpu_step": L, "sequences": [seq_len] * seqs, "tier": ["int8", "w4a4_via_int8", "w4a8"][tier],
                        "attention": "int8_fp8_f32acc", "parallelism": f"image-dp{world}" if scaling == "weak" else "cfg-split2",
-                       "l2": "inputs larger than L2 (block weights stream from HBM every step)"},
+                       "l2": "inputs larger than L2 (block weights stream from HBM every step)",
+                       "launch": "direct" if graph is None else "cuda graph replay"},
             "e2e": {"value": e2e_ms / units, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches_per_block * n_blocks * args.steps, "kernel_status": list(g_stat)}
     if rank == 0:
