@@ -195,6 +195,11 @@ def reference_kernels_on_this_gpu(torch, ops, keep, x, x0, mod, rope, cu, seq_le
             "steps": n, "blocks": len(keep), "per_kernel": profile_kernels(ops, torch, L, F, keep[0][0], iters=4, ref=refk)}
 
 
+# DRAM bytes (read + write, MB) of the four GEMM launches of one block at 16384 tokens, F = 12288, from the ncu capture
+# summarised in profiles/traffic_step1024_one_block.md.
+GEMM_DRAM_MB = {"qkv": 90.1 + 253.2, "o": 160.6 + 47.0, "up_gate": 229.0 + 385.0, "down": 755.7 + 85.5}
+
+
 def gemm_sites(L, F):
     return [("qkv", 3 * D, D, "plain"), ("o", D, D, "gated"), ("up_gate", 2 * F, D, "situ"), ("down", D, F, "gated")]
 
@@ -419,7 +424,11 @@ def main():
             line["roofline"] = {"bound": "tensor", "kernel": "int8_gemm_kernel (4 sites of one block)", "achieved": achieved,
                                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                                 "peak_source": f"2 x bf16 burst of {pk['source']} peaks (no INT8 figure is measured); nominal dense INT8 4500",
-                                "frac_of_nominal": achieved / 4500.0, "traffic": None, "per_kernel": prof}
+                                "frac_of_nominal": achieved / 4500.0,
+                                "traffic": sum(GEMM_DRAM_MB.values()) * 1e6 if (L, F) == (16384, 12288) else None,
+                                "traffic_note": "dram read + write bytes of the four launches at 16384 tokens, F = 12288 (ncu, "
+                                                "profiles/traffic_step1024_one_block.md); algorithmic operand + output bytes: 1610.6e6",
+                                "per_kernel": prof}
             threads = os.cpu_count() or 1
             tb, ta = cpu_sample(F, 256, 1536, threads)
             v = cpu_extrapolate(tb, ta, 256, 1536, seq_len, seqs, n_blocks)
