@@ -290,14 +290,38 @@ struct PrepArgs {
   float* part_amax;
 };
 
+// Packed bf16 pairs: a * b and a + b, each result rounded once to bf16. For bf16 operands these equal the fp32 operation
+// followed by a rounding to bf16 (the fp32 product of two bf16 values is exact; an fp32 sum of two bf16 values is either
+// exact or, when the exponents are more than 16 apart, lands nowhere near a bf16 rounding boundary).
+__device__ __forceinline__ std::uint32_t bmul2(std::uint32_t a, std::uint32_t b) {
+  std::uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ std::uint32_t badd2(std::uint32_t a, std::uint32_t b) {
+  std::uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // RMS-norm + RoPE of one (token, head) row held by 16 lanes x 8 channels (two of the 32 quads of the standalone kernel
 // per lane: its shuffle tree 16, 8, 4, 2, 1 becomes 8, 4, 2, 1 per quad and a final add of the two at lane 0).
-__device__ __forceinline__ void norm_rope_row(const float* x, const float* w, const float* si, const float* co,
-                                              float factor, int lane16, float* y) {
+// x: the row's eight raw bf16 values as four packed pairs; w, co: weight and cosine pairs; si: sine pairs, already negated
+// for the lanes of the low half (lo' = bf16(lo*cos) + bf16(-hi*sin), hi' = bf16(hi*cos) + bf16(lo*sin)). After the first
+// rounding (x * r, with the fp32 r) every step works on bf16 values and is done on packed pairs. y: four packed pairs.
+__device__ __forceinline__ void norm_rope_row(const std::uint32_t (&x)[4], const std::uint32_t (&w)[4],
+                                              const std::uint32_t (&si)[4], const std::uint32_t (&co)[4], float factor,
+                                              std::uint32_t (&y)[4]) {
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(x[i] << 16);
+    f[2 * i + 1] = __uint_as_float(x[i] & 0xFFFF0000u);
+  }
   float quad[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const float* e = x + 4 * h;
+    const float* e = f + 4 * h;
     quad[h] = fadd(fadd(fadd(fmul(e[0], e[0]), fmul(e[1], e[1])), fmul(e[2], e[2])), fmul(e[3], e[3]));
   }
 #pragma unroll
@@ -307,23 +331,11 @@ __device__ __forceinline__ void norm_rope_row(const float* x, const float* w, co
   }
   const float total = __shfl_sync(0xffffffffu, fadd(quad[0], quad[1]), 0, 16);
   const float r = rsqrtf(fadd(fmul(total, factor), 1e-6f));
-  const bool lo_half = lane16 < 8;
 #pragma unroll
-  for (int j = 0; j < 8; j += 2) {
-    // Two channels per packed bf16 conversion.
-    float n0 = fmul(x[j], r), n1 = fmul(x[j + 1], r);
-    rbf2(n0, n1);
-    n0 = fmul(n0, w[j]), n1 = fmul(n1, w[j + 1]);
-    rbf2(n0, n1);
-    const float o0 = __shfl_xor_sync(0xffffffffu, n0, 8, 16), o1 = __shfl_xor_sync(0xffffffffu, n1, 8, 16);
-    // lo' = bf16(lo*cos) + bf16(-hi*sin); hi' = bf16(hi*cos) + bf16(lo*sin): own * cos, then the partner term.
-    float a0 = fmul(n0, co[j]), a1 = fmul(n1, co[j + 1]);
-    float b0 = fmul(lo_half ? -o0 : o0, si[j]), b1 = fmul(lo_half ? -o1 : o1, si[j + 1]);
-    rbf2(a0, a1);
-    rbf2(b0, b1);
-    float s0 = fadd(a0, b0), s1 = fadd(a1, b1);
-    rbf2(s0, s1);
-    y[j] = s0, y[j + 1] = s1;
+  for (int i = 0; i < 4; ++i) {
+    const std::uint32_t n = bmul2(pack_bf2(fmul(f[2 * i], r), fmul(f[2 * i + 1], r)), w[i]);
+    const std::uint32_t o = __shfl_xor_sync(0xffffffffu, n, 8, 16);  // the channel pair 64 further (or back)
+    y[i] = badd2(bmul2(n, co[i]), bmul2(o, si[i]));
   }
 }
 
@@ -344,25 +356,35 @@ __global__ void __launch_bounds__(512, 2) norm_rope_quant_q_kernel(const PrepArg
   const bool valid = t < len;
   const std::int64_t tok = static_cast<std::int64_t>(start) + t;
   const int pair = (lane & 7) * 8;
-  float x[8] = {}, kx[8] = {}, si[8] = {}, co[8] = {}, w[8], qy[8], ky[8];
+  const auto quad = [](uint4 v, std::uint32_t (&o)[4]) { o[0] = v.x, o[1] = v.y, o[2] = v.z, o[3] = v.w; };
+  uint4 xr = make_uint4(0, 0, 0, 0), kr = xr, sr = xr, cr = xr;
   __nv_bfloat16* k_at = p.k + tok * p.k_row + h * p.k_head + lane * 8;
   if (valid) {
-    load8(p.q + tok * p.q_row + h * p.q_head + lane * 8, x);
-    load8(k_at, kx);
-    load8(p.table + tok * p.table_row + pair, si);
-    load8(p.table + tok * p.table_row + 64 + pair, co);
+    xr = *reinterpret_cast<const uint4*>(p.q + tok * p.q_row + h * p.q_head + lane * 8);
+    kr = *reinterpret_cast<const uint4*>(k_at);
+    sr = *reinterpret_cast<const uint4*>(p.table + tok * p.table_row + pair);
+    cr = *reinterpret_cast<const uint4*>(p.table + tok * p.table_row + 64 + pair);
   }
-  load8(p.q_norm + lane * 8, w);
-  norm_rope_row(x, w, si, co, p.norm_factor, lane, qy);
-  load8(p.k_norm + lane * 8, w);
-  norm_rope_row(kx, w, si, co, p.norm_factor, lane, ky);
-  if (valid) {
-    *reinterpret_cast<uint4*>(k_at) =
-        make_uint4(pack_bf2(ky[0], ky[1]), pack_bf2(ky[2], ky[3]), pack_bf2(ky[4], ky[5]), pack_bf2(ky[6], ky[7]));
+  std::uint32_t x[4], kx[4], si[4], co[4], w[4], qy[4], ky[4];
+  quad(xr, x), quad(kr, kx), quad(sr, si), quad(cr, co);
+  if (lane < 8) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) si[i] ^= 0x80008000u;
+  }
+  quad(*reinterpret_cast<const uint4*>(p.q_norm + lane * 8), w);
+  norm_rope_row(x, w, si, co, p.norm_factor, qy);
+  quad(*reinterpret_cast<const uint4*>(p.k_norm + lane * 8), w);
+  norm_rope_row(kx, w, si, co, p.norm_factor, ky);
+  if (valid) *reinterpret_cast<uint4*>(k_at) = make_uint4(ky[0], ky[1], ky[2], ky[3]);
+  float q[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    q[2 * i] = __uint_as_float(qy[i] << 16);
+    q[2 * i + 1] = __uint_as_float(qy[i] & 0xFFFF0000u);
   }
   float qmax = 0.0000001f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) qmax = fmaxf(qmax, fabsf(qy[j]));
+  for (int j = 0; j < 8; ++j) qmax = fmaxf(qmax, fabsf(q[j]));
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) qmax = fmaxf(qmax, __shfl_xor_sync(0xffffffffu, qmax, off));
   __shared__ float s_w[16];
@@ -375,8 +397,7 @@ __global__ void __launch_bounds__(512, 2) norm_rope_quant_q_kernel(const PrepArg
   if (!valid) return;
   const float qs = 127.0f / qmax;
   *reinterpret_cast<uint2*>(p.q_i8 + (tok * p.heads + h) * kHeadDim + lane * 8) =
-      make_uint2(pack_i8x4(qy[0] * qs, qy[1] * qs, qy[2] * qs, qy[3] * qs),
-                 pack_i8x4(qy[4] * qs, qy[5] * qs, qy[6] * qs, qy[7] * qs));
+      make_uint2(pack_i8x4(q[0] * qs, q[1] * qs, q[2] * qs, q[3] * qs), pack_i8x4(q[4] * qs, q[5] * qs, q[6] * qs, q[7] * qs));
 }
 
 // Statistics, one CTA per (512-key chunk, head, sequence): 16 token rows x 16 lanes x 8 channels. Row-thread `row` adds
@@ -481,42 +502,71 @@ __global__ void __launch_bounds__(512) quant_q_kernel(const PrepArgs p) {
       make_uint2(pack_i8x4(x[0] * qs, x[1] * qs, x[2] * qs, x[3] * qs), pack_i8x4(x[4] * qs, x[5] * qs, x[6] * qs, x[7] * qs));
 }
 
-// K and V of one (64 keys, head): K - mean -> int8 with one scale; V * v_recp -> e4m3. CTA = 64 rows x 16 lanes (1024).
-__global__ void __launch_bounds__(1024) quant_kv_kernel(const PrepArgs p) {
+// K and V of one (64 keys, head): K - mean -> int8 with one scale; V * v_recp -> e4m3. CTA = 16 rows x 16 lanes, each
+// thread taking keys row, row + 16, row + 32, row + 48 (eight loads in flight per thread, one block-wide maximum).
+__global__ void __launch_bounds__(256) quant_kv_kernel(const PrepArgs p) {
   const int bx = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int lane = static_cast<int>(threadIdx.x) & 15, row = static_cast<int>(threadIdx.x) >> 4;
   const int start = p.cu[b], len = p.cu[b + 1] - start;
-  const int t = bx * 64 + row;
-  const bool valid = t < len;
-  const std::int64_t tok = static_cast<std::int64_t>(start) + t;
   const std::int64_t stat = (static_cast<std::int64_t>(b) * p.heads + h) * kHeadDim + lane * 8;
-  float x[8] = {}, v[8] = {};
-  if (valid) {
-    load8(p.k + tok * p.k_row + h * p.k_head + lane * 8, x);
-    load8(p.v + tok * p.v_row + h * p.v_head + lane * 8, v);  // in flight across the block reduction
+  uint4 kr[4], vr[4];
+  bool valid[4];
+  std::int64_t tok[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] -= p.k_mean[stat + j];
+  for (int i = 0; i < 4; ++i) {
+    const int t = bx * 64 + row + 16 * i;
+    valid[i] = t < len;
+    tok[i] = static_cast<std::int64_t>(start) + t;
+    kr[i] = vr[i] = make_uint4(0, 0, 0, 0);
+    if (valid[i]) {
+      kr[i] = *reinterpret_cast<const uint4*>(p.k + tok[i] * p.k_row + h * p.k_head + lane * 8);
+      vr[i] = *reinterpret_cast<const uint4*>(p.v + tok[i] * p.v_row + h * p.v_head + lane * 8);
+    }
   }
+  float mean[8], recp[8];
+  *reinterpret_cast<float4*>(mean) = *reinterpret_cast<const float4*>(p.k_mean + stat);
+  *reinterpret_cast<float4*>(mean + 4) = *reinterpret_cast<const float4*>(p.k_mean + stat + 4);
+  *reinterpret_cast<float4*>(recp) = *reinterpret_cast<const float4*>(p.v_recp + stat);
+  *reinterpret_cast<float4*>(recp + 4) = *reinterpret_cast<const float4*>(p.v_recp + stat + 4);
+  float x[4][8];
   float amax = 0.0000001f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
+  for (int i = 0; i < 4; ++i) {
+    const std::uint32_t w[4] = {kr[i].x, kr[i].y, kr[i].z, kr[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      // An absent key contributes 0 (not 0 - mean) to the block maximum.
+      x[i][2 * j] = valid[i] ? __uint_as_float(w[j] << 16) - mean[2 * j] : 0.f;
+      x[i][2 * j + 1] = valid[i] ? __uint_as_float(w[j] & 0xFFFF0000u) - mean[2 * j + 1] : 0.f;
+      amax = fmaxf(amax, fmaxf(fabsf(x[i][2 * j]), fabsf(x[i][2 * j + 1])));
+    }
+  }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  __shared__ float s_w[32];
+  __shared__ float s_w[8];
   if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = amax;
   __syncthreads();
   amax = s_w[0];
 #pragma unroll
-  for (int i = 1; i < 32; ++i) amax = fmaxf(amax, s_w[i]);
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, s_w[i]);
   if (threadIdx.x == 0) p.k_scale[(static_cast<std::int64_t>(b) * p.heads + h) * p.k_blocks + bx] = amax / 127.0f;
-  if (!valid) return;
   const float ks = 127.0f / amax;
-  const std::int64_t o = (tok * p.heads + h) * kHeadDim + lane * 8;
-  *reinterpret_cast<uint2*>(p.k_i8 + o) =
-      make_uint2(pack_i8x4(x[0] * ks, x[1] * ks, x[2] * ks, x[3] * ks), pack_i8x4(x[4] * ks, x[5] * ks, x[6] * ks, x[7] * ks));
 #pragma unroll
-  for (int j = 0; j < 8; ++j) v[j] *= p.v_recp[stat + j];
-  *reinterpret_cast<uint2*>(p.v8 + o) = make_uint2(e4m3x4(v[0], v[1], v[2], v[3]), e4m3x4(v[4], v[5], v[6], v[7]));
+  for (int i = 0; i < 4; ++i) {
+    if (!valid[i]) continue;
+    const std::int64_t o = (tok[i] * p.heads + h) * kHeadDim + lane * 8;
+    *reinterpret_cast<uint2*>(p.k_i8 + o) =
+        make_uint2(pack_i8x4(x[i][0] * ks, x[i][1] * ks, x[i][2] * ks, x[i][3] * ks),
+                   pack_i8x4(x[i][4] * ks, x[i][5] * ks, x[i][6] * ks, x[i][7] * ks));
+    const std::uint32_t w[4] = {vr[i].x, vr[i].y, vr[i].z, vr[i].w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] = __uint_as_float(w[j] << 16) * recp[2 * j];
+      v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u) * recp[2 * j + 1];
+    }
+    *reinterpret_cast<uint2*>(p.v8 + o) = make_uint2(e4m3x4(v[0], v[1], v[2], v[3]), e4m3x4(v[4], v[5], v[6], v[7]));
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -1111,7 +1161,7 @@ int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_v
     quant_q_kernel<<<dim3(l.q_blocks, static_cast<unsigned>(heads), batch), 512, 0, st>>>(pq);
     if (const int rc = check_launch(op)) return rc;
   }
-  quant_kv_kernel<<<dim3(l.k_blocks, static_cast<unsigned>(heads), batch), 1024, 0, st>>>(p);
+  quant_kv_kernel<<<dim3(l.k_blocks, static_cast<unsigned>(heads), batch), 256, 0, st>>>(p);
   if (const int rc = check_launch(op)) return rc;
 
   CUtensorMap map_q, map_k, map_v;

@@ -70,6 +70,22 @@ __device__ __forceinline__ void load16_bf16(const __nv_bfloat16* p, float (&v)[1
     v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
   }
 }
+// Sixteen bf16 values as eight packed pairs (element 2i in the low half of word i).
+__device__ __forceinline__ void load16_packed(const __nv_bfloat16* p, std::uint32_t (&w)[8]) {
+  const uint4 lo = reinterpret_cast<const uint4*>(p)[0], hi = reinterpret_cast<const uint4*>(p)[1];
+  w[0] = lo.x, w[1] = lo.y, w[2] = lo.z, w[3] = lo.w, w[4] = hi.x, w[5] = hi.y, w[6] = hi.z, w[7] = hi.w;
+}
+// Packed bf16 pairs: a * b and a + b, each result rounded once to bf16.
+__device__ __forceinline__ std::uint32_t bmul2(std::uint32_t a, std::uint32_t b) {
+  std::uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ std::uint32_t badd2(std::uint32_t a, std::uint32_t b) {
+  std::uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 __device__ __forceinline__ void store16_bf16(__nv_bfloat16* p, const float (&v)[16]) {
   std::uint32_t w[8];
 #pragma unroll
@@ -184,24 +200,22 @@ __global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
       const int g = half_id + s * halves;
       if (g >= groups) continue;
       const int c0 = g * kGroup + 16 * h;
-      float w[16], sc[16], sh[16];
-      load16_bf16(a.weight + c0, w);
-      load16_bf16(a.mod_scale + c0, sc);
-      load16_bf16(a.mod_shift + c0, sh);
+      // bf16(bf16(bf16(bf16(x*r)*w) * bf16(1+scale)) + shift). After the first rounding every operand is a bf16 value, so
+      // the three remaining steps run on packed pairs (mul.rn / add.rn.bf16x2 round once, exactly as the fp32 operation
+      // followed by a rounding to bf16 does for bf16 operands).
+      std::uint32_t w[8], sc[8], sh[8];
+      load16_packed(a.weight + c0, w);
+      load16_packed(a.mod_scale + c0, sc);
+      load16_packed(a.mod_shift + c0, sh);
 #pragma unroll
       for (int j = 0; j < 16; j += 2) {
-        // bf16(bf16(bf16(bf16(x*r)*w) * bf16(1+scale)) + shift), two elements per packed conversion.
-        float a = fmul(v[s][j], r), b = fmul(v[s][j + 1], r);
-        rbf2(a, b);
-        a = fmul(a, w[j]), b = fmul(b, w[j + 1]);
-        rbf2(a, b);
-        float pa = fadd(1.0f, sc[j]), pb = fadd(1.0f, sc[j + 1]);
-        rbf2(pa, pb);
-        a = fmul(a, pa), b = fmul(b, pb);
-        rbf2(a, b);
-        a = fadd(a, sh[j]), b = fadd(b, sh[j + 1]);
-        rbf2(a, b);
-        v[s][j] = a, v[s][j + 1] = b;
+        const __nv_bfloat162 n0 = __floats2bfloat162_rn(fmul(v[s][j], r), fmul(v[s][j + 1], r));
+        std::uint32_t n = *reinterpret_cast<const std::uint32_t*>(&n0);
+        n = bmul2(n, w[j >> 1]);
+        n = bmul2(n, badd2(0x3F803F80u, sc[j >> 1]));  // 1.0 in both halves
+        n = badd2(n, sh[j >> 1]);
+        v[s][j] = __uint_as_float(n << 16);
+        v[s][j + 1] = __uint_as_float(n & 0xFFFF0000u);
       }
       if (a.y != nullptr) store16_bf16(a.y + row * a.ldy + c0, v[s]);
     }
