@@ -11,11 +11,16 @@
 //                q = clamp(rne(bf16(x_rot / s)), -7, 7), two per byte, even column in the low nibble
 //   norm         r = rsqrtf(mean(x^2) + 1e-6) with the mean summed in torch's reduce order for an [m, k] input;
 //                y = bf16(bf16(bf16(bf16(x*r)*w) * bf16(1+scale)) + shift)
+// The rotation first runs without its four factors 0.5 (results 16 x the reference's, bit for bit, while nothing
+// overflows; the power of two is folded into the quantisation multiplier); a row whose scaled maximum is not a finite
+// number below 2^126 is read again and rotated with the factors in place, so overflow, inf and NaN rows follow the
+// reference exactly.
 // The division x_rot / s of two bf16 values is computed as x_rot * (1/s): the exact quotient of two 8-bit significands
 // is never within 2^-17 (relative) of a bf16 rounding boundary, so the bf16 rounding of the product equals the
 // bf16 rounding of the correctly rounded fp32 quotient; infinities, NaN and zeros propagate identically.
 #include <algorithm>
 #include <string>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -44,21 +49,34 @@ struct Args {
   int bw;        // torch's threads per row for this (m, k)
 };
 
-// Radix-4 butterfly on four operands in digit order.
+// Radix-4 butterfly on four operands in digit order. kHalve = false leaves the factor 0.5 out: the outputs are then twice
+// the reference's, exactly (a power-of-two factor commutes with every fp32 rounding as long as nothing overflows or goes
+// subnormal), and a whole rotation comes out 16 times too large.
+template <bool kHalve>
 __device__ __forceinline__ void butterfly4(float& a, float& b, float& c, float& d) {
   const float s = fadd(a, b), t = fadd(a, -b);
-  const float y0 = fmul(0.5f, fadd(fadd(s, c), -d));
-  const float y1 = fmul(0.5f, fadd(fadd(s, -c), d));
-  const float y2 = fmul(0.5f, fadd(fadd(t, c), d));
-  const float y3 = fmul(0.5f, fadd(fadd(-t, c), d));
+  float y0 = fadd(fadd(s, c), -d), y1 = fadd(fadd(s, -c), d), y2 = fadd(fadd(t, c), d), y3 = fadd(fadd(-t, c), d);
+  if constexpr (kHalve) y0 = fmul(0.5f, y0), y1 = fmul(0.5f, y1), y2 = fmul(0.5f, y2), y3 = fmul(0.5f, y3);
   a = y0, b = y1, c = y2, d = y3;
 }
 // The two stages whose digits are the low and high 2 bits of the register index.
+template <bool kHalve>
 __device__ __forceinline__ void stages_on_registers(float (&v)[16]) {
 #pragma unroll
-  for (int i = 0; i < 16; i += 4) butterfly4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+  for (int i = 0; i < 16; i += 4) butterfly4<kHalve>(v[i], v[i + 1], v[i + 2], v[i + 3]);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) butterfly4(v[i], v[i + 4], v[i + 8], v[i + 12]);
+  for (int i = 0; i < 4; ++i) butterfly4<kHalve>(v[i], v[i + 4], v[i + 8], v[i + 12]);
+}
+// max(a, |b|, |c|) that returns NaN when any operand is NaN.
+__device__ __forceinline__ float max3_abs_nan(float a, float b, float c) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(fabsf(b)), "f"(fabsf(c)));
+  return r;
+}
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
 }
 
 __device__ __forceinline__ void load16_bf16(const __nv_bfloat16* p, float (&v)[16]) {
@@ -131,9 +149,9 @@ __device__ float torch_order_sum_squares(const __nv_bfloat16* xr, int k, int bw,
 // The quantised bytes are scattered into a 256-byte shared tile in natural order, so each lane stores 16 (INT8) or 8
 // (INT4) contiguous bytes.
 template <int kSlots, bool kNorm, bool kInt4>
-__global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
+__global__ void __launch_bounds__(kSlots == 1 ? 256 : 512, kSlots == 1 ? (kNorm ? 8 : 6) : 1) rotate_quantize_kernel(const Args a) {
   extern __shared__ float smem_f[];
-  __shared__ float s_warp_max[16];
+  __shared__ float s_warp_max[2][16];
   __shared__ float s_inv_rms;
   __shared__ float s_part[512];
   const int tid = static_cast<int>(threadIdx.x), lane = tid & 31, warp = tid >> 5;
@@ -145,16 +163,19 @@ __global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
   std::uint8_t* qtile = reinterpret_cast<std::uint8_t*>(smem_f + halves * kTileFloats) + half_id * kGroup;
 
   float v[kSlots][16];
+  const auto load_row = [&] {
 #pragma unroll
-  for (int s = 0; s < kSlots; ++s) {
-    const int g = half_id + s * halves;
-    if (g < groups) {
-      load16_bf16(xr + g * kGroup + 16 * h, v[s]);
-    } else {
+    for (int s = 0; s < kSlots; ++s) {
+      const int g = half_id + s * halves;
+      if (g < groups) {
+        load16_bf16(xr + g * kGroup + 16 * h, v[s]);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[s][j] = 0.f;
+        for (int j = 0; j < 16; ++j) v[s][j] = 0.f;
+      }
     }
-  }
+  };
+  load_row();
 
   if constexpr (kNorm) {
     if constexpr (kSlots == 1) {
@@ -194,6 +215,10 @@ __global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
       if (lane == 0) s_inv_rms = rsqrtf(fadd(fmul(ss, a.factor), 1e-6f));
     }
     __syncthreads();
+  }
+  // The norm + modulate prologue on the registers (a no-op without it); `store_y` also writes the optional bf16 copy.
+  const auto prologue = [&](bool store_y) {
+    if constexpr (!kNorm) return;
     const float r = s_inv_rms;
 #pragma unroll
     for (int s = 0; s < kSlots; ++s) {
@@ -217,37 +242,62 @@ __global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
         v[s][j] = __uint_as_float(n << 16);
         v[s][j + 1] = __uint_as_float(n & 0xFFFF0000u);
       }
-      if (a.y != nullptr) store16_bf16(a.y + row * a.ldy + c0, v[s]);
+      if (store_y && a.y != nullptr) store16_bf16(a.y + row * a.ldy + c0, v[s]);
     }
-  }
+  };
+  prologue(true);
 
-  float amax = 0.f;
+  // The rotation, the rounding to bf16 and the row's absolute maximum. kExact = false is the fast form: no factor 0.5 in
+  // the butterflies, so the rotated values (and the maximum) are 16 times the reference's, bit for bit, provided nothing
+  // overflowed on the way; its maximum propagates NaN, so that an overflow (which always ends in an inf or a NaN) or a
+  // non-finite input shows in it. kExact = true follows the reference literally (fmaxf, which skips NaN).
+  const auto rotate = [&](auto exact_tag, int slot) -> float {
+    constexpr bool kExact = decltype(exact_tag)::value;
+    float amax = 0.f;
 #pragma unroll
-  for (int s = 0; s < kSlots; ++s) {
-    // Warp-uniform: both halves of a warp transpose together (an idle half runs on zeros).
-    if ((half_id & ~1) + s * halves >= groups) continue;
-    stages_on_registers(v[s]);
+    for (int s = 0; s < kSlots; ++s) {
+      // Warp-uniform: both halves of a warp transpose together (an idle half runs on zeros).
+      if ((half_id & ~1) + s * halves >= groups) continue;
+      stages_on_registers<kExact>(v[s]);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) tile[h * kTileStride + j] = v[s][j];
-    __syncwarp();
+      for (int j = 0; j < 16; ++j) tile[h * kTileStride + j] = v[s][j];
+      __syncwarp();
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[s][j] = tile[j * kTileStride + h];
-    __syncwarp();
-    stages_on_registers(v[s]);
-    if (half_id + s * halves < groups) {
+      for (int j = 0; j < 16; ++j) v[s][j] = tile[j * kTileStride + h];
+      __syncwarp();
+      stages_on_registers<kExact>(v[s]);
+      if (half_id + s * halves < groups) {
 #pragma unroll
-      for (int j = 0; j < 16; j += 2) {
-        rbf2(v[s][j], v[s][j + 1]);
-        amax = fmaxf(amax, fmaxf(fabsf(v[s][j]), fabsf(v[s][j + 1])));
+        for (int j = 0; j < 16; j += 2) {
+          rbf2(v[s][j], v[s][j + 1]);
+          if constexpr (kExact) amax = fmaxf(amax, fmaxf(fabsf(v[s][j]), fabsf(v[s][j + 1])));
+          else amax = max3_abs_nan(amax, v[s][j], v[s][j + 1]);
+        }
       }
     }
-  }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  if (lane == 0) s_warp_max[warp] = amax;
-  __syncthreads();
-  amax = s_warp_max[0];
-  for (int w = 1; w < (static_cast<int>(blockDim.x) >> 5); ++w) amax = fmaxf(amax, s_warp_max[w]);
+    for (int off = 16; off > 0; off >>= 1) {
+      const float o = __shfl_xor_sync(0xffffffffu, amax, off);
+      amax = kExact ? fmaxf(amax, o) : max_nan(amax, o);
+    }
+    if (lane == 0) s_warp_max[slot][warp] = amax;
+    __syncthreads();
+    amax = s_warp_max[slot][0];
+    for (int w = 1; w < (static_cast<int>(blockDim.x) >> 5); ++w) {
+      amax = kExact ? fmaxf(amax, s_warp_max[slot][w]) : max_nan(amax, s_warp_max[slot][w]);
+    }
+    return amax;
+  };
+  float amax = rotate(std::false_type{}, 0);
+  float unscale = 0.0625f;  // the rotated values in registers are 16 x the reference's
+  if (!(amax < 8.5e37f)) {  // 2^126: an overflow, a NaN or an inf somewhere (same answer in every thread of the row)
+    load_row();
+    prologue(false);
+    amax = rotate(std::true_type{}, 1);
+    unscale = 1.0f;
+  } else {
+    amax = fmul(amax, 0.0625f);
+  }
 
   float s_bf;
   if constexpr (kInt4) {
@@ -259,7 +309,8 @@ __global__ void __launch_bounds__(512) rotate_quantize_kernel(const Args a) {
     if (tid == 0) a.scale[row] = s;
     s_bf = rbf(s);
   }
-  const float inv_s = __frcp_rn(s_bf);
+  // x_rot * (1 / s) with x_rot = unscale * (register value): the power of two moves into the reciprocal, exactly.
+  const float inv_s = fmul(__frcp_rn(s_bf), unscale);
   constexpr float kLo = kInt4 ? -7.f : -128.f, kHi = kInt4 ? 7.f : 127.f;
   std::uint8_t* qr = static_cast<std::uint8_t*>(a.q) + row * a.ldq;
 #pragma unroll
