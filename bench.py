@@ -197,7 +197,7 @@ def reference_kernels_on_this_gpu(torch, ops, keep, x, x0, mod, rope, cu, seq_le
 
 # DRAM bytes (read + write, MB) of the four GEMM launches of one block at 16384 tokens, F = 12288, from the ncu capture
 # summarised in profiles/traffic_step1024_one_block.md.
-GEMM_DRAM_MB = {"qkv": 90.1 + 253.2, "o": 160.6 + 47.0, "up_gate": 229.0 + 385.0, "down": 755.7 + 85.5}
+GEMM_DRAM_MB = {"qkv": 90.4 + 253.1, "o": 160.6 + 47.3, "up_gate": 231.7 + 380.4, "down": 725.2 + 85.7}
 
 
 def gemm_sites(L, F):
