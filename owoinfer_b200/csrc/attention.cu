@@ -154,23 +154,11 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x for x <= ~9 on the FMA and integer pipes (no special-function unit): x = n + f with n = round(x), |f| <= 1/2;
-// 2^f by a cubic (relative error < 7e-4, far below e4m3's 2^-4 steps), 2^n by adding n to the exponent field.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float z = x + 12582912.0f;          // low mantissa bits of z hold n (two's complement)
-  const float f = x - (z - 12582912.0f);
-  const float p = fmaf(fmaf(fmaf(0.0555041087f, f, 0.240226507f), f, 0.693147181f), f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(z) << 23));
-}
 #ifndef B2_TRACE_WARP
 #define B2_TRACE_WARP 2
 #endif
 #ifndef B2_MMA_SLEEP_NS
 #define B2_MMA_SLEEP_NS 100
-#endif
-#ifndef B2_EXP_POLY_MASK
-#define B2_EXP_POLY_MASK 0  // bit (i & 3) set: score i uses ex2_poly. Measured on B200: 0 (all on the special-function unit) is fastest
 #endif
 __device__ __forceinline__ float rcp_approx(float x) {
   float y;
@@ -683,7 +671,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
   extern __shared__ std::uint8_t smem_raw[];
   __shared__ __align__(8) std::uint64_t s_q_full, s_k_full[kKvStages], s_k_empty[kKvStages], s_v_full[kKvStages],
-      s_v_empty[kKvStages], s_s_full[2], s_p_full[2], s_pv_done[2], s_s_ready;
+      s_v_empty[kKvStages], s_step[2], s_p_full[2], s_s_ready;
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
   const std::uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -702,9 +690,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(smem_u32(&s_v_empty[s]), 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&s_s_full[i]), 1);
+      mbar_init(smem_u32(&s_step[i]), 1);
       mbar_init(smem_u32(&s_p_full[i]), 4);
-      mbar_init(smem_u32(&s_pv_done[i]), 1);
     }
     mbar_init(smem_u32(&s_s_ready), 4);
     s_abort = 0;
@@ -768,7 +755,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           umma_i8(tmem_s + static_cast<std::uint32_t>(u & 1) * kSubK, dq + 2u * k4, d + 2u * k4, idesc_qk, 1u);  // onto the pre-fill
         }
         if ((u & 1) != 0 || u + 1 >= n_sub) tc_commit(smem_u32(&s_k_empty[s]));
-        tc_commit(smem_u32(&s_s_full[u & 1]));
+        if (u < 2) tc_commit(smem_u32(&s_step[u]));  // start-up: S(0) and S(1) are the first completions of the two barriers
       }
       __syncwarp();
       return true;
@@ -796,11 +783,13 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                   (u | k2) != 0 ? 1u : 0u);
         }
         if ((u & 1) != 0 || u + 1 >= n_sub) tc_commit(smem_u32(&s_v_empty[s]));
-        tc_commit(smem_u32(&s_pv_done[u & 1]));
       }
       __syncwarp();
       TRACE(6);
       if (u + 2 < n_sub && !issue_qk(u + 2)) break;
+      // One completion per step: P·V(u) has landed (its P buffer and O are free again) and S(u + 2) is computed.
+      if (elect_one()) tc_commit(smem_u32(&s_step[u & 1]));
+      __syncwarp();
       TRACE(7);
     }
   } else {
@@ -856,9 +845,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     for (int u = 0; u < n_sub; ++u) {
       const std::uint32_t s_cols = tmem_s + lane_off + static_cast<std::uint32_t>(u & 1) * kSubK;
       TRACE(4);
-      // S(u) computed; P·V(u - 2), which read this sub-tile's P buffer, landed.
-      if (!warp_wait(smem_u32(&s_s_full[u & 1]), (u >> 1) & 1u) ||
-          (u >= 2 && !warp_wait(smem_u32(&s_pv_done[u & 1]), ((u >> 1) - 1) & 1u))) {
+      // Completion u / 2 of s_step[u % 2]: S(u) computed and P·V(u - 2), which read this sub-tile's P buffer, landed (the MMA
+      // warp's step u - 2; for u < 2 the start-up Q·K^T).
+      if (!warp_wait(smem_u32(&s_step[u & 1]), (u >> 1) & 1u)) {
         dead = true;
         break;
       }
@@ -896,7 +885,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         // O is about to be rescaled: every P·V issued so far (the last one is u - 1) has to have landed.
         if (!o_idle) {
           o_idle = true;
-          if (!warp_wait(smem_u32(&s_pv_done[(u - 1) & 1]), ((u - 1) >> 1) & 1u)) {
+          if (!warp_wait(smem_u32(&s_step[(u - 1) & 1]), (((u - 1) >> 1) + 1) & 1u)) {  // the MMA warp's step u - 1
             dead = true;
             break;
           }
@@ -937,7 +926,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         o_scale = grow;
       }
     }
-    if (!dead && warp_wait(smem_u32(&s_pv_done[(n_sub - 1) & 1]), ((n_sub - 1) >> 1) & 1u)) {
+    if (!dead && warp_wait(smem_u32(&s_step[(n_sub - 1) & 1]), (((n_sub - 1) >> 1) + 1) & 1u)) {  // the last step
       tc_fence_after();
       const float inv_d = rcp_approx(d_run);
       const int row = q0 + r_local;
