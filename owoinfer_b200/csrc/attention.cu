@@ -560,12 +560,18 @@ __global__ void __launch_bounds__(256) quant_kv_kernel(const PrepArgs p) {
 // ---------------------------------------------------------------------------------------------------------------
 // The attention kernel.
 // ---------------------------------------------------------------------------------------------------------------
-// One softmax pass of one thread over its row's 64 scores of a sub-tile. The score accumulator was pre-filled with the
-// integer 0x4B400000 before Q·K^T, so a column read back is the bit pattern of the fp32 number 12582912 + S (exact:
-// |S| < 2^22): the scores arrive as floats with no conversion, their order is the integers' order, and the constant
-// is folded into `bias`. P = exp2(f * c + bias) with packed fp32 pairs for the FMA and the denominator; e4m3 P goes
-// into the swizzled P tile (row = 128 bytes, 16-byte chunk n of row r stored at chunk n ^ (r % 8); this sub-tile owns
-// chunks chunk0 .. chunk0 + 3). Returns the largest biased score (0 if none) and the sum of the unrounded P.
+// One softmax pass of one thread over its row's 64 scores of a sub-tile. |S| < 2^22, so the integer S + 0x4B400000 is
+// the bit pattern of the fp32 number 12582912 + S: one integer add converts (none when the accumulator was pre-filled
+// with that constant before Q·K^T, B2_ATTN_PREFILL), the order of the floats is the order of the integers, and the
+// constant is folded into `bias`. P = exp2(f * c + bias) with packed fp32 pairs for the FMA and the denominator; e4m3 P
+// goes into the swizzled P tile (row = 128 bytes, 16-byte chunk n of row r stored at chunk n ^ (r % 8); this sub-tile
+// owns chunks chunk0 .. chunk0 + 3). Returns the largest biased score (0 if none) and the sum of the unrounded P.
+#ifndef B2_ATTN_PREFILL
+#define B2_ATTN_PREFILL 0  // measured on B200: the pre-fill's tcgen05.wait::st before each hand-over costs more than the add
+#endif
+// Added to a score read back from TMEM: 0 when the accumulator was pre-filled with 0x4B400000, else that constant.
+constexpr std::uint32_t kScoreBias = B2_ATTN_PREFILL ? 0u : 0x4B400000u;
+
 template <bool kFull>
 __device__ __forceinline__ void softmax_pass(std::uint32_t s_cols, float c, float bias, int valid, std::uint8_t* prow,
                                              int chunk0, int row_xor, float& bmax_out, float& sum_out) {
@@ -576,7 +582,7 @@ __device__ __forceinline__ void softmax_pass(std::uint32_t s_cols, float c, floa
     float pv[16];
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
-      const float f0 = __uint_as_float(r[i]), f1 = __uint_as_float(r[i + 1]);
+      const float f0 = __uint_as_float(r[i] + kScoreBias), f1 = __uint_as_float(r[i + 1] + kScoreBias);
       float e0, e1;
       unpack2(fma2(pack2(f0, f1), c2, bias2), e0, e1);
       pv[i] = ex2(e0);
@@ -752,7 +758,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const std::uint64_t d = (s != 0 ? dk1 : dk0) + (u & 1) * kHalfTile;
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
-          umma_i8(tmem_s + static_cast<std::uint32_t>(u & 1) * kSubK, dq + 2u * k4, d + 2u * k4, idesc_qk, 1u);  // onto the pre-fill
+          umma_i8(tmem_s + static_cast<std::uint32_t>(u & 1) * kSubK, dq + 2u * k4, d + 2u * k4, idesc_qk, (B2_ATTN_PREFILL || k4 != 0) ? 1u : 0u);  // onto the pre-fill, if any
         }
         if ((u & 1) != 0 || u + 1 >= n_sub) tc_commit(smem_u32(&s_k_empty[s]));
         if (u < 2) tc_commit(smem_u32(&s_step[u]));  // start-up: S(0) and S(1) are the first completions of the two barriers
@@ -829,14 +835,17 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       tmem_st_wait();
     };
-    // Both score buffers start out pre-filled (see softmax_pass); the MMA warp waits for that once.
+    // With B2_ATTN_PREFILL both score buffers start out pre-filled (see softmax_pass); the MMA warp waits for the softmax
+    // warps once either way.
     const auto prefill_s = [&](std::uint32_t cols) {
       tmem_fill_32x32(cols, 0x4B400000u);
       tmem_fill_32x32(cols + 32, 0x4B400000u);
     };
-    prefill_s(tmem_s + lane_off);
-    prefill_s(tmem_s + lane_off + kSubK);
-    tmem_st_wait();
+    if (B2_ATTN_PREFILL) {
+      prefill_s(tmem_s + lane_off);
+      prefill_s(tmem_s + lane_off + kSubK);
+      tmem_st_wait();
+    }
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&s_s_ready));
@@ -863,7 +872,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           tmem_ld_32x32(s_cols + cc * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) bmax = fmaxf(bmax, (cc * 32 + i < valid) ? __uint_as_float(r[i]) : 0.f);
+          for (int i = 0; i < 32; ++i) bmax = fmaxf(bmax, (cc * 32 + i < valid) ? __uint_as_float(r[i] + kScoreBias) : 0.f);
         }
         m_run = (bmax - 12582912.0f) * c - (a.p_offset - kHeadroom);
       }
@@ -906,8 +915,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (dead) break;
       d_run += d_tile;
       TRACE(2);
-      // S is consumed (pre-fill it for Q·K^T of sub-tile u + 2) and P written: both go to the MMA warp.
-      if (u + 2 < n_sub) {
+      // S is consumed (and, with B2_ATTN_PREFILL, pre-filled again for Q·K^T of sub-tile u + 2) and P written: both go to
+      // the MMA warp.
+      if (B2_ATTN_PREFILL && u + 2 < n_sub) {
         prefill_s(s_cols);
         tmem_st_wait();
       }
