@@ -130,22 +130,45 @@ class UlyssesBlockRunner:
         self.cu_one = [torch.tensor([0, s], dtype=torch.int32, device=device) for s in self.seq_lens]
         self.ws = [torch.empty(max(256, ops.attention_q8_workspace_bytes(s, s, 1, s, self.hp)), dtype=torch.uint8, device=device)
                    for s in self.seq_lens]
+        self.comm_stream = torch.cuda.Stream(device=device) if self.world > 1 else None
 
     def run(self, x, mod, rope_local, w):
         """x: bf16 [L_local, D] updated in place; mod: bf16 [6 D]; rope_local: bf16 [L_local, 128] (this rank's rows of the
-        table); w: dict with norm1, norm2, q_norm, k_norm and qkv / o / up_gate / down = (int8 weight, f32 scale)."""
-        ops, D, F, L = self.ops, self.D, self.F, self.L
+        table); w: dict with norm1, norm2, q_norm, k_norm and qkv / o / up_gate / down = (int8 weight, f32 scale).
+        The exchanges run on a second stream, one sequence at a time, so that the all-to-all of one sequence overlaps the
+        attention of another."""
+        ops, D, F = self.ops, self.D, self.F
         xq_d = self.xq[:, :D]
         m = [mod[i * D:(i + 1) * D] for i in range(6)]
         ops.rms_norm_modulate_rotate_quantize(x, w["norm1"], m[1], m[0], q=xq_d, scale=self.scale)
         ops.int8_gemm(xq_d, self.scale, w["qkv"][0], w["qkv"][1], out=self.qkv)
         ops.qk_norm_rope_moss(self.qkv, self.heads, w["q_norm"], w["k_norm"], rope_local)
-        full = exchange_tokens_to_heads(self.qkv, self.local_lens, self.heads, self.group)
+        cur = torch.cuda.current_stream()
+        comm = self.comm_stream if self.world > 1 else cur
+        comm.wait_stream(cur)
+        n_seq = len(self.seq_lens)
+        full, arrived, parts, returned = [None] * n_seq, [], [None] * n_seq, []
+        start = 0
+        with torch.cuda.stream(comm):
+            for i, c in enumerate(self.local_lens):
+                full[i] = exchange_tokens_to_heads(self.qkv[start:start + c], [c], self.heads, self.group)[0]
+                full[i].record_stream(cur)
+                arrived.append(comm.record_event())
+                start += c
         for i, t in enumerate(full):
-            q3, k3, v3 = t[:, 0], t[:, 1], t[:, 2]
+            cur.wait_event(arrived[i])
             s = self.seq_lens[i]
-            ops.attention_q8(q3, k3, v3, self.attn_full[i], self.cu_one[i], self.cu_one[i], s, ops.SM_SCALE, workspace=self.ws[i])
-        attn = exchange_heads_to_tokens(self.attn_full, self.local_lens, self.heads, self.group)
+            ops.attention_q8(t[:, 0], t[:, 1], t[:, 2], self.attn_full[i], self.cu_one[i], self.cu_one[i], s, ops.SM_SCALE,
+                             workspace=self.ws[i])
+            done = cur.record_event()
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                parts[i] = exchange_heads_to_tokens([self.attn_full[i]], [self.local_lens[i]], self.heads, self.group)
+                parts[i].record_stream(cur)
+                returned.append(comm.record_event())
+        for e in returned:
+            cur.wait_event(e)
+        attn = torch.cat(parts, dim=0) if n_seq > 1 else parts[0]
         ops.rotate_quantize(attn, q=xq_d, scale=self.scale)
         ops.int8_gemm_gated_residual(xq_d, self.scale, w["o"][0], w["o"][1], m[2], x)
         ops.rms_norm_modulate_rotate_quantize(x, w["norm2"], m[4], m[3], q=xq_d, scale=self.scale)
@@ -153,7 +176,6 @@ class UlyssesBlockRunner:
         xq_f = self.xq[:, :F]
         ops.rotate_quantize(self.ffn, q=xq_f, scale=self.scale)
         ops.int8_gemm_gated_residual(xq_f, self.scale, w["down"][0], w["down"][1], m[5], x)
-        del L
         return x
 
 
