@@ -8,6 +8,7 @@ Default workload `step1024`: the full INT8 'high'-tier denoising step at 1024^2 
 one pass of all blocks over the image's 16384 tokens through the C ABI (b2_dit_step). Other workloads:
   block1024            one block on one 8192-token sequence (BASELINE configs[1])
   step1024_cfgsplit    the step with the CFG halves on two GPUs (N = 2, strong scaling against step1024 at N = 1)
+  step2048             the 2048^2 step (2 x 20480 tokens) on one GPU through b2_dit_step: the base of step2048_ulysses
   step2048_ulysses     the 2048^2 step (two 20480-token sequences) with Ulysses sequence parallelism over N GPUs
   turbo1024            the step with grouped 4-bit weights (W4A8), one image per GPU
 Prints ONE JSON line on rank 0.
@@ -133,7 +134,7 @@ def workload_shape(name: str, world: int):
         return 8192, 2
     if name == "step1024_cfgsplit":
         return 8192, 1
-    if name == "step2048_ulysses":
+    if name in ("step2048", "step2048_ulysses"):
         return 20480, 2
     raise SystemExit(f"unknown workload {name}")
 
@@ -318,7 +319,8 @@ def main():
     cfg_row = rank if scaling == "strong" else 0
     x0 = synth.activations(L, D, 1001 + rank + cfg_row)
     mod = synth.modulation(D, 2001)
-    rope_one = ops.moss_rope_table(64, 64, seq_len - 4096)
+    grid = 128 if seq_len > 16384 else 64  # 2048^2: a 128 x 128 latent grid + 4096 text tokens
+    rope_one = ops.moss_rope_table(grid, grid, seq_len - grid * grid)
     rope = rope_one.repeat(seqs, 1).contiguous()
     cu = synth.cu_seqlens([seq_len] * seqs)
     run = ops.block_run(L, cu, seq_len, D=D, F=F, heads=HEADS, tier=tier)
@@ -402,7 +404,7 @@ def main():
 
     # value: ms per image-step aggregated over the job: N images advance per step under weak scaling.
     units = world if scaling == "weak" else 1
-    line = {"metric": METRIC, "value": ms_step / units, "unit": "ms", "n_gpus": world, "steps": args.steps,
+    line = {"metric": ("dit_ms_per_step_2048" if seq_len > 16384 else METRIC), "value": ms_step / units, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False, "scaling": scaling,
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": args.workload, "blocks": n_blocks, "d": D, "heads": HEADS, "ffn": F,
