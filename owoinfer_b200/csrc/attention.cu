@@ -6,12 +6,13 @@
 //     stats      per (512-key chunk, head, sequence): partial per-channel K sums and V |max| in a fixed order
 //     finalize   k_mean = bf16(sum / len); v_scale = amax / v_range; v_recp = v_range / amax
 //     quantise   Q per (32 tokens, head) [when not fused]; K - k_mean per (64 keys, head) -> int8; V * v_recp -> e4m3
-//   attention (tensor-core-bound): one CTA per (128 query rows, head, sequence), two CTAs per SM; 128-key tiles
-//     S = Q8 · K8^T   tcgen05.mma kind::i8, int32 accumulator in TMEM (exact)
-//     softmax         8 warps, two threads per row (one 64-key block each): S -> fp32 (exact: |S| < 2^22), scaled by
-//                     sm_scale * log2e * q_scale * k_scale[64-key block], running max / denominator in fp32, P = exp2(.)
-//                     shifted so that its maximum stays within [p_range / 2, p_range] (the reference maximum may lag the
-//                     true one by one binade, which makes rescaling O rare), rounded to e4m3 into a swizzled shared tile
+//   attention: one CTA per (128 query rows, head, sequence), two CTAs per SM; K/V in 128-key tiles, the tensor work in
+//   64-key sub-tiles with the score accumulator double-buffered in TMEM
+//     S = Q8 · K8^T   tcgen05.mma kind::i8 (N = 64), int32 accumulator in TMEM (exact)
+//     softmax         4 warps, one thread per query row: S -> fp32 (exact: |S| < 2^22), scaled by
+//                     sm_scale * log2e * q_scale * k_scale[64-key block], P = exp2(.) against a reference maximum that
+//                     is raised only when its headroom runs out (which makes rescaling O rare), denominator in fp32
+//                     from the unrounded P, P rounded to e4m3 into a swizzled shared tile
 //     O += P8 · V8    tcgen05.mma kind::f8f6f4, fp32 accumulator in TMEM; V is read in its natural [key, channel]
 //                     layout as an MN-major operand, so the pre-pass needs no transpose
 //     out = O / d * v_scale[channel] -> bf16

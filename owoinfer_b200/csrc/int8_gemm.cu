@@ -1,16 +1,18 @@
 // INT8 x INT8 -> INT32 GEMM for sm_100a with the dequantisation and the following element-wise op fused into the
 // epilogue: out = epilogue(sum_k x_q[r,k] * w[c,k]).
 //
-// Structure (one persistent CTA per SM, 320 threads, warp-specialised):
-//   warp 0  TMA producer: per 128-byte K block, one 128-row box of A and one or two 128-row boxes of B land in a
-//           128-byte-swizzled shared-memory stage (4 to 6 stages), completion on the stage's "full" mbarrier.
-//   warp 1  MMA issuer: one thread issues tcgen05.mma kind::i8 (M 128, N 128 or 256, K 32; four per stage) on
-//           shared-memory descriptors; tcgen05.commit frees the stage ("empty" mbarrier) and, after the last K block,
-//           publishes the accumulator ("tmem_full").
-//   warps 2-9  epilogue: each warp reads its 32 TMEM lanes (one output row per thread) and half of the tile's columns,
-//           64 columns per TMEM round trip, applies the epilogue and stores; the tile's per-column vectors (w_scale,
-//           bias, gate) are staged once in shared memory. Two accumulators (2 x N TMEM columns) let the epilogue of tile
-//           i overlap the main loop of tile i + 1.
+// Structure (one persistent CTA per SM, warp-specialised; by default a CTA pair shares a 256 x 256 tile, cta_group::2):
+//   warp 0  TMA producer: per 128-byte K block, this CTA's 128-row box of A and its 128 (pair) or 128 / 256 (single
+//           CTA) rows of B land in a 128-byte-swizzled shared-memory stage (4 to 6 stages), completion on the stage's
+//           "full" mbarrier (the leader CTA's, for a pair).
+//   warp 1  MMA issuer: the warp walks the loop in uniform control flow, one elected lane issues tcgen05.mma kind::i8
+//           (M 128 or 256 for a pair, N 128 or 256, K 32; four per stage) on shared-memory descriptors; tcgen05.commit
+//           frees the stage ("empty" mbarrier) and, after the last K block, publishes the accumulator ("tmem_full").
+//   warps 2..  epilogue (8 warps; 16 for SiTU-GLU): each warp reads its 32 TMEM lanes (one output row per thread) and
+//           its share of the tile's columns, applies the epilogue and stores; its per-column vectors (w_scale, bias,
+//           gate) are staged in shared memory. Two accumulators (2 x N TMEM columns) let the epilogue of tile i overlap
+//           the main loop of tile i + 1.
+// Tiles are visited in bands of M tiles (see tile_coords and the launch code) so that the operands stay in L2.
 // The int32 accumulators are exact, so every tile shape gives the same bits. Epilogues (single-rounded fp32, no FMA
 // contraction; reference: src/kernels/quant/int8_gemm_impl.cuh:73-188):
 //   plain           bf16(((float)acc * xs[r]) * ws[c] + bias[c])
