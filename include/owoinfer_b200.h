@@ -35,7 +35,11 @@ typedef enum b2_status {
 const char* b2_last_error_message(void);
 
 /* kInt8NumericsVersion (src/kernels/quant/quant.h:38), kInt4NumericsVersion (src/kernels/quant4/quant4.h:36),
- * attention_q8::kNumericsVersion (src/kernels/attention_q8/attention_q8.h:78): which = 0, 1, 2. */
+ * attention_q8::kNumericsVersion (src/kernels/attention_q8/attention_q8.h:73), kGroupedDecodeVersion
+ * (src/kernels/quant/w4a8_decode.h:27): which = 0, 1, 2, 3; any other value returns 0. The INT8, INT4 and grouped-decode
+ * values are the reference's (the outputs are bit-identical to its kernels). The attention value carries the
+ * reference's contract version in its low half and this library's kernel revision in its high half: the output meets
+ * the reference's tolerances but not its bits. */
 uint32_t b2_numerics_version(int which);
 
 /* ---------------------------------------------------------------------------------------------------------------
@@ -70,9 +74,18 @@ int b2_unpack_int4(const void* packed, int64_t ldp, int8_t* out, int64_t ldo, in
 
 /* quant::decode_grouped_int8 (src/kernels/quant/w4a8_decode.h:39), 4-bit codes only: packed [rows,k/2]; group scales
  * s_rel [rows,k/group] as e4m3 bytes (scale_kind 0, the reference's format) or fp16 (scale_kind 1); codebook f32 [16]
- * or NULL (level = code - 8); out int8 [rows,k]. group % 16 == 0, k % group == 0. */
+ * or NULL (level = code - 8); out int8 [rows,k]. group % 16 == 0, k % group == 0, rows < 2^31, k <= 131071.
+ * Untrusted scales, as in the reference (w4a8_decode.cu:57-62): a group whose scale is NaN or negative decodes to zeros
+ * and ORs 1 into the device word `invalid` (never cleared here); invalid == NULL uses a word inside the library, read
+ * with b2_w4_invalid_scales. */
 int b2_decode_grouped_int8(const void* packed, const void* s_rel, int scale_kind, const float* codebook, int64_t rows,
-                           int64_t k, int group, int8_t* out, void* stream);
+                           int64_t k, int group, int8_t* out, unsigned* invalid, void* stream);
+
+/* The library's own "a group scale was NaN or negative" word of the current device (set by b2_decode_grouped_int8 with
+ * invalid == NULL, by b2_w4a8_gemm* and by the W4A8 tier of the block): copied to *host_value, then zeroed when
+ * clear != 0. Synchronises the device: for load-time checks and tests, not for the hot path. The reference hands the
+ * caller's word to every decode (w4a8_decode.h:39); this is that word kept by the library. */
+int b2_w4_invalid_scales(unsigned* host_value, int clear);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * INT8 x INT8 -> INT32 GEMM with fused epilogues.
@@ -114,7 +127,8 @@ int b2_int8_gemm_acc(const b2_int8_operands* op, int32_t* acc, int64_t ldacc, vo
  * INT8 activations; bit-identical to quant::decode_grouped_int8 followed by quant::int8_gemm
  * (src/kernels/quant/w4a8_decode.h:1-39 + src/kernels/quant/quant.h:92). scratch: device int8 [n,k] for the decoded
  * weight (caller-owned; may be reused across calls). epilogue: 0 plain (aux = bias or NULL), 1 gated residual
- * (aux = gate, out = residual in place), 2 SiTU-GLU. */
+ * (aux = gate, out = residual in place), 2 SiTU-GLU. Every argument is checked before the decode is launched; m == 0
+ * launches nothing. A NaN or negative group scale decodes to zeros and is reported by b2_w4_invalid_scales. */
 typedef struct b2_w4_weight {
   const void* packed;   /* uint8 [n, k/2] */
   const void* s_rel;    /* [n, k/group] e4m3 or fp16 */
@@ -260,8 +274,9 @@ size_t b2_block_quant_workspace_bytes(const b2_block_run* run);
 /* moss_dit::run_block_quant (src/models/moss_dit/dit_block_quant.h:145), all-quantized route with 8-bit attention. */
 int b2_run_block_quant(const b2_block_weights* w, const b2_block_buffers* a, const b2_block_run* run, void* stream);
 
-/* The block loop of MossDit::forward (src/models/moss_dit/moss_dit.cpp:1427-1460): blocks[i] applied in order to x,
- * mods[i] the per-block modulation (the reference shares one vector; pass the same pointer). */
+/* The block loop of MossDit::forward (src/models/moss_dit/moss_dit.cpp:1427-1460): blocks[i] applied in order to a->x.
+ * Every block reads the one modulation vector a->mod, as in the reference, where the timestep embedding produces one
+ * vector per step that all blocks share; a per-block modulation is not supported. */
 int b2_dit_step(const b2_block_weights* blocks, int num_blocks, const b2_block_buffers* a, const b2_block_run* run,
                 void* stream);
 

@@ -359,6 +359,28 @@ int orc_decode_grouped_int8(const u8* packed, const void* s_rel, int scale_kind,
   return 0;
 }
 
+// The same decode under the GPU kernel's rule for untrusted scales (src/kernels/quant/w4a8_decode.cu:57-62): a group
+// whose scale is NaN or negative decodes to zeros and ORs 1 into *invalid; every other group decodes as above.
+void orc_decode_grouped_int8_device_rule(const u8* packed, const void* s_rel, int scale_kind, const float* codebook,
+                                         i64 rows, i64 k, int group, i8* out, unsigned* invalid) {
+  const i64 groups = k / group;
+  for (i64 r = 0; r < rows; ++r) {
+    const u8* p = packed + r * (k / 2);
+    for (i64 gi = 0; gi < groups; ++gi) {
+      const float s = scale_kind == 0 ? e4m3_to_float(static_cast<const u8*>(s_rel)[r * groups + gi])
+                                      : half_to_float(static_cast<const u16*>(s_rel)[r * groups + gi]);
+      const bool ok = !(std::isnan(s) || s < 0.0f);
+      if (!ok) *invalid |= 1u;
+      for (i64 c = gi * group; c < (gi + 1) * group; ++c) {
+        const unsigned code = (p[c / 2] >> ((c & 1) * 4)) & 0xFu;
+        const float level = codebook != nullptr ? codebook[code] : static_cast<float>(code) - 8.0f;
+        const float v = std::nearbyint(level * s);
+        out[r * k + c] = ok ? static_cast<i8>(std::min(127.0f, std::max(-127.0f, v))) : i8{0};
+      }
+    }
+  }
+}
+
 // Offline ConvRot weight quantiser (what turns bf16 weights into the GEMM's INT8 operand):
 // W_rot = W · H_g per group with the products summed in column order, s = max(absmax / 127, 1e-30), q = rne(W_rot / s).
 // src/weights/quant/quant_codec.cpp:50-96,148-159.

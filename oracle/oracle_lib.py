@@ -142,6 +142,21 @@ def decode_grouped_int8(packed, s_rel, group, codebook=None):
     return out
 
 
+def decode_grouped_int8_device_rule(packed, s_rel, group, codebook=None):
+    """The GPU kernel's rule for untrusted scales: (int8 [rows, k], invalid word); bad groups decode to zeros."""
+    packed = _c(packed, np.uint8)
+    rows, kb = packed.shape
+    k = kb * 2
+    kind = 0 if s_rel.dtype == np.uint8 else 1
+    s_rel = np.ascontiguousarray(s_rel)
+    cb = None if codebook is None else _c(codebook, np.float32)
+    out = np.empty((rows, k), np.int8)
+    invalid = C.c_uint(0)
+    lib().orc_decode_grouped_int8_device_rule(_p(packed), _p(s_rel), i32(kind), _p(cb), i64(rows), i64(k), i32(group),
+                                              _p(out), C.byref(invalid))
+    return out, int(invalid.value)
+
+
 def quantize_convrot_rows_bf16(w, g=256):
     w = _c(w, np.uint16)
     rows, k = w.shape

@@ -1,6 +1,7 @@
 // Host plumbing of the C ABI: thread-local error text, device queries, TMA tensor-map construction.
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -22,15 +23,15 @@ int fail_cuda(const char* op, cudaError_t e) {
 }
 
 int sm_count() {
-  static int cached[64] = {};
+  static std::atomic<int> cached[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 bool make_tensor_map_2d(CUtensorMap* map, const void* base, std::uint64_t inner, std::uint64_t rows,
@@ -72,8 +73,17 @@ extern "C" {
 const char* b2_last_error_message(void) { return b2::g_last_error.c_str(); }
 
 uint32_t b2_numerics_version(int which) {
-  (void)which;
-  return 1;
+  // 0, 1, 3: bit-identical to the reference kernels of these versions. 2: the attention output follows the reference's
+  // version-1 contract inside its tolerances but is produced by a different kernel (P is rounded against a lazily raised
+  // maximum), so the high half carries this library's own revision of that kernel.
+  constexpr std::uint32_t kInt8 = 1, kInt4 = 1, kAttention = (2u << 16) | 1u, kGroupedDecode = 1;
+  switch (which) {
+    case 0: return kInt8;
+    case 1: return kInt4;
+    case 2: return kAttention;
+    case 3: return kGroupedDecode;
+    default: return 0;
+  }
 }
 
 }  // extern "C"

@@ -78,7 +78,7 @@ int site_operands(const char* op, const b2_linear& lin, int tier, std::int8_t* w
   }
   if (lin.w4 == nullptr) return fail_invalid(op, "missing grouped 4-bit weight");
   if (const int rc = b2_decode_grouped_int8(lin.w4->packed, lin.w4->s_rel, lin.w4->scale_kind, lin.w4->codebook, n, k,
-                                            lin.w4->group, w_unpack, stream)) {
+                                            lin.w4->group, w_unpack, nullptr, stream)) {
     return rc;
   }
   *w = w_unpack, *ws = lin.w4->s_channel;

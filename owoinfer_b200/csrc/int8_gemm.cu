@@ -23,6 +23,7 @@
 // Every wait on an mbarrier is bounded (one second of %globaltimer); on expiry the CTA raises a status word, drains
 // and frees its TMEM instead of hanging.
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <string>
 
@@ -301,7 +302,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // memory, four columns per lane; only the warp itself reads them back, so a warp-level sync is enough.
       float* vec = s_vec[warp - 2];
       __syncwarp();
-      {
+      if constexpr (kEpi != Epi::kAcc) {  // the accumulator dump reads no per-column vector (and allows any n)
         constexpr int kHalfCols = kBN / (kEpiWarps / 4);  // columns of one warp's part of the tile
         for (int j = lane * 4; j < (kEpi == Epi::kSituGlu ? 64 : 128); j += 128) {
           int col;
@@ -604,15 +605,16 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
   }
   auto kernel = int8_gemm_kernel<kBN, kEpi, kCtas>;
   // Opt in to the large dynamic shared-memory size once per device and instantiation.
-  static bool configured[64] = {};
+  // (Setting the attribute twice from two threads is harmless; the flag only saves the call.)
+  static std::atomic<bool> configured[64] = {};
   int dev = 0;
   if (const cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return fail_cuda(op, e);
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
+  if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
     if (const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
         e != cudaSuccess) {
       return fail_cuda(op, e);
     }
-    if (dev >= 0 && dev < 64) configured[dev] = true;
+    if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   p.m_tiles = (p.m + kBM * kCtas - 1) / (kBM * kCtas);
   if constexpr (kEpi == Epi::kSituGlu) p.n_tiles = (p.half + 127) / 128;
@@ -689,13 +691,43 @@ int gemm_status_word(int* host_value) {
 
 using namespace b2;
 
+namespace b2 {
+namespace {
+
+// Argument checks of the three epilogues, shared by the INT8 entry points and the W4A8 ones (which run them, with the
+// scratch standing in for the weight, before anything is launched).
+int check_plain(const char* op, const b2_int8_operands* a, const void* bias, const void* out, std::int64_t ldo) {
+  if (const int rc = check_operands(op, a)) return rc;
+  if (const int rc = check_output(op, "out", out, ldo, a->n)) return rc;
+  if (bias != nullptr && !aligned_to(bias, 16)) return fail_invalid(op, "bias must be 16-byte aligned");
+  return B2_OK;
+}
+int check_gated(const char* op, const b2_int8_operands* a, const void* bias, const void* gate, const void* residual,
+                std::int64_t ldr) {
+  if (const int rc = check_operands(op, a)) return rc;
+  if (const int rc = check_output(op, "residual", residual, ldr, a->n)) return rc;
+  if (bias != nullptr && !aligned_to(bias, 16)) return fail_invalid(op, "bias must be 16-byte aligned");
+  if (gate == nullptr || !aligned_to(gate, 16)) return fail_invalid(op, "gate must be a 16-byte aligned device vector");
+  return B2_OK;
+}
+int check_situ(const char* op, const b2_int8_operands* a, const void* out, std::int64_t ldo) {
+  if (a != nullptr && a->n % 8 != 0) return fail_invalid(op, "n = 2F needs F % 4 == 0, got n " + std::to_string(a->n));
+  if (const int rc = check_operands(op, a)) return rc;
+  const std::int64_t f = a->n / 2;
+  if (out == nullptr || !aligned_to(out, 8) || ldo < f || ldo % 4 != 0) {
+    return fail_invalid(op, "out must be 8-byte aligned with a row stride >= F and a multiple of 4, got " + std::to_string(ldo));
+  }
+  return B2_OK;
+}
+
+}  // namespace
+}  // namespace b2
+
 extern "C" {
 
 int b2_int8_gemm(const b2_int8_operands* op_, const void* bias, void* out, int64_t ldo, void* stream, int tile) {
   constexpr const char* op = "int8_gemm";
-  if (const int rc = check_operands(op, op_)) return rc;
-  if (const int rc = check_output(op, "out", out, ldo, op_->n)) return rc;
-  if (bias != nullptr && !aligned_to(bias, 16)) return fail_invalid(op, "bias must be 16-byte aligned");
+  if (const int rc = check_plain(op, op_, bias, out, ldo)) return rc;
   if (op_->m == 0) return B2_OK;
   GemmParams p = base_params(op_);
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -706,10 +738,7 @@ int b2_int8_gemm(const b2_int8_operands* op_, const void* bias, void* out, int64
 int b2_int8_gemm_gated_residual(const b2_int8_operands* op_, const void* bias, const void* gate, void* residual,
                                 int64_t ldr, void* stream, int tile) {
   constexpr const char* op = "int8_gemm_gated_residual";
-  if (const int rc = check_operands(op, op_)) return rc;
-  if (const int rc = check_output(op, "residual", residual, ldr, op_->n)) return rc;
-  if (bias != nullptr && !aligned_to(bias, 16)) return fail_invalid(op, "bias must be 16-byte aligned");
-  if (gate == nullptr || !aligned_to(gate, 16)) return fail_invalid(op, "gate must be a 16-byte aligned device vector");
+  if (const int rc = check_gated(op, op_, bias, gate, residual, ldr)) return rc;
   if (op_->m == 0) return B2_OK;
   GemmParams p = base_params(op_);
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -720,17 +749,12 @@ int b2_int8_gemm_gated_residual(const b2_int8_operands* op_, const void* bias, c
 
 int b2_int8_gemm_situ_glu(const b2_int8_operands* op_, void* out, int64_t ldo, void* stream, int tile) {
   constexpr const char* op = "int8_gemm_situ_glu";
-  if (op_ != nullptr && op_->n % 8 != 0) return fail_invalid(op, "n = 2F needs F % 4 == 0, got n " + std::to_string(op_->n));
-  if (const int rc = check_operands(op, op_)) return rc;
-  const std::int64_t f = op_->n / 2;
-  if (out == nullptr || !aligned_to(out, 8) || ldo < f || ldo % 4 != 0) {
-    return fail_invalid(op, "out must be 8-byte aligned with a row stride >= F and a multiple of 4, got " + std::to_string(ldo));
-  }
+  if (const int rc = check_situ(op, op_, out, ldo)) return rc;
   if (op_->m == 0) return B2_OK;
   SituTables t;
   if (const int rc = situ_tables(as_stream(stream), &t)) return rc;
   GemmParams p = base_params(op_);
-  p.half = static_cast<int>(f);
+  p.half = static_cast<int>(op_->n / 2);
   p.out = static_cast<__nv_bfloat16*>(out), p.ldo = ldo;
   p.t_gate = t.gate, p.t_hidden = t.hidden;
   return dispatch<Epi::kSituGlu>(op, op_, p, as_stream(stream), tile);
@@ -751,10 +775,21 @@ int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_
   constexpr const char* op = "w4a8_gemm";
   if (w == nullptr || scratch == nullptr) return fail_invalid(op, "null weight or scratch");
   if (epilogue < 0 || epilogue > 2) return fail_invalid(op, "epilogue must be 0 (plain), 1 (gated residual) or 2 (SiTU-GLU)");
-  if (const int rc = b2_decode_grouped_int8(w->packed, w->s_rel, w->scale_kind, w->codebook, n, k, w->group, scratch, stream)) {
+  // Every argument of the GEMM is checked (the scratch standing in for the decoded weight) before the decode is launched.
+  const b2_int8_operands a{x_q, ldx, x_scale, scratch, w->s_channel, m, n, k};
+  if (const int rc = epilogue == 0   ? check_plain(op, &a, aux, out, ldo)
+                     : epilogue == 1 ? check_gated(op, &a, nullptr, aux, out, ldo)
+                                     : check_situ(op, &a, out, ldo)) {
     return rc;
   }
-  b2_int8_operands a{x_q, ldx, x_scale, scratch, w->s_channel, m, n, k};
+  if (w->packed == nullptr || w->s_rel == nullptr || !aligned_to(w->packed, 8) || w->group <= 0 || w->group % 16 != 0 ||
+      k % w->group != 0 || (w->scale_kind != 0 && w->scale_kind != 1)) {
+    return fail_invalid(op, "weight needs packed codes (8-byte aligned), group scales, group % 16 == 0, k % group == 0 and scale_kind 0 or 1");
+  }
+  if (m == 0) return B2_OK;
+  if (const int rc = b2_decode_grouped_int8(w->packed, w->s_rel, w->scale_kind, w->codebook, n, k, w->group, scratch, nullptr, stream)) {
+    return rc;
+  }
   if (epilogue == 0) return b2_int8_gemm(&a, aux, out, ldo, stream, B2_TILE_AUTO);
   if (epilogue == 1) return b2_int8_gemm_gated_residual(&a, nullptr, aux, out, ldo, stream, B2_TILE_AUTO);
   return b2_int8_gemm_situ_glu(&a, out, ldo, stream, B2_TILE_AUTO);
@@ -766,7 +801,8 @@ int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_
 int b2_w4a8_gemm_noalloc(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_w4_weight* w, int64_t m, int64_t n,
                          int64_t k, int epilogue, const void* aux, void* out, int64_t ldo, void* stream) {
   constexpr const char* op = "w4a8_gemm_noalloc";
-  if (n <= 0 || k <= 0 || static_cast<std::uint64_t>(n) * static_cast<std::uint64_t>(k) > kStaticScratchBytes) {
+  // Division, not a product: n * k cannot wrap, whatever the caller passes.
+  if (n <= 0 || k <= 0 || static_cast<std::uint64_t>(n) > kStaticScratchBytes / static_cast<std::uint64_t>(k)) {
     return fail_invalid(op, "the decoded weight (n * k = " + std::to_string(n) + " * " + std::to_string(k) +
                                 " bytes) does not fit the built-in scratch of " + std::to_string(kStaticScratchBytes) +
                                 " bytes; use b2_w4a8_gemm with a caller-owned scratch buffer");
@@ -775,6 +811,5 @@ int b2_w4a8_gemm_noalloc(const int8_t* x_q, int64_t ldx, const float* x_scale, c
   if (const int rc = static_scratch(&scratch)) return rc;
   return b2_w4a8_gemm(x_q, ldx, x_scale, w, m, n, k, epilogue, aux, out, ldo, scratch, stream);
 }
-
 
 }  // extern "C"

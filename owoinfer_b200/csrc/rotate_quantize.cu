@@ -456,9 +456,13 @@ __device__ __forceinline__ float e4m3_bits_to_float(std::uint32_t b) {
   return (b & 0x80) ? -mag : mag;
 }
 
-// 16 columns per thread (8 packed bytes): level * group scale, rne, clamp to +-127.
+// Raised (OR 1) by a decode that met a NaN or negative group scale and was given no word of the caller's.
+__device__ unsigned g_w4_invalid = 0;
+
+// 16 columns per thread (8 packed bytes): level * group scale, rne, clamp to +-127. A group whose scale is NaN or
+// negative decodes to zeros and raises *invalid (src/kernels/quant/w4a8_decode.cu:57-62).
 __global__ void decode_grouped_kernel(const std::uint8_t* packed, const void* s_rel, int scale_kind, const float* codebook,
-                                      std::int64_t rows, std::int64_t k, int group, std::int8_t* out) {
+                                      std::int64_t rows, std::int64_t k, int group, std::int8_t* out, unsigned* invalid) {
   __shared__ float s_cb[16];
   if (threadIdx.x < 16) s_cb[threadIdx.x] = codebook != nullptr ? codebook[threadIdx.x] : static_cast<float>(threadIdx.x) - 8.0f;
   __syncthreads();
@@ -470,6 +474,7 @@ __global__ void decode_grouped_kernel(const std::uint8_t* packed, const void* s_
     float s;
     if (scale_kind == 0) s = e4m3_bits_to_float(static_cast<const std::uint8_t*>(s_rel)[gi]);
     else s = __half2float(__ushort_as_half(static_cast<const unsigned short*>(s_rel)[gi]));
+    const bool ok = !(isnan(s) || s < 0.0f);
     const uint2 in = *reinterpret_cast<const uint2*>(packed + r * (k / 2) + c0 / 2);
     const std::uint32_t w[2] = {in.x, in.y};
     std::uint32_t o[4];
@@ -483,9 +488,10 @@ __global__ void decode_grouped_kernel(const std::uint8_t* packed, const void* s_
         const float vq = fminf(127.f, fmaxf(-127.f, rintf(fmul(s_cb[code], s))));
         word |= (static_cast<std::uint32_t>(static_cast<int>(vq)) & 0xFF) << (8 * b);
       }
-      o[j] = word;
+      o[j] = ok ? word : 0u;
     }
     *reinterpret_cast<uint4*>(out + r * k + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+    if (!ok) atomicOr(invalid, 1u);
   }
 }
 
@@ -571,20 +577,38 @@ int b2_unpack_int4(const void* packed, int64_t ldp, int8_t* out, int64_t ldo, in
 }
 
 int b2_decode_grouped_int8(const void* packed, const void* s_rel, int scale_kind, const float* codebook, int64_t rows,
-                           int64_t k, int group, int8_t* out, void* stream) {
+                           int64_t k, int group, int8_t* out, unsigned* invalid, void* stream) {
   constexpr const char* op = "decode_grouped_int8";
   if (rows < 0 || k <= 0 || group <= 0 || group % 16 != 0 || k % group != 0 || (scale_kind != 0 && scale_kind != 1)) {
     return fail_invalid(op, "needs group % 16 == 0, k % group == 0 and scale_kind 0 (e4m3) or 1 (fp16)");
   }
+  // The extents of a GEMM weight: the kernel's index arithmetic (rows * k / 16 work items) cannot wrap inside them.
+  if (rows > 0x7fffffff || k > 131071) return fail_invalid(op, "needs rows < 2^31 and k <= 131071");
   if (rows == 0) return B2_OK;
   if (packed == nullptr || s_rel == nullptr || out == nullptr || !aligned_to(packed, 8) || !aligned_to(out, 16)) {
     return fail_invalid(op, "null or misaligned operand");
   }
+  if (invalid == nullptr) {
+    void* word = nullptr;
+    if (const cudaError_t e = cudaGetSymbolAddress(&word, g_w4_invalid); e != cudaSuccess) return fail_cuda(op, e);
+    invalid = static_cast<unsigned*>(word);
+  }
   const std::int64_t total = rows * (k / 16);
   const unsigned blocks = static_cast<unsigned>(std::min<std::int64_t>((total + 255) / 256, 148 * 16));
   decode_grouped_kernel<<<blocks, 256, 0, as_stream(stream)>>>(static_cast<const std::uint8_t*>(packed), s_rel, scale_kind,
-                                                              codebook, rows, k, group, out);
+                                                              codebook, rows, k, group, out, invalid);
   return check_launch(op);
+}
+
+int b2_w4_invalid_scales(unsigned* host_value, int clear) {
+  constexpr const char* op = "w4_invalid_scales";
+  if (host_value == nullptr) return fail_invalid(op, "null output");
+  if (const cudaError_t e = cudaMemcpyFromSymbol(host_value, g_w4_invalid, sizeof(unsigned)); e != cudaSuccess) return fail_cuda(op, e);
+  if (clear != 0) {
+    const unsigned zero = 0;
+    if (const cudaError_t e = cudaMemcpyToSymbol(g_w4_invalid, &zero, sizeof(unsigned)); e != cudaSuccess) return fail_cuda(op, e);
+  }
+  return B2_OK;
 }
 
 }  // extern "C"

@@ -80,14 +80,21 @@ def unpack_int4(packed, out=None):
     return out
 
 
-def decode_grouped_int8(packed, s_rel, group, codebook=None, out=None):
+def decode_grouped_int8(packed, s_rel, group, codebook=None, out=None, invalid=None):
+    """invalid: optional uint32/int32 device tensor of one element, OR-ed with 1 when a group scale is NaN or negative."""
     rows, kb = packed.shape
     k = kb * 2
     kind = 0 if s_rel.dtype in (torch.uint8, torch.int8) else 1
     out = torch.empty((rows, k), dtype=torch.int8, device=packed.device) if out is None else out
     check(_lib.lib().b2_decode_grouped_int8(_ptr(packed), _ptr(s_rel), C.c_int(kind), _ptr(codebook), C.c_int64(rows),
-                                            C.c_int64(k), C.c_int(group), _ptr(out), _stream()))
+                                            C.c_int64(k), C.c_int(group), _ptr(out), _ptr(invalid), _stream()))
     return out
+
+
+def w4_invalid_scales(clear=False):
+    v = C.c_uint(0)
+    check(_lib.lib().b2_w4_invalid_scales(C.byref(v), C.c_int(1 if clear else 0)))
+    return int(v.value)
 
 
 # ------------------------------------------------------------------------------------------------ GEMMs

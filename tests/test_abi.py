@@ -29,7 +29,12 @@ def test_library_exports_every_declared_symbol():
 
 def test_numerics_versions():
     lib = _lib.lib()
-    assert [lib.b2_numerics_version(i) for i in range(3)] == [1, 1, 1]
+    # quant.h:38, quant4.h:36, w4a8_decode.h:27: bit-identical to the reference's version 1; the attention word carries
+    # the reference's contract version (attention_q8.h:73) in its low half and this kernel's own revision above it.
+    assert [lib.b2_numerics_version(i) for i in (0, 1, 3)] == [1, 1, 1]
+    att = lib.b2_numerics_version(2)
+    assert att & 0xFFFF == 1 and att >> 16 >= 1
+    assert lib.b2_numerics_version(7) == 0 and lib.b2_numerics_version(-1) == 0
 
 
 def _status(rc):
@@ -100,6 +105,63 @@ def test_gemm_rejects_bad_operands():
     assert rc == -1
     # m == 0: nothing runs.
     assert lib.b2_int8_gemm(C.byref(_ops(m=0)), None, A16, C.c_int64(264), None, 0) == 0
+
+
+def _w4(packed=A16, s_rel=A16, kind=0, group=64, s_channel=A16):
+    return _lib.W4Weight(packed.value, s_rel.value, kind, group, None, s_channel.value)
+
+
+def test_w4a8_gemm_checks_every_argument_before_the_decode():
+    """Nothing may be launched for a rejected call (the operands here are fake addresses: a launch would fault, and this
+    process has no device at all): the GEMM's own argument rules are applied up front."""
+    lib = _lib.lib()
+    f = lib.b2_w4a8_gemm
+    i64 = C.c_int64
+
+    def call(x=A16, ldx=512, xs=A16, w=None, m=4, n=264, k=512, epi=0, aux=None, out=A16, ldo=264, scratch=A16):
+        w = _w4() if w is None else w
+        return _status(f(x, i64(ldx), xs, C.byref(w), i64(m), i64(n), i64(k), C.c_int(epi), aux, out, i64(ldo), scratch, None))
+
+    assert call(x=None)[0] == -1                 # x_q null with m > 0
+    assert call(x=A8)[0] == -1                   # x_q misaligned
+    assert call(ldx=500)[0] == -1                # ldx % 16
+    assert call(k=520, ldx=520)[0] == -1         # k % 16
+    assert call(n=260, ldo=264)[0] == -1         # n % 8
+    assert call(out=None)[0] == -1
+    assert call(ldo=256)[0] == -1                # ldo < n
+    assert call(epi=1, aux=None)[0] == -1        # gated residual without a gate
+    assert call(epi=1, aux=A8)[0] == -1          # misaligned gate
+    assert call(epi=2, n=268)[0] == -1           # F % 4
+    assert call(epi=3)[0] == -1
+    assert call(scratch=None)[0] == -1
+    assert call(n=1 << 33)[0] == -1 and call(k=1 << 31, ldx=1 << 31)[0] == -1
+    assert call(w=_w4(group=24))[0] == -1        # group % 16
+    assert call(w=_w4(group=96))[0] == -1        # k % group
+    assert call(w=_w4(kind=2))[0] == -1
+    assert call(w=_w4(packed=C.c_void_p(0x1004)))[0] == -1
+    assert call(m=0)[0] == 0                     # no-op, nothing decoded
+
+
+def test_w4a8_noalloc_size_check_cannot_wrap():
+    """n * k is compared by division: extents whose 64-bit product wraps to a small number are still refused."""
+    lib = _lib.lib()
+    f = lib.b2_w4a8_gemm_noalloc
+    i64 = C.c_int64
+    w = _w4()
+    for n, k in ((1 << 33, 1 << 31), (1 << 62, 4), (1 << 40, 1 << 24), (4096, 8192), (0, 512), (512, 0), (-8, 512)):
+        rc, msg = _status(f(A16, i64(512), A16, C.byref(w), i64(4), i64(n), i64(k), C.c_int(0), None, A16, i64(264), None))
+        assert rc == -1 and "does not fit" in msg, (n, k, msg)
+
+
+def test_decode_grouped_rejects_bad_extents():
+    lib = _lib.lib()
+    f = lib.b2_decode_grouped_int8
+    i64 = C.c_int64
+    assert f(A16, A16, 0, None, i64(1 << 33), i64(512), 64, A16, None, None) == -1
+    assert f(A16, A16, 0, None, i64(8), i64(1 << 20), 64, A16, None, None) == -1
+    assert f(A16, A16, 0, None, i64(8), i64(512), 24, A16, None, None) == -1
+    assert f(A16, A16, 3, None, i64(8), i64(512), 64, A16, None, None) == -1
+    assert f(None, None, 0, None, i64(0), i64(512), 64, None, None, None) == 0
 
 
 def test_attention_rejects_bad_arguments():

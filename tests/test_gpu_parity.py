@@ -278,6 +278,45 @@ def test_w4a8_gemm_equals_decode_then_gemm(ops):
     assert (u16(got) == orc.int8_gemm_situ_glu(xq.cpu().numpy(), xs.cpu().numpy(), w8, s_ch.cpu().numpy())).mean() >= 0.999
 
 
+def test_grouped_decode_untrusted_scales(ops):
+    """src/kernels/quant/w4a8_decode.cu:57-62: a NaN or negative group scale zeroes its group and raises the invalid
+    word, both through the caller's word and through the library's own (which the W4A8 GEMM uses)."""
+    rng = np.random.default_rng(3)
+    packed = rng.integers(0, 256, (24, 256), dtype=np.uint8)
+    srel = rng.integers(0x20, 0x48, (24, 8), dtype=np.uint8)
+    srel[2, 1], srel[9, 7], srel[17, 0] = 0x7F, 0xFF, 0xB0
+    want, flag = orc.decode_grouped_int8_device_rule(packed, srel, 64)
+    assert flag == 1
+    word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ops.decode_grouped_int8(dev(packed), dev(srel), 64, invalid=word)
+    assert np.array_equal(got.cpu().numpy(), want) and int(word.item()) == 1
+    ops.w4_invalid_scales(clear=True)
+    got = ops.decode_grouped_int8(dev(packed), dev(srel), 64)
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert ops.w4_invalid_scales(clear=True) == 1 and ops.w4_invalid_scales() == 0
+    # fp16 scales, and a clean tensor leaves the word alone
+    s16 = np.full((24, 8), 0x3C00, np.uint16)
+    s16[5, 5] = 0xBC00
+    want, _ = orc.decode_grouped_int8_device_rule(packed, s16, 64)
+    word.zero_()
+    got = ops.decode_grouped_int8(dev(packed), dev(s16.view(np.int16)), 64, invalid=word)
+    assert np.array_equal(got.cpu().numpy(), want) and int(word.item()) == 1
+    word.zero_()
+    ops.decode_grouped_int8(dev(packed), dev(np.full((24, 8), 0x38, np.uint8)), 64, invalid=word)
+    assert int(word.item()) == 0
+
+
+def test_gemm_acc_with_ragged_n(ops):
+    """The accumulator dump takes any n (it reads no per-column vector): n % 4 != 0, with the scale vectors allocated at
+    exactly n and m elements so that a read past their end would be caught by the allocator's neighbours."""
+    rng = np.random.default_rng(9)
+    for m, n, k in ((37, 130, 256), (129, 257, 512), (5, 7, 64)):
+        a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+        b = rng.integers(-128, 128, (n, k), dtype=np.int8)
+        acc = ops.int8_gemm_acc(dev(a), dev(b))
+        assert np.array_equal(acc.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32).T)
+
+
 def test_gemm_linearity_at_full_size(ops):
     # Size-independent property at the BASELINE shape (8192 x 9216 x 3072): acc(x, w) + acc(x2, w) == acc over the
     # concatenated K of [x | x2] and [w | w], checked on the int32 accumulators through sampled rows' exact dot products.

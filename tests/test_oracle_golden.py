@@ -182,6 +182,33 @@ def test_against_reference_codec_sources():
     assert np.array_equal(orc.decode_grouped_int8(packed, vals.astype(np.float16).view(np.uint16), 64), want)
 
 
+def test_grouped_decode_device_rule_for_untrusted_scales():
+    """src/kernels/quant/w4a8_decode.cu:57-62: a NaN (0x7F, 0xFF) or negative group scale decodes its group to zeros and
+    raises the invalid word; every other group decodes as the CPU codec does (which rejects the whole tensor instead,
+    quant_codec.cpp:196)."""
+    rng = np.random.default_rng(11)
+    packed = rng.integers(0, 256, (12, 128), dtype=np.uint8)
+    srel = rng.integers(0x20, 0x48, (12, 4), dtype=np.uint8)
+    clean, flag = orc.decode_grouped_int8_device_rule(packed, srel, 64)
+    assert flag == 0 and np.array_equal(clean, orc.decode_grouped_int8(packed, srel, 64))
+    bad = srel.copy()
+    bad[1, 0], bad[5, 3], bad[7, 2] = 0x7F, 0xFF, 0xA8  # NaN, NaN, a negative value
+    got, flag = orc.decode_grouped_int8_device_rule(packed, bad, 64)
+    want = clean.copy()
+    want[1, 0:64] = 0
+    want[5, 192:256] = 0
+    want[7, 128:192] = 0
+    assert flag == 1 and np.array_equal(got, want)
+    with pytest.raises(ValueError):
+        orc.decode_grouped_int8(packed, bad, 64)
+    # fp16 scales: NaN, -1.0 and -0.0 (not negative: decodes to zeros through the product, no flag).
+    s16 = np.full((12, 4), 0x3C00, np.uint16)  # 1.0
+    s16[0, 0], s16[2, 1], s16[3, 2] = 0x7E00, 0xBC00, 0x8000
+    got, flag = orc.decode_grouped_int8_device_rule(packed, s16, 64)
+    assert flag == 1 and not got[0, 0:64].any() and not got[2, 64:128].any() and not got[3, 128:192].any()
+    assert got[0, 64:].any() and got[4].any()
+
+
 # ------------------------------------------------------------------ QK norm + RoPE, RoPE table
 
 def test_rope_bands():
