@@ -6,7 +6,7 @@ python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAM
 Default workload `step1024`: the full INT8 'high'-tier denoising step at 1024^2 (42 blocks of d=3072, 24x128 heads, MLP
 12288, CFG batch 2 = two 8192-token sequences per image), one image per GPU (no collective: weak scaling). One "step" is
 one pass of all blocks over the image's 16384 tokens through the C ABI (b2_dit_step). Other workloads:
-  block1024            one block on one 8192-token sequence (BASELINE configs[1])
+  block1024            one block on one 8192-token sequence
   step1024_cfgsplit    the step with the CFG halves on two GPUs (N = 2, strong scaling against step1024 at N = 1)
   step2048             the 2048^2 step (2 x 20480 tokens) on one GPU through b2_dit_step: the base of step2048_ulysses
   step2048_ulysses     the 2048^2 step (two 20480-token sequences) with Ulysses sequence parallelism over N GPUs
@@ -139,6 +139,24 @@ def workload_shape(name: str, world: int):
     raise SystemExit(f"unknown workload {name}")
 
 
+TIER_NAMES = ["int8", "w4a4_via_int8", "w4a8"]
+
+
+def workload_config(args, world: int, launch: str):
+    """The `config` object of the JSON line: the same for this library's arm and for the reference arm."""
+    seq_len, seqs = workload_shape(args.workload, world)
+    n_blocks = 1 if args.workload == "block1024" else args.blocks
+    strong = args.workload == "step1024_cfgsplit"
+    return {"workload": args.workload, "blocks": n_blocks, "d": D, "heads": HEADS, "ffn": args.ffn,
+            "tokens_per_gpu_step": seq_len * seqs, "sequences": [seq_len] * seqs,
+            "tier": TIER_NAMES[2 if args.workload == "turbo1024" else 0], "attention": "int8_fp8_f32acc",
+            "parallelism": "cfg-split2" if strong else f"image-dp{world}",
+            "l2": "inputs larger than L2 (block weights stream from HBM every step)", "launch": launch}
+
+
+CPU_SAMPLE_TOKENS, CPU_SAMPLE_KEYS = 256, 1536  # both CPU legs time the same bounded sample
+
+
 def run_reference(args, rank, world):
     """The reference arm: the reference engine has no CPU implementation of the quantized block and ships no sm_100
     kernel, so its CPU path for this metric is the oracle port of its arithmetic, run with every host thread on a bounded
@@ -148,7 +166,7 @@ def run_reference(args, rank, world):
     threads = os.cpu_count() or 1
     seq_len, seqs = workload_shape(args.workload, 1)
     blocks = 1 if args.workload == "block1024" else args.blocks
-    bt, at = 128, 1024
+    bt, at = CPU_SAMPLE_TOKENS, CPU_SAMPLE_KEYS
     vals = []
     for i in range(args.warmup + args.steps):
         tb, ta = cpu_sample(args.ffn, bt, at, threads)
@@ -156,13 +174,14 @@ def run_reference(args, rank, world):
             vals.append(cpu_extrapolate(tb, ta, bt, at, seq_len, seqs, blocks))
     v = statistics.mean(vals)
     sample = (f"per step: one block on {bt} tokens + 8-bit attention of one {at}-token sequence x 24 heads, extrapolated "
-              f"(linear part by tokens, attention by tokens^2) to {blocks} blocks x {seqs} x {seq_len} tokens")
+              f"(linear part by tokens, attention by tokens^2) to {blocks} blocks x {seqs} x {seq_len} tokens; a CPU port of "
+              "the reference's arithmetic (the reference has no CPU implementation of the quantized block)")
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": v, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8", "data": "synthetic",
-            "config": {"workload": args.workload, "blocks": blocks, "ffn": args.ffn, "tokens_per_step": seq_len * seqs,
-                       "note": "CPU port of the reference's arithmetic (the reference has no CPU block path)"},
-            "cpu_baseline": {"value": v, "unit": "ms", "cores": threads, "kind": "port", "sample": sample},
+            "warmup": args.warmup, "ms_per_step": v, "higher_is_better": False,
+            "scaling": "strong" if args.workload == "step1024_cfgsplit" else "weak", "vs_baseline": None,
+            "dtype": "int8", "data": "synthetic", "extrapolated": True,
+            "config": workload_config(args, max(1, args.gpus), "cuda graph replay"),
+            "cpu_baseline": {"value": v, "unit": "ms", "cores": threads, "kind": "port", "sample": sample, "extrapolated": True},
             "e2e": {"value": v, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -196,9 +215,11 @@ def reference_kernels_on_this_gpu(torch, ops, keep, x, x0, mod, rope, cu, seq_le
             "steps": n, "blocks": len(keep), "per_kernel": profile_kernels(ops, torch, L, F, keep[0][0], iters=4, ref=refk)}
 
 
-# DRAM bytes (read + write, MB) of the four GEMM launches of one block at 16384 tokens, F = 12288, from the ncu capture
-# summarised in profiles/traffic_step1024_one_block.md.
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, MB) of the four GEMM launches of one block at 16384 tokens,
+# F = 12288, from one ncu capture of exactly those launches. They describe the GEMM kernel as of GEMM_DRAM_COMMIT; a change
+# to its tile order or tile shape needs a new capture.
 GEMM_DRAM_MB = {"qkv": 90.4 + 253.1, "o": 160.6 + 47.3, "up_gate": 231.7 + 380.4, "down": 725.2 + 85.7}
+GEMM_DRAM_COMMIT = "a8d2e72"
 
 
 def gemm_sites(L, F):
@@ -274,7 +295,51 @@ def profile_kernels(ops, torch, L, F, w, iters=8, ref=None):
         _, wsa = ops.attention_q8(*views, o, cu, cu, sl, ops.SM_SCALE, norm_rope=(qn, qn, rope))
         ms = timed(lambda: ops.attention_q8(*views, o, cu, cu, sl, ops.SM_SCALE, workspace=wsa, norm_rope=(qn, qn, rope)))
     out["attention_q8"] = {"ms": ms, "tops": 4.0 * seqs * sl * sl * D / ms / 1e9}
+    if ref:
+        return out
+    ms = timed(lambda: ops.attention_q8_preprocess(*views, cu, cu, sl, workspace=wsa, norm_rope=(qn, qn, rope)))
+    out["attention_prepass"] = {"ms": ms, "gbs": (9.0 * L * D + 256.0 * L) / ms / 1e6}
     return out
+
+
+def roofline_record(prof, L, F, seq_len, seqs):
+    """The `roofline` object: every kernel family of one block with its bound, its achieved rate from the launch times
+    measured in this run (CUDA events, each launch alone after an L2 flush) and its share of the block; the top-level
+    figures are the tensor-bound kernels (the four GEMM sites and the attention kernel, 85-90 % of a block) taken
+    together, i.e. weighted by their time."""
+    pk = peaks()
+    tensor_peak, hbm_peak = 2.0 * pk["bf16"], pk["hbm_gbs"]
+    src = f"{pk['source']} peaks: 2 x bf16 burst for the 8-bit tensor work (no INT8/FP8 figure is measured; nominal dense 4500), copy bandwidth for HBM"
+    gemm_ops = sum(2.0 * L * n * k for _, n, k, _ in gemm_sites(L, F))
+    gemm_ms = sum(prof[name]["ms"] for name, *_ in gemm_sites(L, F))
+    attn_ops = 4.0 * seqs * seq_len * seq_len * D
+    pre_ms = prof["attention_prepass"]["ms"]
+    attn_ms = max(prof["attention_q8"]["ms"] - pre_ms, 1e-6)
+    pre_bytes = 9.0 * L * D + 256.0 * L
+    rows = [
+        ("int8_gemm_kernel (qkv, o, up_gate, down)", "tensor", gemm_ops / gemm_ms / 1e9, gemm_ms),
+        ("attention_kernel", "tensor", attn_ops / attn_ms / 1e9, attn_ms),
+        ("attention pre-pass (norm_rope_quant_q, stats, finalize, quant_kv)", "hbm", pre_bytes / pre_ms / 1e6, pre_ms),
+        ("rotate_quantize_kernel with the norm prologue (two per block)", "hbm", prof["norm_rotate_quantize"]["gbs"],
+         2.0 * prof["norm_rotate_quantize"]["ms"]),
+        ("rotate_quantize_kernel (attention output, FFN hidden)", "hbm",
+         3.0 * L * (D + F) / (prof["rotate_quantize"]["ms"] + prof["rotate_quantize_ffn"]["ms"]) / 1e6,
+         prof["rotate_quantize"]["ms"] + prof["rotate_quantize_ffn"]["ms"]),
+    ]
+    block_ms = sum(r[3] for r in rows)
+    kernels = [{"name": n, "bound": b, "achieved": a, "peak": tensor_peak if b == "tensor" else hbm_peak,
+                "unit": "TOP/s" if b == "tensor" else "GB/s", "frac": a / (tensor_peak if b == "tensor" else hbm_peak),
+                "ms_per_block": ms, "share_of_block": ms / block_ms} for n, b, a, ms in rows]
+    achieved = (gemm_ops + attn_ops) / (gemm_ms + attn_ms) / 1e9
+    full = (L, F) == (16384, 12288)
+    return {"bound": "tensor", "kernel": "int8_gemm_kernel (4 sites) + attention_kernel of one block, weighted by time",
+            "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
+            "frac_of_nominal": achieved / 4500.0, "peak_source": src,
+            "traffic": sum(GEMM_DRAM_MB.values()) * 1e6 if full else None,
+            "traffic_note": ("dram read + write bytes of the four GEMM launches at 16384 tokens, F = 12288, from an ncu capture of the "
+                             f"kernel as of commit {GEMM_DRAM_COMMIT} (algorithmic operand + output bytes: 1610.6e6); the attention "
+                             "kernel moves its operands through L2 (under 0.2e9 DRAM bytes per launch)"),
+            "block_ms_sum_of_kernels": block_ms, "kernels": kernels, "per_kernel": prof}
 
 
 def main():
@@ -407,35 +472,20 @@ def main():
     line = {"metric": ("dit_ms_per_step_2048" if seq_len > 16384 else METRIC), "value": ms_step / units, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False, "scaling": scaling,
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": args.workload, "blocks": n_blocks, "d": D, "heads": HEADS, "ffn": F,
-                       "tokens_per_gpu_step": L, "sequences": [seq_len] * seqs, "tier": ["int8", "w4a4_via_int8", "w4a8"][tier],
-                       "attention": "int8_fp8_f32acc", "parallelism": f"image-dp{world}" if scaling == "weak" else "cfg-split2",
-                       "l2": "inputs larger than L2 (block weights stream from HBM every step)",
-                       "launch": "direct" if graph is None else "cuda graph replay"},
+            "config": workload_config(args, world, "direct" if graph is None else "cuda graph replay"),
             "e2e": {"value": e2e_ms / units, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches_per_block * n_blocks * args.steps, "kernel_status": list(g_stat)}
     if rank == 0:
         line["clocks"] = clocks
         if not args.no_profile:
-            pk = peaks()
             prof = profile_kernels(ops, torch, L, F, keep[0][0] if tier == ops.TIER_INT8 else synth.block_weights(D, F, 1, tier=0))
-            total_ops = sum(2.0 * L * n * k for _, n, k, _ in gemm_sites(L, F))
-            total_ms = sum(prof[name]["ms"] for name, *_ in gemm_sites(L, F))
-            achieved = total_ops / total_ms / 1e9
-            peak = 2.0 * pk["bf16"]
-            line["roofline"] = {"bound": "tensor", "kernel": "int8_gemm_kernel (4 sites of one block)", "achieved": achieved,
-                                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                                "peak_source": f"2 x bf16 burst of {pk['source']} peaks (no INT8 figure is measured); nominal dense INT8 4500",
-                                "frac_of_nominal": achieved / 4500.0,
-                                "traffic": sum(GEMM_DRAM_MB.values()) * 1e6 if (L, F) == (16384, 12288) else None,
-                                "traffic_note": "dram read + write bytes of the four launches at 16384 tokens, F = 12288 (ncu, "
-                                                "profiles/traffic_step1024_one_block.md); algorithmic operand + output bytes: 1610.6e6",
-                                "per_kernel": prof}
+            line["roofline"] = roofline_record(prof, L, F, seq_len, seqs)
             threads = os.cpu_count() or 1
-            tb, ta = cpu_sample(F, 256, 1536, threads)
-            v = cpu_extrapolate(tb, ta, 256, 1536, seq_len, seqs, n_blocks)
-            line["cpu_baseline"] = {"value": v, "unit": "ms", "cores": threads, "kind": "port",
-                                    "sample": f"one block on 256 tokens ({tb:.2f} s) + attention of one 1536-token sequence x 24 "
+            bt, at = CPU_SAMPLE_TOKENS, CPU_SAMPLE_KEYS
+            tb, ta = cpu_sample(F, bt, at, threads)
+            v = cpu_extrapolate(tb, ta, bt, at, seq_len, seqs, n_blocks)
+            line["cpu_baseline"] = {"value": v, "unit": "ms", "cores": threads, "kind": "port", "extrapolated": True,
+                                    "sample": f"one block on {bt} tokens ({tb:.2f} s) + attention of one {at}-token sequence x 24 "
                                               f"heads ({ta:.2f} s), extrapolated to {n_blocks} blocks x {seqs} x {seq_len} tokens"}
             if world == 1 and tier == ops.TIER_INT8 and not args.no_ref_gpu:
                 line["reference_gpu"] = reference_kernels_on_this_gpu(torch, ops, keep, x, x0, mod, rope, cu, seq_len, L, F)

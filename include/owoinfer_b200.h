@@ -203,6 +203,19 @@ int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_v
                     int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
                     const b2_qk_norm_rope* norm_rope);
 
+/* Test hook. b2_attention_q8 with the same arguments, which additionally stores the raw int32 Q8·K8^T accumulators that
+ * the attention kernel's softmax threads read from tensor memory, for the 128 query rows of tile `tile_q` of
+ * (sequence `seq`, head `head`): scores int32 [128, ld], row r = query tile_q * 128 + r of the sequence, column j = key j
+ * (ld >= 64 * ceil(kv_len / 64)); rows at or past the sequence's end and columns at or past kv_len are unspecified.
+ * The regular output is produced as well (by a second instantiation of the same kernel). These are the integer scores
+ * of third_party/sageattention/csrc/qattn/qk_int_sv_f8_cuda_sm89.cuh:290-345; the reference has no such hook (its
+ * tests compute them with a scalar kernel, tests/unit/test_attention_q8.cu). */
+int b2_attention_q8_debug_scores(const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
+                                 const b2_view3* out, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
+                                 int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
+                                 const b2_qk_norm_rope* norm_rope, int seq, int head, int tile_q, int32_t* scores,
+                                 int64_t ld);
+
 /* The workspace layout of attention_q8.cu:47-73 as this library carves it (byte offsets from the 256-byte aligned base),
  * exposed so tests can compare the pre-pass outputs with the oracle: q_i8, k_i8 int8 and v8 e4m3 [total, heads, 128]
  * (V stays in its natural layout: the tensor core reads it as an MN-major operand, so there is no transposed, padded or

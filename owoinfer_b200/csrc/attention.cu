@@ -35,8 +35,8 @@ constexpr std::size_t kAlign = 256;
 
 __device__ int g_attn_status = 0;
 #ifdef B2_ATTN_TRACE
-__device__ long long g_attn_trace[4096];
-#define TRACE(slot) do { if (tracing) a.trace[u * 8 + (slot)] = clock64(); } while (0)
+__device__ long long g_attn_trace[8192];
+#define TRACE(slot) do { if (tracing) a.trace[u * 16 + (slot)] = clock64(); } while (0)
 #else
 #define TRACE(slot) do { } while (0)
 #endif
@@ -561,20 +561,70 @@ __global__ void __launch_bounds__(256) quant_kv_kernel(const PrepArgs p) {
 // ---------------------------------------------------------------------------------------------------------------
 // The attention kernel.
 // ---------------------------------------------------------------------------------------------------------------
-// One softmax pass of one thread over its row's 64 scores of a sub-tile. |S| < 2^22, so the integer S + 0x4B400000 is
-// the bit pattern of the fp32 number 12582912 + S: one integer add converts (none when the accumulator was pre-filled
-// with that constant before Q·K^T, B2_ATTN_PREFILL), the order of the floats is the order of the integers, and the
-// constant is folded into `bias`. P = exp2(f * c + bias) with packed fp32 pairs for the FMA and the denominator; e4m3 P
-// goes into the swizzled P tile (row = 128 bytes, 16-byte chunk n of row r stored at chunk n ^ (r % 8); this sub-tile
-// owns chunks chunk0 .. chunk0 + 3). Returns the largest biased score (0 if none) and the sum of the unrounded P.
-#ifndef B2_ATTN_PREFILL
-#define B2_ATTN_PREFILL 0  // measured on B200: the pre-fill's tcgen05.wait::st before each hand-over costs more than the add
+// The score accumulator as the softmax threads see it. |S| < 2^22, so the integer S + 0x4B400000 is the bit pattern of
+// the fp32 number 12582912 + S: the order of those floats is the order of the integers and the constant folds into the
+// softmax bias. B2_ATTN_CONST_BIAS = 1 (default) lets the tensor core add the constant: each score accumulator is first
+// written by a K = 16 bf16 MMA of two constant operands whose dot product is exactly 12582912.0f (bit pattern
+// 0x4B400000), and the INT8 MMAs of Q·K^T then accumulate their exact integers on top of those bits, so a score read
+// back from tensor memory already is the float. With 0 the softmax threads add the constant with one integer add per
+// score.
+#ifndef B2_ATTN_CONST_BIAS
+#define B2_ATTN_CONST_BIAS 1
 #endif
-// Added to a score read back from TMEM: 0 when the accumulator was pre-filled with 0x4B400000, else that constant.
-constexpr std::uint32_t kScoreBias = B2_ATTN_PREFILL ? 0u : 0x4B400000u;
+constexpr std::uint32_t kScoreBits = 0x4B400000u;                       // 12582912.0f
+constexpr std::uint32_t kScoreBias = B2_ATTN_CONST_BIAS ? 0u : kScoreBits;  // what a thread still has to add
+// Of every 8 scores (4 pairs) this many pairs take 2^x from a polynomial on the FMA pipe instead of the special-function
+// unit (0 = none).
+#ifndef B2_ATTN_POLY_PAIRS
+#define B2_ATTN_POLY_PAIRS 0
+#endif
 
+__device__ __forceinline__ std::uint64_t add2_rm(std::uint64_t a, std::uint64_t b) {
+  std::uint64_t d;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ std::uint64_t sub2(std::uint64_t a, std::uint64_t b) {
+  std::uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^x for a pair without the special-function unit: x = floor(x) + r by a round-down add of 1.5 * 2^23 (whose low
+// mantissa bits then hold floor(x)), a cubic for 2^r on [0, 1) (relative error below 1e-4, far inside the e4m3 rounding
+// of P), and the integer part added into the exponent field. Inputs below -125 give the result for -125 (< 2^-124: zero
+// for every use here).
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
+  const std::uint64_t magic = pack2(12582912.f, 12582912.f);
+  const std::uint64_t x = pack2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const std::uint64_t fl_m = add2_rm(x, magic);
+  const std::uint64_t r = sub2(x, sub2(fl_m, magic));
+  std::uint64_t p = fma2(pack2(0.0555054f, 0.0555054f), r, pack2(0.2402265f, 0.2402265f));
+  p = fma2(p, r, pack2(0.6931472f, 0.6931472f));
+  p = fma2(p, r, pack2(1.f, 1.f));
+  float q0, q1, f0, f1;
+  unpack2(p, q0, q1);
+  unpack2(fl_m, f0, f1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(f0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(f1) << 23));
+}
+
+// One thread's 64 scores of a sub-tile, as read from tensor memory (four 16-column loads).
+struct ScoreRegs {
+  std::uint32_t a[16], b[16], c[16], d[16];
+};
+__device__ __forceinline__ void load_scores(std::uint32_t s_cols, ScoreRegs& r) {  // asynchronous: tmem_ld_wait() before use
+  tmem_ld_32x16(s_cols, r.a);
+  tmem_ld_32x16(s_cols + 16, r.b);
+  tmem_ld_32x16(s_cols + 32, r.c);
+  tmem_ld_32x16(s_cols + 48, r.d);
+}
+
+// One softmax pass of one thread over its row's 64 scores of a sub-tile, already in registers. P = exp2(f * c + bias)
+// with packed fp32 pairs for the FMA and the denominator (f the biased score, the constant folded into `bias`); e4m3 P goes
+// into the swizzled P tile (row = 128 bytes, 16-byte chunk n of row r stored at chunk n ^ (r % 8); this sub-tile owns
+// chunks chunk0 .. chunk0 + 3). Returns the largest biased score (0 if none) and the sum of the unrounded P.
 template <bool kFull>
-__device__ __forceinline__ void softmax_pass(std::uint32_t s_cols, float c, float bias, int valid, std::uint8_t* prow,
+__device__ __forceinline__ void softmax_pass(const ScoreRegs& s, float c, float bias, int valid, std::uint8_t* prow,
                                              int chunk0, int row_xor, float& bmax_out, float& sum_out) {
   const std::uint64_t c2 = pack2(c, c), bias2 = pack2(bias, bias);
   std::uint64_t dA = pack2(0.f, 0.f), dB = dA;
@@ -586,8 +636,12 @@ __device__ __forceinline__ void softmax_pass(std::uint32_t s_cols, float c, floa
       const float f0 = __uint_as_float(r[i] + kScoreBias), f1 = __uint_as_float(r[i + 1] + kScoreBias);
       float e0, e1;
       unpack2(fma2(pack2(f0, f1), c2, bias2), e0, e1);
-      pv[i] = ex2(e0);
-      pv[i + 1] = ex2(e1);
+      if (((i >> 1) & 3) < B2_ATTN_POLY_PAIRS) {
+        exp2_poly2(e0, e1, pv[i], pv[i + 1]);
+      } else {
+        pv[i] = ex2(e0);
+        pv[i + 1] = ex2(e1);
+      }
       if constexpr (kFull) {
         bmax = fmax3(bmax, f0, f1);
       } else {
@@ -606,16 +660,10 @@ __device__ __forceinline__ void softmax_pass(std::uint32_t s_cols, float c, floa
         make_uint4(e4m3x4(pv[0], pv[1], pv[2], pv[3]), e4m3x4(pv[4], pv[5], pv[6], pv[7]),
                    e4m3x4(pv[8], pv[9], pv[10], pv[11]), e4m3x4(pv[12], pv[13], pv[14], pv[15]));
   };
-  std::uint32_t ra[16], rb[16], rc[16], rd[16];
-  tmem_ld_32x16(s_cols, ra);
-  tmem_ld_32x16(s_cols + 16, rb);
-  tmem_ld_32x16(s_cols + 32, rc);
-  tmem_ld_32x16(s_cols + 48, rd);
-  tmem_ld_wait();
-  chunk(ra, 0);
-  chunk(rb, 1);
-  chunk(rc, 2);
-  chunk(rd, 3);
+  chunk(s.a, 0);
+  chunk(s.b, 1);
+  chunk(s.c, 2);
+  chunk(s.d, 3);
   float d0, d1, d2, d3;
   unpack2(dA, d0, d1);
   unpack2(dB, d2, d3);
@@ -623,10 +671,24 @@ __device__ __forceinline__ void softmax_pass(std::uint32_t s_cols, float c, floa
   sum_out = (d0 + d1) + (d2 + d3);
 }
 
+// The largest biased score among the first `valid` of the 64 (0 if none).
+__device__ __forceinline__ float max_score(const ScoreRegs& s, int valid) {
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    m = fmaxf(m, i < valid ? __uint_as_float(s.a[i] + kScoreBias) : 0.f);
+    m = fmaxf(m, 16 + i < valid ? __uint_as_float(s.b[i] + kScoreBias) : 0.f);
+    m = fmaxf(m, 32 + i < valid ? __uint_as_float(s.c[i] + kScoreBias) : 0.f);
+    m = fmaxf(m, 48 + i < valid ? __uint_as_float(s.d[i] + kScoreBias) : 0.f);
+  }
+  return m;
+}
+
 constexpr int kTileQ = 128, kTileK = 128, kSubK = 64;
 constexpr int kKvStages = 2;
 constexpr int kTileBytes = 128 * 128;
-constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 1) + 1024;  // Q, K/V stages, P, alignment slack
+constexpr int kConstBytes = B2_ATTN_CONST_BIAS ? 128 * 32 : 0;  // the constant operand of the score bias: 128 rows of 16 bf16
+constexpr int kAttnSmem = kTileBytes * (1 + 2 * kKvStages + 1) + kConstBytes + 1024;  // Q, K/V stages, P, constant, alignment slack
 constexpr int kAttnThreads = 192;  // TMA warp, MMA warp, 4 softmax warps
 constexpr std::uint32_t kTmemCols = 256;  // S(u % 2): columns [64 (u % 2), +64); O: columns [128, 256)
 // Softmax reference maximum: set kHeadroom binades above what the largest P needs, raised again once fewer than kRaise
@@ -645,18 +707,48 @@ struct AttnArgs {
   int heads, q_blocks, k_blocks;
   float scale_log2;  // sm_scale * log2(e)
   float p_offset;
+  // Test hook (kDump instantiation only): the raw integer scores of one (sequence, head, query tile).
+  std::int32_t* dump;
+  std::int64_t dump_ld;
+  int dump_seq, dump_head, dump_tile;
 #ifdef B2_ATTN_TRACE
   long long* trace;  // [sub-tile][8] clock64 stamps of CTA (0,0,0), softmax warp 2 lane 0 and the MMA warp
 #endif
 };
 
+// Shared-memory matrix descriptor of a K-major operand stored as 32-byte rows with the 32-byte swizzle: 8-row groups are
+// 256 bytes apart; layout type 6.
+__device__ __forceinline__ std::uint64_t umma_desc_sw32(std::uint32_t smem_addr) {
+  std::uint64_t d = 0;
+  d |= static_cast<std::uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<std::uint64_t>(1) << 16;
+  d |= static_cast<std::uint64_t>(256 >> 4) << 32;
+  d |= static_cast<std::uint64_t>(1) << 46;
+  d |= static_cast<std::uint64_t>(6) << 61;
+  return d;
+}
+__device__ __forceinline__ void umma_bf16(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
+                                          std::uint32_t idesc, std::uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // One CTA per (128 query rows, head, sequence), two CTAs per SM. K and V arrive in 128-key tiles; the tensor work runs in
 // 64-key sub-tiles u = 0, 1, ... (one K scale block each) with the score accumulator double-buffered in TMEM, so the MMA
 // warp computes S(u + 1) while the softmax warps turn S(u) into P(u):
-//   MMA warp      S(u % 2) = Q · K(u)^T (N = 64), O += P(u % 2) · V(u) (K = 64)
-//   softmax warps one thread per query row (TMEM lane), 64 scores per sub-tile: no exchange between threads
+//   MMA warp      S(u % 2) = [bias constant +] Q · K(u)^T (N = 64), O += P(u % 2) · V(u) (K = 64)
+//   softmax warps one thread per query row (TMEM lane), 64 scores per sub-tile: no exchange between threads. A warp's
+//                 loop is a chain of latencies (barrier test, tensor-memory load, votes, fences), so it is software
+//                 pipelined: the loads of S(u + 1) are issued right after P(u) is handed over and land during the
+//                 bookkeeping in between, and the K scale of the next sub-tile is fetched a whole pass ahead.
 //   P             e4m3, the two buffers interleaved in one swizzled [128 x 128 B] tile: buffer i = bytes [64 i, +64) of
 //                 each row
+// kDump: the instantiation behind b2_attention_q8_debug_scores, which also stores one tile's raw integer scores.
+template <bool kDump>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const AttnArgs a) {
@@ -686,6 +778,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const auto k_smem = [&](int s) { return base + kTileBytes * (1 + s); };
   const auto v_smem = [&](int s) { return base + kTileBytes * (1 + kKvStages + s); };
   const std::uint32_t p_smem = base + kTileBytes * (1 + 2 * kKvStages);
+  const std::uint32_t const_smem = p_smem + kTileBytes;
   std::uint8_t* p_generic = smem_raw + (p_smem - smem_u32(smem_raw));
 
   if (threadIdx.x == 0) {
@@ -742,13 +835,15 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #endif
     constexpr std::uint32_t idesc_qk = umma_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, 0, 0, 128, kSubK);
     constexpr std::uint32_t idesc_pv = umma_idesc(/*f32*/ 1, /*e4m3*/ 0, /*e4m3*/ 0, 0, /*B MN-major*/ 1, 128, 128);
+    constexpr std::uint32_t idesc_bias = umma_idesc(/*f32*/ 1, /*bf16*/ 1, /*bf16*/ 1, 0, 0, 128, kSubK);
     const std::uint64_t dq = umma_desc_sw128(q_smem), dp = umma_desc_sw128(p_smem);
+    const std::uint64_t dconst = umma_desc_sw32(const_smem);
     static_assert(kKvStages == 2, "the descriptors below are selected, not indexed");
     const std::uint64_t dk0 = umma_desc_sw128(k_smem(0)), dk1 = umma_desc_sw128(k_smem(1));
     const std::uint64_t dv0 = umma_desc_sw128(v_smem(0)), dv1 = umma_desc_sw128(v_smem(1));
     // 64 keys = 64 rows of 128 bytes of a K or V tile: 8192 bytes, 512 in the descriptors' 16-byte units.
     constexpr std::uint32_t kHalfTile = 64 * 128 / 16;
-    // S(u % 2) = Q · K(u)^T. The K tile goes back to the TMA warp after its second half.
+    // S(u % 2) = [12582912.0f +] Q · K(u)^T. The K tile goes back to the TMA warp after its second half.
     const auto issue_qk = [&](int u) -> bool {
       const int s = (u >> 1) % kKvStages;
       bool got = true;
@@ -756,10 +851,13 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (__any_sync(0xffffffffu, !got)) return false;
       tc_fence_after();
       if (elect_one()) {
+        const std::uint32_t d_s = tmem_s + static_cast<std::uint32_t>(u & 1) * kSubK;
+        // The constant operand serves as A (128 rows) and as B (its first 64 rows): every row holds the same 16 values.
+        if (B2_ATTN_CONST_BIAS) umma_bf16(d_s, dconst, dconst, idesc_bias, 0u);
         const std::uint64_t d = (s != 0 ? dk1 : dk0) + (u & 1) * kHalfTile;
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
-          umma_i8(tmem_s + static_cast<std::uint32_t>(u & 1) * kSubK, dq + 2u * k4, d + 2u * k4, idesc_qk, (B2_ATTN_PREFILL || k4 != 0) ? 1u : 0u);  // onto the pre-fill, if any
+          umma_i8(d_s, dq + 2u * k4, d + 2u * k4, idesc_qk, (B2_ATTN_CONST_BIAS || k4 != 0) ? 1u : 0u);
         }
         if ((u & 1) != 0 || u + 1 >= n_sub) tc_commit(smem_u32(&s_k_empty[s]));
         if (u < 2) tc_commit(smem_u32(&s_step[u]));  // start-up: S(0) and S(1) are the first completions of the two barriers
@@ -804,17 +902,18 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // P = exp2(S * c - m) against the reference maximum m carried over from the earlier sub-tiles, while the sub-tile's
     // own maximum is tracked on the side. m is kept kHeadroom binades above what the largest P would need, so scores
     // above everything seen so far still fit; when they do not (P would pass p_range), the warp raises m for those
-    // rows, rescales O and the denominator and runs the pass again on the same S. Sub-tile 0 has no carried maximum
-    // and reads its scores once more, for the maximum only.
+    // rows, rescales O and the denominator and runs the pass again on the same S.
     const int quarter = warp & 3;
     const int r_local = quarter * 32 + lane;  // row of the tile == TMEM lane
     const std::uint32_t lane_off = static_cast<std::uint32_t>(quarter * 32) << 16;
     const std::int64_t sc_base = static_cast<std::int64_t>(b) * a.heads + h;
     const float qs = a.q_scale[sc_base * a.q_blocks + (q0 + quarter * 32) / 32] * a.scale_log2;
     const float* k_scale = a.k_scale + sc_base * a.k_blocks;
+    const int n_scales = min(n_sub, a.k_blocks);
 #ifdef B2_ATTN_TRACE
     const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == B2_TRACE_WARP && lane == 0;
 #endif
+    const bool dumping = kDump && b == a.dump_seq && h == a.dump_head && bq == a.dump_tile;
     constexpr float kNone = -5000000.0f;  // "no score": below every scaled score
     float m_run = kNone, d_run = 0.f;
     float o_scale = 1.0f;  // factor O still has to be multiplied by (applied once the P·V before it have landed)
@@ -836,62 +935,68 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       tmem_st_wait();
     };
-    // With B2_ATTN_PREFILL both score buffers start out pre-filled (see softmax_pass); the MMA warp waits for the softmax
-    // warps once either way.
-    const auto prefill_s = [&](std::uint32_t cols) {
-      tmem_fill_32x32(cols, 0x4B400000u);
-      tmem_fill_32x32(cols + 32, 0x4B400000u);
-    };
-    if (B2_ATTN_PREFILL) {
-      prefill_s(tmem_s + lane_off);
-      prefill_s(tmem_s + lane_off + kSubK);
-      tmem_st_wait();
+    if (B2_ATTN_CONST_BIAS) {
+      // This thread's row of the constant operand: 16 bf16 = two identical 16-byte halves (so the 32-byte swizzle, which
+      // only swaps the halves, cannot matter) of 2048, 1024, 1024, 0 ...: 2 (2^22 + 2^20 + 2^20) = 12582912 exactly.
+      std::uint8_t* crow = smem_raw + (const_smem - smem_u32(smem_raw)) + r_local * 32;
+      const uint4 half = make_uint4(0x44804500u, 0x00004480u, 0u, 0u);
+      *reinterpret_cast<uint4*>(crow) = half;
+      *reinterpret_cast<uint4*>(crow + 16) = half;
+      fence_proxy_async_smem();
     }
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&s_s_ready));
     std::uint8_t* prow = p_generic + r_local * 128;
     bool dead = false;  // a bounded wait expired: leave without touching anything else
-    for (int u = 0; u < n_sub; ++u) {
+    ScoreRegs sr;
+    float ks_cur = n_scales > 0 ? k_scale[0] : 0.f, ks_next = 0.f;
+    // S(0): completion 0 of s_step[0] (the start-up Q·K^T).
+    if (!warp_wait(smem_u32(&s_step[0]), 0u)) dead = true;
+    if (!dead) {
+      tc_fence_after();
+      load_scores(tmem_s + lane_off, sr);
+    }
+    for (int u = 0; !dead && u < n_sub; ++u) {
+      // Here S(u) is computed, P·V(u - 2) (which read this sub-tile's P buffer) has landed and the loads of S(u) are in
+      // flight.
       const std::uint32_t s_cols = tmem_s + lane_off + static_cast<std::uint32_t>(u & 1) * kSubK;
       TRACE(4);
-      // Completion u / 2 of s_step[u % 2]: S(u) computed and P·V(u - 2), which read this sub-tile's P buffer, landed (the MMA
-      // warp's step u - 2; for u < 2 the start-up Q·K^T).
-      if (!warp_wait(smem_u32(&s_step[u & 1]), (u >> 1) & 1u)) {
-        dead = true;
-        break;
-      }
-      tc_fence_after();
-      TRACE(0);
-      const float c = (u < a.k_blocks) ? qs * k_scale[u] : 0.f;
+      const float c = u < n_scales ? qs * ks_cur : 0.f;
+      if (u + 1 < n_scales) ks_next = k_scale[u + 1];  // used a whole pass from now
       const int valid = min(kSubK, kv_len - u * kSubK);  // valid keys of this sub-tile (>= 1)
-      if (u == 0) {
-        float bmax = 0.f;  // below every biased score (those are >= 2^22)
-#pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
-          std::uint32_t r[32];
-          tmem_ld_32x32(s_cols + cc * 32, r);
-          tmem_ld_wait();
+      TRACE(8);
+      tmem_ld_wait();
+      TRACE(0);
+      if constexpr (kDump) {
+        if (dumping) {
+          std::int32_t* drow = a.dump + static_cast<std::int64_t>(r_local) * a.dump_ld + u * kSubK;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) bmax = fmaxf(bmax, (cc * 32 + i < valid) ? __uint_as_float(r[i] + kScoreBias) : 0.f);
+          for (int i = 0; i < 16; ++i) {
+            drow[i] = static_cast<std::int32_t>(sr.a[i] + kScoreBias - kScoreBits);
+            drow[16 + i] = static_cast<std::int32_t>(sr.b[i] + kScoreBias - kScoreBits);
+            drow[32 + i] = static_cast<std::int32_t>(sr.c[i] + kScoreBias - kScoreBits);
+            drow[48 + i] = static_cast<std::int32_t>(sr.d[i] + kScoreBias - kScoreBits);
+          }
         }
-        m_run = (bmax - 12582912.0f) * c - (a.p_offset - kHeadroom);
       }
+      if (u == 0) m_run = (max_score(sr, valid) - 12582912.0f) * c - (a.p_offset - kHeadroom);
       bool o_idle = u < 1;  // every P·V up to u - 1 has to land before O is rescaled
       float mx, d_tile;
       for (;;) {
         const float bias = -fmaf(12582912.0f, c, m_run);
         float bmax;
         if (valid == kSubK) {
-          softmax_pass<true>(s_cols, c, bias, valid, prow, 4 * (u & 1), r_local & 7, bmax, d_tile);
+          softmax_pass<true>(sr, c, bias, valid, prow, 4 * (u & 1), r_local & 7, bmax, d_tile);
         } else {
-          softmax_pass<false>(s_cols, c, bias, valid, prow, 4 * (u & 1), r_local & 7, bmax, d_tile);
+          softmax_pass<false>(sr, c, bias, valid, prow, 4 * (u & 1), r_local & 7, bmax, d_tile);
         }
         TRACE(1);
         mx = bmax != 0.f ? (bmax - 12582912.0f) * c : kNone;
         const bool over = mx - m_run > a.p_offset;  // some P of this row passed p_range: the pass has to run again
-        const bool any_over = __any_sync(0xffffffffu, over);
-        if (!any_over && !__any_sync(0xffffffffu, o_scale != 1.0f)) break;
+        const bool act = __any_sync(0xffffffffu, over || o_scale != 1.0f);
+        TRACE(9);
+        if (!act) break;
         // O is about to be rescaled: every P·V issued so far (the last one is u - 1) has to have landed.
         if (!o_idle) {
           o_idle = true;
@@ -911,31 +1016,44 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           alpha *= grow;
         }
         if (u > 0) rescale_o(alpha);
-        if (!any_over) break;
+        if (!__any_sync(0xffffffffu, over)) break;
+        load_scores(s_cols, sr);  // the pass consumed its registers: the scores are still in tensor memory
+        tmem_ld_wait();
       }
       if (dead) break;
       d_run += d_tile;
       TRACE(2);
-      // S is consumed (and, with B2_ATTN_PREFILL, pre-filled again for Q·K^T of sub-tile u + 2) and P written: both go to
-      // the MMA warp.
-      if (B2_ATTN_PREFILL && u + 2 < n_sub) {
-        prefill_s(s_cols);
-        tmem_st_wait();
-      }
+      // S is consumed and P written: both go to the MMA warp.
       fence_proxy_async_smem();
+      TRACE(10);
       tc_fence_before();
       __syncwarp();
+      TRACE(11);
       if (lane == 0) mbar_arrive(smem_u32(&s_p_full[u & 1]));
       TRACE(3);
-      // Less than kRaise binades of headroom left: raise the reference for the sub-tiles to come. P·V of this one was
-      // computed against the old reference, so O is rescaled after it lands (at the end of the next pass).
-      if (u + 1 < n_sub && mx - m_run > a.p_offset - kRaise) {
-        const float m_new = mx - (a.p_offset - kHeadroom);
-        const float grow = ex2(m_run - m_new);
-        m_run = m_new;
-        d_run *= grow;
-        o_scale = grow;
+      if (u + 1 < n_sub) {
+        // Completion (u + 1) / 2 of s_step[(u + 1) % 2]: S(u + 1) computed and P·V(u - 1) landed (the MMA warp's step u - 1;
+        // for u + 1 < 2 the start-up Q·K^T). Its loads fly while the bookkeeping below runs.
+        if (!warp_wait(smem_u32(&s_step[(u + 1) & 1]), ((u + 1) >> 1) & 1u)) {
+          dead = true;
+          break;
+        }
+        TRACE(12);
+        tc_fence_after();
+        load_scores(tmem_s + lane_off + static_cast<std::uint32_t>((u + 1) & 1) * kSubK, sr);
+        TRACE(13);
+        // Less than kRaise binades of headroom left: raise the reference for the sub-tiles to come. P·V of this one was
+        // computed against the old reference, so O is rescaled after it lands (at the end of the next pass).
+        if (mx - m_run > a.p_offset - kRaise) {
+          const float m_new = mx - (a.p_offset - kHeadroom);
+          const float grow = ex2(m_run - m_new);
+          m_run = m_new;
+          d_run *= grow;
+          o_scale = grow;
+        }
+        ks_cur = ks_next;
       }
+      TRACE(14);
     }
     if (!dead && warp_wait(smem_u32(&s_step[(n_sub - 1) & 1]), (((n_sub - 1) >> 1) + 1) & 1u)) {  // the last step
       tc_fence_after();
@@ -1078,11 +1196,17 @@ int b2_attention_q8_layout(const b2_attention_options* o, int64_t total_q, int64
   return B2_OK;
 }
 
-int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
-                    const b2_view3* out, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
-                    int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
-                    const b2_qk_norm_rope* norm_rope) {
-  constexpr const char* op = "attention_q8";
+namespace {
+struct ScoreDump {
+  std::int32_t* scores = nullptr;
+  std::int64_t ld = 0;
+  int seq = 0, head = 0, tile = 0;
+};
+
+int attention_impl(const char* op, const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
+                   const b2_view3* out, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
+                   int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
+                   const b2_qk_norm_rope* norm_rope, const ScoreDump* dump) {
   if (o == nullptr) return fail_invalid(op, "null options");
   if (const int rc = check_view(op, q, "q")) return rc;
   if (const int rc = check_view(op, k, "k")) return rc;
@@ -1178,6 +1302,10 @@ int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_v
   a.heads = static_cast<int>(heads), a.q_blocks = l.q_blocks, a.k_blocks = l.k_blocks;
   a.scale_log2 = scale * 1.44269504088896340736f;
   a.p_offset = static_cast<float>(std::floor(std::log2(static_cast<double>(p_range)) * 1000.0) / 1000.0);
+  if (dump != nullptr) {
+    a.dump = dump->scores, a.dump_ld = dump->ld;
+    a.dump_seq = dump->seq, a.dump_head = dump->head, a.dump_tile = dump->tile;
+  }
 #ifdef B2_ATTN_TRACE
   {
     void* tp = nullptr;
@@ -1185,13 +1313,37 @@ int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_v
     a.trace = static_cast<long long*>(tp);
   }
 #endif
-  if (const cudaError_t e = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+  const auto kernel = dump != nullptr ? attention_kernel<true> : attention_kernel<false>;
+  if (const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
       e != cudaSuccess) {
     return fail_cuda(op, e);
   }
   const dim3 grid((max_seqlen + kTileQ - 1) / kTileQ, static_cast<unsigned>(heads), batch);
-  attention_kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(map_q, map_k, map_v, a);
+  kernel<<<grid, kAttnThreads, kAttnSmem, st>>>(map_q, map_k, map_v, a);
   return check_launch(op);
+}
+}  // namespace
+
+int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
+                    const b2_view3* out, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
+                    int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
+                    const b2_qk_norm_rope* norm_rope) {
+  return attention_impl("attention_q8", o, q, k, v, out, cu_seqlens_q, cu_seqlens_k, batch, max_seqlen, scale, workspace,
+                        workspace_bytes, stream, norm_rope, nullptr);
+}
+
+int b2_attention_q8_debug_scores(const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
+                                 const b2_view3* out, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
+                                 int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
+                                 const b2_qk_norm_rope* norm_rope, int seq, int head, int tile_q, int32_t* scores,
+                                 int64_t ld) {
+  constexpr const char* op = "attention_q8_debug_scores";
+  if (scores == nullptr || seq < 0 || seq >= batch || head < 0 || tile_q < 0 || ld < (static_cast<std::int64_t>(max_seqlen) + 63) / 64 * 64) {
+    return fail_invalid(op, "needs a scores buffer with ld >= 64 * ceil(max_seqlen / 64) and a (seq, head, tile_q) inside the problem");
+  }
+  const ScoreDump dump{scores, ld, seq, head, tile_q};
+  return attention_impl(op, o, q, k, v, out, cu_seqlens_q, cu_seqlens_k, batch, max_seqlen, scale, workspace, workspace_bytes,
+                        stream, norm_rope, &dump);
 }
 
 #ifdef B2_ATTN_TRACE

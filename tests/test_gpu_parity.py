@@ -456,6 +456,38 @@ def test_attention_int32_scores_are_exact(ops):
     assert np.array_equal(acc, q8.astype(np.int32) @ k8.astype(np.int32).T)
 
 
+@pytest.mark.parametrize("lens,seq,head,tile", [([300, 1061], 1, 2, 8), ([300, 1061], 0, 0, 2), ([777], 0, 1, 0),
+                                                 ([64], 0, 0, 0), ([4500], 0, 2, 17)])
+def test_attention_kernel_own_scores_are_exact(ops, lens, seq, head, tile):
+    """The attention kernel's own Q8 K8^T accumulators (its N = 64 instruction shape, its half-tile descriptor offsets, its
+    score buffers in tensor memory), dumped as the softmax threads read them, against the integer dot products of the
+    pre-pass outputs: bit for bit, on lengths that are no multiple of 64 or 128 (third_party/sageattention/csrc/qattn/
+    qk_int_sv_f8_cuda_sm89.cuh:290-345 computes the same int32 scores)."""
+    rng = np.random.default_rng(sum(lens))
+    heads, total, mx = 3, sum(lens), max(lens)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    qkv = bfdev(rand_bf16(rng, (total, 3 * heads * 128), 2.0))
+    q3, k3, v3 = _views(qkv, total, heads)
+    out = torch.zeros((total, heads, 128), dtype=torch.bfloat16, device="cuda")
+    cu_d = dev(cu)
+    scores, ws = ops.attention_q8_debug_scores(q3, k3, v3, out, cu_d, cu_d, mx, ops.SM_SCALE, seq=seq, head=head, tile_q=tile)
+    torch.cuda.synchronize()
+    lay = ops.attention_q8_layout(total, total, len(lens), mx, heads)
+    wsn = ws.cpu().numpy()
+    q_i8 = _grab(wsn, lay.q_i8, np.int8, (total, heads, 128))
+    k_i8 = _grab(wsn, lay.k_i8, np.int8, (total, heads, 128))
+    n = lens[seq]
+    q0, rows = tile * 128, min(128, n - tile * 128)
+    assert rows > 0
+    want = orc.qk_scores(q_i8, k_i8, head, int(cu[seq]) + q0, rows, int(cu[seq]), n)
+    got = scores.cpu().numpy()[:rows, :n]
+    assert np.array_equal(got, want)
+    # The same call also produced the regular output.
+    ref_out = torch.zeros_like(out)
+    ops.attention_q8(q3, k3, v3, ref_out, cu_d, cu_d, mx, ops.SM_SCALE)
+    assert torch.equal(out, ref_out)
+
+
 def test_attention_golden_vectors(ops):
     q, k, v = (load("attention_q8", "oracle_" + n) for n in "qkv")
     cu = load("attention_q8", "oracle_cu_seqlens")
