@@ -203,6 +203,13 @@ int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_v
                     int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
                     const b2_qk_norm_rope* norm_rope);
 
+/* attention_q8::detail::preprocess (src/kernels/attention_q8/q8_preprocess.cu:389): the pre-pass of b2_attention_q8
+ * alone. Fills the workspace (layout: b2_attention_q8_layout) with q_i8, k_i8, v8 and the scales; with norm_rope the
+ * QK-norm + RoPE runs first and k is rewritten in place. Same argument rules as b2_attention_q8. */
+int b2_attention_q8_preprocess(const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
+                               const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch, int max_seqlen,
+                               void* workspace, size_t workspace_bytes, void* stream, const b2_qk_norm_rope* norm_rope);
+
 /* Test hook. b2_attention_q8 with the same arguments, which additionally stores the raw int32 Q8·K8^T accumulators that
  * the attention kernel's softmax threads read from tensor memory, for the 128 query rows of tile `tile_q` of
  * (sequence `seq`, head `head`): scores int32 [128, ld], row r = query tile_q * 128 + r of the sequence, column j = key j

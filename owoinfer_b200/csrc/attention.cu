@@ -1206,18 +1206,20 @@ struct ScoreDump {
 int attention_impl(const char* op, const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
                    const b2_view3* out, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
                    int max_seqlen, float scale, void* workspace, size_t workspace_bytes, void* stream,
-                   const b2_qk_norm_rope* norm_rope, const ScoreDump* dump) {
+                   const b2_qk_norm_rope* norm_rope, const ScoreDump* dump, bool prepass_only = false) {
   if (o == nullptr) return fail_invalid(op, "null options");
   if (const int rc = check_view(op, q, "q")) return rc;
   if (const int rc = check_view(op, k, "k")) return rc;
   if (const int rc = check_view(op, v, "v")) return rc;
-  if (const int rc = check_view(op, out, "out")) return rc;
+  if (!prepass_only) {
+    if (const int rc = check_view(op, out, "out")) return rc;
+  }
   if (o->variant != B2_ATTENTION_Q8_FP8_F32ACC) {
     return fail_status(B2_ERR_NOT_SUPPORTED, op, "only the e4m3 P·V variant with fp32 accumulation (int8_fp8_f32acc) is built for sm_100a");
   }
   const std::int64_t total_q = q->tokens, heads = q->heads, total_k = k->tokens, kv_heads = k->heads;
   if (v->tokens != total_k || v->heads != kv_heads) return fail_invalid(op, "k and v must both be [total_k, num_kv_heads, 128]");
-  if (out->tokens != total_q || out->heads != heads) return fail_invalid(op, "out must have q's shape");
+  if (!prepass_only && (out->tokens != total_q || out->heads != heads)) return fail_invalid(op, "out must have q's shape");
   if (kv_heads != heads) return fail_status(B2_ERR_NOT_SUPPORTED, op, "num_heads must equal num_kv_heads (the DiT's joint attention)");
   if (heads > 65535 || batch > 65535 || batch < 1) return fail_invalid(op, "batch and num_heads must be in [1, 65535]");
   if (cu_seqlens_q == nullptr || cu_seqlens_k == nullptr) return fail_invalid(op, "null cu_seqlens");
@@ -1287,6 +1289,7 @@ int attention_impl(const char* op, const b2_attention_options* o, const b2_view3
   }
   quant_kv_kernel<<<dim3(l.k_blocks, static_cast<unsigned>(heads), batch), 256, 0, st>>>(p);
   if (const int rc = check_launch(op)) return rc;
+  if (prepass_only) return B2_OK;
 
   CUtensorMap map_q, map_k, map_v;
   const std::uint64_t row_bytes = static_cast<std::uint64_t>(heads) * kHeadDim;
@@ -1330,6 +1333,13 @@ int b2_attention_q8(const b2_attention_options* o, const b2_view3* q, const b2_v
                     const b2_qk_norm_rope* norm_rope) {
   return attention_impl("attention_q8", o, q, k, v, out, cu_seqlens_q, cu_seqlens_k, batch, max_seqlen, scale, workspace,
                         workspace_bytes, stream, norm_rope, nullptr);
+}
+
+int b2_attention_q8_preprocess(const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,
+                               const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch, int max_seqlen,
+                               void* workspace, size_t workspace_bytes, void* stream, const b2_qk_norm_rope* norm_rope) {
+  return attention_impl("attention_q8_preprocess", o, q, k, v, nullptr, cu_seqlens_q, cu_seqlens_k, batch, max_seqlen, 1.0f,
+                        workspace, workspace_bytes, stream, norm_rope, nullptr, true);
 }
 
 int b2_attention_q8_debug_scores(const b2_attention_options* o, const b2_view3* q, const b2_view3* k, const b2_view3* v,

@@ -210,6 +210,23 @@ def attention_q8(q, k, v, out, cu_seqlens_q, cu_seqlens_k, max_seqlen, scale, wo
     return out, workspace
 
 
+def attention_q8_preprocess(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen, workspace=None, options=None, norm_rope=None):
+    """The pre-pass of attention_q8 alone; returns the workspace it filled."""
+    o = options or attention_options()
+    batch = cu_seqlens_q.shape[0] - 1
+    if workspace is None:
+        nbytes = attention_q8_workspace_bytes(q.shape[0], k.shape[0], batch, max_seqlen, q.shape[1], k.shape[1], o)
+        workspace = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
+    nr = None
+    if norm_rope is not None:
+        nr = _lib.QkNormRope(norm_rope[0].data_ptr(), norm_rope[1].data_ptr(), norm_rope[2].data_ptr(), _ld(norm_rope[2]))
+    vq, vk, vv = _view3(q), _view3(k), _view3(v)
+    check(_lib.lib().b2_attention_q8_preprocess(C.byref(o), C.byref(vq), C.byref(vk), C.byref(vv), _ptr(cu_seqlens_q),
+                                                _ptr(cu_seqlens_k), C.c_int(batch), C.c_int(max_seqlen), _ptr(workspace),
+                                                C.c_size_t(workspace.numel()), _stream(), None if nr is None else C.byref(nr)))
+    return workspace
+
+
 def attention_q8_debug_scores(q, k, v, out, cu_seqlens_q, cu_seqlens_k, max_seqlen, scale, seq, head, tile_q, workspace=None,
                               options=None, norm_rope=None):
     """attention_q8 that also returns the attention kernel's own int32 Q·K^T accumulators of one (sequence, head, 128-row

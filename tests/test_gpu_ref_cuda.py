@@ -183,13 +183,15 @@ def test_attention_peaked_scores(ops, keys):
 
 
 def _block_metrics(got, want):
-    """cos, max|g-w| / max|w| (a norm-type bound, as the reference's own block tests use), and the per-element error
-    max |g-w| / (|w| + 0.01 rms(w)), which an outlier channel cannot hide."""
+    """cos; max|g-w| / max|w| (a norm-type bound, as the reference's own block tests use); the per-element error
+    max |g-w| / (|w| + rms(w)), whose denominator is the element's own size floored at the tensor's rms, so that a large
+    value in an outlier channel cannot hide an error on an ordinary element (a floor much below the rms would instead
+    measure bf16 rounding flips on elements near zero); and the relative L2 error."""
     g, t = got.float().flatten(), want.float().flatten()
     cos = torch.nn.functional.cosine_similarity(g, t, dim=0).item()
     max_rel = ((g - t).abs().max() / t.abs().max()).item()
     rms = t.pow(2).mean().sqrt()
-    per_elem = ((g - t).abs() / (t.abs() + 0.01 * rms)).max().item()
+    per_elem = ((g - t).abs() / (t.abs() + rms)).max().item()
     rel_l2 = ((g - t).norm() / t.norm()).item()
     return cos, max_rel, per_elem, rel_l2
 
@@ -236,4 +238,4 @@ def test_block_at_benchmark_shapes(ops, lens, grid, tier):
     cos, max_rel, per_elem, rel_l2 = _ours_vs_ref_block(ops, lens, 12288, grid, 11 + len(lens) + tier, tier)
     print("block", lens, "tier", tier, dict(cos=cos, max_rel=max_rel, per_elem=per_elem, rel_l2=rel_l2))
     assert cos >= 0.9995 and max_rel <= 1e-2, (cos, max_rel, per_elem, rel_l2)
-    assert per_elem <= 0.25 and rel_l2 <= 1e-2, (cos, max_rel, per_elem, rel_l2)
+    assert per_elem <= 5e-2 and rel_l2 <= 1e-2, (cos, max_rel, per_elem, rel_l2)
