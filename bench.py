@@ -43,6 +43,7 @@ def parse():
     p.add_argument("--no-profile", action="store_true", help="skip the per-kernel roofline pass and the CPU baseline")
     p.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own CUDA kernels on this GPU")
     p.add_argument("--no-graph", action="store_true", help="enqueue the step's kernels directly instead of replaying a CUDA graph")
+    p.add_argument("--no-ulysses", action="store_true", help="N >= 2: skip the sequence-parallel 2048^2 record added to the line")
     return p.parse_args()
 
 
@@ -302,6 +303,63 @@ def profile_kernels(ops, torch, L, F, w, iters=8, ref=None):
     return out
 
 
+def single_gpu_step_ms(torch, ops, synth, seq_lens, blocks, F, steps, warmup):
+    """ms per step of the whole step on THIS GPU alone through b2_dit_step (CUDA-graph replay): the base the
+    sequence-parallel record is compared with."""
+    L, seq_len = sum(seq_lens), max(seq_lens)
+    keep, bws = [], []
+    for b in range(blocks):
+        w = synth.block_weights(D, F, 3000 + 100 * b)
+        keep.append(w)
+        bws.append(ops.BlockWeights(w["norm1"], w["norm2"], w["q_norm"], w["k_norm"], w["qkv"], w["o"], w["up_gate"], w["down"]))
+    x0 = synth.activations(L, D, 1003)
+    mod = synth.modulation(D, 2001)
+    grid = 128 if seq_len > 16384 else 64
+    rope = torch.cat([ops.moss_rope_table(grid, grid, s - grid * grid) for s in seq_lens]).contiguous()
+    cu = synth.cu_seqlens(seq_lens)
+    run = ops.block_run(L, cu, seq_len, D=D, F=F, heads=HEADS)
+    ws = torch.empty(ops.block_quant_workspace_bytes(run), dtype=torch.uint8, device="cuda")
+    x = x0.clone()
+    bufs = ops.block_buffers(x, mod, rope, ws)
+    ops.dit_step(bws, bufs, run)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.dit_step(bws, bufs, run)
+    for _ in range(max(warmup, 3)):
+        x.copy_(x0)
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        x.copy_(x0)
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def ulysses_record(torch, dist, ops, synth, args, rank, world):
+    """N >= 2: the 2048^2 step (two 20480-token sequences) over all N ranks (groups x sequence parallel), the same step on
+    rank 0's GPU alone, the speed-up and the exchange time the step does not hide. Every rank takes part; rank 0 returns
+    the record."""
+    from owoinfer_b200 import parallel
+    steps, warmup = min(args.steps, 5), 3
+    ms, rec = parallel.measure_ulysses(rank, world, args.blocks, args.ffn, steps, warmup)
+    base = None
+    if rank == 0:
+        base = single_gpu_step_ms(torch, ops, synth, rec["sequences"], args.blocks, args.ffn, min(args.steps, 3), 3)
+        torch.cuda.empty_cache()
+    dist.barrier()
+    if rank != 0:
+        return None
+    rec.update({"workload": "step2048_ulysses", "metric": "dit_ms_per_step_2048", "n_gpus": world, "ms_per_step": ms,
+                "steps": steps, "warmup": warmup, "single_gpu_ms_per_step": base, "speedup_vs_single_gpu": base / ms,
+                "exposed_exchange_frac": None if rec["exposed_exchange_ms"] is None else rec["exposed_exchange_ms"] / ms})
+    return rec
+
+
 def roofline_record(prof, L, F, seq_len, seqs):
     """The `roofline` object: every kernel family of one block with its bound, its achieved rate from the launch times
     measured in this run (CUDA events, each launch alone after an L2 flush) and its share of the block; the top-level
@@ -489,6 +547,15 @@ def main():
                                               f"heads ({ta:.2f} s), extrapolated to {n_blocks} blocks x {seqs} x {seq_len} tokens"}
             if world == 1 and tier == ops.TIER_INT8 and not args.no_ref_gpu:
                 line["reference_gpu"] = reference_kernels_on_this_gpu(torch, ops, keep, x, x0, mod, rope, cu, seq_len, L, F)
+    if world > 1 and args.workload == "step1024" and not args.no_ulysses and tier == ops.TIER_INT8:
+        # The headline above is image data parallel (no collective). The sequence-parallel configuration, the one with an
+        # exchange step, rides along as its own record: free the headline's buffers first.
+        del blocks, keep, bufs, ws, graph, x, x0, hx, hout
+        torch.cuda.empty_cache()
+        rec = ulysses_record(torch, dist, ops, synth, args, rank, world)
+        if rank == 0:
+            line["ulysses"] = rec
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

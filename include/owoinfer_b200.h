@@ -51,6 +51,13 @@ uint32_t b2_numerics_version(int which);
 int b2_rotate_quantize(const void* x, int64_t ldx, int8_t* q, int64_t ldq, float* scale, int64_t m, int k,
                        void* stream);
 
+/* b2_rotate_quantize on a column-chunked input: columns [i * chunk_cols, (i + 1) * chunk_cols) of every row are read
+ * from chunk i, a bf16 [m, chunk_cols] matrix of row stride ldx that starts chunk_stride elements after chunk i - 1
+ * (chunk_cols % 256 == 0, k % chunk_cols == 0). Same bits as b2_rotate_quantize on the assembled rows. The input layout
+ * of the sequence-parallel block's output projection; no counterpart in the reference. */
+int b2_rotate_quantize_chunked(const void* x, int64_t ldx, int chunk_cols, int64_t chunk_stride, int8_t* q, int64_t ldq,
+                               float* scale, int64_t m, int k, void* stream);
+
 /* quant::rms_norm_modulate_rotate_quantize (src/kernels/quant/quant.h:62). norm_weight, mod_scale, mod_shift bf16 [k],
  * 16-byte aligned. y (optional, may be NULL): bf16 [m,k] stride ldy receives the norm output. The mean of squares is
  * summed in the order torch uses for an [m,k] input, which depends on m: call once per tensor the reference normalises. */
@@ -109,6 +116,13 @@ typedef enum b2_int8_tile { B2_TILE_AUTO = 0, B2_TILE_128x256 = 1, B2_TILE_128x1
 /* quant::int8_gemm (src/kernels/quant/quant.h:92): out = bf16((acc * x_scale[r]) * w_scale[c] + bias[c]).
  * bias bf16 [n] or NULL; out bf16 stride ldo, 16-byte aligned, ldo % 8 == 0, n % 8 == 0. */
 int b2_int8_gemm(const b2_int8_operands* op, const void* bias, void* out, int64_t ldo, void* stream, int tile);
+
+/* b2_int8_gemm with a column-chunked output: columns [i * chunk_cols, (i + 1) * chunk_cols) of every row go to chunk i,
+ * a bf16 [m, chunk_cols] matrix of row stride ldo that starts chunk_stride elements after chunk i - 1
+ * (chunk_cols % 8 == 0, n % chunk_cols == 0, ldo >= chunk_cols). Same values as b2_int8_gemm. The output layout of the
+ * sequence-parallel block's QKV projection (one chunk per destination rank); no counterpart in the reference. */
+int b2_int8_gemm_chunked(const b2_int8_operands* op, const void* bias, void* out, int64_t ldo, int chunk_cols,
+                         int64_t chunk_stride, void* stream, int tile);
 
 /* quant::int8_gemm_gated_residual (src/kernels/quant/quant.h:98): residual += bf16(bf16(y) * gate[c]) in place. */
 int b2_int8_gemm_gated_residual(const b2_int8_operands* op, const void* bias, const void* gate, void* residual,
@@ -299,6 +313,47 @@ int b2_run_block_quant(const b2_block_weights* w, const b2_block_buffers* a, con
  * vector per step that all blocks share; a per-block modulation is not supported. */
 int b2_dit_step(const b2_block_weights* blocks, int num_blocks, const b2_block_buffers* a, const b2_block_run* run,
                 void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Sequence-parallel (Ulysses) block: one process per GPU, `size` ranks share every sequence. A rank owns a contiguous
+ * 1/size slice of each sequence's tokens outside attention and heads/size heads of the full sequences inside it; two
+ * exchanges per block over NCCL point-to-point calls on the caller's stream. The output equals the single-GPU block's
+ * bit for bit. The reference engine is single-GPU (include/mossinfer/mossinfer.h:314): no counterpart there.
+ * ------------------------------------------------------------------------------------------------------------- */
+
+/* A communicator of one sequence-parallel group. Rank 0 of the group calls b2_sp_unique_id and hands the 128 bytes to
+ * the other ranks by any means; then every rank of the group calls b2_sp_comm_create (a collective; the rank's device
+ * must be current). size == 1 needs no id and no NCCL. NCCL is bound at run time (libnccl.so.2, preferring a copy the
+ * process has already loaded); B2_ERR_NOT_SUPPORTED when none is found. */
+typedef struct b2_sp_comm b2_sp_comm;
+int b2_sp_unique_id(void* id, size_t id_bytes);
+int b2_sp_comm_create(const void* id, size_t id_bytes, int size, int rank, b2_sp_comm** out);
+int b2_sp_comm_destroy(b2_sp_comm* comm);
+/* Measurement aid: with on != 0 every message of the group's exchanges becomes a device copy of the same size inside this
+ * GPU (wrong results, same kernels and byte counts), so that "step with exchanges" minus "step with local copies" is the
+ * communication time a step does not hide. */
+int b2_sp_comm_local_exchange(b2_sp_comm* comm, int on);
+
+/* local: the block run of this rank. tokens = sum over the sequences of seq_len / size (the rank's rows of x, sequence
+ * by sequence); cu_seqlens (device int32 [batch + 1]), batch and max_seqlen describe the FULL sequences; tier must be
+ * B2_TIER_INT8; heads / size must be even. seq_lens_host: host int32 [batch], the full lengths, each a multiple of size. */
+typedef struct b2_sp_run {
+  size_t struct_size;
+  b2_block_run local;
+  const int32_t* seq_lens_host;
+} b2_sp_run;
+
+size_t b2_block_quant_sp_workspace_bytes(const b2_sp_run* run, int size);
+
+/* b2_run_block_quant on this rank's token shard. a->x: bf16 [local.tokens, D]; a->rope: the FULL table, bf16
+ * [sum of seq_lens, 128] (QK-norm + RoPE run on the full sequences inside the attention pre-pass); a->workspace:
+ * b2_block_quant_sp_workspace_bytes. w->qkv holds the QKV weight with its rows (and scales) reordered for the group:
+ * [destination rank r][q | k | v][head r * heads/size + j][128 rows], so that the GEMM's column block r is what rank r
+ * needs. Every rank of the group must make the same sequence of calls (the exchanges are collective). */
+int b2_run_block_quant_sp(const b2_block_weights* w, const b2_block_buffers* a, const b2_sp_run* run, b2_sp_comm* comm,
+                          void* stream);
+int b2_dit_step_sp(const b2_block_weights* blocks, int num_blocks, const b2_block_buffers* a, const b2_sp_run* run,
+                   b2_sp_comm* comm, void* stream);
 
 /* Every mbarrier wait inside the tensor-core kernels is bounded; a CTA whose wait expired raises a device word, drains
  * and returns instead of hanging. This reads the two words (GEMM, attention): 0 = no wait ever expired on this device.

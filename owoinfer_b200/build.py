@@ -11,7 +11,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "csrc", "build")
 LIB = os.path.join(HERE, "libowoinfer_b200.so")
-SOURCES = ["api.cu", "rotate_quantize.cu", "int8_gemm.cu", "attention.cu", "block.cu"]
+SOURCES = ["api.cu", "rotate_quantize.cu", "int8_gemm.cu", "attention.cu", "block.cu", "sp_block.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "-I", os.path.join(ROOT, "include"), "-I", CSRC]
@@ -45,7 +45,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     with cf.ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
         objs = list(ex.map(lambda s: _compile(s, verbose), SOURCES))
     if _stale(LIB, objs):
-        subprocess.check_call([NVCC, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
+        subprocess.check_call([NVCC, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-ldl"])
     return LIB
 
 

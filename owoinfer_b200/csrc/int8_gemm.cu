@@ -71,6 +71,10 @@ struct GemmParams {
   std::int64_t ldacc;
   const std::uint16_t* t_gate;
   const std::uint16_t* t_hidden;
+  // Plain epilogue only, column-chunked output (0 = off): columns [i * chunk_cols, (i + 1) * chunk_cols) of every row go
+  // to chunk i, an [m, chunk_cols] matrix of row stride ldo that starts chunk_stride elements after chunk i - 1.
+  int chunk_cols;
+  std::int64_t chunk_stride;
 };
 
 __device__ int g_gemm_status = 0;  // set to 1 by a CTA whose bounded wait expired
@@ -447,7 +451,14 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int i = 0; i < 8; ++i) y[i] = fadd(res[i], rbf(fmul(rbf(y[i]), gate[i])));
               }
               const uint4 packed = make_uint4(pack2(y[0], y[1]), pack2(y[2], y[3]), pack2(y[4], y[5]), pack2(y[6], y[7]));
-              if constexpr (kEpi == Epi::kPlain) __stcs(reinterpret_cast<uint4*>(orow + col), packed);  // streaming, as above
+              if constexpr (kEpi == Epi::kPlain) {
+                __nv_bfloat16* dst = orow + col;
+                if (p.chunk_cols != 0) {  // chunk_cols % 8 == 0: a vector of 8 columns stays inside one chunk
+                  const int chunk = col / p.chunk_cols;
+                  dst = p.out + chunk * p.chunk_stride + static_cast<std::int64_t>(row) * p.ldo + (col - chunk * p.chunk_cols);
+                }
+                __stcs(reinterpret_cast<uint4*>(dst), packed);  // streaming, as above
+              }
               else *reinterpret_cast<uint4*>(orow + col) = packed;
             }
           }
@@ -732,6 +743,23 @@ int b2_int8_gemm(const b2_int8_operands* op_, const void* bias, void* out, int64
   GemmParams p = base_params(op_);
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.out = static_cast<__nv_bfloat16*>(out), p.ldo = ldo;
+  return dispatch<Epi::kPlain>(op, op_, p, as_stream(stream), tile);
+}
+
+int b2_int8_gemm_chunked(const b2_int8_operands* op_, const void* bias, void* out, int64_t ldo, int chunk_cols,
+                         int64_t chunk_stride, void* stream, int tile) {
+  constexpr const char* op = "int8_gemm_chunked";
+  if (const int rc = check_operands(op, op_)) return rc;
+  if (chunk_cols <= 0 || chunk_cols % 8 != 0 || op_->n % chunk_cols != 0 || chunk_stride % 8 != 0) {
+    return fail_invalid(op, "needs chunk_cols % 8 == 0, n % chunk_cols == 0 and chunk_stride % 8 == 0");
+  }
+  if (const int rc = check_output(op, "out", out, ldo, chunk_cols)) return rc;
+  if (bias != nullptr && !aligned_to(bias, 16)) return fail_invalid(op, "bias must be 16-byte aligned");
+  if (op_->m == 0) return B2_OK;
+  GemmParams p = base_params(op_);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.out = static_cast<__nv_bfloat16*>(out), p.ldo = ldo;
+  p.chunk_cols = chunk_cols, p.chunk_stride = chunk_stride;
   return dispatch<Epi::kPlain>(op, op_, p, as_stream(stream), tile);
 }
 

@@ -111,6 +111,28 @@ def int8_gemm(x_q, x_scale, w, w_scale, bias=None, out=None, tile=TILE_AUTO):
     return out
 
 
+def int8_gemm_chunked(x_q, x_scale, w, w_scale, chunk_cols, bias=None, out=None, tile=TILE_AUTO):
+    """The plain GEMM with its output split by columns: out is [n / chunk_cols, m, chunk_cols]."""
+    op = _operands(x_q, x_scale, w, w_scale)
+    chunks = op.n // chunk_cols
+    out = torch.empty((chunks, op.m, chunk_cols), dtype=torch.bfloat16, device=x_q.device) if out is None else out
+    check(_lib.lib().b2_int8_gemm_chunked(C.byref(op), _ptr(bias), _ptr(out), C.c_int64(out.stride(1)), C.c_int(chunk_cols),
+                                          C.c_int64(out.stride(0)), _stream(), C.c_int(tile)))
+    return out
+
+
+def rotate_quantize_chunked(x_chunks, q=None, scale=None):
+    """x_chunks: bf16 [chunks, m, chunk_cols]; quantises the rows of the column-concatenated [m, chunks * chunk_cols]."""
+    chunks, m, cw = x_chunks.shape
+    k = chunks * cw
+    q = torch.empty((m, k), dtype=torch.int8, device=x_chunks.device) if q is None else q
+    scale = torch.empty(m, dtype=torch.float32, device=x_chunks.device) if scale is None else scale
+    check(_lib.lib().b2_rotate_quantize_chunked(_ptr(x_chunks), C.c_int64(x_chunks.stride(1)), C.c_int(cw),
+                                                C.c_int64(x_chunks.stride(0)), _ptr(q), C.c_int64(_ld(q)), _ptr(scale),
+                                                C.c_int64(m), C.c_int(k), _stream()))
+    return q, scale
+
+
 def int8_gemm_gated_residual(x_q, x_scale, w, w_scale, gate, residual, bias=None, tile=TILE_AUTO):
     op = _operands(x_q, x_scale, w, w_scale)
     check(_lib.lib().b2_int8_gemm_gated_residual(C.byref(op), _ptr(bias), _ptr(gate), _ptr(residual),
@@ -318,3 +340,59 @@ def dit_step(blocks, buffers, run):
 
 
 SM_SCALE = 1.0 / math.sqrt(128.0)
+
+
+# ------------------------------------------------------------------------------------------------ sequence parallel
+
+class SpComm:
+    """Communicator of one sequence-parallel group (b2_sp_comm). `unique_id` is the bytes rank 0 of the group got from
+    sp_unique_id(); size 1 needs none."""
+
+    def __init__(self, size: int, rank: int, unique_id: bytes | None = None):
+        self.size, self.rank = size, rank
+        self.handle = C.c_void_p()
+        buf = (C.c_char * 128).from_buffer_copy(unique_id) if unique_id is not None else None
+        check(_lib.lib().b2_sp_comm_create(buf, C.c_size_t(128 if buf is not None else 0), C.c_int(size), C.c_int(rank),
+                                           C.byref(self.handle)))
+
+    def local_exchange(self, on: bool):
+        check(_lib.lib().b2_sp_comm_local_exchange(self.handle, C.c_int(1 if on else 0)))
+
+    def close(self):
+        if self.handle:
+            _lib.lib().b2_sp_comm_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+
+def sp_unique_id() -> bytes:
+    buf = (C.c_char * 128)()
+    check(_lib.lib().b2_sp_unique_id(buf, C.c_size_t(128)))
+    return bytes(buf)
+
+
+def sp_run(seq_lens, size, cu_seqlens_full, D=3072, F=12288, heads=24, fused_norm_rope=-1):
+    """b2_sp_run of one rank: seq_lens are the FULL sequence lengths (host ints), cu_seqlens_full their device prefix sums."""
+    r = _lib.SpRun()
+    r.struct_size = C.sizeof(_lib.SpRun)
+    r.local = block_run(sum(s // size for s in seq_lens), cu_seqlens_full, max(seq_lens), D=D, F=F, heads=heads,
+                        fused_norm_rope=fused_norm_rope)
+    arr = (C.c_int32 * len(seq_lens))(*seq_lens)
+    r.seq_lens_host = C.cast(arr, C.c_void_p)
+    r._keep = (arr, cu_seqlens_full)
+    return r
+
+
+def block_quant_sp_workspace_bytes(run, size) -> int:
+    n = int(_lib.lib().b2_block_quant_sp_workspace_bytes(C.byref(run), C.c_int(size)))
+    if n == 0:
+        raise ValueError(_lib.lib().b2_last_error_message().decode())
+    return n
+
+
+def run_block_quant_sp(weights: BlockWeights, bufs, run, comm: SpComm):
+    check(_lib.lib().b2_run_block_quant_sp(C.byref(weights.struct), C.byref(bufs), C.byref(run), comm.handle, _stream()))
+
+
+def dit_step_sp(blocks, bufs, run, comm: SpComm):
+    arr = (_lib.BlockWeights * len(blocks))(*[b.struct for b in blocks])
+    check(_lib.lib().b2_dit_step_sp(arr, C.c_int(len(blocks)), C.byref(bufs), C.byref(run), comm.handle, _stream()))

@@ -13,8 +13,10 @@ The reference engine is single-GPU; everything here is new. Three ways to spread
                         after the first exchange and are summed in the same order as on one GPU, so the N-GPU block
                         output equals the 1-GPU output bit for bit.
 
-The exchange helpers are plain torch + torch.distributed and run on any backend (tests use gloo on CPU); the block
-itself calls the CUDA library through `ops`.
+The sequence-parallel block itself is C++ behind the C ABI (b2_run_block_quant_sp: NCCL point-to-point exchanges, no
+packing pass, no allocation); this module holds the partition arithmetic, the load-time QKV row order that path needs,
+the glue that builds one communicator per group from a torch.distributed job, and torch re-statements of the two
+exchanges that run on any backend (the CPU tests check the layout arithmetic with gloo).
 """
 from __future__ import annotations
 
@@ -103,155 +105,159 @@ def exchange_heads_to_tokens(attn_full, local_lens, heads: int, group=None) -> t
     return torch.cat(parts, dim=0)
 
 
-# ----------------------------------------------------------------------------------------------------------- the block
+# ----------------------------------------------------------------------------------------------------------- layouts
 
-class UlyssesBlockRunner:
-    """One all-INT8 block on this rank's token shard, kernels queued on the current stream, all-to-alls on the process
-    group. Buffers are allocated once for the run's shape."""
+def group_layout(world: int, n_sequences: int):
+    """How a job of `world` ranks splits `n_sequences` independent sequences (CFG rows): (groups, sp) with groups * sp ==
+    world. Independent sequences go to separate groups first (no collective between them); what is left of the ranks
+    shares each sequence's tokens. 8 ranks and 2 sequences: 2 groups x sequence-parallel 4."""
+    groups = 1
+    for g in range(min(world, n_sequences), 0, -1):
+        if world % g == 0 and n_sequences % g == 0:
+            groups = g
+            break
+    return groups, world // groups
 
-    def __init__(self, seq_lens, D: int, F: int, heads: int, group=None, device="cuda"):
-        from . import ops
-        self.ops = ops
-        self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+def sp_qkv_row_order(heads: int, size: int) -> torch.Tensor:
+    """Row order of the fused QKV weight [3 * heads * 128, k] (q heads, k heads, v heads) for a sequence-parallel group of
+    `size` ranks: [destination rank r][q | k | v][head r * heads/size + j][128]. Apply to the weight rows and to the scale
+    vector at load time (index_select)."""
+    hp = heads // size
+    idx = torch.arange(3 * heads * 128).view(3, size, hp, 128)   # [qkv, rank, head, row]
+    return idx.permute(1, 0, 2, 3).reshape(-1)
+
+
+def permute_qkv(weight: torch.Tensor, scale: torch.Tensor, heads: int, size: int):
+    order = sp_qkv_row_order(heads, size).to(weight.device)
+    return weight.index_select(0, order).contiguous(), scale.index_select(0, order).contiguous()
+
+
+def make_sp_comm(group_ranks, rank: int, group=None):
+    """One b2_sp_comm over `group_ranks` (global ranks, this rank among them). The id is created by the group's first
+    rank and handed round with torch.distributed (the job's default group carries it; `group` is the torch group of
+    exactly these ranks, or None when the group is the whole job)."""
+    from . import ops
+    size = len(group_ranks)
+    if size == 1:
+        return ops.SpComm(1, 0)
+    box = [ops.sp_unique_id() if rank == group_ranks[0] else None]
+    dist.broadcast_object_list(box, src=group_ranks[0], group=group)
+    return ops.SpComm(size, group_ranks.index(rank), box[0])
+
+
+class SpBlock:
+    """The C++ sequence-parallel block on one rank: buffers sized once for the run, weights in the group's QKV row order."""
+
+    def __init__(self, seq_lens, comm, D: int, F: int, heads: int, device="cuda"):
+        from . import ops, synth
+        self.ops, self.comm = ops, comm
         self.seq_lens = list(seq_lens)
-        self.local_lens = ulysses_local_lengths(self.seq_lens, self.world)
-        self.D, self.F, self.heads = D, F, heads
-        if heads % self.world != 0:
-            raise ValueError(f"{heads} heads do not split over {self.world} ranks")
-        self.hp = heads // self.world
-        L = sum(self.local_lens)
-        self.L = L
-        self.xq = torch.empty((L, max(D, F)), dtype=torch.int8, device=device)
-        self.scale = torch.empty(L, dtype=torch.float32, device=device)
-        self.qkv = torch.empty((L, 3 * D), dtype=torch.bfloat16, device=device)
-        self.ffn = torch.empty((L, F), dtype=torch.bfloat16, device=device)
-        self.attn_full = [torch.empty((s, self.hp, 128), dtype=torch.bfloat16, device=device) for s in self.seq_lens]
-        self.cu_one = [torch.tensor([0, s], dtype=torch.int32, device=device) for s in self.seq_lens]
-        self.ws = [torch.empty(max(256, ops.attention_q8_workspace_bytes(s, s, 1, s, self.hp)), dtype=torch.uint8, device=device)
-                   for s in self.seq_lens]
-        self.comm_stream = torch.cuda.Stream(device=device) if self.world > 1 else None
+        self.local_lens = ulysses_local_lengths(self.seq_lens, comm.size)
+        self.L = sum(self.local_lens)
+        self.cu_full = synth.cu_seqlens(self.seq_lens, device)
+        self.run = ops.sp_run(self.seq_lens, comm.size, self.cu_full, D=D, F=F, heads=heads)
+        self.ws = torch.empty(ops.block_quant_sp_workspace_bytes(self.run, comm.size), dtype=torch.uint8, device=device)
+        self.heads = heads
 
-    def run(self, x, mod, rope_local, w):
-        """x: bf16 [L_local, D] updated in place; mod: bf16 [6 D]; rope_local: bf16 [L_local, 128] (this rank's rows of the
-        table); w: dict with norm1, norm2, q_norm, k_norm and qkv / o / up_gate / down = (int8 weight, f32 scale).
-        The exchanges run on a second stream, one sequence at a time, so that the all-to-all of one sequence overlaps the
-        attention of another."""
-        ops, D, F = self.ops, self.D, self.F
-        xq_d = self.xq[:, :D]
-        m = [mod[i * D:(i + 1) * D] for i in range(6)]
-        ops.rms_norm_modulate_rotate_quantize(x, w["norm1"], m[1], m[0], q=xq_d, scale=self.scale)
-        ops.int8_gemm(xq_d, self.scale, w["qkv"][0], w["qkv"][1], out=self.qkv)
-        ops.qk_norm_rope_moss(self.qkv, self.heads, w["q_norm"], w["k_norm"], rope_local)
-        cur = torch.cuda.current_stream()
-        comm = self.comm_stream if self.world > 1 else cur
-        comm.wait_stream(cur)
-        n_seq = len(self.seq_lens)
-        full, arrived, parts, returned = [None] * n_seq, [], [None] * n_seq, []
-        start = 0
-        with torch.cuda.stream(comm):
-            for i, c in enumerate(self.local_lens):
-                full[i] = exchange_tokens_to_heads(self.qkv[start:start + c], [c], self.heads, self.group)[0]
-                full[i].record_stream(cur)
-                arrived.append(comm.record_event())
-                start += c
-        for i, t in enumerate(full):
-            cur.wait_event(arrived[i])
-            s = self.seq_lens[i]
-            ops.attention_q8(t[:, 0], t[:, 1], t[:, 2], self.attn_full[i], self.cu_one[i], self.cu_one[i], s, ops.SM_SCALE,
-                             workspace=self.ws[i])
-            done = cur.record_event()
-            with torch.cuda.stream(comm):
-                comm.wait_event(done)
-                parts[i] = exchange_heads_to_tokens([self.attn_full[i]], [self.local_lens[i]], self.heads, self.group)
-                parts[i].record_stream(cur)
-                returned.append(comm.record_event())
-        for e in returned:
-            cur.wait_event(e)
-        attn = torch.cat(parts, dim=0) if n_seq > 1 else parts[0]
-        ops.rotate_quantize(attn, q=xq_d, scale=self.scale)
-        ops.int8_gemm_gated_residual(xq_d, self.scale, w["o"][0], w["o"][1], m[2], x)
-        ops.rms_norm_modulate_rotate_quantize(x, w["norm2"], m[4], m[3], q=xq_d, scale=self.scale)
-        ops.int8_gemm_situ_glu(xq_d, self.scale, w["up_gate"][0], w["up_gate"][1], out=self.ffn)
-        xq_f = self.xq[:, :F]
-        ops.rotate_quantize(self.ffn, q=xq_f, scale=self.scale)
-        ops.int8_gemm_gated_residual(xq_f, self.scale, w["down"][0], w["down"][1], m[5], x)
-        return x
+    def weights(self, w):
+        """ops.BlockWeights of a synth.block_weights dict, the QKV rows reordered for this group."""
+        qkv = permute_qkv(w["qkv"][0], w["qkv"][1], self.heads, self.comm.size)
+        return self.ops.BlockWeights(w["norm1"], w["norm2"], w["q_norm"], w["k_norm"], qkv, w["o"], w["up_gate"], w["down"])
+
+    def buffers(self, x_local, mod, rope_full):
+        return self.ops.block_buffers(x_local, mod, rope_full, self.ws)
 
 
 # ----------------------------------------------------------------------------------------------------------- the bench
 
-def bench_ulysses(args, rank: int, world: int, local: int):
-    """bench.py --workload step2048_ulysses: the 2048^2 INT8 step (CFG batch 2: two sequences of 16384 image + 4096 text
-    tokens) with every sequence's tokens sharded over all ranks. Strong scaling: the job is one image."""
+def measure_ulysses(rank: int, world: int, blocks: int, F: int, steps: int, warmup: int, seq_lens=(20480, 20480)):
+    """The 2048^2 INT8 step (CFG batch 2: two sequences of 16384 image + 4096 text tokens) over all ranks of the job:
+    the two sequences go to two groups (no collective between them), the ranks of a group share their sequence's tokens
+    (Ulysses). Strong scaling: the job is one image. Returns (ms per step as the max over ranks, record of the layout)."""
     from . import ops, synth
-    D, heads, F = 3072, 24, args.ffn
-    seq_lens = [20480, 20480]
-    n_blocks = args.blocks
-    group = None
-    runner = UlyssesBlockRunner(seq_lens, D, F, heads, group)
-    weights = [synth.block_weights(D, F, 3000 + 100 * b) for b in range(n_blocks)]
-    x_full_rows = sum(seq_lens)
-    x0 = shard_tokens(synth.activations(x_full_rows, D, 1003), seq_lens, world, rank).contiguous()
+    D, heads = 3072, 24
+    seq_lens = list(seq_lens)
+    n_groups, sp = group_layout(world, len(seq_lens))
+    gid, grank = rank // sp, rank % sp
+    ranks = list(range(gid * sp, (gid + 1) * sp))
+    torch_groups = [dist.new_group(list(range(g * sp, (g + 1) * sp))) for g in range(n_groups)] if world > 1 and sp > 1 and n_groups > 1 else None
+    comm = make_sp_comm(ranks, rank, None if torch_groups is None else torch_groups[gid])
+    per_group = len(seq_lens) // n_groups
+    mine = seq_lens[gid * per_group:(gid + 1) * per_group]          # the sequences this group runs
+    first_row = sum(seq_lens[:gid * per_group])
+    blk = SpBlock(mine, comm, D, F, heads)
+    weights, keep = [], []
+    for b in range(blocks):
+        w = synth.block_weights(D, F, 3000 + 100 * b)
+        keep.append(w)
+        weights.append(blk.weights(w))
+    x_all = synth.activations(sum(seq_lens), D, 1003)
+    x0 = shard_tokens(x_all[first_row:first_row + sum(mine)], mine, sp, grank).contiguous()
+    del x_all
     mod = synth.modulation(D, 2001)
-    rope_one = ops.moss_rope_table(128, 128, 4096)
-    rope_local = shard_tokens(rope_one.repeat(len(seq_lens), 1), seq_lens, world, rank).contiguous()
+    grid = 128
+    rope_full = torch.cat([ops.moss_rope_table(grid, grid, s - grid * grid) for s in mine]).contiguous()
     x = x0.clone()
+    bufs = blk.buffers(x, mod, rope_full)
 
     def step():
         x.copy_(x0)
-        for w in weights:
-            runner.run(x, mod, rope_local, w)
+        ops.dit_step_sp(weights, bufs, blk.run, comm)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    elapsed = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-    if world > 1:
-        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-    ms_step = float(elapsed.item()) / args.steps
+    def timed():
+        for _ in range(max(warmup, 3)):
+            step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        barrier()
+        elapsed = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        return float(elapsed.item()) / steps
 
-    hx = x0.cpu().pin_memory()
-    hout = torch.empty_like(hx).pin_memory()
+    ms = timed()
+    ms_local = None
+    if sp > 1:  # the same step with every message replaced by a copy of equal size on the GPU itself
+        comm.local_exchange(True)
+        ms_local = timed()
+        comm.local_exchange(False)
+    hp = heads // sp
+    c = sum(mine) // sp
+    sent = (sp - 1) * c * (3 * hp * 128 + hp * 128) * 2
+    rec = {"layout": f"{n_groups} group(s) x sequence-parallel {sp}", "groups": n_groups, "sp": sp, "sequences": seq_lens,
+           "blocks": blocks, "ffn": F, "all_to_all_bytes_sent_per_gpu_per_block": sent, "kernel_status": list(ops.kernel_status()),
+           "ms_with_local_copies_for_exchanges": ms_local, "exposed_exchange_ms": None if ms_local is None else ms - ms_local,
+           "launches_per_block": 16 + (2 * (sp - 1) * per_group * 2 if sp > 1 else 0)}
+    comm.close()
+    del weights, keep, blk, bufs
+    torch.cuda.empty_cache()
+    return ms, rec
 
-    def e2e_step():
-        x0.copy_(hx, non_blocking=True)
-        step()
-        hout.copy_(x, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
 
-    e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    barrier()
-    e2e = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], device="cuda")
-    if world > 1:
-        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+def bench_ulysses(args, rank: int, world: int, local: int):
+    """bench.py --workload step2048_ulysses: prints the line of the 2048^2 sequence-parallel step on N GPUs."""
+    from . import ops
+    ms_step, rec = measure_ulysses(rank, world, args.blocks, args.ffn, args.steps, args.warmup)
     if rank == 0:
-        launches = (11 + 4 * len(seq_lens)) * n_blocks * args.steps
         line = {"metric": "dit_ms_per_step_2048", "value": ms_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
                 "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-                "config": {"workload": "step2048_ulysses", "blocks": n_blocks, "d": D, "heads": heads, "ffn": F,
-                           "sequences": seq_lens, "tier": "int8", "attention": "int8_fp8_f32acc",
-                           "parallelism": f"ulysses-sp{world}", "collective": "2 NCCL all-to-alls per block and sequence",
+                "config": {"workload": "step2048_ulysses", "blocks": args.blocks, "d": 3072, "heads": 24, "ffn": args.ffn,
+                           "sequences": rec["sequences"], "tier": "int8", "attention": "int8_fp8_f32acc",
+                           "parallelism": rec["layout"], "collective": "2 NCCL point-to-point exchanges per block inside a group",
                            "l2": "inputs larger than L2 (block weights stream from HBM every step)"},
-                "e2e": {"value": float(e2e.item()), "unit": "ms", "h2d_bytes_per_step": hx.numel() * 2,
-                        "d2h_bytes_per_step": hout.numel() * 2},
-                "gpu_launches": launches, "kernel_status": list(ops.kernel_status())}
+                "ulysses": rec, "gpu_launches": rec["launches_per_block"] * args.blocks * args.steps,
+                "kernel_status": list(ops.kernel_status())}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -317,6 +317,29 @@ def test_gemm_acc_with_ragged_n(ops):
         assert np.array_equal(acc.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32).T)
 
 
+def test_chunked_gemm_and_chunked_rotate_equal_the_plain_forms(ops):
+    """The column-chunked output of the GEMM and the column-chunked input of the rotation (the layouts the
+    sequence-parallel block exchanges) hold the same bits as the plain calls."""
+    from owoinfer_b200 import synth
+    m, k = 700, 1024
+    for n, chunk in ((1536, 768), (2304, 1152), (1536, 1536)):
+        x = synth.activations(m, k, 3 + n)
+        xq, xs = ops.rotate_quantize(x)
+        w, ws = synth.convrot_int8_weight(n, k, 5 + n)
+        bias = synth.vector(n, 6, 0.05)
+        plain = ops.int8_gemm(xq, xs, w, ws, bias=bias)
+        chunks = ops.int8_gemm_chunked(xq, xs, w, ws, chunk, bias=bias)
+        assert chunks.shape == (n // chunk, m, chunk)
+        want = plain.view(m, n // chunk, chunk).permute(1, 0, 2)
+        assert torch.equal(chunks.view(torch.int16), want.contiguous().view(torch.int16))
+    for k2, chunk in ((1024, 256), (3072, 768), (1536, 1536)):
+        a = synth.activations(333, k2, 9 + k2)
+        q, s = ops.rotate_quantize(a)
+        ch = a.view(333, k2 // chunk, chunk).permute(1, 0, 2).contiguous()
+        q2, s2 = ops.rotate_quantize_chunked(ch)
+        assert torch.equal(q, q2) and torch.equal(s.view(torch.int32), s2.view(torch.int32))
+
+
 def test_gemm_linearity_at_full_size(ops):
     # Size-independent property at the BASELINE shape (8192 x 9216 x 3072): acc(x, w) + acc(x2, w) == acc over the
     # concatenated K of [x | x2] and [w | w], checked on the int32 accumulators through sampled rows' exact dot products.
@@ -598,6 +621,23 @@ def test_block_config0_against_oracle(ops):
     want = _oracle_block(ops, x, mod, w, rope, cu, lens, heads, 0)
     cos, max_rel = _rel_metrics(u16(got), want)
     assert cos >= 0.9995 and max_rel <= 1e-2, (cos, max_rel)
+
+
+def test_sequence_parallel_block_of_one_rank_equals_the_block(ops):
+    """b2_run_block_quant_sp with a group of one (no NCCL involved): its chunked GEMM output, its strided attention views,
+    its chunked rotation input and its own buffer layout must reproduce b2_run_block_quant bit for bit, fused and
+    separate QK-norm + RoPE, two sequences."""
+    from owoinfer_b200 import parallel
+    lens, D, F, heads = [1700, 1500], 512, 1024, 4
+    x, mod, w, rope, cu = _block_case(ops, lens, D, F, heads, 0, 5)
+    want = _run_block(ops, x, mod, w, rope, cu, lens, D, F, heads, 0, -1)
+    comm = ops.SpComm(1, 0)
+    blk = parallel.SpBlock(lens, comm, D, F, heads)
+    got = x.clone()
+    ops.run_block_quant_sp(blk.weights(w), blk.buffers(got, mod, rope), blk.run, comm)
+    torch.cuda.synchronize()
+    comm.close()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
 
 
 def test_block_fused_equals_separate_norm_rope_and_graph_replay(ops):

@@ -28,6 +28,66 @@ def test_shard_roundtrip_and_uneven_rejected():
         parallel.ulysses_local_lengths([10], 4)
 
 
+def test_group_layout_and_qkv_row_order():
+    assert parallel.group_layout(8, 2) == (2, 4) and parallel.group_layout(4, 2) == (2, 2)
+    assert parallel.group_layout(2, 2) == (2, 1) and parallel.group_layout(1, 2) == (1, 1)
+    assert parallel.group_layout(4, 1) == (1, 4) and parallel.group_layout(6, 4) == (2, 3)
+    heads, size = 8, 4
+    order = parallel.sp_qkv_row_order(heads, size)
+    assert sorted(order.tolist()) == list(range(3 * heads * 128))
+    # Column block r of the reordered GEMM output = [q | k | v] of heads r * hp .. r * hp + hp - 1.
+    hp = heads // size
+    cols = torch.arange(3 * heads * 128).view(3, heads, 128)
+    for r in range(size):
+        block = order[r * 3 * hp * 128:(r + 1) * 3 * hp * 128].view(3, hp, 128)
+        assert torch.equal(block, cols[:, r * hp:(r + 1) * hp])
+    w = torch.arange(3 * heads * 128 * 2).view(3 * heads * 128, 2)
+    pw, ps = parallel.permute_qkv(w, torch.arange(3 * heads * 128), heads, size)
+    assert torch.equal(pw[:, 0] // 2, ps) and torch.equal(ps, order)
+    assert torch.equal(parallel.sp_qkv_row_order(heads, 1), torch.arange(3 * heads * 128))
+
+
+def test_sp_run_is_validated_before_any_work():
+    """b2_block_quant_sp_workspace_bytes / b2_run_block_quant_sp refuse runs the path cannot serve (no GPU needed)."""
+    import ctypes as C
+    from owoinfer_b200 import _lib
+    lib = _lib.lib()
+
+    def run(seq_lens, size, heads=24, tier=0, tokens=None):
+        r = _lib.SpRun()
+        r.struct_size = C.sizeof(_lib.SpRun)
+        b = r.local
+        b.struct_size = C.sizeof(_lib.BlockRun)
+        b.tokens = sum(s // size for s in seq_lens) if tokens is None else tokens
+        b.D, b.F, b.heads = heads * 128, 1024, heads
+        b.cu_seqlens, b.batch, b.max_seqlen, b.tier = 0x1000, len(seq_lens), max(seq_lens), tier
+        arr = (C.c_int32 * len(seq_lens))(*seq_lens)
+        r.seq_lens_host = C.cast(arr, C.c_void_p)
+        r._keep = arr
+        return r
+
+    need = lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096, 2048], 4)), 4)
+    assert need > 0
+    assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096, 2048], 4)), 8) == 0       # 3 heads per rank: odd
+    assert b"even number per rank" in lib.b2_last_error_message()
+    assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096, 2050], 4)), 4) == 0       # length not divisible
+    assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096], 4, tier=2)), 4) == 0     # INT8 tier only
+    assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096], 4, tokens=1000)), 4) == 0
+    assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096], 5)), 5) == 0             # heads % size
+    # A group of one needs neither an id nor NCCL.
+    comm = C.c_void_p()
+    assert lib.b2_sp_comm_create(None, C.c_size_t(0), 1, 0, C.byref(comm)) == 0 and comm.value
+    assert lib.b2_sp_comm_create(None, C.c_size_t(0), 2, 0, C.byref(C.c_void_p())) == -1      # size 2 without an id
+    assert lib.b2_sp_comm_create(None, C.c_size_t(0), 2, 2, C.byref(C.c_void_p())) == -1
+    w, a = _lib.BlockWeights(), _lib.BlockBuffers()
+    w.struct_size, a.struct_size = C.sizeof(_lib.BlockWeights), C.sizeof(_lib.BlockBuffers)
+    a.x = a.mod = a.rope = a.workspace = 0x10000
+    a.workspace_bytes = need - 1
+    assert lib.b2_run_block_quant_sp(C.byref(w), C.byref(a), C.byref(run([4096, 2048], 1)), comm, None) == -1
+    assert b"workspace" in lib.b2_last_error_message()
+    assert lib.b2_sp_comm_destroy(comm) == 0
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
