@@ -16,12 +16,27 @@ _LIB_PATH = os.path.join(_DIR, "liboracle.so")
 _REF_PATH = os.path.join(_DIR, "_ref", "libref_codec.so")
 
 
+def reference_root():
+    """Where the reference engine's source tree is, or None: the MOSSINFER_REFERENCE environment variable, else a
+    directory named `reference` beside this repository."""
+    env = os.environ.get("MOSSINFER_REFERENCE")
+    if env:
+        return env if os.path.isdir(env) else None
+    beside = os.path.join(os.path.dirname(os.path.dirname(_DIR)), "reference")
+    return beside if os.path.isdir(os.path.join(beside, "src")) else None
+
+
+def make_args():
+    ref = reference_root()
+    return ["make", "-C", _DIR] + ([f"REF={ref}"] if ref else [])
+
+
 def build(force: bool = False) -> None:
     """Compile liboracle.so (and _ref/libref_codec.so when the reference tree is present)."""
     src = os.path.join(_DIR, "oracle.cpp")
     stale = not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
     if force or stale:
-        subprocess.check_call(["make", "-C", _DIR, "-B", "all"], stdout=subprocess.DEVNULL)
+        subprocess.check_call(make_args() + ["-B", "all"], stdout=subprocess.DEVNULL)
 
 
 _lib = None

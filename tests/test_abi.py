@@ -219,6 +219,36 @@ def test_block_rejects_mismatched_buffers():
     assert _status(lib.b2_run_block_quant(C.byref(w), C.byref(b), C.byref(run), None))[0] == -1
 
 
+def test_cpp_shim_compiles_against_the_reference_headers():
+    """include/owoinfer_b200_shim.hpp takes moss_dit::run_block_quant's parameters in its order
+    (src/models/moss_dit/dit_block_quant.h:145-146): checked by the compiler against the reference's own headers."""
+    import shutil
+    import subprocess
+    from oracle import oracle_lib
+    ref = oracle_lib.reference_root()
+    cuda_inc = "/usr/local/cuda/include"
+    if ref is None or shutil.which("g++") is None or not os.path.exists(os.path.join(cuda_inc, "cuda_runtime.h")):
+        pytest.skip("needs the reference tree, g++ and the CUDA headers")
+    caller = """
+#include "owoinfer_b200_shim.hpp"
+namespace md = mi::moss_dit;
+void call(const md::BlockTensors& w, const md::QuantBlockBuffers& a, const md::BlockRun& run, const md::QkvGemm& g,
+          const md::FusedRouteSnapshot& r, cudaStream_t s, void* ws, std::size_t n) {
+  // the reference's own entry point and the adapter take the same leading arguments
+  void (*ref_fn)(const md::BlockTensors&, const md::QuantBlockBuffers&, const md::BlockRun&, const md::QkvGemm&,
+                 const md::FusedRouteSnapshot&, md::AttentionMode, cudaStream_t, int) = &md::run_block_quant;
+  (void)ref_fn;
+  if (md::b200_can_run(w, a, run, md::AttentionMode::kQ8Fp8F32Acc)) {
+    md::run_block_quant_b200(w, a, run, g, r, md::AttentionMode::kQ8Fp8F32Acc, s, 0, ws, n);
+  }
+  (void)md::b200_workspace_bytes(w, run);
+}
+"""
+    r = subprocess.run(["g++", "-std=c++20", "-fsyntax-only", "-I", os.path.join(ref, "src"), "-I", os.path.join(ROOT, "include"),
+                        "-I", cuda_inc, "-x", "c++", "-"], input=caller, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+
+
 def test_python_layer_fails_loudly_without_library(tmp_path, monkeypatch):
     monkeypatch.setattr(_lib, "_lib", None)
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "missing.so"))
