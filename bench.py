@@ -303,21 +303,22 @@ def profile_kernels(ops, torch, L, F, w, iters=8, ref=None):
     return out
 
 
-def single_gpu_step_ms(torch, ops, synth, seq_lens, blocks, F, steps, warmup):
+def single_gpu_step_ms(torch, ops, synth, seq_lens, blocks, F, steps, warmup, tier=0):
     """ms per step of the whole step on THIS GPU alone through b2_dit_step (CUDA-graph replay): the base the
-    sequence-parallel record is compared with."""
+    sequence-parallel record is compared with, and the grouped 4-bit tier's figure beside the INT8 headline."""
     L, seq_len = sum(seq_lens), max(seq_lens)
     keep, bws = [], []
     for b in range(blocks):
-        w = synth.block_weights(D, F, 3000 + 100 * b)
-        keep.append(w)
-        bws.append(ops.BlockWeights(w["norm1"], w["norm2"], w["q_norm"], w["k_norm"], w["qkv"], w["o"], w["up_gate"], w["down"]))
+        w = synth.block_weights(D, F, 3000 + 100 * b, tier=tier)
+        lin = {n: (ops.make_w4(w[n][0], w[n][1], 64, w[n][2]) if tier == ops.TIER_W4A8 else w[n]) for n in ("qkv", "o", "up_gate", "down")}
+        keep.append((w, lin))
+        bws.append(ops.BlockWeights(w["norm1"], w["norm2"], w["q_norm"], w["k_norm"], lin["qkv"], lin["o"], lin["up_gate"], lin["down"]))
     x0 = synth.activations(L, D, 1003)
     mod = synth.modulation(D, 2001)
     grid = 128 if seq_len > 16384 else 64
     rope = torch.cat([ops.moss_rope_table(grid, grid, s - grid * grid) for s in seq_lens]).contiguous()
     cu = synth.cu_seqlens(seq_lens)
-    run = ops.block_run(L, cu, seq_len, D=D, F=F, heads=HEADS)
+    run = ops.block_run(L, cu, seq_len, D=D, F=F, heads=HEADS, tier=tier)
     ws = torch.empty(ops.block_quant_workspace_bytes(run), dtype=torch.uint8, device="cuda")
     x = x0.clone()
     bufs = ops.block_buffers(x, mod, rope, ws)
@@ -450,7 +451,7 @@ def main():
     ws = torch.empty(ops.block_quant_workspace_bytes(run), dtype=torch.uint8, device="cuda")
     x = x0.clone()
     bufs = ops.block_buffers(x, mod, rope, ws)
-    launches_per_block = 12 if tier == ops.TIER_INT8 else 16
+    launches_per_block = 12  # the grouped 4-bit tier decodes inside its GEMMs (e4m3 group scales): the same twelve launches
 
     # The step (504 launches) is captured once into a CUDA graph and replayed, as the reference's engine does with its step
     # graphs; the first SiTU-GLU call fills its tables outside any capture, hence the eager call first.
@@ -547,6 +548,12 @@ def main():
                                               f"heads ({ta:.2f} s), extrapolated to {n_blocks} blocks x {seqs} x {seq_len} tokens"}
             if world == 1 and tier == ops.TIER_INT8 and not args.no_ref_gpu:
                 line["reference_gpu"] = reference_kernels_on_this_gpu(torch, ops, keep, x, x0, mod, rope, cu, seq_len, L, F)
+            if world == 1 and args.workload == "step1024":
+                # The same step with grouped 4-bit weights (W4A8, group 64, e4m3 group scales), decoded inside the GEMMs.
+                del blocks, keep, bufs, graph
+                torch.cuda.empty_cache()
+                line["extra"] = {"turbo1024_ms": single_gpu_step_ms(torch, ops, synth, [seq_len] * seqs, n_blocks, F, min(args.steps, 5), 3,
+                                                                    tier=ops.TIER_W4A8)}
     if world > 1 and args.workload == "step1024" and not args.no_ulysses and tier == ops.TIER_INT8:
         # The headline above is image data parallel (no collective). The sequence-parallel configuration, the one with an
         # exchange step, rides along as its own record: free the headline's buffers first.

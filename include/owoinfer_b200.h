@@ -355,11 +355,20 @@ int b2_run_block_quant_sp(const b2_block_weights* w, const b2_block_buffers* a, 
 int b2_dit_step_sp(const b2_block_weights* blocks, int num_blocks, const b2_block_buffers* a, const b2_sp_run* run,
                    b2_sp_comm* comm, void* stream);
 
-/* Every mbarrier wait inside the tensor-core kernels is bounded; a CTA whose wait expired raises a device word, drains
- * and returns instead of hanging. This reads the two words (GEMM, attention): 0 = no wait ever expired on this device.
+/* Every mbarrier wait inside the tensor-core kernels is bounded (200 ms); a CTA whose wait expired raises a device word,
+ * drains and returns instead of hanging. This reads the two words (GEMM, attention): 0 = no wait ever expired on this device.
  * Synchronises the device; for tests and post-mortems, not for the hot path. No counterpart in the reference (its
  * kernels have no device-side waits). */
 int b2_kernel_status(int* gemm, int* attention);
+/* Zeroes both words (after a post-mortem). Synchronises the device. */
+int b2_kernel_status_clear(void);
+/* Test hook of the bounded waits. wait_limit_ns != 0 sets how long a wait inside the GEMM kernel may last on the current
+ * device (default 200 ms; the attention kernel's limit is fixed at 200 ms). skip_gemm_stage != 0 makes the TMA warp of
+ * every GEMM CTA leave out the loads of the last K block of its first tile: that stage's barrier then never completes,
+ * the waits run out after the limit, every CTA raises the status word, drains, frees its tensor memory and returns (the
+ * output of that launch is garbage, nothing faults or hangs). Call again with (0-or-limit, 0) to switch it off.
+ * No counterpart in the reference. */
+int b2_debug_bounded_wait(uint64_t wait_limit_ns, int skip_gemm_stage);
 
 #ifdef __cplusplus
 }

@@ -35,7 +35,8 @@ int sm_count() {
 }
 
 bool make_tensor_map_2d(CUtensorMap* map, const void* base, std::uint64_t inner, std::uint64_t rows,
-                        std::uint64_t row_stride, std::uint32_t inner_box, std::uint32_t row_box, const char* op) {
+                        std::uint64_t row_stride, std::uint32_t inner_box, std::uint32_t row_box, const char* op,
+                        int swizzle_bytes) {
   static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {
@@ -55,7 +56,8 @@ bool make_tensor_map_2d(CUtensorMap* map, const void* base, std::uint64_t inner,
   const cuuint32_t box[2] = {inner_box, row_box};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     fail_status(B2_ERR_CUDA, op, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)) +

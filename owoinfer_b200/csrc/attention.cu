@@ -56,7 +56,7 @@ __device__ __forceinline__ bool wait_bar(std::uint32_t bar, std::uint32_t parity
       if (mbar_try_wait_hint(bar, parity)) return true;
     }
     if (*abort_word != 0) return false;
-    if (global_ns() - t0 > 1000000000ull) {
+    if (global_ns() - t0 > 200000000ull) {
       *abort_word = 1;
       return false;
     }
@@ -76,7 +76,7 @@ __device__ __forceinline__ bool wait_bar_relaxed(std::uint32_t bar, std::uint32_
       if (mbar_try_wait(bar, parity)) return true;
     }
     if (*abort_word != 0) return false;
-    if (global_ns() - t0 > 1000000000ull) {
+    if (global_ns() - t0 > 200000000ull) {
       *abort_word = 1;
       return false;
     }
@@ -1141,6 +1141,11 @@ float resolve(float v) { return v > 0 ? v : 448.f; }
 
 int attn_status_word(int* host_value) {
   const cudaError_t e = cudaMemcpyFromSymbol(host_value, g_attn_status, sizeof(int));
+  return e == cudaSuccess ? B2_OK : fail_cuda("attention_status", e);
+}
+int attn_status_clear() {
+  const int zero = 0;
+  const cudaError_t e = cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int));
   return e == cudaSuccess ? B2_OK : fail_cuda("attention_status", e);
 }
 

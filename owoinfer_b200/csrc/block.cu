@@ -76,13 +76,7 @@ int site_operands(const char* op, const b2_linear& lin, int tier, std::int8_t* w
     *w = w_unpack, *ws = lin.scale;
     return B2_OK;
   }
-  if (lin.w4 == nullptr) return fail_invalid(op, "missing grouped 4-bit weight");
-  if (const int rc = b2_decode_grouped_int8(lin.w4->packed, lin.w4->s_rel, lin.w4->scale_kind, lin.w4->codebook, n, k,
-                                            lin.w4->group, w_unpack, nullptr, stream)) {
-    return rc;
-  }
-  *w = w_unpack, *ws = lin.w4->s_channel;
-  return B2_OK;
+  return fail_status(B2_ERR_INTERNAL, op, "unexpected tier");
 }
 
 }  // namespace
@@ -138,19 +132,27 @@ int b2_run_block_quant(const b2_block_weights* w, const b2_block_buffers* a, con
     if (const int rc = b2_convrot_quantize_int4(in, k, x4, k / 2, scale, L, static_cast<int>(k), st)) return rc;
     return b2_unpack_int4(x4, k / 2, xq, k, L, k, st);
   };
-  const auto operands = [&](const b2_linear& lin, std::int64_t n, std::int64_t k, b2_int8_operands* o) -> int {
+  // One linear site with its epilogue (0 plain, 1 gated residual with gate `aux`, 2 SiTU-GLU) under the run's tier. The
+  // grouped 4-bit tier goes through b2_w4a8_gemm, which decodes inside the GEMM where the weight's format allows and
+  // through the scratch otherwise.
+  const auto site = [&](const b2_linear& lin, std::int64_t n, std::int64_t k, int epilogue, const void* aux, void* out,
+                        std::int64_t ldo) -> int {
+    if (run->tier == B2_TIER_W4A8) {
+      if (lin.w4 == nullptr) return fail_invalid(op, "missing grouped 4-bit weight");
+      return b2_w4a8_gemm(xq, k, scale, lin.w4, L, n, k, epilogue, aux, out, ldo, w_unpack, st);
+    }
     const std::int8_t* wq = nullptr;
     const float* wsc = nullptr;
     if (const int rc = site_operands(op, lin, run->tier, w_unpack, n, k, st, &wq, &wsc)) return rc;
-    *o = b2_int8_operands{xq, k, scale, wq, wsc, L, n, k};
-    return B2_OK;
+    const b2_int8_operands o{xq, k, scale, wq, wsc, L, n, k};
+    if (epilogue == 0) return b2_int8_gemm(&o, aux, out, ldo, st, B2_TILE_AUTO);
+    if (epilogue == 1) return b2_int8_gemm_gated_residual(&o, nullptr, aux, out, ldo, st, B2_TILE_AUTO);
+    return b2_int8_gemm_situ_glu(&o, out, ldo, st, B2_TILE_AUTO);
   };
 
-  b2_int8_operands g{};
   // QKV projection.
   if (const int rc = quant_norm(w->norm1, mod + 1 * D, mod + 0 * D)) return rc;
-  if (const int rc = operands(w->qkv, 3 * D, D, &g)) return rc;
-  if (const int rc = b2_int8_gemm(&g, nullptr, qkv, 3 * D, st, B2_TILE_AUTO)) return rc;
+  if (const int rc = site(w->qkv, 3 * D, D, 0, nullptr, qkv, 3 * D)) return rc;
 
   // Attention. QK-norm + RoPE inside the pre-pass from 3072 tokens on (same bits either way).
   const bool fused = run->fused_norm_rope < 0 ? L >= kFusedNormRopeMinTokens : run->fused_norm_rope != 0;
@@ -170,18 +172,15 @@ int b2_run_block_quant(const b2_block_weights* w, const b2_block_buffers* a, con
 
   // x += o(attn) * gate_a.
   if (const int rc = quant_plain(attn, D)) return rc;
-  if (const int rc = operands(w->o, D, D, &g)) return rc;
-  if (const int rc = b2_int8_gemm_gated_residual(&g, nullptr, mod + 2 * D, a->x, D, st, B2_TILE_AUTO)) return rc;
+  if (const int rc = site(w->o, D, D, 1, mod + 2 * D, a->x, D)) return rc;
 
   // ffn = situ_glu(up_gate(rms_norm_modulate(x))).
   if (const int rc = quant_norm(w->norm2, mod + 4 * D, mod + 3 * D)) return rc;
-  if (const int rc = operands(w->up_gate, 2 * F, D, &g)) return rc;
-  if (const int rc = b2_int8_gemm_situ_glu(&g, ffn, F, st, B2_TILE_AUTO)) return rc;
+  if (const int rc = site(w->up_gate, 2 * F, D, 2, nullptr, ffn, F)) return rc;
 
   // x += down(ffn) * gate_f.
   if (const int rc = quant_plain(ffn, F)) return rc;
-  if (const int rc = operands(w->down, D, F, &g)) return rc;
-  return b2_int8_gemm_gated_residual(&g, nullptr, mod + 5 * D, a->x, D, st, B2_TILE_AUTO);
+  return site(w->down, D, F, 1, mod + 5 * D, a->x, D);
 }
 
 int b2_kernel_status(int* gemm, int* attention) {
@@ -191,6 +190,15 @@ int b2_kernel_status(int* gemm, int* attention) {
   if (gemm != nullptr) *gemm = g;
   if (attention != nullptr) *attention = t;
   return B2_OK;
+}
+
+int b2_kernel_status_clear(void) {
+  if (const int rc = gemm_status_clear()) return rc;
+  return attn_status_clear();
+}
+
+int b2_debug_bounded_wait(uint64_t wait_limit_ns, int skip_gemm_stage) {
+  return gemm_debug_set(wait_limit_ns, skip_gemm_stage != 0 ? 1 : 0);
 }
 
 int b2_dit_step(const b2_block_weights* blocks, int num_blocks, const b2_block_buffers* a, const b2_block_run* run,

@@ -31,15 +31,22 @@ inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 // Device words that a tensor-core kernel raises when one of its bounded waits expired (0 = never).
 int gemm_status_word(int* host_value);
 int attn_status_word(int* host_value);
+int gemm_status_clear();
+int attn_status_clear();
+// Test hooks of the GEMM kernel's bounded waits: the limit in nanoseconds (0 = leave it) and the "skip one stage" switch.
+int gemm_debug_set(unsigned long long wait_limit_ns, int skip_stage);
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
 // 2-D tensor of bytes: inner extent `inner` bytes (contiguous), `rows` rows of `row_stride` bytes; box inner_box x row_box,
-// 128-byte swizzle. Returns false (and sets the last error) on failure.
+// swizzle of `swizzle_bytes` (128 or 64). Returns false (and sets the last error) on failure.
 bool make_tensor_map_2d(CUtensorMap* map, const void* base, std::uint64_t inner, std::uint64_t rows,
-                        std::uint64_t row_stride, std::uint32_t inner_box, std::uint32_t row_box, const char* op);
+                        std::uint64_t row_stride, std::uint32_t inner_box, std::uint32_t row_box, const char* op,
+                        int swizzle_bytes = 128);
+// The device word that a grouped 4-bit decode raises on a NaN or negative group scale (address on the current device).
+int w4_invalid_word(void** out);
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------------------------------------------

@@ -20,10 +20,11 @@
 //   SiTU-GLU        h = bf16(deq(acc_hidden)), g = bf16(deq(acc_gate)); out = bf16(gateF[g] * hiddenF[h]) with the two
 //                   factors tabulated over every bf16 input. The B tile of output columns [128 t, 128 t + 128) is hidden
 //                   rows 128 t.. followed by gate rows F + 128 t.., so one thread finds both halves in its TMEM lane.
-// Every wait on an mbarrier is bounded (one second of %globaltimer); on expiry the CTA raises a status word, drains
+// Every wait on an mbarrier is bounded (200 ms of %globaltimer by default); on expiry the CTA raises a status word, drains
 // and frees its TMEM instead of hanging.
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -48,7 +49,11 @@ enum class Epi : int { kPlain = 0, kGatedResidual = 1, kSituGlu = 2, kAcc = 3 };
 __host__ __device__ constexpr int epi_warps(Epi e, int bn) {
   return e == Epi::kSituGlu ? 16 : bn != 256 ? 8 : e == Epi::kGatedResidual ? B2_EPI_WARPS_GATED : e == Epi::kPlain ? B2_EPI_WARPS_PLAIN : 8;
 }
-__host__ __device__ constexpr int threads_of(Epi e, int bn) { return 64 + 32 * epi_warps(e, bn); }
+// W4A8: four more warps expand the packed 4-bit weight tile into the INT8 operand stage (one weight row per thread).
+constexpr int kConvWarps = 4;
+__host__ __device__ constexpr int threads_of(Epi e, int bn, bool w4 = false) {
+  return 64 + 32 * epi_warps(e, bn) + (w4 ? 32 * kConvWarps : 0);
+}
 // Shared-memory slice of the SiTU factor tables: inputs with 2^-26 <= |x| < 2^6 (bf16 exponent field 101..132), where all
 // but a vanishing share of the pre-activations fall. Gate factors: [sign][exponent - 101][mantissa]; hidden factors: the
 // positive half only (25 tanh(h / 25) is odd and every rounding in it is sign-symmetric, so the factor of -h is the
@@ -75,9 +80,21 @@ struct GemmParams {
   // to chunk i, an [m, chunk_cols] matrix of row stride ldo that starts chunk_stride elements after chunk i - 1.
   int chunk_cols;
   std::int64_t chunk_stride;
+  // W4A8 (kW4 kernels): the B tensor map covers the packed codes [n, k / 2]; group scales e4m3 [n, k / group]; the 16
+  // levels (codebook or code - 8); the word that a NaN or negative scale raises.
+  const std::uint8_t* w4_srel;
+  int w4_group;
+  const float* w4_codebook;
+  unsigned* w4_invalid;
 };
 
 __device__ int g_gemm_status = 0;  // set to 1 by a CTA whose bounded wait expired
+// How long a wait on an mbarrier may last. A step never comes near it (the longest wait of a healthy launch is one K
+// loop, tens of microseconds); an operator does not notice it.
+__device__ unsigned long long g_gemm_wait_limit_ns = 200000000ull;
+// Test hook: 1 = the TMA warp of every CTA leaves out the loads of the last K block of its first tile, so that the
+// stage's barrier never completes and the bounded waits run out.
+__device__ int g_gemm_test_skip_stage = 0;
 
 __device__ __forceinline__ std::uint64_t global_ns() {
   std::uint64_t t;
@@ -85,14 +102,14 @@ __device__ __forceinline__ std::uint64_t global_ns() {
   return t;
 }
 
-// Bounded mbarrier wait on wall time (1 s). Returns false when it gave up or another role already aborted.
+// Bounded mbarrier wait on wall time (g_gemm_wait_limit_ns). Returns false when it gave up or another role already aborted.
 __device__ __forceinline__ bool wait_bar(std::uint32_t bar, std::uint32_t parity, volatile int* abort_word) {
   if (mbar_try_wait(bar, parity)) return true;
   const std::uint64_t t0 = global_ns();
   for (;;) {
     if (mbar_try_wait_hint(bar, parity)) return true;
     if (*abort_word != 0) return false;
-    if (global_ns() - t0 > 1000000000ull) {
+    if (global_ns() - t0 > g_gemm_wait_limit_ns) {
       *abort_word = 1;
       return false;
     }
@@ -133,26 +150,51 @@ __device__ __forceinline__ float situ_factor_full(const std::uint16_t* full, std
 }
 
 // kCtas == 2: a CTA pair shares one 256 x 256 tile; each CTA stages its 128 rows of A and 128 of the 256 rows of B.
-template <int kBN, int kCtas>
+// kW4: the stage also holds the packed 4-bit weight tile (half the bytes of the INT8 one) that the TMA warp brings and
+// the converter warps expand into the B operand.
+template <int kBN, int kCtas, bool kW4 = false>
 struct Shape {
-  static constexpr int kStages = (kBN == 256 && kCtas == 1) ? 4 : 6;
+  static constexpr int kStages = kW4 ? 4 : (kBN == 256 && kCtas == 1) ? 4 : 6;
   static constexpr int kABytes = kBM * kBK;
   static constexpr int kBBytes = (kBN / kCtas) * kBK;
-  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kPBytes = kW4 ? kBBytes / 2 : 0;
+  static constexpr int kStageBytes = kABytes + kBBytes + kPBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
 };
 
-template <int kBN, Epi kEpi, int kCtas>
-__global__ void __launch_bounds__(threads_of(kEpi, kBN), 1)
+// Eight 4-bit codes (nibble i = column i) -> eight INT8 values through the 16-entry table `t` of their (row, group):
+// two byte permutes pick among entries 0..7 and 8..15 by the low three bits of each code, a third takes the right one by
+// the code's top bit.
+__device__ __forceinline__ void expand8(std::uint32_t w, const uint4& t, std::uint32_t& lo, std::uint32_t& hi) {
+  const std::uint32_t s1 = w & 0x77777777u, s2 = ((w >> 1) & 0x44444444u) | 0x32103210u;
+  lo = __byte_perm(__byte_perm(t.x, t.y, s1), __byte_perm(t.z, t.w, s1), s2);
+  hi = __byte_perm(__byte_perm(t.x, t.y, s1 >> 16), __byte_perm(t.z, t.w, s1 >> 16), s2 >> 16);
+}
+__device__ __forceinline__ float e4m3_value(std::uint32_t b) {
+  const std::uint32_t e = (b >> 3) & 0xF, mant = b & 7;
+  float mag;
+  if (e == 0xF && mant == 7) mag = __int_as_float(0x7FC00000);
+  else if (e == 0) mag = static_cast<float>(mant) * 0.001953125f;  // 2^-9
+  else mag = __uint_as_float(((e + 120u) << 23) | (mant << 20));
+  return (b & 0x80) ? -mag : mag;
+}
+
+template <int kBN, Epi kEpi, int kCtas, bool kW4 = false>
+__global__ void __launch_bounds__(threads_of(kEpi, kBN, kW4), 1)
 int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   static_assert(kCtas == 1 || kBN == 256, "CTA pairs run 256 x 256 tiles");
-  using S = Shape<kBN, kCtas>;
+  static_assert(!kW4 || kBN / kCtas == 128, "W4A8: one weight row of the stage per converter thread");
+  using S = Shape<kBN, kCtas, kW4>;
   const std::uint32_t rank = kCtas == 2 ? cluster_ctarank() : 0u;   // CTA of the pair; rank 0 issues the MMAs
   const int tile0 = kCtas == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int tile_step = kCtas == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   constexpr int kStages = S::kStages;
   extern __shared__ std::uint8_t smem_raw[];
   __shared__ __align__(8) std::uint64_t s_full[kStages], s_empty[kStages], s_tmem_full[2], s_tmem_empty[2];
+  __shared__ __align__(8) std::uint64_t s_pfull[kW4 ? kStages : 1];  // W4A8: the packed tile of a stage has landed
+  // W4A8: for every e4m3 scale byte the 16 INT8 values clamp(rint(level[c] * scale), +-127); zeros for a NaN or negative
+  // scale. 4 KB, filled once per CTA.
+  __shared__ __align__(16) uint4 s_lut[kW4 ? 256 : 1];
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
   // Per epilogue warp: w_scale, bias, gate of its 128 columns (SiTU-GLU: w_scale of its 32 hidden and 32 gate columns).
@@ -165,11 +207,14 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const std::uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const auto a_addr = [&](int s) { return tiles_base + static_cast<std::uint32_t>(s) * S::kStageBytes; };
   const auto b_addr = [&](int s) { return a_addr(s) + S::kABytes; };
+  const auto p_addr = [&](int s) { return b_addr(s) + S::kBBytes; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&s_full[s]), 1);
+      // W4A8: the TMA's arrival (A) plus one per converter warp of the pair (B).
+      mbar_init(smem_u32(&s_full[s]), kW4 ? 1 + kConvWarps * kCtas : 1);
       mbar_init(smem_u32(&s_empty[s]), 1);
+      if constexpr (kW4) mbar_init(smem_u32(&s_pfull[s]), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&s_tmem_full[i]), 1);
@@ -187,6 +232,19 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else {
       tmem_alloc(smem_u32(&s_tmem_base), 512);
       tmem_relinquish();
+    }
+  }
+  if constexpr (kW4) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+      const float sc = e4m3_value(static_cast<std::uint32_t>(i));
+      const bool ok = !(isnan(sc) || sc < 0.0f);
+      std::uint32_t wds[4] = {0u, 0u, 0u, 0u};
+      for (int c = 0; c < 16 && ok; ++c) {
+        const float level = p.w4_codebook != nullptr ? p.w4_codebook[c] : static_cast<float>(c) - 8.0f;
+        const float v = fminf(127.f, fmaxf(-127.f, rintf(fmul(level, sc))));
+        wds[c >> 2] |= (static_cast<std::uint32_t>(static_cast<int>(v)) & 0xFFu) << (8 * (c & 3));
+      }
+      s_lut[i] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
     }
   }
   if constexpr (kEpi == Epi::kSituGlu) {
@@ -223,12 +281,27 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           row_b1 = nt * kBN + 128;
         }
         if (kCtas == 2 && rank == 1) row_b0 = row_b1;  // the pair's second CTA stages the second 128 rows of B
+        const bool skip_last = g_gemm_test_skip_stage != 0 && tile == tile0;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = static_cast<int>(it % kStages);
           const std::uint32_t ph = (it / kStages) & 1u;
           if (!wait_bar(smem_u32(&s_empty[s]), ph ^ 1u, abort_word)) break;
+          if (skip_last && kb + 1 == k_blocks) break;  // test hook: this stage never fills
           const std::uint32_t full = smem_u32(&s_full[s]);
-          if constexpr (kCtas == 2) {
+          if constexpr (kW4) {
+            // A as in the INT8 kernel; the packed weight tile (64 bytes per row and K block) lands on this CTA's own
+            // barrier, where its converter warps pick it up.
+            if constexpr (kCtas == 2) {
+              if (rank == 0) mbar_expect_tx(full, 2 * S::kABytes);
+              tma_load_2d_pair(a_addr(s), &map_a, map_to_cta(full, 0), kb * kBK, row_a);
+            } else {
+              mbar_expect_tx(full, S::kABytes);
+              tma_load_2d(a_addr(s), &map_a, full, kb * kBK, row_a);
+            }
+            const std::uint32_t pfull = smem_u32(&s_pfull[s]);
+            mbar_expect_tx(pfull, S::kPBytes);
+            tma_load_2d(p_addr(s), &map_b, pfull, kb * (kBK / 2), row_b0);
+          } else if constexpr (kCtas == 2) {
             // Both CTAs' copies complete on the leader's barrier, which expects the bytes of the whole pair.
             if (rank == 0) mbar_expect_tx(full, 2 * S::kStageBytes);
             const std::uint32_t full_leader = map_to_cta(full, 0);
@@ -293,6 +366,66 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
     }
     __syncwarp();
+  } else if (kW4 && warp >= 2 + epi_warps(kEpi, kBN)) {
+    // W4A8 converters: thread r owns weight row r of the CTA's 128-row stage. Per K block it reads the row's 64 packed
+    // bytes (TMA wrote them with the 64-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ ((r / 2) % 4)), looks the
+    // (row, group) table up by the group's scale byte and writes the 128 INT8 values into the B stage in the
+    // 128-byte-swizzled layout the MMA reads (chunk n of row r at n ^ (r % 8)); then the warp arrives on the stage's
+    // "full" barrier (the leader's, for a pair) in place of a TMA completion.
+    const int r = (warp - 2 - epi_warps(kEpi, kBN)) * 32 + lane;
+    const int groups = p.k / p.w4_group;
+    std::uint32_t it = 0;
+    bool bad = false;
+    for (int tile = tile0; tile < total_tiles && *abort_word == 0; tile += tile_step) {
+      int mt, nt;
+      tile_coords(p, tile, &mt, &nt);
+      int wrow;  // the weight row behind stage row r
+      if constexpr (kEpi == Epi::kSituGlu) wrow = (rank == 1 ? p.half : 0) + nt * 128 + r;  // hidden rows, gate rows
+      else wrow = nt * kBN + static_cast<int>(rank) * 128 + r;
+      const bool row_ok = kEpi == Epi::kSituGlu ? nt * 128 + r < p.half : wrow < p.n;
+      const std::uint8_t* srow = p.w4_srel + static_cast<std::int64_t>(row_ok ? wrow : 0) * groups;
+      bool dead = false;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = static_cast<int>(it % kStages);
+        const std::uint32_t ph = (it / kStages) & 1u;
+        // The scale bytes of this K block (one per 16 columns at most), fetched before the wait.
+        std::uint32_t sb[8];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          const int col = kb * kBK + 16 * n;
+          sb[n] = (row_ok && col < p.k) ? static_cast<std::uint32_t>(__ldg(srow + col / p.w4_group)) : 0u;
+        }
+        if (!wait_bar(smem_u32(&s_pfull[s]), ph, abort_word)) {
+          dead = true;
+          break;
+        }
+        const std::uint8_t* pk = smem_raw + (p_addr(s) - smem_u32(smem_raw)) + r * 64;
+        std::uint8_t* brow = smem_raw + (b_addr(s) - smem_u32(smem_raw)) + r * 128;
+        const int psw = (r >> 1) & 3, bsw = r & 7;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // 16 packed bytes = 32 columns = two 16-byte chunks of the B row
+          const uint4 w = *reinterpret_cast<const uint4*>(pk + ((c ^ psw) * 16));
+          const uint4 t0 = s_lut[sb[2 * c]], t1 = s_lut[sb[2 * c + 1]];
+          // NaN (0x7F, 0xFF) or negative (sign bit over a non-zero magnitude): the table row is zeros; report it.
+          bad |= (sb[2 * c] & 0x7Fu) == 0x7Fu || sb[2 * c] > 0x80u || (sb[2 * c + 1] & 0x7Fu) == 0x7Fu || sb[2 * c + 1] > 0x80u;
+          uint4 o0, o1;
+          expand8(w.x, t0, o0.x, o0.y);
+          expand8(w.y, t0, o0.z, o0.w);
+          expand8(w.z, t1, o1.x, o1.y);
+          expand8(w.w, t1, o1.z, o1.w);
+          *reinterpret_cast<uint4*>(brow + (((2 * c) ^ bsw) * 16)) = o0;
+          *reinterpret_cast<uint4*>(brow + (((2 * c + 1) ^ bsw) * 16)) = o1;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (kCtas == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&s_full[s]), 0));
+          else mbar_arrive(smem_u32(&s_full[s]));
+        }
+      }
+      if (dead) break;
+    }
+    if (bad) atomicOr(p.w4_invalid, 1u);
   } else {
     // Epilogue: 8 warps. Warp w may touch TMEM lanes [32 (w % 4), 32 (w % 4) + 32); warps 2..5 take the first half of the
     // tile's columns, warps 6..9 the second half (SiTU-GLU: output columns, each needing its hidden and gate accumulator).
@@ -602,19 +735,25 @@ int check_output(const char* op, const char* name, const void* p, std::int64_t l
   return B2_OK;
 }
 
-template <int kBN, Epi kEpi, int kCtas>
+// kW4: a->w points at the packed 4-bit codes [n, k / 2] (p.w4_* describe the rest of the weight).
+template <int kBN, Epi kEpi, int kCtas, bool kW4 = false>
 int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaStream_t stream) {
-  using S = Shape<kBN, kCtas>;
+  using S = Shape<kBN, kCtas, kW4>;
   CUtensorMap map_a, map_b;
   if (!make_tensor_map_2d(&map_a, a->x_q, static_cast<std::uint64_t>(a->k), static_cast<std::uint64_t>(a->m),
                           static_cast<std::uint64_t>(a->ldx), kBK, 128, op)) {
     return B2_ERR_CUDA;
   }
-  if (!make_tensor_map_2d(&map_b, a->w, static_cast<std::uint64_t>(a->k), static_cast<std::uint64_t>(a->n),
-                          static_cast<std::uint64_t>(a->k), kBK, 128, op)) {
+  if constexpr (kW4) {
+    if (!make_tensor_map_2d(&map_b, a->w, static_cast<std::uint64_t>(a->k / 2), static_cast<std::uint64_t>(a->n),
+                            static_cast<std::uint64_t>(a->k / 2), kBK / 2, 128, op, 64)) {
+      return B2_ERR_CUDA;
+    }
+  } else if (!make_tensor_map_2d(&map_b, a->w, static_cast<std::uint64_t>(a->k), static_cast<std::uint64_t>(a->n),
+                                 static_cast<std::uint64_t>(a->k), kBK, 128, op)) {
     return B2_ERR_CUDA;
   }
-  auto kernel = int8_gemm_kernel<kBN, kEpi, kCtas>;
+  auto kernel = int8_gemm_kernel<kBN, kEpi, kCtas, kW4>;
   // Opt in to the large dynamic shared-memory size once per device and instantiation.
   // (Setting the attribute twice from two threads is harmless; the flag only saves the call.)
   static std::atomic<bool> configured[64] = {};
@@ -645,7 +784,7 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
   if constexpr (kCtas == 2) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * std::min(total, sm_count() / 2)));
-    cfg.blockDim = dim3(threads_of(kEpi, kBN));
+    cfg.blockDim = dim3(threads_of(kEpi, kBN, kW4));
     cfg.dynamicSmemBytes = S::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr{};
@@ -656,7 +795,7 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
     return check_launch(op);
   } else {
     const int grid = std::min(total, sm_count());
-    kernel<<<grid, threads_of(kEpi, kBN), S::kSmemBytes, stream>>>(map_a, map_b, p);
+    kernel<<<grid, threads_of(kEpi, kBN, kW4), S::kSmemBytes, stream>>>(map_a, map_b, p);
     return check_launch(op);
   }
 }
@@ -683,6 +822,26 @@ int dispatch(const char* op, const b2_int8_operands* a, const GemmParams& p, cud
   }
 }
 
+// W4A8 with the decode inside the GEMM: CTA pairs (256 x 256 tiles) when there are enough of them, else 128 x 128 tiles
+// (plain and gated-residual epilogues only). Returns B2_ERR_NOT_SUPPORTED when no such kernel serves the shape.
+template <Epi kEpi>
+int dispatch_w4(const char* op, const b2_int8_operands* a, const GemmParams& p, cudaStream_t stream) {
+  const std::int64_t n256 = kEpi == Epi::kSituGlu ? (p.half + 127) / 128 : (a->n + 255) / 256;
+  const int t = pick_tile(B2_TILE_AUTO, a->m, n256);
+  if (t == B2_TILE_2CTA_256x256) return launch_kernel<256, kEpi, 2, true>(op, a, p, stream);
+  if constexpr (kEpi == Epi::kSituGlu) return B2_ERR_NOT_SUPPORTED;
+  else return launch_kernel<128, kEpi, 1, true>(op, a, p, stream);
+}
+
+// B2_W4A8_FUSED=0 in the environment sends every W4A8 GEMM through the decode-to-scratch route (for A/B timing).
+bool w4a8_fused_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("B2_W4A8_FUSED");
+    return v == nullptr || v[0] != '0';
+  }();
+  return on;
+}
+
 GemmParams base_params(const b2_int8_operands* a) {
   GemmParams p{};
   p.m = static_cast<int>(a->m), p.n = static_cast<int>(a->n), p.k = static_cast<int>(a->k);
@@ -696,6 +855,20 @@ GemmParams base_params(const b2_int8_operands* a) {
 int gemm_status_word(int* host_value) {
   const cudaError_t e = cudaMemcpyFromSymbol(host_value, g_gemm_status, sizeof(int));
   return e == cudaSuccess ? B2_OK : fail_cuda("gemm_status", e);
+}
+int gemm_status_clear() {
+  const int zero = 0;
+  const cudaError_t e = cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+  return e == cudaSuccess ? B2_OK : fail_cuda("gemm_status", e);
+}
+int gemm_debug_set(unsigned long long wait_limit_ns, int skip_stage) {
+  if (wait_limit_ns != 0) {
+    if (const cudaError_t e = cudaMemcpyToSymbol(g_gemm_wait_limit_ns, &wait_limit_ns, sizeof(wait_limit_ns)); e != cudaSuccess) {
+      return fail_cuda("debug_bounded_wait", e);
+    }
+  }
+  const cudaError_t e = cudaMemcpyToSymbol(g_gemm_test_skip_stage, &skip_stage, sizeof(int));
+  return e == cudaSuccess ? B2_OK : fail_cuda("debug_bounded_wait", e);
 }
 
 }  // namespace b2
@@ -801,10 +974,12 @@ int b2_int8_gemm_acc(const b2_int8_operands* op_, int32_t* acc, int64_t ldacc, v
 int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_w4_weight* w, int64_t m, int64_t n,
                  int64_t k, int epilogue, const void* aux, void* out, int64_t ldo, int8_t* scratch, void* stream) {
   constexpr const char* op = "w4a8_gemm";
-  if (w == nullptr || scratch == nullptr) return fail_invalid(op, "null weight or scratch");
+  if (w == nullptr) return fail_invalid(op, "null weight");
   if (epilogue < 0 || epilogue > 2) return fail_invalid(op, "epilogue must be 0 (plain), 1 (gated residual) or 2 (SiTU-GLU)");
-  // Every argument of the GEMM is checked (the scratch standing in for the decoded weight) before the decode is launched.
-  const b2_int8_operands a{x_q, ldx, x_scale, scratch, w->s_channel, m, n, k};
+  // Every argument of the GEMM is checked (the scratch, or without one the packed codes, standing in for the decoded
+  // weight) before anything is launched.
+  const b2_int8_operands a{x_q, ldx, x_scale, scratch != nullptr ? scratch : static_cast<const std::int8_t*>(w->packed),
+                           w->s_channel, m, n, k};
   if (const int rc = epilogue == 0   ? check_plain(op, &a, aux, out, ldo)
                      : epilogue == 1 ? check_gated(op, &a, nullptr, aux, out, ldo)
                                      : check_situ(op, &a, out, ldo)) {
@@ -815,6 +990,37 @@ int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_
     return fail_invalid(op, "weight needs packed codes (8-byte aligned), group scales, group % 16 == 0, k % group == 0 and scale_kind 0 or 1");
   }
   if (m == 0) return B2_OK;
+  // Decode inside the GEMM (no scratch traffic) for the reference's weight format: e4m3 group scales, a group size that
+  // fits the 128-column K blocks, 16-byte aligned packed rows.
+  const bool fusable = w->scale_kind == 0 && (128 % w->group == 0 || w->group % 128 == 0) && k % 32 == 0 &&
+                       aligned_to(w->packed, 16) && !(epilogue == 2 && pick_tile(B2_TILE_AUTO, m, (n / 2 + 127) / 128) != B2_TILE_2CTA_256x256);
+  const bool fused = fusable && w4a8_fused_enabled();
+  if (!fused && scratch == nullptr) {
+    return fail_invalid(op, "this weight (fp16 group scales, a group size that does not fit 128-column blocks, or a shape too "
+                            "small for the fused tiles) is decoded to a scratch buffer first: scratch must not be null");
+  }
+  if (fused) {
+    b2_int8_operands f = a;
+    f.w = static_cast<const std::int8_t*>(w->packed);
+    GemmParams p = base_params(&f);
+    p.w4_srel = static_cast<const std::uint8_t*>(w->s_rel), p.w4_group = w->group, p.w4_codebook = w->codebook;
+    void* word = nullptr;
+    if (const int rc = w4_invalid_word(&word)) return rc;
+    p.w4_invalid = static_cast<unsigned*>(word);
+    p.out = static_cast<__nv_bfloat16*>(out), p.ldo = ldo;
+    if (epilogue == 0) {
+      p.bias = static_cast<const __nv_bfloat16*>(aux);
+      return dispatch_w4<Epi::kPlain>(op, &f, p, as_stream(stream));
+    }
+    if (epilogue == 1) {
+      p.gate = static_cast<const __nv_bfloat16*>(aux);
+      return dispatch_w4<Epi::kGatedResidual>(op, &f, p, as_stream(stream));
+    }
+    SituTables t;
+    if (const int rc = situ_tables(as_stream(stream), &t)) return rc;
+    p.half = static_cast<int>(n / 2), p.t_gate = t.gate, p.t_hidden = t.hidden;
+    return dispatch_w4<Epi::kSituGlu>(op, &f, p, as_stream(stream));
+  }
   if (const int rc = b2_decode_grouped_int8(w->packed, w->s_rel, w->scale_kind, w->codebook, n, k, w->group, scratch, nullptr, stream)) {
     return rc;
   }

@@ -505,6 +505,13 @@ __global__ void decode_grouped_kernel(const std::uint8_t* packed, const void* s_
 }  // namespace
 }  // namespace b2
 
+namespace b2 {
+int w4_invalid_word(void** out) {
+  const cudaError_t e = cudaGetSymbolAddress(out, g_w4_invalid);
+  return e == cudaSuccess ? B2_OK : fail_cuda("w4_invalid_word", e);
+}
+}  // namespace b2
+
 using namespace b2;
 
 extern "C" {

@@ -165,8 +165,13 @@ def make_w4(packed, s_rel, group, s_channel, codebook=None):
 
 
 def w4a8_gemm(x_q, x_scale, w4, n, epilogue=0, aux=None, out=None, scratch=None):
+    """scratch: int8 [n, k] for the weights that are decoded ahead of the GEMM (allocated when None); False passes no
+    scratch at all (only weights the fused kernel takes: e4m3 scales, tile-sized shapes)."""
     m, k = x_q.shape
-    scratch = torch.empty((n, k), dtype=torch.int8, device=x_q.device) if scratch is None else scratch
+    if scratch is False:
+        scratch = None
+    elif scratch is None:
+        scratch = torch.empty((n, k), dtype=torch.int8, device=x_q.device)
     if out is None:
         out = torch.empty((m, n // 2 if epilogue == 2 else n), dtype=torch.bfloat16, device=x_q.device)
     check(_lib.lib().b2_w4a8_gemm(_ptr(x_q), C.c_int64(_ld(x_q)), _ptr(x_scale), C.byref(w4), C.c_int64(m), C.c_int64(n),
@@ -276,6 +281,14 @@ def kernel_status():
     g, a = C.c_int(0), C.c_int(0)
     check(_lib.lib().b2_kernel_status(C.byref(g), C.byref(a)))
     return g.value, a.value
+
+
+def kernel_status_clear():
+    check(_lib.lib().b2_kernel_status_clear())
+
+
+def debug_bounded_wait(wait_limit_ns: int, skip_gemm_stage: bool):
+    check(_lib.lib().b2_debug_bounded_wait(C.c_uint64(wait_limit_ns), C.c_int(1 if skip_gemm_stage else 0)))
 
 
 # ------------------------------------------------------------------------------------------------ block / step

@@ -102,8 +102,9 @@ def grouped_w4_weight(n: int, k: int, seed: int, group: int = 64, device="cuda",
     return pack_int4(level + 8), s_store.contiguous(), s_channel
 
 
-def block_weights(D: int, F: int, seed: int, device="cuda", tier: int = 0):
-    """Tensors of one block: norms plus the four linears in the tier's storage (see ops.BlockWeights)."""
+def block_weights(D: int, F: int, seed: int, device="cuda", tier: int = 0, fp16_scales: bool = False):
+    """Tensors of one block: norms plus the four linears in the tier's storage (see ops.BlockWeights). The grouped 4-bit
+    tier stores its group scales as e4m3 bytes (the reference's file format) unless fp16_scales is set."""
     from . import ops
     w = {
         "norm1": vector(D, seed + 1, 0.1, 1.0, device), "norm2": vector(D, seed + 2, 0.1, 1.0, device),
@@ -116,7 +117,7 @@ def block_weights(D: int, F: int, seed: int, device="cuda", tier: int = 0):
         elif tier == ops.TIER_W4A4_VIA_INT8:
             w[name] = convrot_int4_weight(n, k, seed + 10 + i, device)
         else:
-            w[name] = grouped_w4_weight(n, k, seed + 10 + i, 64, device)
+            w[name] = grouped_w4_weight(n, k, seed + 10 + i, 64, device, fp16_scales=fp16_scales)
     return w
 
 

@@ -133,7 +133,8 @@ def test_w4a8_gemm_checks_every_argument_before_the_decode():
     assert call(epi=1, aux=A8)[0] == -1          # misaligned gate
     assert call(epi=2, n=268)[0] == -1           # F % 4
     assert call(epi=3)[0] == -1
-    assert call(scratch=None)[0] == -1
+    rc, msg = call(scratch=None, w=_w4(kind=1))   # fp16 group scales are decoded to a scratch first: it must be there
+    assert rc == -1 and "scratch" in msg
     assert call(n=1 << 33)[0] == -1 and call(k=1 << 31, ldx=1 << 31)[0] == -1
     assert call(w=_w4(group=24))[0] == -1        # group % 16
     assert call(w=_w4(group=96))[0] == -1        # k % group

@@ -278,6 +278,56 @@ def test_w4a8_gemm_equals_decode_then_gemm(ops):
     assert (u16(got) == orc.int8_gemm_situ_glu(xq.cpu().numpy(), xs.cpu().numpy(), w8, s_ch.cpu().numpy())).mean() >= 0.999
 
 
+@pytest.mark.parametrize("m,n,k,group", [(150, 520, 1024, 64), (4096, 2304, 1024, 64), (700, 384, 2048, 128),
+                                         (4100, 1536, 512, 32), (260, 256, 3072, 256)])
+def test_w4a8_gemm_decoding_inside_the_kernel(ops, m, n, k, group):
+    """The W4A8 GEMM whose converter warps expand the packed codes into the INT8 operand stage (e4m3 group scales, no
+    scratch): bit-identical to quant::decode_grouped_int8 followed by the INT8 GEMM (src/kernels/quant/w4a8_decode.h:1-39,
+    quant.h:92-111) for the three epilogues, on CTA-pair tiles and on 128 x 128 tiles, with ragged m and n."""
+    from owoinfer_b200 import synth
+    packed, s_rel, s_ch = synth.grouped_w4_weight(n, k, 70 + n, group, fp16_scales=False)
+    assert s_rel.dtype == torch.uint8
+    torch.manual_seed(m)
+    xq = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda")
+    xs = torch.rand(m, device="cuda") * 1e-2
+    w4 = ops.make_w4(packed, s_rel, group, s_ch)
+    w8 = ops.decode_grouped_int8(packed, s_rel, group)
+    assert np.array_equal(w8.cpu().numpy(), orc.decode_grouped_int8(packed.cpu().numpy(), s_rel.cpu().numpy(), group))
+    bias = synth.vector(n, 6, 0.05)
+    got = ops.w4a8_gemm(xq, xs, w4, n, aux=bias, scratch=False)
+    assert torch.equal(got.view(torch.int16), ops.int8_gemm(xq, xs, w8, s_ch, bias=bias).view(torch.int16))
+    gate = synth.vector(n, 7, 0.3)
+    res = synth.activations(m, n, 51)
+    a, b = res.clone(), res.clone()
+    ops.w4a8_gemm(xq, xs, w4, n, epilogue=1, aux=gate, out=a, scratch=False)
+    ops.int8_gemm_gated_residual(xq, xs, w8, s_ch, gate, b)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    glu = ops.w4a8_gemm(xq, xs, w4, n, epilogue=2)   # small shapes fall back to the scratch route for this epilogue
+    assert torch.equal(glu.view(torch.int16), ops.int8_gemm_situ_glu(xq, xs, w8, s_ch).view(torch.int16))
+    assert ops.w4_invalid_scales() == 0
+
+
+def test_w4a8_fused_codebook_and_untrusted_scales(ops):
+    """A 16-entry codebook instead of code - 8, and NaN / negative group scales: those groups contribute zeros and the
+    library's invalid word is raised (src/kernels/quant/w4a8_decode.cu:57-62), exactly as the stand-alone decode does."""
+    from owoinfer_b200 import synth
+    m, n, k, group = 300, 512, 1024, 64
+    packed, s_rel, s_ch = synth.grouped_w4_weight(n, k, 99, group, fp16_scales=False)
+    cb = torch.tensor([-9.5, -7, -5.5, -4, -3, -2.25, -1.5, -0.5, 0.5, 1.5, 2.25, 3, 4, 5.5, 7, 9.5], dtype=torch.float32, device="cuda")
+    s_rel = s_rel.clone()
+    s_rel[3, 1], s_rel[77, 15], s_rel[500, 0] = 0x7F, 0xFF, 0xB0
+    xq = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda")
+    xs = torch.rand(m, device="cuda") * 1e-2
+    w4 = ops.make_w4(packed, s_rel, group, s_ch, codebook=cb)
+    ops.w4_invalid_scales(clear=True)
+    got = ops.w4a8_gemm(xq, xs, w4, n, scratch=False)
+    assert ops.w4_invalid_scales(clear=True) == 1
+    w8, flag = orc.decode_grouped_int8_device_rule(packed.cpu().numpy(), s_rel.cpu().numpy(), group, cb.cpu().numpy())
+    assert flag == 1
+    want = ops.int8_gemm(xq, xs, dev(w8), s_ch)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
 def test_grouped_decode_untrusted_scales(ops):
     """src/kernels/quant/w4a8_decode.cu:57-62: a NaN or negative group scale zeroes its group and raises the invalid
     word, both through the caller's word and through the library's own (which the W4A8 GEMM uses)."""
@@ -340,8 +390,31 @@ def test_chunked_gemm_and_chunked_rotate_equal_the_plain_forms(ops):
         assert torch.equal(q, q2) and torch.equal(s.view(torch.int32), s2.view(torch.int32))
 
 
+def test_bounded_wait_runs_out_and_the_kernel_returns_a_status(ops):
+    """Every device-side wait has a time limit. With the limit at 2 ms and the TMA warp told to leave one stage unfilled,
+    the MMA warp's wait for that stage runs out: the CTA raises the status word, drains, frees its tensor memory and
+    returns. Nothing faults or hangs, the context stays usable, and the same GEMM is correct right after."""
+    rng = np.random.default_rng(21)
+    m, n, k = 128, 128, 512
+    a = dev(rng.integers(-128, 128, (m, k), dtype=np.int8))
+    b = dev(rng.integers(-128, 128, (n, k), dtype=np.int8))
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == (0, 0)
+    ops.debug_bounded_wait(2_000_000, True)
+    try:
+        ops.int8_gemm_acc(a, b, tile=ops.TILE_128x128)
+        torch.cuda.synchronize()
+        assert ops.kernel_status() == (1, 0)
+    finally:
+        ops.debug_bounded_wait(200_000_000, False)
+        ops.kernel_status_clear()
+    acc = ops.int8_gemm_acc(a, b, tile=ops.TILE_128x128)
+    assert np.array_equal(acc.cpu().numpy(), a.cpu().numpy().astype(np.int32) @ b.cpu().numpy().astype(np.int32).T)
+    assert ops.kernel_status() == (0, 0)
+
+
 def test_gemm_linearity_at_full_size(ops):
-    # Size-independent property at the BASELINE shape (8192 x 9216 x 3072): acc(x, w) + acc(x2, w) == acc over the
+    # Size-independent property at the benchmarked QKV shape (8192 x 9216 x 3072): acc(x, w) + acc(x2, w) == acc over the
     # concatenated K of [x | x2] and [w | w], checked on the int32 accumulators through sampled rows' exact dot products.
     torch.manual_seed(0)
     m, n, k = 8192, 9216, 3072
@@ -586,7 +659,9 @@ def _oracle_block(ops, x, mod, w, rope, cu, lens, heads, tier):
             return t[0].cpu().numpy(), t[1].cpu().numpy()
         if tier == ops.TIER_W4A4_VIA_INT8:
             return orc.unpack_int4(t[0].cpu().numpy()), t[1].cpu().numpy()
-        return orc.decode_grouped_int8(t[0].cpu().numpy(), t[1].cpu().numpy().view(np.uint16), 64), t[2].cpu().numpy()
+        srel = t[1].cpu().numpy()
+        srel = srel if srel.dtype == np.uint8 else srel.view(np.uint16)   # e4m3 bytes or fp16 bits
+        return orc.decode_grouped_int8(t[0].cpu().numpy(), srel, 64), t[2].cpu().numpy()
     ow = {k: u16(w[k]) for k in ("norm1", "norm2", "q_norm", "k_norm")}
     ow.update(qkv=lin(w["qkv"]), o=lin(w["o"]), up=lin(w["up_gate"]), down=lin(w["down"]))
     return orc.block_quant(u16(x), u16(mod), u16(rope), ow, cu.cpu().numpy(), max(lens), heads=heads,
@@ -608,7 +683,19 @@ def test_block_small_against_oracle(ops, tier, fused):
     got = _run_block(ops, x, mod, w, rope, cu, lens, D, F, heads, tier, fused)
     want = _oracle_block(ops, x, mod, w, rope, cu, lens, heads, tier)
     cos, max_rel = _rel_metrics(u16(got), want)
-    # BASELINE: bf16 block outputs within max-relative-error 1e-2 and cosine >= 0.9995.
+    # The bar of the block: bf16 outputs within max-relative-error 1e-2 and cosine >= 0.9995 of the reference arithmetic.
+    assert cos >= 0.9995 and max_rel <= 1e-2, (cos, max_rel)
+
+
+def test_block_w4a8_with_fp16_group_scales(ops):
+    """The same tier with fp16 group scales, which the fused kernel does not take: the decode-to-scratch route."""
+    from owoinfer_b200 import synth
+    lens, D, F, heads = [200, 141], 512, 1024, 4
+    x, mod, w, rope, cu = _block_case(ops, lens, D, F, heads, 2, 2)
+    w16 = synth.block_weights(D, F, 3002, tier=2, fp16_scales=True)
+    got = _run_block(ops, x, mod, w16, rope, cu, lens, D, F, heads, 2, -1)
+    want = _oracle_block(ops, x, mod, w16, rope, cu, lens, heads, 2)
+    cos, max_rel = _rel_metrics(u16(got), want)
     assert cos >= 0.9995 and max_rel <= 1e-2, (cos, max_rel)
 
 
