@@ -53,7 +53,7 @@ int b2_rotate_quantize(const void* x, int64_t ldx, int8_t* q, int64_t ldq, float
 
 /* b2_rotate_quantize on a column-chunked input: columns [i * chunk_cols, (i + 1) * chunk_cols) of every row are read
  * from chunk i, a bf16 [m, chunk_cols] matrix of row stride ldx that starts chunk_stride elements after chunk i - 1
- * (chunk_cols % 256 == 0, k % chunk_cols == 0). Same bits as b2_rotate_quantize on the assembled rows. The input layout
+ * (chunk_cols % 16 == 0, k % chunk_cols == 0). Same bits as b2_rotate_quantize on the assembled rows. The input layout
  * of the sequence-parallel block's output projection; no counterpart in the reference. */
 int b2_rotate_quantize_chunked(const void* x, int64_t ldx, int chunk_cols, int64_t chunk_stride, int8_t* q, int64_t ldq,
                                float* scale, int64_t m, int k, void* stream);

@@ -48,7 +48,8 @@ struct Args {
   float factor;  // float(m) / float(m * k)
   int bw;        // torch's threads per row for this (m, k)
   // Column-chunked input (0 = off): columns [i * chunk_w, (i + 1) * chunk_w) of every row live in chunk i, a [m, chunk_w]
-  // matrix of row stride ldx that starts chunk_stride elements after chunk i - 1. chunk_w % 256 == 0.
+  // matrix of row stride ldx that starts chunk_stride elements after chunk i - 1. chunk_w % 16 == 0 (a lane's 16
+  // elements stay inside one chunk).
   int chunk_w;
   std::int64_t chunk_stride;
 };
@@ -172,10 +173,10 @@ __global__ void __launch_bounds__(kSlots == 1 ? 256 : 512, kSlots == 1 ? (kNorm 
     for (int s = 0; s < kSlots; ++s) {
       const int g = half_id + s * halves;
       if (g < groups) {
-        const int col = g * kGroup;
+        const int col = g * kGroup + 16 * h;
         const __nv_bfloat16* src = a.chunk_w == 0 ? xr + col
                                                   : a.x + (col / a.chunk_w) * a.chunk_stride + row * a.ldx + col % a.chunk_w;
-        load16_bf16(src + 16 * h, v[s]);
+        load16_bf16(src, v[s]);
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[s][j] = 0.f;
@@ -528,8 +529,8 @@ int b2_rotate_quantize(const void* x, int64_t ldx, int8_t* q, int64_t ldq, float
 int b2_rotate_quantize_chunked(const void* x, int64_t ldx, int chunk_cols, int64_t chunk_stride, int8_t* q, int64_t ldq,
                                float* scale, int64_t m, int k, void* stream) {
   constexpr const char* op = "rotate_quantize_chunked";
-  if (chunk_cols <= 0 || chunk_cols % kGroup != 0 || k % chunk_cols != 0 || chunk_stride % 8 != 0 || ldx < chunk_cols) {
-    return fail_invalid(op, "needs chunk_cols % 256 == 0, k % chunk_cols == 0, ldx >= chunk_cols and chunk_stride % 8 == 0");
+  if (chunk_cols <= 0 || chunk_cols % 16 != 0 || k % chunk_cols != 0 || chunk_stride % 8 != 0 || ldx < chunk_cols) {
+    return fail_invalid(op, "needs chunk_cols % 16 == 0, k % chunk_cols == 0, ldx >= chunk_cols and chunk_stride % 8 == 0");
   }
   if (const int rc = check_common(op, x, std::max<std::int64_t>(ldx, k), q, ldq, scale, m, k, false)) return rc;
   if (ldx % 8 != 0) return fail_invalid(op, "ldx % 8 != 0");

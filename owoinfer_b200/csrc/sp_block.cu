@@ -12,8 +12,14 @@
 // (token, head), so the bits do not depend on where they run), with the full-sequence RoPE table on every rank.
 // The K mean and V maximum of the pre-pass are per (sequence, head): local after the exchange and summed in the same
 // order as on one GPU, so the block output equals the single-GPU output bit for bit.
-// Transport: NCCL point-to-point calls grouped per exchange, enqueued on the caller's stream; receive buffers are this
-// GPU's own memory (no tensor map ever covers a peer's memory). The library is bound at run time (dlopen of
+// The heads of a rank are processed in two halves so that the exchanges hide under compute: the QKV projection runs as
+// two GEMMs (weight rows ordered [half][destination rank][q | k | v][head][128]); the exchange of half 0 runs on a second
+// stream under the GEMM of half 1, the exchange of half 1 under the attention of half 0, the return exchange of half 0
+// under the attention of half 1. What a step still waits for is the tail of the first exchange and the return exchange
+// of half 1. (An odd number of heads per rank runs as one "half".)
+// Transport: NCCL point-to-point calls grouped per exchange, enqueued on the communicator's own stream and fenced with
+// events against the caller's stream; receive buffers are this GPU's own memory (no tensor map ever covers a peer's
+// memory). The library is bound at run time (dlopen of
 // libnccl.so.2, preferring a copy the process has already loaded), so the single-GPU library has no NCCL dependency.
 // The reference engine is single-GPU (include/mossinfer/mossinfer.h:314); block sequencing as in
 // src/models/moss_dit/dit_block_quant.cpp:196-608.
@@ -33,6 +39,9 @@ struct b2_sp_comm {
   ncclComm_t comm = nullptr;
   int size = 0, rank = 0;
   bool local_exchange = false;  // measurement aid: every message becomes a device copy of the same size on this GPU
+  cudaStream_t side = nullptr;  // the exchanges' stream
+  cudaEvent_t ready[2] = {nullptr, nullptr};     // main -> side: the data of half h is ready to be sent
+  cudaEvent_t arrived[2] = {nullptr, nullptr};   // side -> main: the exchange of half h has landed
 };
 
 namespace b2 {
@@ -93,7 +102,9 @@ struct SpLayout {
   std::size_t xq, scale, send1, full, attn_full, recv2, ffn, attn_ws, total;
   std::size_t attn_ws_bytes;
   std::int64_t tokens_local, tokens_full;
-  int hp;  // heads per rank
+  int hp;      // heads per rank
+  int halves;  // 2 when hp is even, else 1
+  int hh;      // heads per half
 };
 
 int check_sp_run(const char* op, const b2_sp_run* run, int size) {
@@ -104,8 +115,8 @@ int check_sp_run(const char* op, const b2_sp_run* run, int size) {
     return fail_invalid(op, "needs D == heads * 128, D and F multiples of 256, tokens >= 0");
   }
   if (r.tier != B2_TIER_INT8) return fail_status(B2_ERR_NOT_SUPPORTED, op, "the sequence-parallel block runs the INT8 tier only");
-  if (size < 1 || r.heads % size != 0 || (r.heads / size) % 2 != 0) {
-    return fail_status(B2_ERR_NOT_SUPPORTED, op, "heads must split evenly over the ranks into an even number per rank (256-column rotation groups)");
+  if (size < 1 || r.heads % size != 0) {
+    return fail_status(B2_ERR_NOT_SUPPORTED, op, "heads must split evenly over the ranks of the group");
   }
   if (r.batch < 1 || r.max_seqlen < 1 || r.cu_seqlens == nullptr || run->seq_lens_host == nullptr) {
     return fail_invalid(op, "needs cu_seqlens (device, full sequences), seq_lens_host, batch >= 1, max_seqlen >= 1");
@@ -125,7 +136,8 @@ SpLayout carve(const b2_sp_run* run, int size) {
   const b2_block_run& r = run->local;
   const std::size_t L = static_cast<std::size_t>(r.tokens), D = static_cast<std::size_t>(r.D), F = static_cast<std::size_t>(r.F);
   l.tokens_local = r.tokens, l.tokens_full = r.tokens * size, l.hp = r.heads / size;
-  const std::size_t W = 3 * static_cast<std::size_t>(l.hp) * 128, full = L * size;
+  l.halves = l.hp % 2 == 0 ? 2 : 1, l.hh = l.hp / l.halves;
+  const std::size_t W = 3 * static_cast<std::size_t>(l.hp) * 128, full = L * size;  // all halves together
   std::size_t at = 0;
   const auto take = [&](std::size_t bytes) {
     const std::size_t off = at;
@@ -139,7 +151,7 @@ SpLayout carve(const b2_sp_run* run, int size) {
   l.attn_full = take(full * (W / 3) * 2);
   l.recv2 = take(static_cast<std::size_t>(size) * L * (W / 3) * 2);
   l.ffn = take(L * F * 2);
-  l.attn_ws_bytes = b2_attention_q8_workspace_bytes(&r.attention, l.tokens_full, l.tokens_full, r.batch, r.max_seqlen, l.hp, l.hp);
+  l.attn_ws_bytes = b2_attention_q8_workspace_bytes(&r.attention, l.tokens_full, l.tokens_full, r.batch, r.max_seqlen, l.hh, l.hh);
   l.attn_ws = take(l.attn_ws_bytes);
   l.total = at;
   return l;
@@ -223,13 +235,30 @@ int b2_sp_comm_create(const void* id, size_t id_bytes, int size, int rank, b2_sp
       return fail_nccl(op, r);
     }
   }
+  // The exchanges' stream and the four events that fence it against the caller's stream (created here, once: the block
+  // itself allocates nothing).
+  cudaError_t e = cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking);
+  for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+    e = cudaEventCreateWithFlags(&c->ready[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->arrived[i], cudaEventDisableTiming);
+  }
+  if (e != cudaSuccess) {
+    b2_sp_comm_destroy(c);
+    return fail_cuda(op, e);
+  }
   *out = c;
   return B2_OK;
 }
 
 int b2_sp_comm_destroy(b2_sp_comm* comm) {
   if (comm == nullptr) return B2_OK;
+  if (comm->side != nullptr) cudaStreamSynchronize(comm->side);
   if (comm->comm != nullptr) nccl().comm_destroy(comm->comm);
+  for (int i = 0; i < 2; ++i) {
+    if (comm->ready[i] != nullptr) cudaEventDestroy(comm->ready[i]);
+    if (comm->arrived[i] != nullptr) cudaEventDestroy(comm->arrived[i]);
+  }
+  if (comm->side != nullptr) cudaStreamDestroy(comm->side);
   delete comm;
   return B2_OK;
 }
@@ -268,16 +297,17 @@ int b2_run_block_quant_sp(const b2_block_weights* w, const b2_block_buffers* a, 
   const b2_block_run& r = run->local;
   const std::int64_t L = r.tokens, D = r.D, F = r.F;
   if (L == 0) return B2_OK;
-  const int P = comm->size, hp = l.hp, batch = r.batch;
-  const std::int64_t W = 3LL * hp * 128, Wo = static_cast<std::int64_t>(hp) * 128;
-  cudaStream_t st = as_stream(stream);
+  const int P = comm->size, batch = r.batch, halves = l.halves, hh = l.hh;
+  const std::int64_t Wh = 3LL * hh * 128, Wo = static_cast<std::int64_t>(hh) * 128;  // per half: q | k | v, and the output
+  const std::int64_t T = l.tokens_full;
+  cudaStream_t st = as_stream(stream), side = comm->side;
   auto* base = static_cast<std::uint8_t*>(a->workspace);
   auto* xq = reinterpret_cast<std::int8_t*>(base + l.xq);
   auto* scale = reinterpret_cast<float*>(base + l.scale);
-  auto* send1 = reinterpret_cast<__nv_bfloat16*>(base + l.send1);
-  auto* full = reinterpret_cast<__nv_bfloat16*>(base + l.full);
-  auto* attn_full = reinterpret_cast<__nv_bfloat16*>(base + l.attn_full);
-  auto* recv2 = reinterpret_cast<__nv_bfloat16*>(base + l.recv2);
+  auto* send1 = reinterpret_cast<__nv_bfloat16*>(base + l.send1);      // [half][destination][L][Wh]
+  auto* full = reinterpret_cast<__nv_bfloat16*>(base + l.full);        // [half][T][Wh]
+  auto* attn_full = reinterpret_cast<__nv_bfloat16*>(base + l.attn_full);  // [half][T][Wo]
+  auto* recv2 = reinterpret_cast<__nv_bfloat16*>(base + l.recv2);      // [source][half][L][Wo]
   auto* ffn = reinterpret_cast<__nv_bfloat16*>(base + l.ffn);
   const auto* mod = static_cast<const __nv_bfloat16*>(a->mod);
   // Row offsets of every sequence in the local shard and in the full buffers.
@@ -287,50 +317,68 @@ int b2_run_block_quant_sp(const b2_block_weights* w, const b2_block_buffers* a, 
     off_full[i + 1] = off_full[i] + run->seq_lens_host[i];
   }
   const auto chunk_len = [&](int i) { return off_local[i + 1] - off_local[i]; };
+  const auto cuda_ok = [&](cudaError_t e) { return e == cudaSuccess ? B2_OK : fail_cuda(op, e); };
 
-  // QKV projection of the local rows, each destination rank's columns into its own [L, W] matrix.
+  // QKV projection of the local rows, one GEMM per half of the heads; each destination rank's columns of a half go into
+  // that destination's own [L, Wh] matrix. As soon as a half is computed its exchange starts on the side stream.
   if (const int rc = b2_rms_norm_modulate_rotate_quantize(a->x, D, w->norm1, mod + 1 * D, mod + 0 * D, xq, D, scale, L,
                                                           static_cast<int>(D), st, nullptr, 0)) {
     return rc;
   }
-  b2_int8_operands g{xq, D, scale, w->qkv.w, w->qkv.scale, L, 3 * D, D};
-  if (const int rc = b2_int8_gemm_chunked(&g, nullptr, send1, W, static_cast<int>(W), L * W, st, B2_TILE_AUTO)) return rc;
-
-  // Exchange #1: tokens -> heads.
-  if (const int rc = exchange(
-          op, comm, batch, [&](int i, int s) { return send1 + (s * L + off_local[i]) * W; },
-          [&](int i, int s) { return full + (off_full[i] + s * chunk_len(i)) * W; },
-          [&](int i) { return static_cast<std::size_t>(chunk_len(i) * W); }, st)) {
-    return rc;
+  const std::int64_t n_half = 3 * D / halves;
+  for (int h = 0; h < halves; ++h) {
+    const b2_int8_operands g{xq, D, scale, w->qkv.w + h * n_half * D, w->qkv.scale + h * n_half, L, n_half, D};
+    if (const int rc = b2_int8_gemm_chunked(&g, nullptr, send1 + h * P * L * Wh, Wh, static_cast<int>(Wh), L * Wh, st, B2_TILE_AUTO)) return rc;
+    if (const int rc = cuda_ok(cudaEventRecord(comm->ready[h], st))) return rc;
+    // Exchange #1 of this half: tokens -> heads.
+    if (const int rc = cuda_ok(cudaStreamWaitEvent(side, comm->ready[h], 0))) return rc;
+    if (const int rc = exchange(
+            op, comm, batch, [&](int i, int s) { return send1 + ((h * P + s) * L + off_local[i]) * Wh; },
+            [&](int i, int s) { return full + (h * T + off_full[i] + s * chunk_len(i)) * Wh; },
+            [&](int i) { return static_cast<std::size_t>(chunk_len(i) * Wh); }, side)) {
+      return rc;
+    }
+    if (const int rc = cuda_ok(cudaEventRecord(comm->arrived[h], side))) return rc;
   }
 
-  // Attention over the full sequences, this rank's heads; QK-norm + RoPE in its pre-pass from 3072 tokens on.
-  const std::int64_t T = l.tokens_full;
+  // Attention over the full sequences, this rank's heads, half by half; QK-norm + RoPE in its pre-pass from 3072 tokens
+  // on. The return exchange of a half starts as soon as its attention is done.
   const bool fused = r.fused_norm_rope < 0 ? T >= kFusedNormRopeMinTokens : r.fused_norm_rope != 0;
-  if (!fused) {
-    if (const int rc = b2_qk_norm_rope_moss(full, W, T, hp, w->q_norm, w->k_norm, a->rope, 128, st)) return rc;
-  }
-  const b2_view3 vq{full, T, hp, W, 128}, vk{full + Wo, T, hp, W, 128}, vv{full + 2 * Wo, T, hp, W, 128};
-  const b2_view3 vo{attn_full, T, hp, Wo, 128};
   const b2_qk_norm_rope nr{w->q_norm, w->k_norm, a->rope, 128};
   b2_attention_options ao = r.attention;
   if (ao.variant == 0) ao.variant = B2_ATTENTION_Q8_FP8_F32ACC;
   const float sm_scale = static_cast<float>(1.0 / std::sqrt(128.0));
-  if (const int rc = b2_attention_q8(&ao, &vq, &vk, &vv, &vo, r.cu_seqlens, r.cu_seqlens, batch, r.max_seqlen, sm_scale,
-                                     base + l.attn_ws, l.attn_ws_bytes, st, fused ? &nr : nullptr)) {
-    return rc;
+  for (int h = 0; h < halves; ++h) {
+    if (const int rc = cuda_ok(cudaStreamWaitEvent(st, comm->arrived[h], 0))) return rc;
+    __nv_bfloat16* fh = full + h * T * Wh;
+    __nv_bfloat16* oh = attn_full + h * T * Wo;
+    if (!fused) {
+      if (const int rc = b2_qk_norm_rope_moss(fh, Wh, T, hh, w->q_norm, w->k_norm, a->rope, 128, st)) return rc;
+    }
+    const b2_view3 vq{fh, T, hh, Wh, 128}, vk{fh + Wo, T, hh, Wh, 128}, vv{fh + 2 * Wo, T, hh, Wh, 128};
+    const b2_view3 vo{oh, T, hh, Wo, 128};
+    if (const int rc = b2_attention_q8(&ao, &vq, &vk, &vv, &vo, r.cu_seqlens, r.cu_seqlens, batch, r.max_seqlen, sm_scale,
+                                       base + l.attn_ws, l.attn_ws_bytes, st, fused ? &nr : nullptr)) {
+      return rc;
+    }
+    if (const int rc = cuda_ok(cudaEventRecord(comm->ready[h], st))) return rc;
+    // Exchange #2 of this half: heads -> tokens, into one [L, Wo] matrix per (source rank, half).
+    if (const int rc = cuda_ok(cudaStreamWaitEvent(side, comm->ready[h], 0))) return rc;
+    if (const int rc = exchange(
+            op, comm, batch, [&](int i, int s) { return oh + (off_full[i] + s * chunk_len(i)) * Wo; },
+            [&](int i, int s) { return recv2 + ((s * halves + h) * L + off_local[i]) * Wo; },
+            [&](int i) { return static_cast<std::size_t>(chunk_len(i) * Wo); }, side)) {
+      return rc;
+    }
+    if (const int rc = cuda_ok(cudaEventRecord(comm->arrived[h], side))) return rc;
+  }
+  for (int h = 0; h < halves; ++h) {
+    if (const int rc = cuda_ok(cudaStreamWaitEvent(st, comm->arrived[h], 0))) return rc;
   }
 
-  // Exchange #2: heads -> tokens, into one [L, Wo] matrix per source rank.
-  if (const int rc = exchange(
-          op, comm, batch, [&](int i, int s) { return attn_full + (off_full[i] + s * chunk_len(i)) * Wo; },
-          [&](int i, int s) { return recv2 + (s * L + off_local[i]) * Wo; },
-          [&](int i) { return static_cast<std::size_t>(chunk_len(i) * Wo); }, st)) {
-    return rc;
-  }
-
-  // x += o(attn) * gate_a, the rotation reading the per-source matrices as column chunks.
+  // x += o(attn) * gate_a, the rotation reading the per-(source, half) matrices as column chunks in head order.
   if (const int rc = b2_rotate_quantize_chunked(recv2, Wo, static_cast<int>(Wo), L * Wo, xq, D, scale, L, static_cast<int>(D), st)) return rc;
+  b2_int8_operands g{};
   g = b2_int8_operands{xq, D, scale, w->o.w, w->o.scale, L, D, D};
   if (const int rc = b2_int8_gemm_gated_residual(&g, nullptr, mod + 2 * D, a->x, D, st, B2_TILE_AUTO)) return rc;
 

@@ -121,11 +121,13 @@ def group_layout(world: int, n_sequences: int):
 
 def sp_qkv_row_order(heads: int, size: int) -> torch.Tensor:
     """Row order of the fused QKV weight [3 * heads * 128, k] (q heads, k heads, v heads) for a sequence-parallel group of
-    `size` ranks: [destination rank r][q | k | v][head r * heads/size + j][128]. Apply to the weight rows and to the scale
-    vector at load time (index_select)."""
+    `size` ranks: [half h][destination rank r][q | k | v][head r * heads/size + h * hh + j][128], where a rank's heads/size
+    heads are processed in two halves of hh heads (one "half" when that number is odd). Apply to the weight rows and to
+    the scale vector at load time (index_select)."""
     hp = heads // size
-    idx = torch.arange(3 * heads * 128).view(3, size, hp, 128)   # [qkv, rank, head, row]
-    return idx.permute(1, 0, 2, 3).reshape(-1)
+    halves = 2 if hp % 2 == 0 else 1
+    idx = torch.arange(3 * heads * 128).view(3, size, halves, hp // halves, 128)   # [qkv, rank, half, head, row]
+    return idx.permute(2, 1, 0, 3, 4).reshape(-1)
 
 
 def permute_qkv(weight: torch.Tensor, scale: torch.Tensor, heads: int, size: int):

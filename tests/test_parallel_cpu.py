@@ -35,16 +35,22 @@ def test_group_layout_and_qkv_row_order():
     heads, size = 8, 4
     order = parallel.sp_qkv_row_order(heads, size)
     assert sorted(order.tolist()) == list(range(3 * heads * 128))
-    # Column block r of the reordered GEMM output = [q | k | v] of heads r * hp .. r * hp + hp - 1.
+    # Column block (half h, rank r) of the reordered GEMM output = [q | k | v] of heads r * hp + h * hh .. + hh - 1.
     hp = heads // size
+    hh = hp // 2
     cols = torch.arange(3 * heads * 128).view(3, heads, 128)
-    for r in range(size):
-        block = order[r * 3 * hp * 128:(r + 1) * 3 * hp * 128].view(3, hp, 128)
-        assert torch.equal(block, cols[:, r * hp:(r + 1) * hp])
+    for h in range(2):
+        for r in range(size):
+            at = (h * size + r) * 3 * hh * 128
+            block = order[at:at + 3 * hh * 128].view(3, hh, 128)
+            assert torch.equal(block, cols[:, r * hp + h * hh:r * hp + (h + 1) * hh])
+    odd = parallel.sp_qkv_row_order(6, 2)   # three heads per rank: one "half"
+    assert torch.equal(odd[:3 * 3 * 128].view(3, 3, 128), torch.arange(3 * 6 * 128).view(3, 6, 128)[:, 0:3])
     w = torch.arange(3 * heads * 128 * 2).view(3 * heads * 128, 2)
     pw, ps = parallel.permute_qkv(w, torch.arange(3 * heads * 128), heads, size)
     assert torch.equal(pw[:, 0] // 2, ps) and torch.equal(ps, order)
-    assert torch.equal(parallel.sp_qkv_row_order(heads, 1), torch.arange(3 * heads * 128))
+    one = parallel.sp_qkv_row_order(heads, 1)   # a group of one still runs its heads in two halves
+    assert torch.equal(one[:3 * 4 * 128].view(3, 4, 128), cols[:, 0:4]) and torch.equal(one[3 * 4 * 128:].view(3, 4, 128), cols[:, 4:8])
 
 
 def test_sp_run_is_validated_before_any_work():
@@ -68,24 +74,29 @@ def test_sp_run_is_validated_before_any_work():
 
     need = lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096, 2048], 4)), 4)
     assert need > 0
-    assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096, 2048], 4)), 8) == 0       # 3 heads per rank: odd
-    assert b"even number per rank" in lib.b2_last_error_message()
+    assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096, 2048], 8)), 8) > 0        # 3 heads per rank: one half
     assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096, 2050], 4)), 4) == 0       # length not divisible
     assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096], 4, tier=2)), 4) == 0     # INT8 tier only
     assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096], 4, tokens=1000)), 4) == 0
     assert lib.b2_block_quant_sp_workspace_bytes(C.byref(run([4096], 5)), 5) == 0             # heads % size
-    # A group of one needs neither an id nor NCCL.
-    comm = C.c_void_p()
-    assert lib.b2_sp_comm_create(None, C.c_size_t(0), 1, 0, C.byref(comm)) == 0 and comm.value
+    # Argument errors come before anything touches a device.
     assert lib.b2_sp_comm_create(None, C.c_size_t(0), 2, 0, C.byref(C.c_void_p())) == -1      # size 2 without an id
     assert lib.b2_sp_comm_create(None, C.c_size_t(0), 2, 2, C.byref(C.c_void_p())) == -1
     w, a = _lib.BlockWeights(), _lib.BlockBuffers()
     w.struct_size, a.struct_size = C.sizeof(_lib.BlockWeights), C.sizeof(_lib.BlockBuffers)
-    a.x = a.mod = a.rope = a.workspace = 0x10000
-    a.workspace_bytes = need - 1
-    assert lib.b2_run_block_quant_sp(C.byref(w), C.byref(a), C.byref(run([4096, 2048], 1)), comm, None) == -1
-    assert b"workspace" in lib.b2_last_error_message()
-    assert lib.b2_sp_comm_destroy(comm) == 0
+    assert lib.b2_run_block_quant_sp(C.byref(w), C.byref(a), C.byref(run([4096, 2048], 1)), None, None) == -1
+    assert b"communicator" in lib.b2_last_error_message()
+    # A group of one needs neither an id nor NCCL, only a device for its stream and events (absent here: a CUDA error,
+    # not a crash).
+    comm = C.c_void_p()
+    rc = lib.b2_sp_comm_create(None, C.c_size_t(0), 1, 0, C.byref(comm))
+    assert rc in (0, -8)
+    if rc == 0:
+        a.x = a.mod = a.rope = a.workspace = 0x10000
+        a.workspace_bytes = need - 1
+        assert lib.b2_run_block_quant_sp(C.byref(w), C.byref(a), C.byref(run([4096, 2048], 1)), comm, None) == -1
+        assert b"workspace" in lib.b2_last_error_message()
+        assert lib.b2_sp_comm_destroy(comm) == 0
 
 
 def _free_port():
