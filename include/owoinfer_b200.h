@@ -141,8 +141,11 @@ int b2_int8_gemm_acc(const b2_int8_operands* op, int32_t* acc, int64_t ldacc, vo
  * INT8 activations; bit-identical to quant::decode_grouped_int8 followed by quant::int8_gemm
  * (src/kernels/quant/w4a8_decode.h:1-39 + src/kernels/quant/quant.h:92). scratch: device int8 [n,k] for the decoded
  * weight (caller-owned; may be reused across calls). epilogue: 0 plain (aux = bias or NULL), 1 gated residual
- * (aux = gate, out = residual in place), 2 SiTU-GLU. Every argument is checked before the decode is launched; m == 0
- * launches nothing. A NaN or negative group scale decodes to zeros and is reported by b2_w4_invalid_scales. */
+ * (aux = gate, out = residual in place), 2 SiTU-GLU. Every argument is checked before anything is launched; m == 0
+ * launches nothing. A NaN or negative group scale decodes to zeros and is reported by b2_w4_invalid_scales.
+ * Two routes with identical results: the codes are expanded inside the GEMM's B-operand staging (e4m3 group scales, a
+ * power-of-two group size, k % 128 == 0; chosen automatically for few rows, see b2_debug_w4a8_route; scratch is then not
+ * touched and may be NULL), or decoded to `scratch` (int8 [n, k]) first and multiplied by the INT8 kernel. */
 typedef struct b2_w4_weight {
   const void* packed;   /* uint8 [n, k/2] */
   const void* s_rel;    /* [n, k/group] e4m3 or fp16 */
@@ -153,6 +156,13 @@ typedef struct b2_w4_weight {
 } b2_w4_weight;
 int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_w4_weight* w, int64_t m, int64_t n,
                  int64_t k, int epilogue, const void* aux, void* out, int64_t ldo, int8_t* scratch, void* stream);
+
+/* Which of b2_w4a8_gemm's two routes runs: -1 automatic (the default: decode inside the GEMM up to 256 rows of
+ * activations, where the GEMM is bound by the weight's bytes; decode to the scratch above, where it is bound by the
+ * tensor core and expanding the weight once beats expanding it per M tile), 0 always the scratch, 1 the fused kernel
+ * whenever the weight's format allows. For tests and timing; B2_W4A8_FUSED=0|1 in the environment sets the start value.
+ * No counterpart in the reference. */
+int b2_debug_w4a8_route(int route);
 
 /* b2_w4a8_gemm without a scratch argument, for hosts that cannot give this call any device memory of their own and
  * are not allowed to allocate: a plug-in running on a step path where the CUDA allocator is off limits (an allocation

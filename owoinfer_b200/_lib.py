@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libowoinfer_b200.so")
 EXPORTS = [
     "b2_last_error_message", "b2_numerics_version", "b2_rotate_quantize", "b2_rms_norm_modulate_rotate_quantize",
     "b2_convrot_quantize_int4", "b2_rms_norm_modulate_convrot_quantize_int4", "b2_unpack_int4", "b2_decode_grouped_int8",
-    "b2_int8_gemm", "b2_int8_gemm_gated_residual", "b2_int8_gemm_situ_glu", "b2_int8_gemm_acc", "b2_w4a8_gemm", "b2_w4a8_gemm_noalloc",
+    "b2_int8_gemm", "b2_int8_gemm_gated_residual", "b2_int8_gemm_situ_glu", "b2_int8_gemm_acc", "b2_w4a8_gemm", "b2_w4a8_gemm_noalloc", "b2_debug_w4a8_route",
     "b2_qk_norm_rope_moss", "b2_moss_rope_table", "b2_attention_q8_workspace_bytes", "b2_attention_q8",
     "b2_attention_q8_layout", "b2_attention_q8_debug_scores", "b2_attention_q8_preprocess", "b2_block_quant_workspace_bytes", "b2_run_block_quant", "b2_dit_step",
     "b2_kernel_status", "b2_kernel_status_clear", "b2_debug_bounded_wait", "b2_w4_invalid_scales", "b2_rotate_quantize_chunked", "b2_int8_gemm_chunked", "b2_sp_unique_id",

@@ -46,13 +46,16 @@ enum class Epi : int { kPlain = 0, kGatedResidual = 1, kSituGlu = 2, kAcc = 3 };
 #ifndef B2_EPI_WARPS_PLAIN
 #define B2_EPI_WARPS_PLAIN 8
 #endif
-__host__ __device__ constexpr int epi_warps(Epi e, int bn) {
-  return e == Epi::kSituGlu ? 16 : bn != 256 ? 8 : e == Epi::kGatedResidual ? B2_EPI_WARPS_GATED : e == Epi::kPlain ? B2_EPI_WARPS_PLAIN : 8;
+__host__ __device__ constexpr int epi_warps(Epi e, int bn, bool w4 = false) {
+  // (With the W4A8 converter warps in the CTA, SiTU-GLU keeps 8 epilogue warps: the register file is shared.)
+  return e == Epi::kSituGlu ? (w4 ? 8 : 16) : bn != 256 ? 8 : e == Epi::kGatedResidual ? B2_EPI_WARPS_GATED : e == Epi::kPlain ? B2_EPI_WARPS_PLAIN : 8;
 }
-// W4A8: four more warps expand the packed 4-bit weight tile into the INT8 operand stage (one weight row per thread).
-constexpr int kConvWarps = 4;
+// W4A8: eight more warps expand the packed 4-bit weight tile into the INT8 operand stage (two threads per weight row,
+// 64 columns each).
+constexpr int kConvWarps = 8;
+constexpr std::int64_t kW4FusedMaxRows = 256;  // see fused_pays_off()
 __host__ __device__ constexpr int threads_of(Epi e, int bn, bool w4 = false) {
-  return 64 + 32 * epi_warps(e, bn) + (w4 ? 32 * kConvWarps : 0);
+  return 64 + 32 * epi_warps(e, bn, w4) + (w4 ? 32 * kConvWarps : 0);
 }
 // Shared-memory slice of the SiTU factor tables: inputs with 2^-26 <= |x| < 2^6 (bf16 exponent field 101..132), where all
 // but a vanishing share of the pre-activations fall. Gate factors: [sign][exponent - 101][mantissa]; hidden factors: the
@@ -83,7 +86,8 @@ struct GemmParams {
   // W4A8 (kW4 kernels): the B tensor map covers the packed codes [n, k / 2]; group scales e4m3 [n, k / group]; the 16
   // levels (codebook or code - 8); the word that a NaN or negative scale raises.
   const std::uint8_t* w4_srel;
-  int w4_group;
+  int w4_group;        // a power of two >= 16
+  int w4_group_shift;  // log2(group)
   const float* w4_codebook;
   unsigned* w4_invalid;
 };
@@ -198,7 +202,7 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
   // Per epilogue warp: w_scale, bias, gate of its 128 columns (SiTU-GLU: w_scale of its 32 hidden and 32 gate columns).
-  constexpr int kEpiWarps = epi_warps(kEpi, kBN), kVecFloats = kEpi == Epi::kSituGlu ? 64 : 384;
+  constexpr int kEpiWarps = epi_warps(kEpi, kBN, kW4), kVecFloats = kEpi == Epi::kSituGlu ? 64 * (16 / epi_warps(kEpi, kBN, kW4)) : 384;
   __shared__ __align__(16) float s_vec[kEpiWarps][kVecFloats];
   // SiTU-GLU: the slices of the two factor tables, gate factors then hidden factors.
   __shared__ std::uint16_t s_tab[kEpi == Epi::kSituGlu ? kMiniGate + kMiniHidden : 1];
@@ -366,16 +370,20 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
     }
     __syncwarp();
-  } else if (kW4 && warp >= 2 + epi_warps(kEpi, kBN)) {
-    // W4A8 converters: thread r owns weight row r of the CTA's 128-row stage. Per K block it reads the row's 64 packed
-    // bytes (TMA wrote them with the 64-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ ((r / 2) % 4)), looks the
-    // (row, group) table up by the group's scale byte and writes the 128 INT8 values into the B stage in the
-    // 128-byte-swizzled layout the MMA reads (chunk n of row r at n ^ (r % 8)); then the warp arrives on the stage's
-    // "full" barrier (the leader's, for a pair) in place of a TMA completion.
-    const int r = (warp - 2 - epi_warps(kEpi, kBN)) * 32 + lane;
-    const int groups = p.k / p.w4_group;
+  } else if (kW4 && warp >= 2 + kEpiWarps) {
+    // W4A8 converters: two threads per weight row of the CTA's 128-row stage, 64 columns each. Per K block a thread reads
+    // its 32 packed bytes (TMA wrote the tile with the 64-byte swizzle: 16-byte chunk c of row r sits at chunk
+    // c ^ ((r / 2) % 4)), takes the 16-entry table of each group from shared memory by the group's scale byte (fetched one
+    // K block ahead) and writes the 64 INT8 values into the B stage in the 128-byte-swizzled layout the MMA reads (chunk
+    // n of row r at n ^ (r % 8)); then the warp arrives on the stage's "full" barrier (the leader's, for a pair) in place
+    // of a TMA completion.
+    const int ct = (warp - 2 - kEpiWarps) * 32 + lane;
+    const int r = ct & 127, half = ct >> 7;
+    const int groups = p.k >> p.w4_group_shift;
+    const int nsc = p.w4_group >= 64 ? 1 : 64 >> p.w4_group_shift;   // scales behind a thread's 64 columns: 1, 2 or 4
     std::uint32_t it = 0;
     bool bad = false;
+    const int psw = (r >> 1) & 3, bsw = r & 7;
     for (int tile = tile0; tile < total_tiles && *abort_word == 0; tile += tile_step) {
       int mt, nt;
       tile_coords(p, tile, &mt, &nt);
@@ -384,37 +392,56 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       else wrow = nt * kBN + static_cast<int>(rank) * 128 + r;
       const bool row_ok = kEpi == Epi::kSituGlu ? nt * 128 + r < p.half : wrow < p.n;
       const std::uint8_t* srow = p.w4_srel + static_cast<std::int64_t>(row_ok ? wrow : 0) * groups;
+      // Scale bytes of K block kb for this thread's columns (a zero byte, i.e. zeros, past the row's or the matrix' end).
+      const auto fetch = [&](int kb, std::uint32_t (&sb)[4]) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int col = kb * kBK + half * 64 + q * p.w4_group;
+          sb[q] = (q < nsc && row_ok && col < p.k) ? static_cast<std::uint32_t>(__ldg(srow + (col >> p.w4_group_shift))) : 0u;
+        }
+      };
+      std::uint32_t sb[4], sb_next[4] = {0u, 0u, 0u, 0u};
+      fetch(0, sb);
       bool dead = false;
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const int s = static_cast<int>(it % kStages);
         const std::uint32_t ph = (it / kStages) & 1u;
-        // The scale bytes of this K block (one per 16 columns at most), fetched before the wait.
-        std::uint32_t sb[8];
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          const int col = kb * kBK + 16 * n;
-          sb[n] = (row_ok && col < p.k) ? static_cast<std::uint32_t>(__ldg(srow + col / p.w4_group)) : 0u;
-        }
+        if (kb + 1 < k_blocks) fetch(kb + 1, sb_next);   // lands during this K block's work
         if (!wait_bar(smem_u32(&s_pfull[s]), ph, abort_word)) {
           dead = true;
           break;
         }
         const std::uint8_t* pk = smem_raw + (p_addr(s) - smem_u32(smem_raw)) + r * 64;
         std::uint8_t* brow = smem_raw + (b_addr(s) - smem_u32(smem_raw)) + r * 128;
-        const int psw = (r >> 1) & 3, bsw = r & 7;
+        // The tables of this thread's four 16-column chunks: with nsc scales behind its 64 columns, chunk q uses scale
+        // q * nsc / 4. (Named variables and selects: an indexed array would live in local memory.)
+        const uint4 ta = s_lut[sb[0]];
+        const uint4 tb = nsc >= 2 ? s_lut[sb[1]] : ta;
+        const uint4 tc = nsc == 4 ? s_lut[sb[2]] : tb;
+        const uint4 td = nsc == 4 ? s_lut[sb[3]] : tb;
+        // NaN (0x7F, 0xFF) or negative (sign bit over a non-zero magnitude): the table row is zeros; report it.
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {  // 16 packed bytes = 32 columns = two 16-byte chunks of the B row
-          const uint4 w = *reinterpret_cast<const uint4*>(pk + ((c ^ psw) * 16));
-          const uint4 t0 = s_lut[sb[2 * c]], t1 = s_lut[sb[2 * c + 1]];
-          // NaN (0x7F, 0xFF) or negative (sign bit over a non-zero magnitude): the table row is zeros; report it.
-          bad |= (sb[2 * c] & 0x7Fu) == 0x7Fu || sb[2 * c] > 0x80u || (sb[2 * c + 1] & 0x7Fu) == 0x7Fu || sb[2 * c + 1] > 0x80u;
+        for (int q = 0; q < 4; ++q) bad |= (sb[q] & 0x7Fu) == 0x7Fu || sb[q] > 0x80u;
+        const uint4 t0 = ta, t1 = nsc == 4 ? tb : ta, t2 = nsc == 4 ? tc : tb, t3 = nsc == 4 ? td : tb;
+        {
+          const uint4 w = *reinterpret_cast<const uint4*>(pk + (((2 * half) ^ psw) * 16));
           uint4 o0, o1;
           expand8(w.x, t0, o0.x, o0.y);
           expand8(w.y, t0, o0.z, o0.w);
           expand8(w.z, t1, o1.x, o1.y);
           expand8(w.w, t1, o1.z, o1.w);
-          *reinterpret_cast<uint4*>(brow + (((2 * c) ^ bsw) * 16)) = o0;
-          *reinterpret_cast<uint4*>(brow + (((2 * c + 1) ^ bsw) * 16)) = o1;
+          *reinterpret_cast<uint4*>(brow + (((4 * half) ^ bsw) * 16)) = o0;
+          *reinterpret_cast<uint4*>(brow + (((4 * half + 1) ^ bsw) * 16)) = o1;
+        }
+        {
+          const uint4 w = *reinterpret_cast<const uint4*>(pk + (((2 * half + 1) ^ psw) * 16));
+          uint4 o0, o1;
+          expand8(w.x, t2, o0.x, o0.y);
+          expand8(w.y, t2, o0.z, o0.w);
+          expand8(w.z, t3, o1.x, o1.y);
+          expand8(w.w, t3, o1.z, o1.w);
+          *reinterpret_cast<uint4*>(brow + (((4 * half + 2) ^ bsw) * 16)) = o0;
+          *reinterpret_cast<uint4*>(brow + (((4 * half + 3) ^ bsw) * 16)) = o1;
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -422,6 +449,8 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if constexpr (kCtas == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&s_full[s]), 0));
           else mbar_arrive(smem_u32(&s_full[s]));
         }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) sb[q] = sb_next[q];
       }
       if (dead) break;
     }
@@ -441,12 +470,16 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       __syncwarp();
       if constexpr (kEpi != Epi::kAcc) {  // the accumulator dump reads no per-column vector (and allows any n)
         constexpr int kHalfCols = kBN / (kEpiWarps / 4);  // columns of one warp's part of the tile
-        for (int j = lane * 4; j < (kEpi == Epi::kSituGlu ? 64 : 128); j += 128) {
+        // SiTU-GLU: a warp takes 32-column parts col_half, col_half + kEpiWarps / 4, ... of the tile's 128 output columns
+        // (one part with 16 epilogue warps, two with 8); 64 floats per part.
+        constexpr int kSituParts = kEpi == Epi::kSituGlu ? 16 / kEpiWarps : 1;
+        for (int j = lane * 4; j < (kEpi == Epi::kSituGlu ? 64 * kSituParts : 128); j += 128) {
           int col;
           bool ok;
           if constexpr (kEpi == Epi::kSituGlu) {
-            const int oc = nt * 128 + col_half * 32 + (j & 31);   // output column; j < 32 hidden, j >= 32 gate
-            col = (j < 32 ? 0 : p.half) + oc;
+            const int part = col_half + (j >> 6) * (kEpiWarps / 4);
+            const int oc = nt * 128 + part * 32 + (j & 31);   // output column; (j % 64) < 32 hidden, >= 32 gate
+            col = ((j & 63) < 32 ? 0 : p.half) + oc;
             ok = oc < p.half;
           } else {
             col = nt * kBN + col_half * kHalfCols + j;
@@ -487,8 +520,11 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
       if constexpr (kEpi == Epi::kSituGlu) {
         const int col0 = nt * 128;
-        {
-          const int c0 = col_half * 32;
+        constexpr int kSituParts = 16 / kEpiWarps;
+#pragma unroll 1
+        for (int pi = 0; pi < kSituParts; ++pi) {
+          const int c0 = (col_half + pi * (kEpiWarps / 4)) * 32;
+          const float* pvec = vec + 64 * pi;
           std::uint32_t rh[32], rg[32];
           tmem_ld_32x32(t_row + c0, rh);
           tmem_ld_32x32(t_row + 128 + c0, rg);
@@ -499,8 +535,8 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int v = 0; v < 8; ++v) {
               const int col = col0 + c0 + 4 * v;
               if (col < p.half) {
-                const float4 wh = *reinterpret_cast<const float4*>(vec + 4 * v);
-                const float4 wg = *reinterpret_cast<const float4*>(vec + 32 + 4 * v);
+                const float4 wh = *reinterpret_cast<const float4*>(pvec + 4 * v);
+                const float4 wg = *reinterpret_cast<const float4*>(pvec + 32 + 4 * v);
                 const float whs[4] = {wh.x, wh.y, wh.z, wh.w}, wgs[4] = {wg.x, wg.y, wg.z, wg.w};
                 // Both pre-activations of an output are rounded to bf16 by one packed conversion: hidden bits in the low
                 // half, gate bits in the high half. One subtraction rebases both exponents onto the shared-memory slice
@@ -833,14 +869,21 @@ int dispatch_w4(const char* op, const b2_int8_operands* a, const GemmParams& p, 
   else return launch_kernel<128, kEpi, 1, true>(op, a, p, stream);
 }
 
-// B2_W4A8_FUSED=0 in the environment sends every W4A8 GEMM through the decode-to-scratch route (for A/B timing).
-bool w4a8_fused_enabled() {
-  static const bool on = [] {
-    const char* v = std::getenv("B2_W4A8_FUSED");
-    return v == nullptr || v[0] != '0';
-  }();
-  return on;
+// B2_W4A8_FUSED in the environment overrides the choice between the two W4A8 routes (for A/B timing): 0 = always decode
+// to the scratch first, 1 = decode inside the GEMM whenever the weight's format allows.
+std::atomic<int>& w4a8_route() {  // -1 automatic, 0 scratch, 1 fused; starts from the environment
+  static std::atomic<int> v{[] {
+    const char* e = std::getenv("B2_W4A8_FUSED");
+    return e == nullptr ? -1 : e[0] == '0' ? 0 : 1;
+  }()};
+  return v;
 }
+int w4a8_fused_override() { return w4a8_route().load(std::memory_order_relaxed); }
+bool w4a8_fused_enabled() { return w4a8_fused_override() != 0; }
+// Decoding inside the GEMM redoes the expansion for every M tile that uses a weight tile, decoding to a scratch does it
+// once but moves 2.5 bytes per weight through memory instead of 0.5: the fused kernel wins while the GEMM is bound by
+// the weight's bytes (few rows), the scratch route once it is bound by the tensor core (many rows).
+bool fused_pays_off(std::int64_t m) { return w4a8_fused_override() == 1 || m <= kW4FusedMaxRows; }
 
 GemmParams base_params(const b2_int8_operands* a) {
   GemmParams p{};
@@ -992,7 +1035,7 @@ int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_
   if (m == 0) return B2_OK;
   // Decode inside the GEMM (no scratch traffic) for the reference's weight format: e4m3 group scales, a group size that
   // fits the 128-column K blocks, 16-byte aligned packed rows.
-  const bool fusable = w->scale_kind == 0 && (128 % w->group == 0 || w->group % 128 == 0) && k % 32 == 0 &&
+  const bool fusable = w->scale_kind == 0 && (w->group & (w->group - 1)) == 0 && k % 128 == 0 && fused_pays_off(m) &&
                        aligned_to(w->packed, 16) && !(epilogue == 2 && pick_tile(B2_TILE_AUTO, m, (n / 2 + 127) / 128) != B2_TILE_2CTA_256x256);
   const bool fused = fusable && w4a8_fused_enabled();
   if (!fused && scratch == nullptr) {
@@ -1004,6 +1047,8 @@ int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_
     f.w = static_cast<const std::int8_t*>(w->packed);
     GemmParams p = base_params(&f);
     p.w4_srel = static_cast<const std::uint8_t*>(w->s_rel), p.w4_group = w->group, p.w4_codebook = w->codebook;
+    for (p.w4_group_shift = 0; (1 << p.w4_group_shift) < w->group; ++p.w4_group_shift) {
+    }
     void* word = nullptr;
     if (const int rc = w4_invalid_word(&word)) return rc;
     p.w4_invalid = static_cast<unsigned*>(word);
@@ -1027,6 +1072,12 @@ int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_
   if (epilogue == 0) return b2_int8_gemm(&a, aux, out, ldo, stream, B2_TILE_AUTO);
   if (epilogue == 1) return b2_int8_gemm_gated_residual(&a, nullptr, aux, out, ldo, stream, B2_TILE_AUTO);
   return b2_int8_gemm_situ_glu(&a, out, ldo, stream, B2_TILE_AUTO);
+}
+
+int b2_debug_w4a8_route(int route) {
+  if (route < -1 || route > 1) return fail_invalid("debug_w4a8_route", "route must be -1 (automatic), 0 (scratch) or 1 (fused)");
+  w4a8_route().store(route, std::memory_order_relaxed);
+  return B2_OK;
 }
 
 /* b2_w4a8_gemm for callers that have no device memory to lend as scratch and may not allocate any: the decoded INT8

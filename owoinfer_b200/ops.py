@@ -164,6 +164,11 @@ def make_w4(packed, s_rel, group, s_channel, codebook=None):
     return w
 
 
+def debug_w4a8_route(route: int):
+    """-1 automatic, 0 always decode to the scratch, 1 decode inside the GEMM whenever the weight's format allows."""
+    check(_lib.lib().b2_debug_w4a8_route(C.c_int(route)))
+
+
 def w4a8_gemm(x_q, x_scale, w4, n, epilogue=0, aux=None, out=None, scratch=None):
     """scratch: int8 [n, k] for the weights that are decoded ahead of the GEMM (allocated when None); False passes no
     scratch at all (only weights the fused kernel takes: e4m3 scales, tile-sized shapes)."""

@@ -294,16 +294,23 @@ def test_w4a8_gemm_decoding_inside_the_kernel(ops, m, n, k, group):
     w8 = ops.decode_grouped_int8(packed, s_rel, group)
     assert np.array_equal(w8.cpu().numpy(), orc.decode_grouped_int8(packed.cpu().numpy(), s_rel.cpu().numpy(), group))
     bias = synth.vector(n, 6, 0.05)
-    got = ops.w4a8_gemm(xq, xs, w4, n, aux=bias, scratch=False)
-    assert torch.equal(got.view(torch.int16), ops.int8_gemm(xq, xs, w8, s_ch, bias=bias).view(torch.int16))
-    gate = synth.vector(n, 7, 0.3)
-    res = synth.activations(m, n, 51)
-    a, b = res.clone(), res.clone()
-    ops.w4a8_gemm(xq, xs, w4, n, epilogue=1, aux=gate, out=a, scratch=False)
-    ops.int8_gemm_gated_residual(xq, xs, w8, s_ch, gate, b)
-    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
-    glu = ops.w4a8_gemm(xq, xs, w4, n, epilogue=2)   # small shapes fall back to the scratch route for this epilogue
-    assert torch.equal(glu.view(torch.int16), ops.int8_gemm_situ_glu(xq, xs, w8, s_ch).view(torch.int16))
+    ops.debug_w4a8_route(1)   # the fused kernel whatever the row count (the automatic choice takes it up to 256 rows)
+    try:
+        got = ops.w4a8_gemm(xq, xs, w4, n, aux=bias, scratch=False)
+        assert torch.equal(got.view(torch.int16), ops.int8_gemm(xq, xs, w8, s_ch, bias=bias).view(torch.int16))
+        gate = synth.vector(n, 7, 0.3)
+        res = synth.activations(m, n, 51)
+        a, b = res.clone(), res.clone()
+        ops.w4a8_gemm(xq, xs, w4, n, epilogue=1, aux=gate, out=a, scratch=False)
+        ops.int8_gemm_gated_residual(xq, xs, w8, s_ch, gate, b)
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+        glu = ops.w4a8_gemm(xq, xs, w4, n, epilogue=2)   # small shapes fall back to the scratch route for this epilogue
+        assert torch.equal(glu.view(torch.int16), ops.int8_gemm_situ_glu(xq, xs, w8, s_ch).view(torch.int16))
+    finally:
+        ops.debug_w4a8_route(-1)
+    # The automatic choice gives the same bits on either side of its threshold.
+    auto = ops.w4a8_gemm(xq, xs, w4, n, aux=bias)
+    assert torch.equal(auto.view(torch.int16), got.view(torch.int16))
     assert ops.w4_invalid_scales() == 0
 
 
@@ -320,7 +327,11 @@ def test_w4a8_fused_codebook_and_untrusted_scales(ops):
     xs = torch.rand(m, device="cuda") * 1e-2
     w4 = ops.make_w4(packed, s_rel, group, s_ch, codebook=cb)
     ops.w4_invalid_scales(clear=True)
-    got = ops.w4a8_gemm(xq, xs, w4, n, scratch=False)
+    ops.debug_w4a8_route(1)
+    try:
+        got = ops.w4a8_gemm(xq, xs, w4, n, scratch=False)
+    finally:
+        ops.debug_w4a8_route(-1)
     assert ops.w4_invalid_scales(clear=True) == 1
     w8, flag = orc.decode_grouped_int8_device_rule(packed.cpu().numpy(), s_rel.cpu().numpy(), group, cb.cpu().numpy())
     assert flag == 1

@@ -233,9 +233,14 @@ def test_block_close_to_reference_kernels(ops):
 # one 20480-token sequence of a 2048^2 step; and the grouped 4-bit tier at full width. Gates: cosine >= 0.9995 and
 # max|g-w| / max|w| <= 1e-2 (the reading of "max-relative-error 1e-2" that the reference's own block tests use,
 # tests/unit/test_dit_int8.cpp:307-341), plus the per-element error of _block_metrics, printed and bounded.
-@pytest.mark.parametrize("lens,grid,tier", [([8192], 64, 0), ([8192, 8192], 64, 0), ([20480], 128, 0), ([8192], 64, 2)])
-def test_block_at_benchmark_shapes(ops, lens, grid, tier):
-    cos, max_rel, per_elem, rel_l2 = _ours_vs_ref_block(ops, lens, 12288, grid, 11 + len(lens) + tier, tier)
+@pytest.mark.parametrize("lens,grid,tier,w4_route", [([8192], 64, 0, -1), ([8192, 8192], 64, 0, -1), ([20480], 128, 0, -1),
+                                                     ([8192], 64, 2, -1), ([8192], 64, 2, 1)])
+def test_block_at_benchmark_shapes(ops, lens, grid, tier, w4_route):
+    ops.debug_w4a8_route(w4_route)   # the grouped 4-bit tier through its automatic route and through the fused kernel
+    try:
+        cos, max_rel, per_elem, rel_l2 = _ours_vs_ref_block(ops, lens, 12288, grid, 11 + len(lens) + tier, tier)
+    finally:
+        ops.debug_w4a8_route(-1)
     print("block", lens, "tier", tier, dict(cos=cos, max_rel=max_rel, per_elem=per_elem, rel_l2=rel_l2))
     assert cos >= 0.9995 and max_rel <= 1e-2, (cos, max_rel, per_elem, rel_l2)
     assert per_elem <= 5e-2 and rel_l2 <= 1e-2, (cos, max_rel, per_elem, rel_l2)
