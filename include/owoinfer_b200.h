@@ -365,6 +365,41 @@ int b2_run_block_quant_sp(const b2_block_weights* w, const b2_block_buffers* a, 
 int b2_dit_step_sp(const b2_block_weights* blocks, int num_blocks, const b2_block_buffers* a, const b2_sp_run* run,
                    b2_sp_comm* comm, void* stream);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * Guidance and the velocity update that follow the block loop of a denoising step (fp32 latents, device pointers).
+ * Each op is one fp32 operation rounded once, in the reference's order: identical bits.
+ * ------------------------------------------------------------------------------------------------------------- */
+
+/* pipeline::cfg_combine (src/pipeline/samplers/sampler_driver.h:188; kernel sampler_kernels.cu:304):
+ * out = uncond + g * (cond - uncond). */
+int b2_cfg_combine(const float* cond, const float* uncond, float g, float* out, int64_t n, void* stream);
+/* pipeline::slg_correct (sampler_driver.h:189; kernel sampler_kernels.cu:308): out = pred + scale * (cond - skipped). */
+int b2_slg_correct(const float* pred, const float* cond, const float* skipped, float scale, float* out, int64_t n,
+                   void* stream);
+/* pipeline::euler_update (sampler_driver.h:201; kernel sampler_kernels.cu:209): x += h * v. */
+int b2_euler_update(float* x, const float* v, float h, int64_t n, void* stream);
+/* pipeline::ab2_update (sampler_driver.h:202; kernel sampler_kernels.cu:213): x += h * (a * v - b * v_prev). */
+int b2_ab2_update(float* x, const float* v, const float* v_prev, float h, float a, float b, int64_t n, void* stream);
+
+/* pipeline::guide_prediction in velocity space (src/pipeline/samplers/sampler_driver.cpp:565-577) followed by the
+ * update, in ONE pass over the latent instead of up to four launches: v = cfg ? v_uncond + cfg_scale * (v_cond -
+ * v_uncond) : v_cond; with slg, v = (cfg ? v : v_skip) + slg_scale * (v_cond - v_skip); v is stored to v_out when that
+ * is non-NULL (the next Adams-Bashforth step's v_prev); update 1: x += h * v, update 2: x += h * (a * v - b * v_prev),
+ * update 0: none (then v_out is required). Same bits as the reference's sequence of calls. */
+typedef struct b2_guided_step {
+  size_t struct_size;
+  float* x;               /* [n] latent, updated in place */
+  const float* v_cond;    /* [n] */
+  const float* v_uncond;  /* [n], with cfg */
+  const float* v_skip;    /* [n], with slg */
+  const float* v_prev;    /* [n], update 2 */
+  float* v_out;           /* [n] or NULL; must not alias v_prev */
+  float cfg_scale, slg_scale, h, a, b;
+  int cfg, slg, update;
+  int64_t n;
+} b2_guided_step;
+int b2_guided_velocity_step(const b2_guided_step* step, void* stream);
+
 /* Every mbarrier wait inside the tensor-core kernels is bounded (200 ms); a CTA whose wait expired raises a device word,
  * drains and returns instead of hanging. This reads the two words (GEMM, attention): 0 = no wait ever expired on this device.
  * Synchronises the device; for tests and post-mortems, not for the hot path. No counterpart in the reference (its

@@ -336,3 +336,41 @@ def block_quant(x, mod, rope, w, cu, max_seqlen, heads=24, p_range=448.0, v_rang
     if rc != 0:
         raise ValueError("orc_block_quant failed")
     return x
+
+
+# ---------------------------------------------------------------------------------------------- guidance + update
+# Four fp32 formulas, one rounding per op, in the reference's order (src/pipeline/samplers/sampler_kernels.cu:209-218,
+# 304-310; sequencing src/pipeline/samplers/sampler_driver.cpp:565-577). numpy float32 arithmetic rounds every op once
+# and never contracts.
+
+def _f32(a):
+    return np.asarray(a, dtype=np.float32)
+
+
+def cfg_combine(cond, uncond, g):
+    c, u, g = _f32(cond), _f32(uncond), np.float32(g)
+    return u + g * (c - u)
+
+
+def slg_correct(pred, cond, skipped, scale):
+    p, c, k, s = _f32(pred), _f32(cond), _f32(skipped), np.float32(scale)
+    return p + s * (c - k)
+
+
+def euler_update(x, v, h):
+    return _f32(x) + np.float32(h) * _f32(v)
+
+
+def ab2_update(x, v, v_prev, h, a, b):
+    d = np.float32(a) * _f32(v) - np.float32(b) * _f32(v_prev)
+    return _f32(x) + np.float32(h) * d
+
+
+def guided_velocity(v_cond, v_uncond=None, v_skip=None, cfg_scale=0.0, slg_scale=0.0):
+    """guide_prediction in velocity space: CFG, then SLG on its result (on v_skip itself when CFG is off)."""
+    v = _f32(v_cond)
+    if v_uncond is not None:
+        v = cfg_combine(v_cond, v_uncond, cfg_scale)
+    if v_skip is not None:
+        v = slg_correct(v if v_uncond is not None else v_skip, v_cond, v_skip, slg_scale)
+    return v

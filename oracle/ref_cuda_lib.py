@@ -33,6 +33,11 @@ def lib():
         l.ref_attention_q8_workspace_bytes.restype = sz
         l.ref_attention_q8_workspace_bytes.argtypes = [i64, i32, i32, i32]
         l.ref_attention_q8.argtypes = [vp, i64, i64, i32, vp, i64, vp, i32, i32, f32, vp, sz, i32, vp, vp, vp, vp]
+        if hasattr(l, "ref_cfg_velocity"):
+            l.ref_cfg_velocity.argtypes = [vp, vp, f32, vp, i64, vp]
+            l.ref_slg_velocity.argtypes = [vp, vp, vp, f32, vp, i64, vp]
+            l.ref_velocity_euler.argtypes = [vp, vp, f32, i64, vp]
+            l.ref_ab2.argtypes = [vp, vp, vp, f32, f32, f32, i64, vp]
         _lib = l
     return _lib
 
@@ -96,6 +101,26 @@ def attention_q8(qkv, heads, out, cu, max_seqlen, scale, workspace, norm_rope=No
     _ok(lib().ref_attention_q8(_p(qkv), qkv.stride(0), qkv.shape[0], heads, _p(out), out.stride(0), _p(cu),
                                cu.numel() - 1, max_seqlen, scale, _p(workspace), workspace.numel(),
                                1 if norm_rope else 0, _p(nr[0]), _p(nr[1]), _p(nr[2]), _stream()))
+
+
+def cfg_velocity(c, u, g, out):
+    _ok(lib().ref_cfg_velocity(_p(c), _p(u), g, _p(out), c.numel(), _stream()))
+
+
+def slg_velocity(p, c, k, s, out):
+    _ok(lib().ref_slg_velocity(_p(p), _p(c), _p(k), s, _p(out), c.numel(), _stream()))
+
+
+def velocity_euler(x, v, h):
+    _ok(lib().ref_velocity_euler(_p(x), _p(v), h, x.numel(), _stream()))
+
+
+def ab2(x, v, v_prev, h, a, b):
+    _ok(lib().ref_ab2(_p(x), _p(v), _p(v_prev), h, a, b, x.numel(), _stream()))
+
+
+def has_sampler_kernels() -> bool:
+    return available() and hasattr(lib(), "ref_cfg_velocity")
 
 
 class RefBlock:

@@ -14,6 +14,7 @@
 #include "kernels/attention_q8/q8_kernels.h"
 #include "kernels/fused/qk_norm_rope.h"
 #include "kernels/quant/quant.h"
+#include "pipeline/samplers/sampler_kernels.h"
 #include "kernels/sm75/int8_sm75.h"
 #include "kernels/sm75/sm75.h"
 
@@ -154,6 +155,20 @@ int ref_attention_q8(void* qkv, std::int64_t ld, std::int64_t total, int heads, 
     mi::attention_q8::attention_q8(opt, q, k, v, o, cuq, cuq, max_seqlen, scale, workspace, workspace_bytes,
                                    static_cast<cudaStream_t>(stream), norm_rope ? &nr : nullptr);
   });
+}
+
+// The guidance and velocity-update kernels of the sampler driver (src/pipeline/samplers/sampler_kernels.cu).
+int ref_cfg_velocity(const float* c, const float* u, float g, float* out, std::int64_t n, cudaStream_t st) {
+  return guarded([&] { mi::pipeline::sampler_kernels::cfg_velocity(c, u, g, out, n, st); });
+}
+int ref_slg_velocity(const float* p, const float* c, const float* k, float s, float* out, std::int64_t n, cudaStream_t st) {
+  return guarded([&] { mi::pipeline::sampler_kernels::slg_velocity(p, c, k, s, out, n, st); });
+}
+int ref_velocity_euler(float* x, const float* v, float h, std::int64_t n, cudaStream_t st) {
+  return guarded([&] { mi::pipeline::sampler_kernels::velocity_euler(x, v, h, n, st); });
+}
+int ref_ab2(float* x, const float* v, const float* vp, float h, float a, float b, std::int64_t n, cudaStream_t st) {
+  return guarded([&] { mi::pipeline::sampler_kernels::ab2(x, v, vp, h, a, b, n, st); });
 }
 
 }  // extern "C"

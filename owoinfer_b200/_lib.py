@@ -17,6 +17,7 @@ EXPORTS = [
     "b2_attention_q8_layout", "b2_attention_q8_debug_scores", "b2_attention_q8_preprocess", "b2_block_quant_workspace_bytes", "b2_run_block_quant", "b2_dit_step",
     "b2_kernel_status", "b2_kernel_status_clear", "b2_debug_bounded_wait", "b2_w4_invalid_scales", "b2_rotate_quantize_chunked", "b2_int8_gemm_chunked", "b2_sp_unique_id",
     "b2_sp_comm_create", "b2_sp_comm_destroy", "b2_sp_comm_local_exchange", "b2_block_quant_sp_workspace_bytes", "b2_run_block_quant_sp", "b2_dit_step_sp",
+    "b2_cfg_combine", "b2_slg_correct", "b2_euler_update", "b2_ab2_update", "b2_guided_velocity_step",
 ]
 
 
@@ -67,6 +68,13 @@ class BlockRun(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("tokens", C.c_int64), ("D", C.c_int), ("F", C.c_int), ("heads", C.c_int),
                 ("cu_seqlens", C.c_void_p), ("batch", C.c_int), ("max_seqlen", C.c_int), ("tier", C.c_int),
                 ("attention", AttentionOptions), ("fused_norm_rope", C.c_int)]
+
+
+class GuidedStep(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("x", C.c_void_p), ("v_cond", C.c_void_p), ("v_uncond", C.c_void_p),
+                ("v_skip", C.c_void_p), ("v_prev", C.c_void_p), ("v_out", C.c_void_p), ("cfg_scale", C.c_float),
+                ("slg_scale", C.c_float), ("h", C.c_float), ("a", C.c_float), ("b", C.c_float), ("cfg", C.c_int),
+                ("slg", C.c_int), ("update", C.c_int), ("n", C.c_int64)]
 
 
 class SpRun(C.Structure):

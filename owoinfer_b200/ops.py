@@ -414,3 +414,43 @@ def run_block_quant_sp(weights: BlockWeights, bufs, run, comm: SpComm):
 def dit_step_sp(blocks, bufs, run, comm: SpComm):
     arr = (_lib.BlockWeights * len(blocks))(*[b.struct for b in blocks])
     check(_lib.lib().b2_dit_step_sp(arr, C.c_int(len(blocks)), C.byref(bufs), C.byref(run), comm.handle, _stream()))
+
+
+# ------------------------------------------------------------------------------------------------ guidance + update
+
+def cfg_combine(cond, uncond, g, out=None):
+    out = torch.empty_like(cond) if out is None else out
+    check(_lib.lib().b2_cfg_combine(_ptr(cond), _ptr(uncond), C.c_float(g), _ptr(out), C.c_int64(cond.numel()), _stream()))
+    return out
+
+
+def slg_correct(pred, cond, skipped, scale, out=None):
+    out = torch.empty_like(cond) if out is None else out
+    check(_lib.lib().b2_slg_correct(_ptr(pred), _ptr(cond), _ptr(skipped), C.c_float(scale), _ptr(out), C.c_int64(cond.numel()),
+                                    _stream()))
+    return out
+
+
+def euler_update(x, v, h):
+    check(_lib.lib().b2_euler_update(_ptr(x), _ptr(v), C.c_float(h), C.c_int64(x.numel()), _stream()))
+    return x
+
+
+def ab2_update(x, v, v_prev, h, a, b):
+    check(_lib.lib().b2_ab2_update(_ptr(x), _ptr(v), _ptr(v_prev), C.c_float(h), C.c_float(a), C.c_float(b), C.c_int64(x.numel()),
+                                   _stream()))
+    return x
+
+
+def guided_velocity_step(v_cond, x=None, v_uncond=None, v_skip=None, v_prev=None, v_out=None, cfg_scale=0.0, slg_scale=0.0,
+                         h=0.0, a=0.0, b=0.0, update=0):
+    """One pass: guidance (cfg when v_uncond is given, slg when v_skip is given), optional store of the guided velocity,
+    and the Euler (update 1) or Adams-Bashforth (update 2) step of x."""
+    g = _lib.GuidedStep()
+    g.struct_size = C.sizeof(_lib.GuidedStep)
+    p = lambda t: None if t is None else t.data_ptr()
+    g.x, g.v_cond, g.v_uncond, g.v_skip, g.v_prev, g.v_out = p(x), p(v_cond), p(v_uncond), p(v_skip), p(v_prev), p(v_out)
+    g.cfg_scale, g.slg_scale, g.h, g.a, g.b = cfg_scale, slg_scale, h, a, b
+    g.cfg, g.slg, g.update, g.n = int(v_uncond is not None), int(v_skip is not None), update, v_cond.numel()
+    check(_lib.lib().b2_guided_velocity_step(C.byref(g), _stream()))
+    return x if update else v_out

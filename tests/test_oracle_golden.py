@@ -285,3 +285,24 @@ def test_attention_against_upstream_recording():
     want = bf(load("attention_q8", "upstream_out_int8_fp8_f32acc"))
     cos, rel, mx = _metrics(bf(out).reshape(total, heads, 128), want)
     assert cos >= 0.99999 and mx <= 0.04, (cos, rel, mx)
+
+
+def test_guidance_and_update_formulas_round_once_per_op():
+    """The host emulation of the reference's own test (tests/unit/test_pipeline.cpp:212-238): every product and sum is
+    rounded to fp32 on its own. float64 evaluation rounded at the end differs on some elements, which is what makes the
+    order of roundings part of the contract."""
+    rng = np.random.default_rng(7)
+    a, b, c, x = (rng.normal(0.0, 1.5, 100003).astype(np.float32) for _ in range(4))
+    g, s, h, ka, kb = (np.float32(v) for v in (3.7, 0.85, -0.0412, 1.31, 0.31))
+    want = b + (g * (a - b)).astype(np.float32)
+    assert np.array_equal(orc.cfg_combine(a, b, 3.7), want) and want.dtype == np.float32
+    assert np.array_equal(orc.slg_correct(a, b, c, 0.85), a + s * (b - c))
+    assert np.array_equal(orc.euler_update(x, a, -0.0412), x + h * a)
+    assert np.array_equal(orc.ab2_update(x, a, b, -0.0412, 1.31, 0.31), x + h * (ka * a - kb * b))
+    exact = (b.astype(np.float64) + 3.7 * (a.astype(np.float64) - b.astype(np.float64))).astype(np.float32)
+    assert 0 < np.count_nonzero(exact != want) < want.size // 2
+    # guide_prediction in velocity space: cfg then slg on its result; slg alone starts from the skipped velocity
+    v = orc.guided_velocity(a, b, c, 3.7, 0.85)
+    assert np.array_equal(v, orc.slg_correct(orc.cfg_combine(a, b, 3.7), a, c, 0.85))
+    assert np.array_equal(orc.guided_velocity(a, None, c, 0.0, 0.85), orc.slg_correct(c, a, c, 0.85))
+    assert np.array_equal(orc.guided_velocity(a), a)
