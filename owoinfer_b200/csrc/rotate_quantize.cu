@@ -1,7 +1,9 @@
 // Activation quantisers of the quantized DiT block: ConvRot rotation (x · H256 per 256-column group) + per-token INT8 or
 // INT4 quantisation, optionally preceded by the MOSS RMSNorm + adaLN modulate, plus the small int4 -> int8 helpers
-// (unpack, grouped decode). HBM-bound element-wise work: 128-bit global accesses, rows held in registers between the
-// absmax pass and the quantise pass, shared memory only for the 16 x 16 digit transpose.
+// (unpack, grouped decode). Element-wise work bound by instruction issue first (four stages of exact-order fp32 adds per
+// element) and HBM second: persistent thread blocks, the next row prefetched into shared memory (cp.async) under the
+// current one, the butterflies on packed fp32 pairs (add.rn.f32x2), rows held in registers as packed bf16 between the
+// absmax pass and the quantise pass, shared memory for the 16 x 16 digit transpose and the byte scatter.
 //
 // Numerics (bit for bit those of the reference engine, src/kernels/quant/quant.h:4-23, src/kernels/quant4/quant4.h:1-24):
 //   rotation     four radix-4 stages over the base-4 digits of the in-group index, each output
@@ -19,6 +21,7 @@
 // is never within 2^-17 (relative) of a bf16 rounding boundary, so the bf16 rounding of the product equals the
 // bf16 rounding of the correctly rounded fp32 quotient; infinities, NaN and zeros propagate identically.
 #include <algorithm>
+#include <atomic>
 #include <string>
 #include <type_traits>
 
@@ -29,8 +32,6 @@ namespace {
 
 constexpr int kGroup = 256;
 constexpr int kMaxK = 32768;
-constexpr int kTileStride = 17;                  // floats per row of the 16 x 16 transpose tile (conflict-free)
-constexpr int kTileFloats = 16 * kTileStride;
 constexpr float kBf16Max = 3.38953139e38f;
 
 struct Args {
@@ -54,70 +55,86 @@ struct Args {
   std::int64_t chunk_stride;
 };
 
-// Radix-4 butterfly on four operands in digit order. kHalve = false leaves the factor 0.5 out: the outputs are then twice
-// the reference's, exactly (a power-of-two factor commutes with every fp32 rounding as long as nothing overflows or goes
-// subnormal), and a whole rotation comes out 16 times too large.
+using u32 = std::uint32_t;
+using u64 = std::uint64_t;
+
+// Two fp32 values in one 64-bit register; add / sub / mul round each half on its own (add.rn.f32x2 and friends), so a
+// packed butterfly gives the bits of two scalar ones for half the issue slots.
+__device__ __forceinline__ u64 pack2(float lo, float hi) {
+  u64 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void unpack2(u64 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ u64 add2(u64 a, u64 b) {
+  u64 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ u64 sub2(u64 a, u64 b) {
+  u64 d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
+  u64 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// Radix-4 butterfly on four operands in digit order, each operand a pair (the same element of two 256-groups):
+// y_d = 0.5 * (((m0' + m1') + m2') + m3') with operand 3 - d negated. kHalve = false leaves the factor 0.5 out: the
+// outputs are then twice the reference's, exactly (a power-of-two factor commutes with every fp32 rounding as long as
+// nothing overflows or goes subnormal), and a whole rotation comes out 16 times too large.
 template <bool kHalve>
-__device__ __forceinline__ void butterfly4(float& a, float& b, float& c, float& d) {
-  const float s = fadd(a, b), t = fadd(a, -b);
-  float y0 = fadd(fadd(s, c), -d), y1 = fadd(fadd(s, -c), d), y2 = fadd(fadd(t, c), d), y3 = fadd(fadd(-t, c), d);
-  if constexpr (kHalve) y0 = fmul(0.5f, y0), y1 = fmul(0.5f, y1), y2 = fmul(0.5f, y2), y3 = fmul(0.5f, y3);
+__device__ __forceinline__ void butterfly4(u64& a, u64& b, u64& c, u64& d) {
+  const u64 s = add2(a, b), t = sub2(a, b);
+  u64 y0 = sub2(add2(s, c), d), y1 = add2(sub2(s, c), d), y2 = add2(add2(t, c), d), y3 = add2(sub2(c, t), d);
+  if constexpr (kHalve) {
+    const u64 half = pack2(0.5f, 0.5f);
+    y0 = mul2(half, y0), y1 = mul2(half, y1), y2 = mul2(half, y2), y3 = mul2(half, y3);
+  }
   a = y0, b = y1, c = y2, d = y3;
 }
 // The two stages whose digits are the low and high 2 bits of the register index.
 template <bool kHalve>
-__device__ __forceinline__ void stages_on_registers(float (&v)[16]) {
+__device__ __forceinline__ void stages_on_registers(u64 (&v)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; i += 4) butterfly4<kHalve>(v[i], v[i + 1], v[i + 2], v[i + 3]);
 #pragma unroll
   for (int i = 0; i < 4; ++i) butterfly4<kHalve>(v[i], v[i + 4], v[i + 8], v[i + 12]);
 }
-// max(a, |b|, |c|) that returns NaN when any operand is NaN.
-__device__ __forceinline__ float max3_abs_nan(float a, float b, float c) {
-  float r;
-  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(fabsf(b)), "f"(fabsf(c)));
-  return r;
-}
-__device__ __forceinline__ float max_nan(float a, float b) {
-  float r;
-  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-  return r;
-}
 
-__device__ __forceinline__ void load16_bf16(const __nv_bfloat16* p, float (&v)[16]) {
-  const uint4 lo = reinterpret_cast<const uint4*>(p)[0], hi = reinterpret_cast<const uint4*>(p)[1];
-  const std::uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-  }
-}
 // Sixteen bf16 values as eight packed pairs (element 2i in the low half of word i).
-__device__ __forceinline__ void load16_packed(const __nv_bfloat16* p, std::uint32_t (&w)[8]) {
+__device__ __forceinline__ void load16_packed(const __nv_bfloat16* p, u32 (&w)[8]) {
   const uint4 lo = reinterpret_cast<const uint4*>(p)[0], hi = reinterpret_cast<const uint4*>(p)[1];
   w[0] = lo.x, w[1] = lo.y, w[2] = lo.z, w[3] = lo.w, w[4] = hi.x, w[5] = hi.y, w[6] = hi.z, w[7] = hi.w;
 }
 // Packed bf16 pairs: a * b and a + b, each result rounded once to bf16.
-__device__ __forceinline__ std::uint32_t bmul2(std::uint32_t a, std::uint32_t b) {
-  std::uint32_t d;
+__device__ __forceinline__ u32 bmul2(u32 a, u32 b) {
+  u32 d;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
-__device__ __forceinline__ std::uint32_t badd2(std::uint32_t a, std::uint32_t b) {
-  std::uint32_t d;
+__device__ __forceinline__ u32 badd2(u32 a, u32 b) {
+  u32 d;
   asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
-__device__ __forceinline__ void store16_bf16(__nv_bfloat16* p, const float (&v)[16]) {
-  std::uint32_t w[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    w[i] = *reinterpret_cast<const std::uint32_t*>(&h);
-  }
-  reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-  reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+// Two floats rounded to bf16: lo in the low half.
+__device__ __forceinline__ u32 pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const u32*>(&h);
+}
+__device__ __forceinline__ float bf_lo(u32 w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(u32 w) { return __uint_as_float(w & 0xFFFF0000u); }
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
 // Sum of squares of one row in the order of torch's reduce kernel with `bw` cooperating threads (a power of two,
@@ -127,8 +144,7 @@ __device__ float torch_order_sum_squares(const __nv_bfloat16* xr, int k, int bw,
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
     for (int idx = t; idx * 4 + 3 < k; idx += bw) {
       const uint2 raw = *reinterpret_cast<const uint2*>(xr + idx * 4);
-      const float e0 = __uint_as_float(raw.x << 16), e1 = __uint_as_float(raw.x & 0xFFFF0000u);
-      const float e2 = __uint_as_float(raw.y << 16), e3 = __uint_as_float(raw.y & 0xFFFF0000u);
+      const float e0 = bf_lo(raw.x), e1 = bf_hi(raw.x), e2 = bf_lo(raw.y), e3 = bf_hi(raw.y);
       a0 = fadd(a0, fmul(e0, e0));
       a1 = fadd(a1, fmul(e1, e1));
       a2 = fadd(a2, fmul(e2, e2));
@@ -147,217 +163,325 @@ __device__ float torch_order_sum_squares(const __nv_bfloat16* xr, int k, int bw,
   return __shfl_sync(0xffffffffu, s, 0);
 }
 
-// One thread block per row. A half-warp owns one 256-group at a time, 16 elements per lane; half-warp i takes groups
-// i, i + halves, ... (kSlots of them, kept in registers across the row-wide absmax).
+constexpr int kTileStride = 17;  // 64-bit words per row of the 16 x 16 transpose tile (conflict-free)
+// Per half-warp; the first 512 bytes later hold the quantised bytes. The 8 words of padding put the two tiles of a warp
+// 16 banks apart, so that the narrow stores of its two half-warps into them do not collide.
+constexpr int kTileWords = 16 * kTileStride + 8;
+constexpr int kStages = 2;           // row buffers: the copies run kStages - 1 rows ahead
+constexpr int kNormSmemMaxK = 4096;  // rows up to this length sum their squares from the staged row, in parallel
+
+// Persistent thread blocks, each walking rows blockIdx.x, blockIdx.x + gridDim.x, ...; the next row's bytes are copied
+// into shared memory (cp.async, two row buffers, every lane reading back only what it copied) while the current row is
+// worked on. A half-warp owns a PAIR of 256-groups at a time (groups 2P and 2P + 1, P = half-warp, half-warp + halves,
+// ...: kPairs of them), 16 elements of each per lane, and carries element j of both in one 64-bit register, so that the
+// rotation runs on packed fp32 pairs.
 //   load layout  : lane h holds elements 16 h + j  -> register index j carries digits d0, d1
 //   after the 16 x 16 transpose: element h + 16 j  -> register index j carries digits d2, d3
-// The quantised bytes are scattered into a 256-byte shared tile in natural order, so each lane stores 16 (INT8) or 8
-// (INT4) contiguous bytes.
-template <int kSlots, bool kNorm, bool kInt4>
-__global__ void __launch_bounds__(kSlots == 1 ? 256 : 512, kSlots == 1 ? (kNorm ? 8 : 6) : 1) rotate_quantize_kernel(const Args a) {
-  extern __shared__ float smem_f[];
-  __shared__ float s_warp_max[2][16];
+// The rotated row waits for the row-wide maximum as packed bf16 (group 2P in the low half); the quantised bytes are
+// scattered into a shared tile in natural order, so each lane stores 16 (INT8) or 8 (INT4) contiguous bytes per group.
+template <int kPairs, bool kNorm, bool kInt4>
+__global__ void __launch_bounds__(kPairs == 1 ? 384 : 512, kPairs == 1 ? 2 : 1) rotate_quantize_kernel(const Args a, const int m) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ u32 s_warp_max[4][16];
   __shared__ float s_inv_rms;
   __shared__ float s_part[512];
-  const int tid = static_cast<int>(threadIdx.x), lane = tid & 31, warp = tid >> 5;
-  const int halves = static_cast<int>(blockDim.x) >> 4, half_id = tid >> 4, h = tid & 15;
+  const int tid = static_cast<int>(threadIdx.x), lane = tid & 31, warp = tid >> 5, nthreads = static_cast<int>(blockDim.x);
+  const int halves = nthreads >> 4, half_id = tid >> 4, h = tid & 15, nwarps = nthreads >> 5;
   const int groups = a.k / kGroup;
-  const std::int64_t row = blockIdx.x;
-  const __nv_bfloat16* xr = a.x + row * a.ldx;
-  float* tile = smem_f + half_id * kTileFloats;
-  std::uint8_t* qtile = reinterpret_cast<std::uint8_t*>(smem_f + halves * kTileFloats) + half_id * kGroup;
+  const int stage_vecs = kPairs * 4 * nthreads;
+  uint4* const stages = reinterpret_cast<uint4*>(smem_raw);
+  u64* const tile = reinterpret_cast<u64*>(smem_raw + kStages * stage_vecs * sizeof(uint4)) + half_id * kTileWords;
+  std::uint8_t* const qtile = reinterpret_cast<std::uint8_t*>(tile);
 
-  float v[kSlots][16];
-  const auto load_row = [&] {
+  const auto source = [&](std::int64_t row, int g) {
+    const int col = g * kGroup + 16 * h;
+    return a.chunk_w == 0 ? a.x + row * a.ldx + col : a.x + (col / a.chunk_w) * a.chunk_stride + row * a.ldx + col % a.chunk_w;
+  };
+  // Vector v (0, 1: group 2P; 2, 3: group 2P + 1) of pair slot p, for this thread: [stage][p][v][thread].
+  const auto staged = [&](int st, int p, int v) { return stages + st * stage_vecs + (p * 4 + v) * nthreads + tid; };
+  const auto copy_row = [&](std::int64_t row, int st) {
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-      const int g = half_id + s * halves;
-      if (g < groups) {
-        const int col = g * kGroup + 16 * h;
-        const __nv_bfloat16* src = a.chunk_w == 0 ? xr + col
-                                                  : a.x + (col / a.chunk_w) * a.chunk_stride + row * a.ldx + col % a.chunk_w;
-        load16_bf16(src, v[s]);
+    for (int p = 0; p < kPairs; ++p) {
+#pragma unroll
+      for (int gi = 0; gi < 2; ++gi) {
+        const int g = 2 * (half_id + p * halves) + gi;
+        if (g < groups) {
+          const __nv_bfloat16* src = source(row, g);
+          cp_async16(staged(st, p, 2 * gi), src);
+          cp_async16(staged(st, p, 2 * gi + 1), src + 8);
+        }
+      }
+    }
+  };
+
+  std::int64_t row = blockIdx.x;
+#pragma unroll
+  for (int i = 0; i < kStages - 1; ++i) {
+    if (row + i * static_cast<std::int64_t>(gridDim.x) < m) copy_row(row + i * static_cast<std::int64_t>(gridDim.x), i);
+    cp_async_commit();
+  }
+  for (int it = 0; row < m; row += gridDim.x, ++it) {
+    const int st = it % kStages;
+    const std::int64_t ahead = row + (kStages - 1) * static_cast<std::int64_t>(gridDim.x);
+    if (ahead < m) copy_row(ahead, (it + kStages - 1) % kStages);
+    cp_async_commit();
+    cp_async_wait<kStages - 1>();
+
+    // The raw words of a pair slot: [0, 8) group 2P, [8, 16) group 2P + 1; zeros for a group past the row's end.
+    const auto fetch = [&](int p, u32(&w)[16]) {
+#pragma unroll
+      for (int gi = 0; gi < 2; ++gi) {
+        const bool on = 2 * (half_id + p * halves) + gi < groups;
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        const uint4 lo = on ? *staged(st, p, 2 * gi) : zero, hi = on ? *staged(st, p, 2 * gi + 1) : zero;
+        w[8 * gi + 0] = lo.x, w[8 * gi + 1] = lo.y, w[8 * gi + 2] = lo.z, w[8 * gi + 3] = lo.w;
+        w[8 * gi + 4] = hi.x, w[8 * gi + 5] = hi.y, w[8 * gi + 6] = hi.z, w[8 * gi + 7] = hi.w;
+      }
+    };
+
+    float inv_rms = 0.f;
+    if constexpr (kNorm) {
+      if (kPairs == 1 && a.k <= kNormSmemMaxK) {
+        // Torch's 4 * bw accumulator chains, one per thread, read from the staged row (so every thread's copies have to
+        // be visible first). Chain (t, c) = torch thread t's accumulator c: elements 4 * (t + bw * i) + c, i = 0, 1, ...
+        // in order. Element e sits in the copy of lane (e % 256) / 16 of the half-warp that owns pair e / 512.
+        __syncthreads();
+        const unsigned short* staged_row = reinterpret_cast<const unsigned short*>(stages + st * stage_vecs);
+        // Element e: lane (e % 256) / 16 of half-warp e / 512, vector (e / 256 % 2) * 2 + (e / 8 % 2) (one pair slot).
+        const auto square_at = [&](int e) {
+          const int owner = ((e >> 9) << 4) + ((e >> 4) & 15), vec = ((e >> 8) & 1) * 2 + ((e >> 3) & 1);
+          const float x = __uint_as_float(static_cast<u32>(staged_row[(vec * nthreads + owner) * 8 + (e & 7)]) << 16);
+          return fmul(x, x);
+        };
+        const int chains = 4 * a.bw;
+        for (int ct = tid; ct < chains; ct += nthreads) {
+          float acc = 0.f;
+          if (a.bw == 32) {
+            // 128 chains: term i of chain ct is element ct + 128 i, i.e. lane (ct / 16) % 8 + 8 (i % 2) of half-warp
+            // i / 4, group (i / 2) % 2 of its pair: four terms per half-warp, at fixed offsets from a moving base.
+            const unsigned short* p0 = staged_row + ((((ct >> 3) & 1) * nthreads + ((ct >> 4) & 7)) * 8 + (ct & 7));
+            const unsigned short* p1 = p0 + 2 * nthreads * 8;
+            const auto sq = [](unsigned short bits) {
+              const float x = __uint_as_float(static_cast<u32>(bits) << 16);
+              return fmul(x, x);
+            };
+            const int terms = a.k >> 7;
+            int i = 0;
+#pragma unroll 2
+            for (; i + 4 <= terms; i += 4, p0 += 128, p1 += 128) {
+              const float t0 = sq(p0[0]), t1 = sq(p0[64]), t2 = sq(p1[0]), t3 = sq(p1[64]);
+              acc = fadd(fadd(fadd(fadd(acc, t0), t1), t2), t3);
+            }
+            if (i < terms) acc = fadd(fadd(acc, sq(p0[0])), sq(p0[64]));
+          } else {
+            int e = ct;
+            for (; e + 7 * chains < a.k; e += 8 * chains) {
+              float t[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) t[i] = square_at(e + i * chains);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc = fadd(acc, t[i]);
+            }
+            for (; e < a.k; e += chains) acc = fadd(acc, square_at(e));
+          }
+          const float a1 = __shfl_down_sync(0xffffffffu, acc, 1), a2 = __shfl_down_sync(0xffffffffu, acc, 2);
+          const float a3 = __shfl_down_sync(0xffffffffu, acc, 3);
+          if ((ct & 3) == 0) s_part[ct >> 2] = fadd(fadd(fadd(acc, a1), a2), a3);
+        }
+        __syncthreads();
+        // Torch's tree over its bw partial sums: with 32 of them (every row count from 16 up) each warp runs the shuffle
+        // steps for itself; more (fewer than 16 rows) first fold in shared memory, by one warp.
+        if (a.bw == 32) {
+          float ss = s_part[lane];
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) ss = fadd(ss, __shfl_down_sync(0xffffffffu, ss, off));
+          inv_rms = rsqrtf(fadd(fmul(__shfl_sync(0xffffffffu, ss, 0), a.factor), 1e-6f));
+        } else {
+          if (warp == 0) {
+            for (int off = a.bw / 2; off >= 32; off >>= 1) {
+              for (int t = lane; t < off; t += 32) s_part[t] = fadd(s_part[t], s_part[t + off]);
+              __syncwarp();
+            }
+            float ss = s_part[lane];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) ss = fadd(ss, __shfl_down_sync(0xffffffffu, ss, off));
+            if (lane == 0) s_inv_rms = rsqrtf(fadd(fmul(ss, a.factor), 1e-6f));
+          }
+          __syncthreads();
+          inv_rms = s_inv_rms;
+        }
       } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[s][j] = 0.f;
+        if (warp == 0) {
+          const float ss = torch_order_sum_squares(a.x + row * a.ldx, a.k, a.bw, s_part, lane);
+          if (lane == 0) s_inv_rms = rsqrtf(fadd(fmul(ss, a.factor), 1e-6f));
+        }
+        __syncthreads();
+        inv_rms = s_inv_rms;
       }
     }
-  };
-  load_row();
 
-  if constexpr (kNorm) {
-    if constexpr (kSlots == 1) {
-      // The squares go through shared memory (the transpose tiles, not yet in use, hold a whole row when every half-warp
-      // has one group), so that torch's 4 * bw accumulator chains run on as many threads instead of on one warp.
-      float* sq = smem_f;
-      if (half_id < groups) {
-        float4* dst = reinterpret_cast<float4*>(sq + half_id * kGroup + 16 * h);
+    // The norm + modulate prologue on the raw words of one group (a no-op without it); `store_y` also writes the
+    // optional bf16 copy. bf16(bf16(bf16(bf16(x*r)*w) * bf16(1+scale)) + shift): after the first rounding every operand
+    // is a bf16 value, so the three remaining steps run on packed pairs (mul.rn / add.rn.bf16x2 round once, exactly as
+    // the fp32 operation followed by a rounding to bf16 does for bf16 operands).
+    const auto prologue = [&](u32* w, int g, bool store_y) {
+      if constexpr (kNorm) {
+        if (g >= groups) return;
+        const float r = inv_rms;
+        const int c0 = g * kGroup + 16 * h;
+        u32 nw[8], sc[8], sh[8];
+        load16_packed(a.weight + c0, nw);
+        load16_packed(a.mod_scale + c0, sc);
+        load16_packed(a.mod_shift + c0, sh);
 #pragma unroll
-        for (int j = 0; j < 16; j += 4) {
-          dst[j >> 2] = make_float4(fmul(v[0][j], v[0][j]), fmul(v[0][j + 1], v[0][j + 1]), fmul(v[0][j + 2], v[0][j + 2]),
-                                    fmul(v[0][j + 3], v[0][j + 3]));
+        for (int i = 0; i < 8; ++i) {
+          u32 n = pack_bf16(fmul(bf_lo(w[i]), r), fmul(bf_hi(w[i]), r));
+          n = bmul2(n, nw[i]);
+          n = bmul2(n, badd2(0x3F803F80u, sc[i]));  // 1.0 in both halves
+          w[i] = badd2(n, sh[i]);
+        }
+        if (store_y && a.y != nullptr) {
+          uint4* dst = reinterpret_cast<uint4*>(a.y + row * a.ldy + c0);
+          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
         }
       }
+    };
+
+    // The rotation, the rounding to bf16 and the row's absolute maximum. kExact = false is the fast form: no factor 0.5
+    // in the butterflies, so the rotated values (and the maximum) are 16 times the reference's, bit for bit, provided
+    // nothing overflowed on the way; its maximum propagates NaN (a NaN's bf16 pattern, sign cleared, is above every
+    // number's), so that an overflow (which always ends in an inf or a NaN) or a non-finite input shows in it.
+    // kExact = true follows the reference literally (fmaxf, which skips NaN). Returns the maximum as bf16 bits.
+    u32 rot[kPairs][16];
+    const auto rotate = [&](auto exact_tag, bool store_y, int slot) -> u32 {
+      constexpr bool kExact = decltype(exact_tag)::value;
+      u32 amax2 = 0;
+#pragma unroll
+      for (int p = 0; p < kPairs; ++p) {
+        // Warp-uniform: both halves of a warp transpose together (an idle half runs on zeros).
+        if (2 * ((half_id & ~1) + p * halves) >= groups) continue;
+        u32 w[16];
+        fetch(p, w);
+        prologue(w, 2 * (half_id + p * halves), store_y);
+        prologue(w + 8, 2 * (half_id + p * halves) + 1, store_y);
+        u64 v[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[2 * i] = pack2(bf_lo(w[i]), bf_lo(w[8 + i]));
+          v[2 * i + 1] = pack2(bf_hi(w[i]), bf_hi(w[8 + i]));
+        }
+        stages_on_registers<kExact>(v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) tile[h * kTileStride + j] = v[j];
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = tile[j * kTileStride + h];
+        __syncwarp();
+        stages_on_registers<kExact>(v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float lo, hi;
+          unpack2(v[j], lo, hi);
+          const u32 r = pack_bf16(lo, hi);
+          rot[p][j] = r;
+          u32 mag = r & 0x7FFF7FFFu;
+          if constexpr (kExact) {
+            if ((mag & 0xFFFFu) > 0x7F80u) mag &= 0xFFFF0000u;
+            if ((mag >> 16) > 0x7F80u) mag &= 0x0000FFFFu;
+          }
+          amax2 = __vmaxu2(amax2, mag);
+        }
+      }
+      // A group past the row's end contributed zeros.
+      u32 amax = max(amax2 & 0xFFFFu, amax2 >> 16);
+      amax = __reduce_max_sync(0xffffffffu, amax);
+      if (lane == 0) s_warp_max[slot][warp] = amax;
       __syncthreads();
-      // Chain (t, c) = torch thread t's accumulator c: elements 4 * (t + bw * i) + c, i = 0, 1, ... in order.
-      for (int ct = tid; ct < 4 * a.bw; ct += static_cast<int>(blockDim.x)) {
-        float acc = 0.f;
-        for (int e = ct; e < a.k; e += 4 * a.bw) acc = fadd(acc, sq[e]);
-        const float a1 = __shfl_down_sync(0xffffffffu, acc, 1), a2 = __shfl_down_sync(0xffffffffu, acc, 2);
-        const float a3 = __shfl_down_sync(0xffffffffu, acc, 3);
-        if ((ct & 3) == 0) s_part[ct >> 2] = fadd(fadd(fadd(acc, a1), a2), a3);
-      }
-      __syncthreads();
-      if (warp == 0) {
-        for (int off = a.bw / 2; off >= 32; off >>= 1) {
-          for (int t = lane; t < off; t += 32) s_part[t] = fadd(s_part[t], s_part[t + off]);
-          __syncwarp();
-        }
-        float ss = s_part[lane];
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) ss = fadd(ss, __shfl_down_sync(0xffffffffu, ss, off));
-        if (lane == 0) s_inv_rms = rsqrtf(fadd(fmul(ss, a.factor), 1e-6f));
-      }
-    } else if (warp == 0) {
-      const float ss = torch_order_sum_squares(xr, a.k, a.bw, s_part, lane);
-      if (lane == 0) s_inv_rms = rsqrtf(fadd(fmul(ss, a.factor), 1e-6f));
+      return __reduce_max_sync(0xffffffffu, s_warp_max[slot][lane < nwarps ? lane : 0]);
+    };
+    const u32 amax_bits = rotate(std::false_type{}, true, 2 * (it & 1));
+    float amax, unscale = 0.0625f;           // the rotated values in registers are 16 x the reference's
+    const bool clean = amax_bits < 0x7E80u;  // below 2^126: no overflow, NaN or inf anywhere (the same in every thread)
+    if (clean) {
+      amax = fmul(__uint_as_float(amax_bits << 16), 0.0625f);
+    } else {
+      amax = __uint_as_float(rotate(std::true_type{}, false, 2 * (it & 1) + 1) << 16);
+      unscale = 1.0f;
     }
-    __syncthreads();
-  }
-  // The norm + modulate prologue on the registers (a no-op without it); `store_y` also writes the optional bf16 copy.
-  const auto prologue = [&](bool store_y) {
-    if constexpr (!kNorm) return;
-    const float r = s_inv_rms;
-#pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-      const int g = half_id + s * halves;
-      if (g >= groups) continue;
-      const int c0 = g * kGroup + 16 * h;
-      // bf16(bf16(bf16(bf16(x*r)*w) * bf16(1+scale)) + shift). After the first rounding every operand is a bf16 value, so
-      // the three remaining steps run on packed pairs (mul.rn / add.rn.bf16x2 round once, exactly as the fp32 operation
-      // followed by a rounding to bf16 does for bf16 operands).
-      std::uint32_t w[8], sc[8], sh[8];
-      load16_packed(a.weight + c0, w);
-      load16_packed(a.mod_scale + c0, sc);
-      load16_packed(a.mod_shift + c0, sh);
-#pragma unroll
-      for (int j = 0; j < 16; j += 2) {
-        const __nv_bfloat162 n0 = __floats2bfloat162_rn(fmul(v[s][j], r), fmul(v[s][j + 1], r));
-        std::uint32_t n = *reinterpret_cast<const std::uint32_t*>(&n0);
-        n = bmul2(n, w[j >> 1]);
-        n = bmul2(n, badd2(0x3F803F80u, sc[j >> 1]));  // 1.0 in both halves
-        n = badd2(n, sh[j >> 1]);
-        v[s][j] = __uint_as_float(n << 16);
-        v[s][j + 1] = __uint_as_float(n & 0xFFFF0000u);
-      }
-      if (store_y && a.y != nullptr) store16_bf16(a.y + row * a.ldy + c0, v[s]);
-    }
-  };
-  prologue(true);
 
-  // The rotation, the rounding to bf16 and the row's absolute maximum. kExact = false is the fast form: no factor 0.5 in
-  // the butterflies, so the rotated values (and the maximum) are 16 times the reference's, bit for bit, provided nothing
-  // overflowed on the way; its maximum propagates NaN, so that an overflow (which always ends in an inf or a NaN) or a
-  // non-finite input shows in it. kExact = true follows the reference literally (fmaxf, which skips NaN).
-  const auto rotate = [&](auto exact_tag, int slot) -> float {
-    constexpr bool kExact = decltype(exact_tag)::value;
-    float amax = 0.f;
+    float s_bf;
+    if constexpr (kInt4) {
+      const float amax_bf = rbf(fmaxf(fminf(amax, kBf16Max), 1e-10f));
+      s_bf = rbf(fmul(amax_bf, 1.0f / 7.0f));
+      if (tid == 0) a.scale[row] = s_bf;
+    } else {
+      const float s = fmaxf(fmul(fminf(amax, kBf16Max), 1.0f / 127.0f), 1e-30f);
+      if (tid == 0) a.scale[row] = s;
+      s_bf = rbf(s);
+    }
+    // x_rot * (1 / s) with x_rot = unscale * (register value): the power of two moves into the reciprocal, exactly.
+    const float inv_s = fmul(__frcp_rn(s_bf), unscale);
+    const u64 inv_s2 = pack2(inv_s, inv_s);
+    constexpr float kLo = kInt4 ? -7.f : -128.f, kHi = kInt4 ? 7.f : 127.f;
+    std::uint8_t* qr = static_cast<std::uint8_t*>(a.q) + row * a.ldq;
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-      // Warp-uniform: both halves of a warp transpose together (an idle half runs on zeros).
-      if ((half_id & ~1) + s * halves >= groups) continue;
-      stages_on_registers<kExact>(v[s]);
+    for (int p = 0; p < kPairs; ++p) {
+      if (2 * ((half_id & ~1) + p * halves) >= groups) continue;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) tile[h * kTileStride + j] = v[s][j];
+      for (int j = 0; j < 16; ++j) {
+        float x0, x1;
+        unpack2(mul2(pack2(bf_lo(rot[p][j]), bf_hi(rot[p][j])), inv_s2), x0, x1);
+        const u32 r = pack_bf16(x0, x1);
+        x0 = bf_lo(r), x1 = bf_hi(r);
+        u32 b0, b1;
+        if (!kInt4 && clean) {
+          // A clean row holds finite values of magnitude up to 127.5 (the scale is the row maximum / 127, rounded to
+          // bf16), so only the upper clamp can act.
+          unpack2(add2(pack2(fminf(kHi, x0), fminf(kHi, x1)), pack2(12582912.0f, 12582912.0f)), x0, x1);
+          b0 = __float_as_uint(x0), b1 = __float_as_uint(x1);
+        } else {
+          // Clamp, then round to nearest even: the bounds are integers, so this equals rounding first. fmaxf sends NaN
+          // to the lower bound, infinities saturate. Adding 1.5 * 2^23 rounds to an integer (ties to even) and leaves
+          // its two's complement in the low mantissa bits, whose low byte is the code.
+          b0 = __float_as_uint(fadd(fminf(kHi, fmaxf(kLo, x0)), 12582912.0f));
+          b1 = __float_as_uint(fadd(fminf(kHi, fmaxf(kLo, x1)), 12582912.0f));
+        }
+        // Both groups' codes of element h + 16 j as one 16-bit store (group 2P in the low byte).
+        reinterpret_cast<unsigned short*>(qtile)[h + 16 * j] = static_cast<unsigned short>(__byte_perm(b0, b1, 0x0040));
+      }
       __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 16; ++j) v[s][j] = tile[j * kTileStride + h];
+      // Elements 16 h .. 16 h + 15 of both groups, interleaved; split them into 16 bytes per group.
+      const uint4 mixed[2] = {reinterpret_cast<const uint4*>(qtile)[2 * h], reinterpret_cast<const uint4*>(qtile)[2 * h + 1]};
       __syncwarp();
-      stages_on_registers<kExact>(v[s]);
-      if (half_id + s * halves < groups) {
+      const uint4 bytes[2] = {
+          make_uint4(__byte_perm(mixed[0].x, mixed[0].y, 0x6420), __byte_perm(mixed[0].z, mixed[0].w, 0x6420),
+                     __byte_perm(mixed[1].x, mixed[1].y, 0x6420), __byte_perm(mixed[1].z, mixed[1].w, 0x6420)),
+          make_uint4(__byte_perm(mixed[0].x, mixed[0].y, 0x7531), __byte_perm(mixed[0].z, mixed[0].w, 0x7531),
+                     __byte_perm(mixed[1].x, mixed[1].y, 0x7531), __byte_perm(mixed[1].z, mixed[1].w, 0x7531))};
 #pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-          rbf2(v[s][j], v[s][j + 1]);
-          if constexpr (kExact) amax = fmaxf(amax, fmaxf(fabsf(v[s][j]), fabsf(v[s][j + 1])));
-          else amax = max3_abs_nan(amax, v[s][j], v[s][j + 1]);
+      for (int gi = 0; gi < 2; ++gi) {
+        const int g = 2 * (half_id + p * halves) + gi;
+        if (g >= groups) continue;
+        if constexpr (kInt4) {
+          const u32 w[4] = {bytes[gi].x, bytes[gi].y, bytes[gi].z, bytes[gi].w};
+          u32 out[2];
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const u32 lo = w[2 * i], hi = w[2 * i + 1];
+            // bytes b0..b3 -> nibbles (b0 | b1 << 4), (b2 | b3 << 4)
+            const u32 p0 = (lo & 0xF) | ((lo >> 4) & 0xF0), p1 = ((lo >> 16) & 0xF) | ((lo >> 20) & 0xF0);
+            const u32 p2 = (hi & 0xF) | ((hi >> 4) & 0xF0), p3 = ((hi >> 16) & 0xF) | ((hi >> 20) & 0xF0);
+            out[i] = p0 | (p1 << 8) | (p2 << 16) | (p3 << 24);
+          }
+          *reinterpret_cast<uint2*>(qr + g * (kGroup / 2) + 8 * h) = make_uint2(out[0], out[1]);
+        } else {
+          *reinterpret_cast<uint4*>(qr + g * kGroup + 16 * h) = bytes[gi];
         }
       }
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      const float o = __shfl_xor_sync(0xffffffffu, amax, off);
-      amax = kExact ? fmaxf(amax, o) : max_nan(amax, o);
-    }
-    if (lane == 0) s_warp_max[slot][warp] = amax;
-    __syncthreads();
-    amax = s_warp_max[slot][0];
-    for (int w = 1; w < (static_cast<int>(blockDim.x) >> 5); ++w) {
-      amax = kExact ? fmaxf(amax, s_warp_max[slot][w]) : max_nan(amax, s_warp_max[slot][w]);
-    }
-    return amax;
-  };
-  float amax = rotate(std::false_type{}, 0);
-  float unscale = 0.0625f;  // the rotated values in registers are 16 x the reference's
-  if (!(amax < 8.5e37f)) {  // 2^126: an overflow, a NaN or an inf somewhere (same answer in every thread of the row)
-    load_row();
-    prologue(false);
-    amax = rotate(std::true_type{}, 1);
-    unscale = 1.0f;
-  } else {
-    amax = fmul(amax, 0.0625f);
   }
-
-  float s_bf;
-  if constexpr (kInt4) {
-    const float amax_bf = rbf(fmaxf(fminf(amax, kBf16Max), 1e-10f));
-    s_bf = rbf(fmul(amax_bf, 1.0f / 7.0f));
-    if (tid == 0) a.scale[row] = s_bf;
-  } else {
-    const float s = fmaxf(fmul(fminf(amax, kBf16Max), 1.0f / 127.0f), 1e-30f);
-    if (tid == 0) a.scale[row] = s;
-    s_bf = rbf(s);
-  }
-  // x_rot * (1 / s) with x_rot = unscale * (register value): the power of two moves into the reciprocal, exactly.
-  const float inv_s = fmul(__frcp_rn(s_bf), unscale);
-  constexpr float kLo = kInt4 ? -7.f : -128.f, kHi = kInt4 ? 7.f : 127.f;
-  std::uint8_t* qr = static_cast<std::uint8_t*>(a.q) + row * a.ldq;
-#pragma unroll
-  for (int s = 0; s < kSlots; ++s) {
-    if ((half_id & ~1) + s * halves >= groups) continue;
-#pragma unroll
-    for (int j = 0; j < 16; j += 2) {
-      // Clamp, then round to nearest even: the bounds are integers, so this equals rounding first. fmaxf sends NaN to
-      // the lower bound, infinities saturate. Adding 1.5 * 2^23 rounds to an integer (ties to even) and leaves its two's
-      // complement in the low mantissa bits, whose low byte is the int8 code.
-      float a = fmul(v[s][j], inv_s), b = fmul(v[s][j + 1], inv_s);
-      rbf2(a, b);
-      a = fadd(fminf(kHi, fmaxf(kLo, a)), 12582912.0f);
-      b = fadd(fminf(kHi, fmaxf(kLo, b)), 12582912.0f);
-      qtile[h + 16 * j] = static_cast<std::uint8_t>(__float_as_uint(a));
-      qtile[h + 16 * (j + 1)] = static_cast<std::uint8_t>(__float_as_uint(b));
-    }
-    __syncwarp();
-    const uint4 bytes = *reinterpret_cast<const uint4*>(qtile + 16 * h);
-    __syncwarp();
-    const int g = half_id + s * halves;
-    if (g < groups) {
-      if constexpr (kInt4) {
-        const std::uint32_t w[4] = {bytes.x, bytes.y, bytes.z, bytes.w};
-        std::uint32_t out[2];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const std::uint32_t lo = w[2 * i], hi = w[2 * i + 1];
-          // bytes b0..b3 -> nibbles (b0 | b1 << 4), (b2 | b3 << 4)
-          const std::uint32_t p0 = (lo & 0xF) | ((lo >> 4) & 0xF0), p1 = ((lo >> 16) & 0xF) | ((lo >> 20) & 0xF0);
-          const std::uint32_t p2 = (hi & 0xF) | ((hi >> 4) & 0xF0), p3 = ((hi >> 16) & 0xF) | ((hi >> 20) & 0xF0);
-          out[i] = p0 | (p1 << 8) | (p2 << 16) | (p3 << 24);
-        }
-        *reinterpret_cast<uint2*>(qr + g * (kGroup / 2) + 8 * h) = make_uint2(out[0], out[1]);
-      } else {
-        *reinterpret_cast<uint4*>(qr + g * kGroup + 16 * h) = bytes;
-      }
-    }
-  }
+  cp_async_wait<0>();
 }
 
 int torch_reduce_threads(std::int64_t rows, std::int64_t d) {
@@ -376,25 +500,38 @@ int torch_reduce_threads(std::int64_t rows, std::int64_t d) {
   return static_cast<int>(bw);
 }
 
+// Thread blocks of one shape that fit on an SM: asked of the runtime once per shape and device.
+template <int kPairs, bool kNorm, bool kInt4>
+int launch_shape(const char* op, const Args& a, std::int64_t m, int threads, std::size_t smem, cudaStream_t stream) {
+  static std::atomic<int> resident[64][17];  // [device][warps per block]
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const auto kernel = rotate_quantize_kernel<kPairs, kNorm, kInt4>;
+  std::atomic<int>& slot = resident[dev & 63][threads >> 5];
+  int per_sm = slot.load(std::memory_order_acquire);
+  if (per_sm == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem);
+    if (e != cudaSuccess) return fail_cuda(op, e);
+    if (per_sm < 1) return fail_invalid(op, "the kernel does not fit on an SM for k = " + std::to_string(a.k));
+    slot.store(per_sm, std::memory_order_release);
+  }
+  const std::int64_t blocks = std::min<std::int64_t>(m, static_cast<std::int64_t>(sm_count()) * per_sm);
+  kernel<<<static_cast<unsigned>(blocks), static_cast<unsigned>(threads), smem, stream>>>(a, static_cast<int>(m));
+  return check_launch(op);
+}
+
 template <bool kNorm, bool kInt4>
 int launch(const char* op, const Args& a, std::int64_t m, cudaStream_t stream) {
-  const int groups = a.k / kGroup;
-  // Groups per half-warp so that a row needs at most 16 half-warps when one slot suffices, else up to 32.
-  int slots = 1;
-  while (slots < 4 && (groups + slots - 1) / slots > (slots == 1 ? 16 : 32)) slots *= 2;
-  if (groups == 48) slots = 3;  // k = 12288: 16 half-warps x 3
-  int halves = (groups + slots - 1) / slots;
+  const int groups = a.k / kGroup, pairs = (groups + 1) / 2;
+  // One pair of groups per half-warp up to 24 half-warps (k = 12288), two up to 32 (k = 32768).
+  const int slots = pairs <= 24 ? 1 : 2;
+  int halves = (pairs + slots - 1) / slots;
   halves = (halves + 1) & ~1;
-  const unsigned threads = static_cast<unsigned>(halves * 16);
-  const std::size_t smem = static_cast<std::size_t>(halves) * (kTileFloats * sizeof(float) + kGroup);
-  const dim3 grid(static_cast<unsigned>(m));
-  switch (slots) {
-    case 1: rotate_quantize_kernel<1, kNorm, kInt4><<<grid, threads, smem, stream>>>(a); break;
-    case 2: rotate_quantize_kernel<2, kNorm, kInt4><<<grid, threads, smem, stream>>>(a); break;
-    case 3: rotate_quantize_kernel<3, kNorm, kInt4><<<grid, threads, smem, stream>>>(a); break;
-    default: rotate_quantize_kernel<4, kNorm, kInt4><<<grid, threads, smem, stream>>>(a); break;
-  }
-  return check_launch(op);
+  const int threads = halves * 16;
+  std::size_t smem = static_cast<std::size_t>(kStages) * slots * 4 * threads * 16 + static_cast<std::size_t>(halves) * kTileWords * 8;
+  if (slots == 1) return launch_shape<1, kNorm, kInt4>(op, a, m, threads, smem, stream);
+  return launch_shape<2, kNorm, kInt4>(op, a, m, threads, smem, stream);
 }
 
 int check_common(const char* op, const void* x, std::int64_t ldx, const void* q, std::int64_t ldq, const float* scale,
