@@ -341,6 +341,40 @@ def single_gpu_step_ms(torch, ops, synth, seq_lens, blocks, F, steps, warmup, ti
     return e0.elapsed_time(e1) / steps
 
 
+def forward_shell_ms(torch, ops, synth, grid, text_len, rows, blocks, F, steps):
+    """ms per call of the whole forward (b2_dit_forward: modulation vectors from the time vector, video embedding, RoPE
+    tables, the block loop, head) on `rows` sequences of grid x grid video tokens + text_len text tokens, launched
+    eagerly (no graph), and the same call with zero blocks: the shell's own cost."""
+    import numpy as np
+    bws, keep = [], []
+    for b in range(blocks):
+        w = synth.block_weights(D, F, 3000 + 100 * b)
+        keep.append(w)
+        bws.append(ops.BlockWeights(w["norm1"], w["norm2"], w["q_norm"], w["k_norm"], w["qkv"], w["o"], w["up_gate"], w["down"]))
+    g = torch.Generator(device="cuda").manual_seed(77)
+    t = lambda *shape, s=0.02: (torch.randn(*shape, device="cuda", generator=g) * s).to(torch.bfloat16)
+    f = lambda *shape, s=0.3: torch.randn(*shape, device="cuda", generator=g) * s
+    parts = (t(6 * D, D), f(6 * D), t(2 * D, D), f(2 * D), t(D, 128, s=0.09), t(D, s=0.1), t(D, s=0.1) + 1, t(128, D), t(128, s=0.1))
+    latents = torch.randn(1, 128, grid, grid, device="cuda", generator=g)
+    texts = [torch.randn(text_len, D, device="cuda", generator=g).to(torch.bfloat16) for _ in range(rows)]
+    tv = np.random.default_rng(5).normal(0, 1, D).astype(np.float32)
+    out = {}
+    for name, use in (("forward", bws), ("shell_only", [])):
+        model = ops.DitModel(use, F, *parts)
+        ws = None
+        for _ in range(2):
+            _, ws = ops.dit_forward(model, latents, tv, [(x, 0, 0) for x in texts], workspace=ws)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            ops.dit_forward(model, latents, tv, [(x, 0, 0) for x in texts], workspace=ws)
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = e0.elapsed_time(e1) / steps
+    return out
+
+
 def ulysses_record(torch, dist, ops, synth, args, rank, world):
     """N >= 2: the 2048^2 step (two 20480-token sequences) over all N ranks (groups x sequence parallel), the same step on
     rank 0's GPU alone, the speed-up and the exchange time the step does not hide. Every rank takes part; rank 0 returns
@@ -554,6 +588,11 @@ def main():
                 torch.cuda.empty_cache()
                 line["extra"] = {"turbo1024_ms": single_gpu_step_ms(torch, ops, synth, [seq_len] * seqs, n_blocks, F, min(args.steps, 5), 3,
                                                                     tier=ops.TIER_W4A8)}
+                torch.cuda.empty_cache()
+                # The step as a caller of the forward sees it: latents + time vector in, velocity latents out.
+                fw = forward_shell_ms(torch, ops, synth, 64, seq_len - 64 * 64, seqs, n_blocks, F, min(args.steps, 3))
+                line["extra"]["forward1024_ms"] = fw["forward"]
+                line["extra"]["forward1024_shell_only_ms"] = fw["shell_only"]
     if world > 1 and args.workload == "step1024" and not args.no_ulysses and tier == ops.TIER_INT8:
         # The headline above is image data parallel (no collective). The sequence-parallel configuration, the one with an
         # exchange step, rides along as its own record: free the headline's buffers first.

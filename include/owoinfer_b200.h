@@ -400,6 +400,97 @@ typedef struct b2_guided_step {
 } b2_guided_step;
 int b2_guided_velocity_step(const b2_guided_step* step, void* stream);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * The shell of MossDit::forward around the block loop (src/models/moss_dit/moss_dit.cpp:1181-1477).
+ * ------------------------------------------------------------------------------------------------------------- */
+
+/* moss_dit::latent_to_tokens (src/models/moss_dit/dit_kernels.h:18; dit_kernels.cu:137-158): f32 [channels, hw] ->
+ * bf16 tokens [hw, channels] (row stride ld >= channels, so a wider token matrix can be filled at a column offset). */
+int b2_latent_to_tokens(const float* latents, int channels, int64_t hw, void* tokens, int64_t ld, void* stream);
+/* moss_dit::tokens_to_latent (dit_kernels.h:22): contiguous bf16 [hw, channels] -> f32 [channels, hw]. */
+int b2_tokens_to_latent(const void* tokens, float* latents, int channels, int64_t hw, void* stream);
+/* moss_dit::linear_fp32_row (dit_kernels.h:37; dit_kernels.cu:79-93): out[r] = bf16(dot(w[r, :], x) + bias[r]) with bf16
+ * weights [n, k], fp32 x [k] and bias [n], the dot product in the reference kernel's order (one warp per row, 8 weights
+ * per lane and step, one fma per weight, butterfly of adds): same bits. k % 8 == 0; w and x 16-byte aligned. */
+int b2_linear_fp32_row(const void* w, const float* x, const float* bias, void* out, int n, int k, void* stream);
+/* kernels::rms_norm_modulate_moss (src/kernels/basic/norm.h; bits of basic/norm.cu:67-128, the prologue of
+ * b2_rms_norm_modulate_rotate_quantize without the quantiser): y = bf16(bf16(bf16(bf16(x * r) * w) * bf16(1 + scale)) +
+ * shift), r from the mean of squares in torch's order for an [m, k] input. k % 256 == 0, k <= 4096. */
+int b2_rms_norm_modulate(const void* x, int64_t ldx, const void* norm_weight, const void* mod_scale, const void* mod_shift,
+                         void* y, int64_t ldy, int64_t m, int k, void* stream);
+
+/* The official sinusoid of the timestep (moss_dit.cpp:979-985, distill.cpp:128-135): emb [256] = cos | sin of
+ * timestep * 10000^(-i/128), computed in double and rounded to fp32. Host only. */
+int b2_time_sinusoid(float timestep, float* emb);
+/* TimeEmbeddingFp32 (src/models/moss_dit/distill.h): host fp32 weights of the timestep MLP. */
+typedef struct b2_time_embedding {
+  size_t struct_size;
+  int64_t dim;      /* 3072 */
+  const float* w0;  /* [dim, 256] */
+  const float* b0;  /* [dim] */
+  const float* w2;  /* [dim, dim] */
+  const float* b2;  /* [dim] */
+} b2_time_embedding;
+/* moss_dit::time_vector_fp32 (distill.cpp:126-150): sinusoid -> linear -> SiLU -> linear on the host, each dot product
+ * accumulated in double from the bias on. About 10 ms of one core for dim 3072: cache it per timestep as the reference
+ * does (moss_dit.cpp:954-960). time: host [dim]. */
+int b2_time_vector_fp32(const b2_time_embedding* te, float timestep, float* time);
+
+/* kernels::Gemm::linear for the two bf16 linears of the shell (src/kernels/basic/gemm.h:20-63): out [m, n] = x [m, k] *
+ * w [n, k]^T (+ bias [n]), bf16 in and out, fp32 accumulation, through cuBLASLt bound at run time (libcublasLt.so.12,
+ * preferring a copy the process has already loaded; B2_ERR_NOT_SUPPORTED when none is found). As in the reference the
+ * summation order is the library's. workspace: 256-byte aligned, b2_linear_bf16_workspace_bytes() is plenty. */
+size_t b2_linear_bf16_workspace_bytes(void);
+int b2_linear_bf16(const void* x, int64_t ldx, const void* w, const void* bias, void* out, int64_t ldo, int64_t m, int n,
+                   int k, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The tensors of MossDit outside the blocks (src/models/moss_dit/moss_dit.h:395-440), device memory. */
+typedef struct b2_dit_model {
+  size_t struct_size;
+  const b2_block_weights* blocks; /* host array [num_blocks] */
+  int num_blocks;                 /* 42 */
+  int D, F, heads, latent_channels; /* 3072, 8192 | 12288, 24, 128 */
+  const void* block_mod_w;      /* bf16 [6 D, D]: the one modulation linear every block shares */
+  const float* block_mod_bias;  /* f32 [6 D] */
+  const void* head_mod_w;       /* bf16 [2 D, D] */
+  const float* head_mod_bias;   /* f32 [2 D] */
+  const void* video_w;          /* bf16 [D, 128] */
+  const void* video_bias;       /* bf16 [D] or NULL */
+  const void* final_norm;       /* bf16 [D] */
+  const void* final_w;          /* bf16 [128, D] */
+  const void* final_bias;       /* bf16 [128] or NULL */
+} b2_dit_model;
+
+/* MossDit::Row (moss_dit.h): one sequence of the forward = the video tokens of a latent followed by its text tokens. */
+typedef struct b2_forward_row {
+  const void* text;  /* device bf16 [text_len, D] */
+  int64_t text_len;  /* >= 1 */
+  uint64_t skip;     /* bit b set: the row skips block b (skip-layer guidance) */
+  int latent;        /* which latent of the batch the row reads */
+  float* out;        /* device f32 [128, height, width] */
+} b2_forward_row;
+
+typedef struct b2_forward {
+  size_t struct_size;
+  const float* latents;      /* device f32 [num_latents, 128, height, width] */
+  int num_latents, height, width;
+  const float* time_vector;  /* host f32 [D]: b2_time_vector_fp32 of the step's timestep */
+  const b2_forward_row* rows;
+  int num_rows;              /* 1..8 */
+  int tier;                  /* B2_TIER_* */
+  b2_attention_options attention;
+  void* workspace;           /* b2_dit_forward_workspace_bytes(), 256-byte aligned */
+  size_t workspace_bytes;
+} b2_forward;
+
+size_t b2_dit_forward_workspace_bytes(const b2_dit_model* model, const b2_forward* forward);
+/* MossDit::forward (moss_dit.cpp:1181-1477) for the all-quantized block path, without reference slots, input extension,
+ * step cache, LoRA or streamed weights: modulation vectors from the time vector, video embedding once per latent,
+ * per-row RoPE tables, [video | text] rows, for every block the runs of contiguous rows that do not skip it as one varlen
+ * batch each, then final norm + head modulation, head linear and the transpose back to [128, h, w] per row. Small host
+ * arrays travel as kernel parameters: the call does not synchronise and needs no pinned memory. */
+int b2_dit_forward(const b2_dit_model* model, const b2_forward* forward, void* stream);
+
 /* Every mbarrier wait inside the tensor-core kernels is bounded (200 ms); a CTA whose wait expired raises a device word,
  * drains and returns instead of hanging. This reads the two words (GEMM, attention): 0 = no wait ever expired on this device.
  * Synchronises the device; for tests and post-mortems, not for the hot path. No counterpart in the reference (its

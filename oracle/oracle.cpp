@@ -797,4 +797,56 @@ int orc_block_quant(u16* x, i64 L, int D, int F, int heads, const u16* mod, cons
   return 0;
 }
 
+// ------------------------------------------------------------------------------------------------ forward shell
+
+// moss_dit::linear_fp32_row (src/models/moss_dit/dit_kernels.cu:79-93): one "warp" per output row; lane l takes the
+// 8-weight chunks l, l + 32, ... with one fmaf per weight in column order; the 32 partial sums meet in a butterfly
+// (lane ^ 16, 8, 4, 2, 1: every lane adds its partner's value to its own); out = bf16(lane 0's sum + bias).
+void orc_linear_fp32_row(const u16* w, const float* x, const float* bias, u16* out, int n, int k) {
+  parallel_for(n, g_threads, [&](i64 begin, i64 end) {
+   for (i64 row = begin; row < end; ++row) {
+    float lane[32];
+    for (int l = 0; l < 32; ++l) {
+      float acc = 0.0f;
+      for (int i = l; i < k / 8; i += 32) {
+        for (int j = 0; j < 8; ++j) acc = std::fmaf(bf2f(w[row * k + 8 * i + j]), x[8 * i + j], acc);
+      }
+      lane[l] = acc;
+    }
+    for (int o = 16; o > 0; o /= 2) {
+      float next[32];
+      for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ o];
+      std::memcpy(lane, next, sizeof lane);
+    }
+    out[row] = f2bf(lane[0] + bias[row]);
+   }
+  });
+}
+
+// moss_dit::time_vector_fp32 (src/models/moss_dit/distill.cpp:126-150): the official sinusoid in double rounded to fp32,
+// linear (double accumulation from the bias on, rounded to fp32), SiLU in fp32, linear.
+void orc_time_vector_fp32(const float* w0, const float* b0, const float* w2, const float* b2, i64 dim, float timestep,
+                          float* emb_out, float* time) {
+  float emb[256];
+  for (int i = 0; i < 128; ++i) {
+    const double freq = std::pow(10000.0, -static_cast<double>(i) / 128);
+    const double phase = static_cast<double>(timestep) * freq;
+    emb[i] = static_cast<float>(std::cos(phase));
+    emb[128 + i] = static_cast<float>(std::sin(phase));
+  }
+  if (emb_out != nullptr) std::memcpy(emb_out, emb, sizeof emb);
+  std::vector<float> h(static_cast<std::size_t>(dim));
+  for (i64 r = 0; r < dim; ++r) {
+    double acc = b0[r];
+    for (int c = 0; c < 256; ++c) acc += static_cast<double>(w0[r * 256 + c]) * emb[c];
+    const float v = static_cast<float>(acc);
+    h[static_cast<std::size_t>(r)] = v / (1.0f + std::exp(-v));
+  }
+  for (i64 r = 0; r < dim; ++r) {
+    double acc = b2[r];
+    for (i64 c = 0; c < dim; ++c) acc += static_cast<double>(w2[r * dim + c]) * h[static_cast<std::size_t>(c)];
+    time[r] = static_cast<float>(acc);
+  }
+}
+
 }  // extern "C"

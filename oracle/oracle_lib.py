@@ -374,3 +374,35 @@ def guided_velocity(v_cond, v_uncond=None, v_skip=None, cfg_scale=0.0, slg_scale
     if v_skip is not None:
         v = slg_correct(v if v_uncond is not None else v_skip, v_cond, v_skip, slg_scale)
     return v
+
+
+# ---------------------------------------------------------------------------------------------- forward shell
+
+def linear_fp32_row(w_bits, x, bias):
+    """bf16 bits [n, k], f32 [k], f32 [n] -> bf16 bits [n], in the reference kernel's order (dit_kernels.cu:79-93)."""
+    w = _c(w_bits, np.uint16)
+    n, k = w.shape
+    out = np.empty(n, np.uint16)
+    lib().orc_linear_fp32_row(_p(w), _p(_c(x, np.float32)), _p(_c(bias, np.float32)), _p(out), i32(n), i32(k))
+    return out
+
+
+def time_vector_fp32(w0, b0, w2, b2, timestep):
+    """distill.cpp:126-150. Returns (sinusoid f32 [256], time vector f32 [dim])."""
+    w0, b0, w2, b2 = (_c(a, np.float32) for a in (w0, b0, w2, b2))
+    dim = w2.shape[0]
+    emb, time = np.empty(256, np.float32), np.empty(dim, np.float32)
+    lib().orc_time_vector_fp32(_p(w0), _p(b0), _p(w2), _p(b2), i64(dim), C.c_float(timestep), _p(emb), _p(time))
+    return emb, time
+
+
+def latent_to_tokens(latents):
+    """f32 [C, hw] -> bf16 bits [hw, C] (dit_kernels.cu:19-47: transpose, round to nearest even)."""
+    v = np.ascontiguousarray(np.asarray(latents, np.float32).reshape(latents.shape[0], -1).T)
+    u = v.view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def tokens_to_latent(tokens_bits):
+    """bf16 bits [hw, C] -> f32 [C, hw]."""
+    return np.ascontiguousarray((np.asarray(tokens_bits, np.uint16).astype(np.uint32) << 16).view(np.float32).T)

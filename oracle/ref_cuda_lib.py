@@ -38,6 +38,10 @@ def lib():
             l.ref_slg_velocity.argtypes = [vp, vp, vp, f32, vp, i64, vp]
             l.ref_velocity_euler.argtypes = [vp, vp, f32, i64, vp]
             l.ref_ab2.argtypes = [vp, vp, vp, f32, f32, f32, i64, vp]
+        if hasattr(l, "ref_linear_fp32_row"):
+            l.ref_latent_to_tokens.argtypes = [vp, i64, i64, i64, vp, vp]
+            l.ref_tokens_to_latent.argtypes = [vp, i64, i64, i64, vp, vp]
+            l.ref_linear_fp32_row.argtypes = [vp, i64, i64, vp, vp, vp, vp]
         _lib = l
     return _lib
 
@@ -117,6 +121,24 @@ def velocity_euler(x, v, h):
 
 def ab2(x, v, v_prev, h, a, b):
     _ok(lib().ref_ab2(_p(x), _p(v), _p(v_prev), h, a, b, x.numel(), _stream()))
+
+
+def latent_to_tokens(latents, tokens):
+    c, h, w = latents.shape
+    _ok(lib().ref_latent_to_tokens(_p(latents), c, h, w, _p(tokens), _stream()))
+
+
+def tokens_to_latent(tokens, latents):
+    c, h, w = latents.shape
+    _ok(lib().ref_tokens_to_latent(_p(tokens), c, h, w, _p(latents), _stream()))
+
+
+def linear_fp32_row(w, x, bias, out):
+    _ok(lib().ref_linear_fp32_row(_p(w), w.shape[0], w.shape[1], _p(x), _p(bias), _p(out), _stream()))
+
+
+def has_shell_kernels() -> bool:
+    return available() and hasattr(lib(), "ref_linear_fp32_row")
 
 
 def has_sampler_kernels() -> bool:

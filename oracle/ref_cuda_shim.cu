@@ -14,6 +14,7 @@
 #include "kernels/attention_q8/q8_kernels.h"
 #include "kernels/fused/qk_norm_rope.h"
 #include "kernels/quant/quant.h"
+#include "models/moss_dit/dit_kernels.h"
 #include "pipeline/samplers/sampler_kernels.h"
 #include "kernels/sm75/int8_sm75.h"
 #include "kernels/sm75/sm75.h"
@@ -169,6 +170,26 @@ int ref_velocity_euler(float* x, const float* v, float h, std::int64_t n, cudaSt
 }
 int ref_ab2(float* x, const float* v, const float* vp, float h, float a, float b, std::int64_t n, cudaStream_t st) {
   return guarded([&] { mi::pipeline::sampler_kernels::ab2(x, v, vp, h, a, b, n, st); });
+}
+
+// The shell's exactly specified kernels (src/models/moss_dit/dit_kernels.cu): the two transposes and linear_fp32_row.
+int ref_latent_to_tokens(float* latents, std::int64_t channels, std::int64_t h, std::int64_t w, void* tokens, cudaStream_t st) {
+  return guarded([&] {
+    mi::moss_dit::latent_to_tokens(Tensor::view(latents, DType::kF32, mi::Device::kCUDA, {channels, h, w}),
+                                   Tensor::view(tokens, DType::kBF16, mi::Device::kCUDA, {h * w, channels}), st);
+  });
+}
+int ref_tokens_to_latent(void* tokens, std::int64_t channels, std::int64_t h, std::int64_t w, float* latents, cudaStream_t st) {
+  return guarded([&] {
+    mi::moss_dit::tokens_to_latent(Tensor::view(tokens, DType::kBF16, mi::Device::kCUDA, {h * w, channels}),
+                                   Tensor::view(latents, DType::kF32, mi::Device::kCUDA, {channels, h, w}), st);
+  });
+}
+int ref_linear_fp32_row(void* w, std::int64_t n, std::int64_t k, const float* x, const float* bias, void* out, cudaStream_t st) {
+  return guarded([&] {
+    mi::moss_dit::linear_fp32_row(Tensor::view(w, DType::kBF16, mi::Device::kCUDA, {n, k}), x, bias,
+                                  Tensor::view(out, DType::kBF16, mi::Device::kCUDA, {n}), st);
+  });
 }
 
 }  // extern "C"

@@ -18,6 +18,8 @@ EXPORTS = [
     "b2_kernel_status", "b2_kernel_status_clear", "b2_debug_bounded_wait", "b2_w4_invalid_scales", "b2_rotate_quantize_chunked", "b2_int8_gemm_chunked", "b2_sp_unique_id",
     "b2_sp_comm_create", "b2_sp_comm_destroy", "b2_sp_comm_local_exchange", "b2_block_quant_sp_workspace_bytes", "b2_run_block_quant_sp", "b2_dit_step_sp",
     "b2_cfg_combine", "b2_slg_correct", "b2_euler_update", "b2_ab2_update", "b2_guided_velocity_step",
+    "b2_latent_to_tokens", "b2_tokens_to_latent", "b2_linear_fp32_row", "b2_rms_norm_modulate", "b2_time_sinusoid",
+    "b2_time_vector_fp32", "b2_linear_bf16_workspace_bytes", "b2_linear_bf16", "b2_dit_forward_workspace_bytes", "b2_dit_forward",
 ]
 
 
@@ -70,6 +72,29 @@ class BlockRun(C.Structure):
                 ("attention", AttentionOptions), ("fused_norm_rope", C.c_int)]
 
 
+class TimeEmbedding(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("dim", C.c_int64), ("w0", C.c_void_p), ("b0", C.c_void_p), ("w2", C.c_void_p),
+                ("b2", C.c_void_p)]
+
+
+class DitModel(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("blocks", C.POINTER(BlockWeights)), ("num_blocks", C.c_int), ("D", C.c_int),
+                ("F", C.c_int), ("heads", C.c_int), ("latent_channels", C.c_int), ("block_mod_w", C.c_void_p),
+                ("block_mod_bias", C.c_void_p), ("head_mod_w", C.c_void_p), ("head_mod_bias", C.c_void_p),
+                ("video_w", C.c_void_p), ("video_bias", C.c_void_p), ("final_norm", C.c_void_p), ("final_w", C.c_void_p),
+                ("final_bias", C.c_void_p)]
+
+
+class ForwardRow(C.Structure):
+    _fields_ = [("text", C.c_void_p), ("text_len", C.c_int64), ("skip", C.c_uint64), ("latent", C.c_int), ("out", C.c_void_p)]
+
+
+class Forward(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("latents", C.c_void_p), ("num_latents", C.c_int), ("height", C.c_int),
+                ("width", C.c_int), ("time_vector", C.c_void_p), ("rows", C.POINTER(ForwardRow)), ("num_rows", C.c_int),
+                ("tier", C.c_int), ("attention", AttentionOptions), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
 class GuidedStep(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("x", C.c_void_p), ("v_cond", C.c_void_p), ("v_uncond", C.c_void_p),
                 ("v_skip", C.c_void_p), ("v_prev", C.c_void_p), ("v_out", C.c_void_p), ("cfg_scale", C.c_float),
@@ -98,6 +123,9 @@ def lib() -> C.CDLL:
                                                       C.c_int, C.c_int]
         l.b2_block_quant_workspace_bytes.restype = C.c_size_t
         l.b2_block_quant_workspace_bytes.argtypes = [C.POINTER(BlockRun)]
+        l.b2_linear_bf16_workspace_bytes.restype = C.c_size_t
+        l.b2_dit_forward_workspace_bytes.restype = C.c_size_t
+        l.b2_dit_forward_workspace_bytes.argtypes = [C.POINTER(DitModel), C.POINTER(Forward)]
         l.b2_block_quant_sp_workspace_bytes.restype = C.c_size_t
         l.b2_block_quant_sp_workspace_bytes.argtypes = [C.POINTER(SpRun), C.c_int]
         _lib = l

@@ -1,0 +1,486 @@
+// The shell of MossDit::forward around the quantized block loop (src/models/moss_dit/moss_dit.cpp:1181-1477): the
+// time embedding and the modulation vectors (:949-969, the fp32 form the published files use), the video embedder
+// (:1100-1118), the per-row RoPE tables and joint inputs (:1330-1366), the runs of rows that execute each block with
+// their zero-based cu_seqlens (:1262-1318, without reference slots), the block loop, and the head (:1468-1476).
+// Everything outside the two bf16 linears (embedder 128 -> 3072, head 3072 -> 128: plain library GEMMs, cuBLASLt bound at
+// run time like the reference's, src/kernels/basic/gemm.h:20-63) is specified to the bit by the reference's own kernels
+// and restated here: the transposes (dit_kernels.cu:19-47), linear_fp32_row (:79-93), the head's RMSNorm + modulate
+// (the norm prologue of the activation quantiser) and the host-side time vector (distill.cpp:126-150).
+#include <cublasLt.h>
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace b2 {
+namespace {
+
+constexpr int kTile = 32;
+constexpr int kFreq = 256;
+constexpr std::size_t kLtWorkspaceBytes = std::size_t{4} << 20;
+constexpr int kParamWords = 1000;  // 32-bit words a launch carries by value (kernel parameters hold 4 KB)
+
+// Small host arrays reach the device as kernel parameters (copied at launch: no pinned staging buffer, nothing the
+// caller must keep alive, capturable), as the reference's write_params does (dit_kernels.cu:121-123).
+struct ParamWords {
+  std::uint32_t words[kParamWords];
+};
+__global__ void write_words_kernel(std::uint32_t* dst, const ParamWords p, int n) {
+  for (int i = static_cast<int>(threadIdx.x); i < n; i += static_cast<int>(blockDim.x)) dst[i] = p.words[i];
+}
+int write_words(const char* op, void* dst, const void* src, std::size_t words, cudaStream_t stream) {
+  const std::uint32_t* from = static_cast<const std::uint32_t*>(src);
+  for (std::size_t at = 0; at < words; at += kParamWords) {
+    const int n = static_cast<int>(std::min<std::size_t>(kParamWords, words - at));
+    ParamWords p;
+    std::memcpy(p.words, from + at, static_cast<std::size_t>(n) * 4);
+    write_words_kernel<<<1, 256, 0, stream>>>(static_cast<std::uint32_t*>(dst) + at, p, n);
+    if (const int rc = check_launch(op)) return rc;
+  }
+  return B2_OK;
+}
+
+// out[c * ld + r] = convert(in[r * cols + c]): a [rows, cols] row-major matrix transposed through a padded shared tile,
+// f32 -> bf16 (round to nearest even) or bf16 -> f32.
+template <typename In, typename Out>
+__global__ void __launch_bounds__(kTile * 8) transpose_kernel(const In* in, Out* out, std::int64_t rows, std::int64_t cols, std::int64_t ld) {
+  __shared__ float tile[kTile][kTile + 1];
+  const std::int64_t r0 = static_cast<std::int64_t>(blockIdx.y) * kTile, c0 = static_cast<std::int64_t>(blockIdx.x) * kTile;
+  const int tx = static_cast<int>(threadIdx.x);
+  for (int i = static_cast<int>(threadIdx.y); i < kTile; i += 8) {
+    const std::int64_t r = r0 + i, c = c0 + tx;
+    if (r < rows && c < cols) {
+      if constexpr (std::is_same_v<In, float>) tile[i][tx] = in[r * cols + c];
+      else tile[i][tx] = __bfloat162float(in[r * cols + c]);
+    }
+  }
+  __syncthreads();
+  for (int i = static_cast<int>(threadIdx.y); i < kTile; i += 8) {
+    const std::int64_t c = c0 + i, r = r0 + tx;
+    if (r < rows && c < cols) {
+      if constexpr (std::is_same_v<Out, float>) out[c * ld + r] = tile[tx][i];
+      else out[c * ld + r] = __float2bfloat16_rn(tile[tx][i]);
+    }
+  }
+}
+
+template <typename In, typename Out>
+int launch_transpose(const char* op, const In* in, Out* out, std::int64_t rows, std::int64_t cols, std::int64_t ld, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return B2_OK;
+  const dim3 grid(static_cast<unsigned>((cols + kTile - 1) / kTile), static_cast<unsigned>((rows + kTile - 1) / kTile));
+  transpose_kernel<In, Out><<<grid, dim3(kTile, 8), 0, stream>>>(in, out, rows, cols, ld);
+  return check_launch(op);
+}
+
+// One warp per output row, 8 weights per 16-byte load: lane l takes chunks l, l + 32, ... and accumulates with one fma
+// per weight in column order; the 32 partial sums meet in a butterfly of adds (offsets 16, 8, 4, 2, 1);
+// out = bf16(sum + bias). The order of every operation is the reference kernel's, so the bits are.
+__global__ void __launch_bounds__(256) linear_fp32_row_kernel(const __nv_bfloat16* w, const float* x, const float* bias,
+                                                              __nv_bfloat16* out, int n, int k) {
+  const int row = static_cast<int>(blockIdx.x) * (static_cast<int>(blockDim.x) / 32) + static_cast<int>(threadIdx.x) / 32;
+  const int lane = static_cast<int>(threadIdx.x) % 32;
+  if (row >= n) return;
+  const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<std::int64_t>(row) * k);
+  float acc = 0.0f;
+  for (int i = lane; i < k / 8; i += 32) {
+    const uint4 v = wr[i];
+    const std::uint32_t words[4] = {v.x, v.y, v.z, v.w};
+    const float4 x0 = reinterpret_cast<const float4*>(x)[2 * i], x1 = reinterpret_cast<const float4*>(x)[2 * i + 1];
+    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc = fmaf(__uint_as_float(words[j] << 16), xs[2 * j], acc);
+      acc = fmaf(__uint_as_float(words[j] & 0xFFFF0000u), xs[2 * j + 1], acc);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o /= 2) acc = fadd(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+  if (lane == 0) out[row] = __float2bfloat16_rn(fadd(acc, bias[row]));
+}
+
+// ------------------------------------------------------------------------------------------------ cuBLASLt, bound late
+
+struct LtApi {
+  cublasStatus_t (*create)(cublasLtHandle_t*);
+  cublasStatus_t (*desc_create)(cublasLtMatmulDesc_t*, cublasComputeType_t, cudaDataType_t);
+  cublasStatus_t (*desc_destroy)(cublasLtMatmulDesc_t);
+  cublasStatus_t (*desc_set)(cublasLtMatmulDesc_t, cublasLtMatmulDescAttributes_t, const void*, size_t);
+  cublasStatus_t (*layout_create)(cublasLtMatrixLayout_t*, cudaDataType, uint64_t, uint64_t, int64_t);
+  cublasStatus_t (*layout_destroy)(cublasLtMatrixLayout_t);
+  cublasStatus_t (*pref_create)(cublasLtMatmulPreference_t*);
+  cublasStatus_t (*pref_destroy)(cublasLtMatmulPreference_t);
+  cublasStatus_t (*pref_set)(cublasLtMatmulPreference_t, cublasLtMatmulPreferenceAttributes_t, const void*, size_t);
+  cublasStatus_t (*heuristic)(cublasLtHandle_t, cublasLtMatmulDesc_t, cublasLtMatrixLayout_t, cublasLtMatrixLayout_t,
+                              cublasLtMatrixLayout_t, cublasLtMatrixLayout_t, cublasLtMatmulPreference_t, int,
+                              cublasLtMatmulHeuristicResult_t*, int*);
+  cublasStatus_t (*matmul)(cublasLtHandle_t, cublasLtMatmulDesc_t, const void*, const void*, cublasLtMatrixLayout_t, const void*,
+                           cublasLtMatrixLayout_t, const void*, const void*, cublasLtMatrixLayout_t, void*,
+                           cublasLtMatrixLayout_t, const cublasLtMatmulAlgo_t*, void*, size_t, cudaStream_t);
+  bool ok = false;
+};
+
+// The library a process already holds (a Python process with torch does) comes first, then the loader's search path,
+// then the toolkit's usual place.
+const LtApi& lt() {
+  static LtApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* h = dlopen("libcublasLt.so.12", RTLD_NOW | RTLD_NOLOAD);
+    if (h == nullptr) h = dlopen("libcublasLt.so.12", RTLD_NOW);
+    if (h == nullptr) h = dlopen("/usr/local/cuda/lib64/libcublasLt.so.12", RTLD_NOW);
+    if (h == nullptr) return;
+    bool all = true;
+    const auto bind = [&](auto& fn, const char* name) {
+      fn = reinterpret_cast<std::remove_reference_t<decltype(fn)>>(dlsym(h, name));
+      all = all && fn != nullptr;
+    };
+    bind(api.create, "cublasLtCreate");
+    bind(api.desc_create, "cublasLtMatmulDescCreate");
+    bind(api.desc_destroy, "cublasLtMatmulDescDestroy");
+    bind(api.desc_set, "cublasLtMatmulDescSetAttribute");
+    bind(api.layout_create, "cublasLtMatrixLayoutCreate");
+    bind(api.layout_destroy, "cublasLtMatrixLayoutDestroy");
+    bind(api.pref_create, "cublasLtMatmulPreferenceCreate");
+    bind(api.pref_destroy, "cublasLtMatmulPreferenceDestroy");
+    bind(api.pref_set, "cublasLtMatmulPreferenceSetAttribute");
+    bind(api.heuristic, "cublasLtMatmulAlgoGetHeuristic");
+    bind(api.matmul, "cublasLtMatmul");
+    api.ok = all;
+  });
+  return api;
+}
+
+int lt_handle(cublasLtHandle_t* out) {
+  static std::mutex mu;
+  static std::map<int, cublasLtHandle_t> handles;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = handles.find(dev);
+  if (it == handles.end()) {
+    cublasLtHandle_t h = nullptr;
+    if (lt().create(&h) != CUBLAS_STATUS_SUCCESS) return fail_status(B2_ERR_NOT_SUPPORTED, "linear_bf16", "cublasLtCreate failed");
+    it = handles.emplace(dev, h).first;
+  }
+  *out = it->second;
+  return B2_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ forward: host plan
+
+struct Run {
+  int r0, r1;        // rows [r0, r1)
+  std::int64_t t0, t1;
+  int cu_at;         // index of its first entry in the cu_seqlens array
+  int max_len;
+};
+
+std::size_t align_up(std::size_t v) { return (v + 255) & ~static_cast<std::size_t>(255); }
+
+struct Carve {
+  std::size_t x, rope, mod, head, time, tokens, y, cu, lt, block, total;
+};
+
+int plan_forward(const char* op, const b2_dit_model* m, const b2_forward* f, std::vector<std::int64_t>* off, Carve* c,
+                 b2_block_run* widest) {
+  if (m == nullptr || f == nullptr || m->struct_size < sizeof(b2_dit_model) || f->struct_size < sizeof(b2_forward)) {
+    return fail_invalid(op, "null model or forward, or one from an older header");
+  }
+  if (m->blocks == nullptr || m->num_blocks < 0 || m->num_blocks > 64) return fail_invalid(op, "0..64 blocks (skip masks are 64 bits)");
+  if (m->D != 3072 || m->heads != 24 || m->latent_channels != 128) {
+    return fail_invalid(op, "the MOSS-Image DiT has D = 3072, 24 heads and 128 latent channels");
+  }
+  if (f->height < 1 || f->width < 1 || f->num_latents < 1 || f->num_rows < 1 || f->num_rows > 8 || f->rows == nullptr) {
+    return fail_invalid(op, "needs a latent grid, 1..8 rows and at least one latent");
+  }
+  const std::int64_t hw = static_cast<std::int64_t>(f->height) * f->width;
+  off->assign(1, 0);
+  int max_len = 0;
+  for (int r = 0; r < f->num_rows; ++r) {
+    const b2_forward_row& row = f->rows[r];
+    if (row.text == nullptr || row.text_len < 1 || row.out == nullptr) return fail_invalid(op, "a row needs text [S >= 1, 3072] and an output");
+    if (row.latent < 0 || row.latent >= f->num_latents) return fail_invalid(op, "a row reads a latent that is not there");
+    off->push_back(off->back() + hw + row.text_len);
+    max_len = std::max<std::int64_t>(max_len, hw + row.text_len);
+  }
+  const std::int64_t total = off->back();
+  if (total > 0x7fffffff) return fail_invalid(op, "too many joint tokens");
+  *widest = b2_block_run{};
+  widest->struct_size = sizeof(b2_block_run);
+  widest->tokens = total, widest->D = m->D, widest->F = m->F, widest->heads = m->heads, widest->batch = f->num_rows;
+  widest->max_seqlen = max_len, widest->tier = f->tier, widest->attention = f->attention, widest->fused_norm_rope = -1;
+  static const std::int32_t placeholder = 0;  // sizing reads no offsets; every run of the forward brings its own
+  widest->cu_seqlens = &placeholder;
+  const std::size_t block_bytes = b2_block_quant_workspace_bytes(widest);
+  if (block_bytes == 0) return B2_ERR_INVALID_ARGUMENT;  // the block's own message stands
+  const std::size_t D = static_cast<std::size_t>(m->D);
+  std::size_t at = 0;
+  const auto take = [&](std::size_t bytes) {
+    const std::size_t here = at;
+    at += align_up(bytes);
+    return here;
+  };
+  c->x = take(static_cast<std::size_t>(total) * D * 2);
+  c->rope = take(static_cast<std::size_t>(total) * 128 * 2);
+  c->mod = take(6 * D * 2);
+  c->head = take(2 * D * 2);
+  c->time = take(D * 4);
+  c->tokens = take(static_cast<std::size_t>(hw) * 128 * 2);
+  c->y = take(static_cast<std::size_t>(hw) * D * 2);
+  c->cu = take(static_cast<std::size_t>(f->num_rows + 1) * (f->num_rows * (f->num_rows + 1) / 2) * 4);
+  c->lt = take(kLtWorkspaceBytes);
+  c->block = take(block_bytes);
+  c->total = at;
+  return B2_OK;
+}
+
+}  // namespace
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" {
+
+int b2_latent_to_tokens(const float* latents, int channels, int64_t hw, void* tokens, int64_t ld, void* stream) {
+  constexpr const char* op = "latent_to_tokens";
+  if (channels < 0 || hw < 0 || ld < channels) return fail_invalid(op, "needs channels, hw >= 0 and ld >= channels");
+  if (channels > 0 && hw > 0 && (latents == nullptr || tokens == nullptr)) return fail_invalid(op, "null operand");
+  return launch_transpose(op, latents, static_cast<__nv_bfloat16*>(tokens), channels, hw, ld, as_stream(stream));
+}
+
+int b2_tokens_to_latent(const void* tokens, float* latents, int channels, int64_t hw, void* stream) {
+  constexpr const char* op = "tokens_to_latent";
+  if (channels < 0 || hw < 0) return fail_invalid(op, "needs channels, hw >= 0");
+  if (channels > 0 && hw > 0 && (latents == nullptr || tokens == nullptr)) return fail_invalid(op, "null operand");
+  return launch_transpose(op, static_cast<const __nv_bfloat16*>(tokens), latents, hw, channels, hw, as_stream(stream));
+}
+
+int b2_linear_fp32_row(const void* w, const float* x, const float* bias, void* out, int n, int k, void* stream) {
+  constexpr const char* op = "linear_fp32_row";
+  if (n < 0 || k <= 0 || k % 8 != 0) return fail_invalid(op, "needs n >= 0 and k a positive multiple of 8");
+  if (n == 0) return B2_OK;
+  if (w == nullptr || x == nullptr || bias == nullptr || out == nullptr || !aligned_to(w, 16) || !aligned_to(x, 16)) {
+    return fail_invalid(op, "needs a 16-byte aligned bf16 w [n, k], a 16-byte aligned f32 x [k], an f32 bias [n] and a bf16 out [n]");
+  }
+  linear_fp32_row_kernel<<<static_cast<unsigned>((n + 7) / 8), 256, 0, as_stream(stream)>>>(
+      static_cast<const __nv_bfloat16*>(w), x, bias, static_cast<__nv_bfloat16*>(out), n, k);
+  return check_launch(op);
+}
+
+int b2_time_sinusoid(float timestep, float* emb) {
+  if (emb == nullptr) return fail_invalid("time_sinusoid", "null output");
+  constexpr int kHalf = kFreq / 2;
+  for (int i = 0; i < kHalf; ++i) {
+    const double freq = std::pow(10000.0, -static_cast<double>(i) / kHalf);
+    const double phase = static_cast<double>(timestep) * freq;
+    emb[i] = static_cast<float>(std::cos(phase));
+    emb[kHalf + i] = static_cast<float>(std::sin(phase));
+  }
+  return B2_OK;
+}
+
+int b2_time_vector_fp32(const b2_time_embedding* te, float timestep, float* time) {
+  constexpr const char* op = "time_vector_fp32";
+  if (te == nullptr || te->struct_size < sizeof(b2_time_embedding) || time == nullptr) return fail_invalid(op, "null argument");
+  if (te->w0 == nullptr || te->b0 == nullptr || te->w2 == nullptr || te->b2 == nullptr || te->dim < 1) {
+    return fail_invalid(op, "needs w0 [dim, 256], b0 [dim], w2 [dim, dim], b2 [dim] on the host");
+  }
+  float emb[kFreq];
+  b2_time_sinusoid(timestep, emb);
+  const std::int64_t dim = te->dim;
+  std::vector<float> h(static_cast<std::size_t>(dim));
+  for (std::int64_t r = 0; r < dim; ++r) {
+    double acc = te->b0[r];
+    const float* w = te->w0 + r * kFreq;
+    for (int c = 0; c < kFreq; ++c) acc += static_cast<double>(w[c]) * emb[c];
+    const float v = static_cast<float>(acc);
+    h[static_cast<std::size_t>(r)] = v / (1.0f + std::exp(-v));  // silu
+  }
+  for (std::int64_t r = 0; r < dim; ++r) {
+    double acc = te->b2[r];
+    const float* w = te->w2 + r * dim;
+    for (std::int64_t c = 0; c < dim; ++c) acc += static_cast<double>(w[c]) * h[static_cast<std::size_t>(c)];
+    time[r] = static_cast<float>(acc);
+  }
+  return B2_OK;
+}
+
+size_t b2_linear_bf16_workspace_bytes(void) { return kLtWorkspaceBytes; }
+
+int b2_linear_bf16(const void* x, int64_t ldx, const void* w, const void* bias, void* out, int64_t ldo, int64_t m, int n,
+                   int k, void* workspace, size_t workspace_bytes, void* stream) {
+  constexpr const char* op = "linear_bf16";
+  if (m < 0 || n <= 0 || k <= 0 || ldx < k || ldo < n || k % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0) {
+    return fail_invalid(op, "needs m >= 0, n, k > 0, k, ldx, ldo multiples of 8, ldx >= k and ldo >= n");
+  }
+  if (m == 0) return B2_OK;
+  if (x == nullptr || w == nullptr || out == nullptr || !aligned_to(x, 16) || !aligned_to(w, 16) || !aligned_to(out, 16) ||
+      (bias != nullptr && !aligned_to(bias, 16))) {
+    return fail_invalid(op, "needs 16-byte aligned bf16 x [m, k], w [n, k], out [m, n] (bias bf16 [n] or NULL)");
+  }
+  if (workspace_bytes > 0 && (workspace == nullptr || !aligned_to(workspace, 256))) return fail_invalid(op, "workspace must be 256-byte aligned");
+  const LtApi& api = lt();
+  if (!api.ok) return fail_status(B2_ERR_NOT_SUPPORTED, op, "libcublasLt.so.12 was not found");
+  cublasLtHandle_t handle = nullptr;
+  if (const int rc = lt_handle(&handle)) return rc;
+  // Row-major out [m, n] = x [m, k] * w [n, k]^T is column-major out^T [n, m] = w^T-as-stored (op T) * x-as-stored.
+  cublasLtMatmulDesc_t desc = nullptr;
+  cublasLtMatrixLayout_t la = nullptr, lb = nullptr, lc = nullptr;
+  cublasLtMatmulPreference_t pref = nullptr;
+  cublasStatus_t st = api.desc_create(&desc, CUBLAS_COMPUTE_32F, CUDA_R_32F);
+  const cublasOperation_t ta = CUBLAS_OP_T, tb = CUBLAS_OP_N;
+  if (st == CUBLAS_STATUS_SUCCESS) st = api.desc_set(desc, CUBLASLT_MATMUL_DESC_TRANSA, &ta, sizeof ta);
+  if (st == CUBLAS_STATUS_SUCCESS) st = api.desc_set(desc, CUBLASLT_MATMUL_DESC_TRANSB, &tb, sizeof tb);
+  if (st == CUBLAS_STATUS_SUCCESS && bias != nullptr) {
+    const cublasLtEpilogue_t ep = CUBLASLT_EPILOGUE_BIAS;
+    st = api.desc_set(desc, CUBLASLT_MATMUL_DESC_EPILOGUE, &ep, sizeof ep);
+    if (st == CUBLAS_STATUS_SUCCESS) st = api.desc_set(desc, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof bias);
+  }
+  if (st == CUBLAS_STATUS_SUCCESS) st = api.layout_create(&la, CUDA_R_16BF, static_cast<uint64_t>(k), static_cast<uint64_t>(n), k);
+  if (st == CUBLAS_STATUS_SUCCESS) st = api.layout_create(&lb, CUDA_R_16BF, static_cast<uint64_t>(k), static_cast<uint64_t>(m), ldx);
+  if (st == CUBLAS_STATUS_SUCCESS) st = api.layout_create(&lc, CUDA_R_16BF, static_cast<uint64_t>(n), static_cast<uint64_t>(m), ldo);
+  if (st == CUBLAS_STATUS_SUCCESS) st = api.pref_create(&pref);
+  if (st == CUBLAS_STATUS_SUCCESS) st = api.pref_set(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &workspace_bytes, sizeof workspace_bytes);
+  cublasLtMatmulHeuristicResult_t found{};
+  int count = 0;
+  if (st == CUBLAS_STATUS_SUCCESS) st = api.heuristic(handle, desc, la, lb, lc, lc, pref, 1, &found, &count);
+  if (st == CUBLAS_STATUS_SUCCESS && count == 0) st = CUBLAS_STATUS_NOT_SUPPORTED;
+  const float one = 1.0f, zero = 0.0f;
+  if (st == CUBLAS_STATUS_SUCCESS) {
+    st = api.matmul(handle, desc, &one, w, la, x, lb, &zero, out, lc, out, lc, &found.algo, workspace, workspace_bytes,
+                    as_stream(stream));
+  }
+  if (pref != nullptr) api.pref_destroy(pref);
+  if (lc != nullptr) api.layout_destroy(lc);
+  if (lb != nullptr) api.layout_destroy(lb);
+  if (la != nullptr) api.layout_destroy(la);
+  if (desc != nullptr) api.desc_destroy(desc);
+  if (st != CUBLAS_STATUS_SUCCESS) return fail_status(B2_ERR_CUDA, op, "cuBLASLt status " + std::to_string(static_cast<int>(st)));
+  return B2_OK;
+}
+
+size_t b2_dit_forward_workspace_bytes(const b2_dit_model* model, const b2_forward* forward) {
+  std::vector<std::int64_t> off;
+  Carve c{};
+  b2_block_run widest{};
+  if (plan_forward("dit_forward_workspace_bytes", model, forward, &off, &c, &widest) != B2_OK) return 0;
+  return c.total;
+}
+
+int b2_dit_forward(const b2_dit_model* model, const b2_forward* forward, void* stream_) {
+  constexpr const char* op = "dit_forward";
+  std::vector<std::int64_t> off;
+  Carve c{};
+  b2_block_run widest{};
+  if (const int rc = plan_forward(op, model, forward, &off, &c, &widest)) return rc;
+  const b2_dit_model& m = *model;
+  const b2_forward& f = *forward;
+  if (f.latents == nullptr || f.time_vector == nullptr) return fail_invalid(op, "needs latents and the host time vector");
+  if (m.block_mod_w == nullptr || m.block_mod_bias == nullptr || m.head_mod_w == nullptr || m.head_mod_bias == nullptr ||
+      m.video_w == nullptr || m.final_norm == nullptr || m.final_w == nullptr) {
+    return fail_invalid(op, "the model lacks a modulation, embedder or head tensor");
+  }
+  if (f.workspace == nullptr || !aligned_to(f.workspace, 256) || f.workspace_bytes < c.total) {
+    return fail_invalid(op, "workspace must be 256-byte aligned and hold b2_dit_forward_workspace_bytes() = " + std::to_string(c.total));
+  }
+  cudaStream_t stream = as_stream(stream_);
+  const std::int64_t hw = static_cast<std::int64_t>(f.height) * f.width, D = m.D;
+  unsigned char* base = static_cast<unsigned char*>(f.workspace);
+  __nv_bfloat16* x = reinterpret_cast<__nv_bfloat16*>(base + c.x);
+  __nv_bfloat16* rope = reinterpret_cast<__nv_bfloat16*>(base + c.rope);
+  __nv_bfloat16* mod = reinterpret_cast<__nv_bfloat16*>(base + c.mod);
+  __nv_bfloat16* head = reinterpret_cast<__nv_bfloat16*>(base + c.head);
+  float* time = reinterpret_cast<float*>(base + c.time);
+  __nv_bfloat16* tokens = reinterpret_cast<__nv_bfloat16*>(base + c.tokens);
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(base + c.y);
+  std::int32_t* cu_dev = reinterpret_cast<std::int32_t*>(base + c.cu);
+
+  // The runs of contiguous rows that execute each block, one varlen batch each with zero-based cu_seqlens; a run that
+  // recurs (the usual case: no skips, one run over all rows) is described once.
+  std::vector<std::int32_t> cu;
+  std::map<std::pair<int, int>, Run> unique;
+  std::vector<std::vector<Run>> block_runs(static_cast<std::size_t>(m.num_blocks));
+  for (int bi = 0; bi < m.num_blocks; ++bi) {
+    const auto skips = [&](int r) { return ((f.rows[r].skip >> bi) & 1u) != 0; };
+    for (int r0 = 0; r0 < f.num_rows;) {
+      if (skips(r0)) {
+        ++r0;
+        continue;
+      }
+      int r1 = r0;
+      while (r1 < f.num_rows && !skips(r1)) ++r1;
+      auto it = unique.find({r0, r1});
+      if (it == unique.end()) {
+        Run run{r0, r1, off[static_cast<std::size_t>(r0)], off[static_cast<std::size_t>(r1)], static_cast<int>(cu.size()), 0};
+        for (int r = r0; r <= r1; ++r) {
+          cu.push_back(static_cast<std::int32_t>(off[static_cast<std::size_t>(r)] - off[static_cast<std::size_t>(r0)]));
+          if (r < r1) run.max_len = std::max<int>(run.max_len, static_cast<int>(off[static_cast<std::size_t>(r) + 1] - off[static_cast<std::size_t>(r)]));
+        }
+        it = unique.emplace(std::make_pair(r0, r1), run).first;
+      }
+      block_runs[static_cast<std::size_t>(bi)].push_back(it->second);
+      r0 = r1;
+    }
+  }
+  if (const int rc = write_words(op, cu_dev, cu.data(), cu.size(), stream)) return rc;
+  // time_modulation: the time vector (host, fp32) through the two modulation linears.
+  if (const int rc = write_words(op, time, f.time_vector, static_cast<std::size_t>(D), stream)) return rc;
+  if (const int rc = b2_linear_fp32_row(m.block_mod_w, time, m.block_mod_bias, mod, static_cast<int>(6 * D), static_cast<int>(D), stream)) return rc;
+  if (const int rc = b2_linear_fp32_row(m.head_mod_w, time, m.head_mod_bias, head, static_cast<int>(2 * D), static_cast<int>(D), stream)) return rc;
+
+  // Joint inputs [video_r | text_r] and per-row RoPE tables. The video embedding is the same for every row of a latent:
+  // computed once, into the first row that reads the latent, and copied to its other rows.
+  const std::size_t row_bytes = static_cast<std::size_t>(D) * 2;
+  for (int r = 0; r < f.num_rows; ++r) {
+    int src = r;
+    for (int q = 0; q < r; ++q) {
+      if (f.rows[q].latent == f.rows[r].latent) {
+        src = q;
+        break;
+      }
+    }
+    __nv_bfloat16* xr = x + off[static_cast<std::size_t>(r)] * D;
+    if (src == r) {
+      const float* plane = f.latents + static_cast<std::size_t>(f.rows[r].latent) * 128 * static_cast<std::size_t>(hw);
+      if (const int rc = b2_latent_to_tokens(plane, 128, hw, tokens, 128, stream)) return rc;
+      if (const int rc = b2_linear_bf16(tokens, 128, m.video_w, m.video_bias, xr, D, hw, static_cast<int>(D), 128, base + c.lt, kLtWorkspaceBytes, stream)) return rc;
+    } else if (const cudaError_t e = cudaMemcpyAsync(xr, x + off[static_cast<std::size_t>(src)] * D, static_cast<std::size_t>(hw) * row_bytes, cudaMemcpyDeviceToDevice, stream); e != cudaSuccess) {
+      return fail_cuda(op, e);
+    }
+    if (const int rc = b2_moss_rope_table(rope + off[static_cast<std::size_t>(r)] * 128, 128, f.height, f.width, static_cast<int>(f.rows[r].text_len), stream)) return rc;
+    if (const cudaError_t e = cudaMemcpyAsync(xr + hw * D, f.rows[r].text, static_cast<std::size_t>(f.rows[r].text_len) * row_bytes, cudaMemcpyDeviceToDevice, stream); e != cudaSuccess) {
+      return fail_cuda(op, e);
+    }
+  }
+
+  // The blocks.
+  for (int bi = 0; bi < m.num_blocks; ++bi) {
+    for (const Run& run : block_runs[static_cast<std::size_t>(bi)]) {
+      b2_block_run br = widest;
+      br.tokens = run.t1 - run.t0, br.batch = run.r1 - run.r0, br.max_seqlen = run.max_len, br.cu_seqlens = cu_dev + run.cu_at;
+      b2_block_buffers bb{};
+      bb.struct_size = sizeof bb;
+      bb.x = x + run.t0 * D, bb.mod = mod, bb.rope = rope + run.t0 * 128, bb.workspace = base + c.block;
+      bb.workspace_bytes = c.total - c.block;
+      if (const int rc = b2_run_block_quant(&m.blocks[bi], &bb, &br, stream)) return rc;
+    }
+  }
+
+  // Head: final norm with the head modulation (shift = head[0], scale = head[1]), linear, transpose.
+  for (int r = 0; r < f.num_rows; ++r) {
+    const __nv_bfloat16* xr = x + off[static_cast<std::size_t>(r)] * D;
+    if (const int rc = b2_rms_norm_modulate(xr, D, m.final_norm, head + D, head, y, D, hw, static_cast<int>(D), stream)) return rc;
+    if (const int rc = b2_linear_bf16(y, D, m.final_w, m.final_bias, tokens, 128, hw, 128, static_cast<int>(D), base + c.lt, kLtWorkspaceBytes, stream)) return rc;
+    if (const int rc = b2_tokens_to_latent(tokens, f.rows[r].out, 128, hw, stream)) return rc;
+  }
+  return B2_OK;
+}
+
+}  // extern "C"

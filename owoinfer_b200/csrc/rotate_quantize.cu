@@ -348,6 +348,21 @@ __global__ void __launch_bounds__(kPairs == 1 ? 384 : 512, kPairs == 1 ? 2 : 1) 
       }
     };
 
+    if constexpr (kNorm) {
+      // Norm + modulate alone (no quantiser output asked for): store y and go to the next row.
+      if (a.q == nullptr) {
+#pragma unroll
+        for (int p = 0; p < kPairs; ++p) {
+          if (2 * (half_id + p * halves) >= groups) continue;
+          u32 w[16];
+          fetch(p, w);
+          prologue(w, 2 * (half_id + p * halves), true);
+          prologue(w + 8, 2 * (half_id + p * halves) + 1, true);
+        }
+        continue;
+      }
+    }
+
     // The rotation, the rounding to bf16 and the row's absolute maximum. kExact = false is the fast form: no factor 0.5
     // in the butterflies, so the rotated values (and the maximum) are 16 times the reference's, bit for bit, provided
     // nothing overflowed on the way; its maximum propagates NaN (a NaN's bf16 pattern, sign cleared, is above every
@@ -691,6 +706,29 @@ int b2_rms_norm_modulate_rotate_quantize(const void* x, int64_t ldx, const void*
   if (m == 0) return B2_OK;
   Args a{};
   a.x = static_cast<const __nv_bfloat16*>(x), a.ldx = ldx, a.q = q, a.ldq = ldq, a.scale = scale, a.k = k;
+  a.weight = static_cast<const __nv_bfloat16*>(norm_weight);
+  a.mod_scale = static_cast<const __nv_bfloat16*>(mod_scale);
+  a.mod_shift = static_cast<const __nv_bfloat16*>(mod_shift);
+  a.y = static_cast<__nv_bfloat16*>(y), a.ldy = ldy;
+  a.factor = static_cast<float>(m) / static_cast<float>(m * k);
+  a.bw = bw;
+  return launch<true, false>(op, a, m, as_stream(stream));
+}
+
+int b2_rms_norm_modulate(const void* x, int64_t ldx, const void* norm_weight, const void* mod_scale, const void* mod_shift,
+                         void* y, int64_t ldy, int64_t m, int k, void* stream) {
+  constexpr const char* op = "rms_norm_modulate";
+  if (k <= 0 || k % kGroup != 0 || k > kMaxK) return fail_invalid(op, "k must be a positive multiple of 256 up to 32768, got " + std::to_string(k));
+  if (m < 0 || m > 0x7fffffff) return fail_invalid(op, "row count out of range");
+  if (m > 0 && (x == nullptr || y == nullptr)) return fail_invalid(op, "null operand");
+  if (ldx < k || ldy < k || ldx % 8 != 0 || ldy % 8 != 0 || !aligned_to(x, 16) || !aligned_to(y, 16)) {
+    return fail_invalid(op, "needs 16-byte aligned x and y with ldx, ldy >= k and multiples of 8");
+  }
+  int bw = 32;
+  if (const int rc = check_norm(op, norm_weight, mod_scale, mod_shift, m, k, &bw)) return rc;
+  if (m == 0) return B2_OK;
+  Args a{};
+  a.x = static_cast<const __nv_bfloat16*>(x), a.ldx = ldx, a.k = k;
   a.weight = static_cast<const __nv_bfloat16*>(norm_weight);
   a.mod_scale = static_cast<const __nv_bfloat16*>(mod_scale);
   a.mod_shift = static_cast<const __nv_bfloat16*>(mod_shift);

@@ -454,3 +454,108 @@ def guided_velocity_step(v_cond, x=None, v_uncond=None, v_skip=None, v_prev=None
     g.cfg, g.slg, g.update, g.n = int(v_uncond is not None), int(v_skip is not None), update, v_cond.numel()
     check(_lib.lib().b2_guided_velocity_step(C.byref(g), _stream()))
     return x if update else v_out
+
+
+# ------------------------------------------------------------------------------------------------ forward shell
+
+def latent_to_tokens(latents, tokens=None, col0=0):
+    """f32 [C, h, w] (or [C, hw]) -> bf16 [hw, C]; into columns [col0, col0 + C) of a wider `tokens` when given."""
+    c, hw = latents.shape[0], latents.numel() // latents.shape[0]
+    tokens = torch.empty((hw, c), dtype=torch.bfloat16, device=latents.device) if tokens is None else tokens
+    dst = C.c_void_p(tokens.data_ptr() + 2 * col0)
+    check(_lib.lib().b2_latent_to_tokens(_ptr(latents), C.c_int(c), C.c_int64(hw), dst, C.c_int64(tokens.stride(0)), _stream()))
+    return tokens
+
+
+def tokens_to_latent(tokens, latents=None):
+    hw, c = tokens.shape
+    latents = torch.empty((c, hw), dtype=torch.float32, device=tokens.device) if latents is None else latents
+    check(_lib.lib().b2_tokens_to_latent(_ptr(tokens), _ptr(latents), C.c_int(c), C.c_int64(hw), _stream()))
+    return latents
+
+
+def linear_fp32_row(w, x, bias, out=None):
+    n, k = w.shape
+    out = torch.empty(n, dtype=torch.bfloat16, device=w.device) if out is None else out
+    check(_lib.lib().b2_linear_fp32_row(_ptr(w), _ptr(x), _ptr(bias), _ptr(out), C.c_int(n), C.c_int(k), _stream()))
+    return out
+
+
+def rms_norm_modulate(x, norm_weight, mod_scale, mod_shift, y=None):
+    m, k = x.shape
+    y = torch.empty((m, k), dtype=torch.bfloat16, device=x.device) if y is None else y
+    check(_lib.lib().b2_rms_norm_modulate(_ptr(x), C.c_int64(_ld(x)), _ptr(norm_weight), _ptr(mod_scale), _ptr(mod_shift),
+                                          _ptr(y), C.c_int64(_ld(y)), C.c_int64(m), C.c_int(k), _stream()))
+    return y
+
+
+def time_sinusoid(timestep):
+    import numpy as np
+    emb = np.empty(256, np.float32)
+    check(_lib.lib().b2_time_sinusoid(C.c_float(timestep), emb.ctypes.data_as(C.c_void_p)))
+    return emb
+
+
+def time_vector_fp32(w0, b0, w2, b2, timestep):
+    """Host: numpy f32 weights of the timestep MLP -> the f32 time vector [dim]."""
+    import numpy as np
+    w0, b0, w2, b2 = (np.ascontiguousarray(a, np.float32) for a in (w0, b0, w2, b2))
+    te = _lib.TimeEmbedding()
+    te.struct_size, te.dim = C.sizeof(_lib.TimeEmbedding), w2.shape[0]
+    te.w0, te.b0, te.w2, te.b2 = (a.ctypes.data for a in (w0, b0, w2, b2))
+    out = np.empty(w2.shape[0], np.float32)
+    check(_lib.lib().b2_time_vector_fp32(C.byref(te), C.c_float(timestep), out.ctypes.data_as(C.c_void_p)))
+    return out
+
+
+def linear_bf16(x, w, bias=None, out=None, workspace=None):
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device) if out is None else out
+    if workspace is None:
+        workspace = torch.empty(_lib.lib().b2_linear_bf16_workspace_bytes(), dtype=torch.uint8, device=x.device)
+    check(_lib.lib().b2_linear_bf16(_ptr(x), C.c_int64(_ld(x)), _ptr(w), _ptr(bias), _ptr(out), C.c_int64(_ld(out)),
+                                    C.c_int64(m), C.c_int(n), C.c_int(k), _ptr(workspace), C.c_size_t(workspace.numel()),
+                                    _stream()))
+    return out
+
+
+class DitModel:
+    """b2_dit_model over torch tensors: `blocks` a list of BlockWeights, the rest device tensors (kept alive here)."""
+
+    def __init__(self, blocks, F, block_mod_w, block_mod_bias, head_mod_w, head_mod_bias, video_w, video_bias, final_norm,
+                 final_w, final_bias, D=3072, heads=24):
+        self.keep = (blocks, block_mod_w, block_mod_bias, head_mod_w, head_mod_bias, video_w, video_bias, final_norm, final_w,
+                     final_bias)
+        self.arr = (_lib.BlockWeights * max(1, len(blocks)))(*[b.struct for b in blocks])
+        m = _lib.DitModel()
+        m.struct_size, m.blocks, m.num_blocks = C.sizeof(_lib.DitModel), self.arr, len(blocks)
+        m.D, m.F, m.heads, m.latent_channels = D, F, heads, 128
+        p = lambda t: None if t is None else t.data_ptr()
+        m.block_mod_w, m.block_mod_bias, m.head_mod_w, m.head_mod_bias = p(block_mod_w), p(block_mod_bias), p(head_mod_w), p(head_mod_bias)
+        m.video_w, m.video_bias, m.final_norm, m.final_w, m.final_bias = p(video_w), p(video_bias), p(final_norm), p(final_w), p(final_bias)
+        self.struct = m
+
+
+def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, workspace=None):
+    """rows: list of (text bf16 [S, D], skip mask int, latent index). latents f32 [n, 128, h, w]; time_vector numpy f32 [D].
+    Returns the per-row outputs f32 [128, h, w] (and the workspace, for reuse)."""
+    import numpy as np
+    n, _, h, w = latents.shape
+    outs = [torch.empty((128, h, w), dtype=torch.float32, device=latents.device) for _ in rows]
+    arr = (_lib.ForwardRow * len(rows))()
+    for i, (text, skip, latent) in enumerate(rows):
+        arr[i].text, arr[i].text_len, arr[i].skip, arr[i].latent, arr[i].out = text.data_ptr(), text.shape[0], skip, latent, outs[i].data_ptr()
+    tv = np.ascontiguousarray(time_vector, np.float32)
+    f = _lib.Forward()
+    f.struct_size, f.latents, f.num_latents, f.height, f.width = C.sizeof(_lib.Forward), latents.data_ptr(), n, h, w
+    f.time_vector, f.rows, f.num_rows, f.tier = tv.ctypes.data, arr, len(rows), tier
+    f.attention = _lib.AttentionOptions(ATTENTION_Q8_FP8_F32ACC, 0.0, 0.0)
+    need = _lib.lib().b2_dit_forward_workspace_bytes(C.byref(model.struct), C.byref(f))
+    if need == 0:
+        check(-1)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=latents.device)
+    f.workspace, f.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    check(_lib.lib().b2_dit_forward(C.byref(model.struct), C.byref(f), _stream()))
+    return outs, workspace

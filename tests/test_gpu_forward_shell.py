@@ -1,0 +1,213 @@
+"""The shell of the DiT forward around the block loop: each exactly specified piece against the CPU oracle (and, where
+built, against the reference's own kernels on the same device buffers), the library bf16 linear against float64, and
+b2_dit_forward as a whole against the same sequence of already checked calls (bit for bit), with rows that share a
+latent and rows that skip blocks. Modelled on tests/unit/test_moss_dit.cpp of the reference."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle_lib as orc
+from oracle import ref_cuda_lib as ref
+from owoinfer_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from owoinfer_b200 import ops as o
+    yield o
+    torch.cuda.synchronize()
+    assert o.kernel_status() == (0, 0)
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def bf_to_f64(u):
+    return (np.asarray(u, np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+
+def to_bf16(v):
+    u = np.ascontiguousarray(v, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def bfdev(u):
+    return torch.from_numpy(np.ascontiguousarray(u).view(np.int16)).cuda().view(torch.bfloat16)
+
+
+@pytest.mark.parametrize("c,h,w", [(128, 64, 64), (128, 5, 7), (3, 33, 1), (160, 16, 16)])
+def test_transposes(ops, c, h, w):
+    rng = np.random.default_rng(c + h)
+    lat = rng.normal(0, 2, (c, h, w)).astype(np.float32)
+    lat[0, 0, 0], lat[-1, -1, -1] = np.float32(1.00390625), np.float32(-3.3895314e38)   # a rounding tie, near bf16 max
+    d = torch.from_numpy(lat).cuda()
+    tok = ops.latent_to_tokens(d)
+    assert np.array_equal(bits(tok), orc.latent_to_tokens(lat))
+    back = ops.tokens_to_latent(tok)
+    assert np.array_equal(back.cpu().numpy().view(np.uint32), orc.tokens_to_latent(bits(tok)).view(np.uint32))
+    # into a column range of a wider token matrix (the input-extension layout), the rest untouched
+    wide = torch.full((h * w, c + 24), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.latent_to_tokens(d, tokens=wide, col0=8)
+    assert torch.equal(wide[:, 8:8 + c], tok) and (wide[:, :8] == 7).all() and (wide[:, 8 + c:] == 7).all()
+    if ref.has_shell_kernels():
+        rt = torch.empty_like(tok)
+        ref.latent_to_tokens(d, rt)
+        assert torch.equal(rt.view(torch.int16), tok.view(torch.int16))
+        rl = torch.empty((c, h, w), dtype=torch.float32, device="cuda")
+        ref.tokens_to_latent(tok, rl)
+        assert torch.equal(rl.view(torch.int32).reshape(c, -1), back.view(torch.int32))
+
+
+@pytest.mark.parametrize("n,k", [(18432, 3072), (6144, 3072), (37, 256), (5, 8)])
+def test_linear_fp32_row_same_bits(ops, n, k):
+    rng = np.random.default_rng(n)
+    w = to_bf16(rng.normal(0, 0.03, (n, k)))
+    x = rng.normal(0, 1.5, k).astype(np.float32)
+    bias = rng.normal(0, 0.5, n).astype(np.float32)
+    dw, dx, db = bfdev(w), torch.from_numpy(x).cuda(), torch.from_numpy(bias).cuda()
+    got = ops.linear_fp32_row(dw, dx, db)
+    assert np.array_equal(bits(got), orc.linear_fp32_row(w, x, bias))
+    exact = bf_to_f64(w) @ x.astype(np.float64) + bias
+    assert np.abs(bf_to_f64(bits(got)) - exact).max() <= 2.0 ** -8 * np.abs(exact).max() + 1e-3
+    if ref.has_shell_kernels() and k % 8 == 0:
+        want = torch.empty_like(got)
+        ref.linear_fp32_row(dw, dx, db, want)
+        assert torch.equal(want.view(torch.int16), got.view(torch.int16))
+
+
+def test_time_modulation_chain(ops):
+    """moss_dit.cpp:949-969: host time vector (cached per timestep there), then the two modulation linears."""
+    rng = np.random.default_rng(5)
+    dim = 3072
+    w0, b0 = rng.normal(0, 0.06, (dim, 256)).astype(np.float32), rng.normal(0, 0.1, dim).astype(np.float32)
+    w2, b2 = rng.normal(0, 0.02, (dim, dim)).astype(np.float32), rng.normal(0, 0.1, dim).astype(np.float32)
+    emb, want = orc.time_vector_fp32(w0, b0, w2, b2, 0.7316)
+    assert np.array_equal(ops.time_sinusoid(0.7316).view(np.uint32), emb.view(np.uint32))
+    tv = ops.time_vector_fp32(w0, b0, w2, b2, 0.7316)
+    assert np.array_equal(tv.view(np.uint32), want.view(np.uint32))
+    # against plain float64 linear algebra (a different summation order): close, not identical
+    h = w0.astype(np.float64) @ emb + b0
+    h = h / (1 + np.exp(-h))
+    assert np.allclose(tv, w2.astype(np.float64) @ h.astype(np.float32) + b2, rtol=2e-5, atol=2e-5)
+    mw = to_bf16(rng.normal(0, 0.02, (6 * dim, dim)))
+    mb = rng.normal(0, 0.2, 6 * dim).astype(np.float32)
+    mod = ops.linear_fp32_row(bfdev(mw), torch.from_numpy(tv).cuda(), torch.from_numpy(mb).cuda())
+    assert np.array_equal(bits(mod), orc.linear_fp32_row(mw, want, mb))
+
+
+@pytest.mark.parametrize("m", [1, 9, 64, 4096])
+def test_rms_norm_modulate_is_the_quantiser_prologue(ops, m):
+    rng = np.random.default_rng(m)
+    k = 3072
+    x = to_bf16(rng.normal(0, 1, (m, k)))
+    w, sc, sh = to_bf16(rng.normal(1, 0.1, k)), to_bf16(rng.normal(0, 0.1, k)), to_bf16(rng.normal(0, 0.1, k))
+    y = ops.rms_norm_modulate(bfdev(x), bfdev(w), bfdev(sc), bfdev(sh))
+    y2 = torch.empty_like(y)
+    ops.rms_norm_modulate_rotate_quantize(bfdev(x), bfdev(w), bfdev(sc), bfdev(sh), y=y2)
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+    want = orc.rms_norm_modulate(x, w, sc, sh)
+    # rsqrtf (GPU) against 1 / sqrt (CPU): rare single-step differences
+    assert (bits(y) == want).mean() >= 0.999
+
+
+@pytest.mark.parametrize("m,n,k,bias", [(4096, 3072, 128, True), (4096, 128, 3072, True), (77, 3072, 128, False), (1, 128, 3072, True)])
+def test_linear_bf16_against_float64(ops, m, n, k, bias):
+    rng = np.random.default_rng(m + n)
+    x, w = to_bf16(rng.normal(0, 1, (m, k))), to_bf16(rng.normal(0, 0.05, (n, k)))
+    b = to_bf16(rng.normal(0, 0.5, n)) if bias else None
+    got = ops.linear_bf16(bfdev(x), bfdev(w), None if b is None else bfdev(b))
+    exact = bf_to_f64(x) @ bf_to_f64(w).T + (bf_to_f64(b) if bias else 0.0)
+    err = np.abs(bf_to_f64(bits(got)) - exact)
+    # fp32 accumulation in the library's order, one rounding to bf16: within one bf16 step of the exact value
+    assert (err <= 2.0 ** -8 * np.abs(exact) + 1e-6 * np.sqrt(k)).all()
+    # strided input and output rows
+    xw = torch.zeros((m, k + 16), dtype=torch.bfloat16, device="cuda")
+    xw[:, :k] = bfdev(x)
+    ow = torch.full((m, n + 8), 3.0, dtype=torch.bfloat16, device="cuda")
+    ops.linear_bf16(xw[:, :k], bfdev(w), None if b is None else bfdev(b), out=ow[:, :n])
+    assert torch.equal(ow[:, :n], got) and (ow[:, n:] == 3).all()
+
+
+def _model(ops, blocks, F, seed):
+    rng = np.random.default_rng(seed)
+    D = 3072
+    t = lambda a: bfdev(to_bf16(a))
+    f = lambda a: torch.from_numpy(a.astype(np.float32)).cuda()
+    ws = [synth.block_weights(D, F, seed + 100 * i) for i in range(blocks)]
+    bws = [ops.BlockWeights(w["norm1"], w["norm2"], w["q_norm"], w["k_norm"], w["qkv"], w["o"], w["up_gate"], w["down"]) for w in ws]
+    parts = dict(block_mod_w=t(rng.normal(0, 0.02, (6 * D, D))), block_mod_bias=f(rng.normal(0, 0.3, 6 * D)),
+                 head_mod_w=t(rng.normal(0, 0.02, (2 * D, D))), head_mod_bias=f(rng.normal(0, 0.3, 2 * D)),
+                 video_w=t(rng.normal(0, 0.09, (D, 128))), video_bias=t(rng.normal(0, 0.1, D)),
+                 final_norm=t(rng.normal(1, 0.1, D)), final_w=t(rng.normal(0, 0.02, (128, D))), final_bias=t(rng.normal(0, 0.1, 128)))
+    return ops.DitModel(bws, F, **parts), bws, parts, ws
+
+
+@pytest.mark.parametrize("skips", [(0, 0, 0), (0, 0b10, 0), (0b01, 0b01, 0b10)])
+def test_dit_forward_equals_the_sequence_of_its_parts(ops, skips):
+    D, F, h, w = 3072, 8192, 16, 24
+    hw = h * w
+    model, bws, p, _ = _model(ops, 2, F, 3)
+    rng = np.random.default_rng(11)
+    latents = torch.from_numpy(rng.normal(0, 1, (2, 128, h, w)).astype(np.float32)).cuda()
+    texts = [bfdev(to_bf16(rng.normal(0, 1, (s, D)))) for s in (19, 40, 7)]
+    latent_of = (0, 0, 1)
+    tv = rng.normal(0, 1, D).astype(np.float32)
+    outs, _ = ops.dit_forward(model, latents, tv, [(texts[r], skips[r], latent_of[r]) for r in range(3)])
+    torch.cuda.synchronize()
+
+    # The same forward, call by call.
+    dtv = torch.from_numpy(tv).cuda()
+    mod = ops.linear_fp32_row(p["block_mod_w"], dtv, p["block_mod_bias"])
+    head = ops.linear_fp32_row(p["head_mod_w"], dtv, p["head_mod_bias"])
+    off = [0]
+    for t in texts:
+        off.append(off[-1] + hw + t.shape[0])
+    x = torch.empty((off[-1], D), dtype=torch.bfloat16, device="cuda")
+    rope = torch.empty((off[-1], 128), dtype=torch.bfloat16, device="cuda")
+    emb = [ops.linear_bf16(ops.latent_to_tokens(latents[l]), p["video_w"], p["video_bias"]) for l in range(2)]
+    for r in range(3):
+        x[off[r]:off[r] + hw] = emb[latent_of[r]]
+        x[off[r] + hw:off[r + 1]] = texts[r]
+        rope[off[r]:off[r + 1]] = ops.moss_rope_table(h, w, texts[r].shape[0])
+    for bi in range(2):
+        r0 = 0
+        while r0 < 3:
+            if (skips[r0] >> bi) & 1:
+                r0 += 1
+                continue
+            r1 = r0
+            while r1 < 3 and not (skips[r1] >> bi) & 1:
+                r1 += 1
+            lens = [off[r + 1] - off[r] for r in range(r0, r1)]
+            cu = synth.cu_seqlens(lens)
+            run = ops.block_run(off[r1] - off[r0], cu, max(lens), D=D, F=F)
+            ws = torch.empty(ops.block_quant_workspace_bytes(run), dtype=torch.uint8, device="cuda")
+            ops.run_block_quant(bws[bi], ops.block_buffers(x[off[r0]:off[r1]], mod, rope[off[r0]:off[r1]], ws), run)
+            r0 = r1
+    for r in range(3):
+        y = ops.rms_norm_modulate(x[off[r]:off[r] + hw], p["final_norm"], head[D:], head[:D])
+        want = ops.tokens_to_latent(ops.linear_bf16(y, p["final_w"], p["final_bias"])).reshape(128, h, w)
+        assert torch.equal(outs[r].view(torch.int32), want.view(torch.int32)), f"row {r}"
+    assert torch.isfinite(outs[0]).all() and outs[0].abs().max() > 0
+    if skips == (0, 0, 0):
+        # rows 0 and 1 read the same latent but different text: different outputs
+        assert not torch.equal(outs[0], outs[1])
+
+
+def test_dit_forward_rejects_bad_arguments(ops):
+    model, _, _, _ = _model(ops, 1, 8192, 9)
+    lat = torch.zeros((1, 128, 4, 4), dtype=torch.float32, device="cuda")
+    text = torch.zeros((3, 3072), dtype=torch.bfloat16, device="cuda")
+    tv = np.zeros(3072, np.float32)
+    with pytest.raises(ValueError, match="latent that is not there"):
+        ops.dit_forward(model, lat, tv, [(text, 0, 1)])
+    with pytest.raises(ValueError, match="1..8 rows"):
+        ops.dit_forward(model, lat, tv, [(text, 0, 0)] * 9)
+    small = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    outs, ws = ops.dit_forward(model, lat, tv, [(text, 0, 0)], workspace=small)   # too small a workspace is replaced
+    assert ws.numel() > small.numel() and torch.isfinite(outs[0]).all()
