@@ -375,6 +375,26 @@ def forward_shell_ms(torch, ops, synth, grid, text_len, rows, blocks, F, steps):
     return out
 
 
+def load_file_record(torch, ops, synth, F, blocks=2):
+    """Weight ingestion: a synthetic INT8 file of `blocks` blocks (official names and configs) written to the temporary
+    directory, then opened, checked and copied to the device by b2_dit_file_open; the second open reads from the page cache."""
+    import tempfile
+    import time
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "dit_int8.safetensors")
+        size = synth.write_int8_dit_file(path, blocks, F)
+        ms = []
+        for _ in range(2):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            f = ops.DitFile(path)
+            torch.cuda.synchronize()
+            ms.append((time.perf_counter() - t0) * 1e3)
+            assert f.num_blocks == blocks and f.tier == ops.TIER_INT8
+            f.close()
+    return {"file_bytes": size, "blocks": blocks, "open_ms": ms[1], "gb_per_s": size / ms[1] / 1e6, "first_open_ms": ms[0]}
+
+
 def ulysses_record(torch, dist, ops, synth, args, rank, world):
     """N >= 2: the 2048^2 step (two 20480-token sequences) over all N ranks (groups x sequence parallel), the same step on
     rank 0's GPU alone, the speed-up and the exchange time the step does not hide. Every rank takes part; rank 0 returns
@@ -593,6 +613,7 @@ def main():
                 fw = forward_shell_ms(torch, ops, synth, 64, seq_len - 64 * 64, seqs, n_blocks, F, min(args.steps, 3))
                 line["extra"]["forward1024_ms"] = fw["forward"]
                 line["extra"]["forward1024_shell_only_ms"] = fw["shell_only"]
+                line["extra"]["load_file"] = load_file_record(torch, ops, synth, F)
     if world > 1 and args.workload == "step1024" and not args.no_ulysses and tier == ops.TIER_INT8:
         # The headline above is image data parallel (no collective). The sequence-parallel configuration, the one with an
         # exchange step, rides along as its own record: free the headline's buffers first.

@@ -491,6 +491,39 @@ size_t b2_dit_forward_workspace_bytes(const b2_dit_model* model, const b2_forwar
  * arrays travel as kernel parameters: the call does not synchronise and needs no pinned memory. */
 int b2_dit_forward(const b2_dit_model* model, const b2_forward* forward, void* stream);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * Weight ingestion: a ComfyUI-layout safetensors file of the quantized MOSS-Image DiT -> device tensors.
+ * What quant::read_model + to_model_index + the block upload do in the reference for this path
+ * (src/weights/quant/quant_model.h:1-45, quant_model.cpp:205-285, src/models/moss_dit/dit_weights.cpp:194-300).
+ * ------------------------------------------------------------------------------------------------------------- */
+
+typedef struct b2_dit_file b2_dit_file;
+typedef struct b2_dit_file_info {
+  size_t struct_size;
+  int num_blocks;
+  int F;                  /* FFN width read from layers.0.proj.ffn_down */
+  int tier;               /* B2_TIER_*: the one tier of every block linear in the file */
+  int has_shell;          /* the tensors outside the blocks are there: b2_dit_file_model() can run b2_dit_forward */
+  int has_time_embedding; /* time_embedding.0 / .2 are there: b2_dit_file_time_embedding() is not NULL */
+  size_t device_bytes;
+} b2_dit_file_info;
+
+/* Reads the header, checks every tensor the model needs (names, dtypes, shapes, per-module comfy_quant configs or the
+ * legacy _quantization_metadata key, scales finite and > 0) before any tensor byte is read, then copies the tensors into
+ * one device allocation on the current device: int8_tensorwise + convrot (group 256) as stored (a scalar scale expanded
+ * to rows), convrot_w4a4 and asym_w4a8_int8 packed as stored for the tiers that decode them on the device. q / k / v
+ * stored apart are stacked into the fused QKV matrix. Everything else in the file (text embedder, other models'
+ * tensors) is ignored. Errors: B2_ERR_INVALID_ARGUMENT with a message that names the file and the tensor. */
+int b2_dit_file_open(const char* path, b2_dit_file** out);
+int b2_dit_file_get_info(const b2_dit_file* file, b2_dit_file_info* info);
+/* The loaded model; blocks[] always, the shell tensors when has_shell. Valid until b2_dit_file_close. */
+const b2_dit_model* b2_dit_file_model(const b2_dit_file* file);
+/* Host fp32 copy of the timestep MLP for b2_time_vector_fp32, or NULL. The file's bf16 values are exact in fp32; the
+ * reference runs this MLP in bf16 through cuBLASLt (moss_dit.cpp:970-990) unless a fp32 replacement is installed
+ * (distill.h), so results agree with its fp32 form, not bit for bit with its bf16 form. */
+const b2_time_embedding* b2_dit_file_time_embedding(const b2_dit_file* file);
+void b2_dit_file_close(b2_dit_file* file);
+
 /* Every mbarrier wait inside the tensor-core kernels is bounded (200 ms); a CTA whose wait expired raises a device word,
  * drains and returns instead of hanging. This reads the two words (GEMM, attention): 0 = no wait ever expired on this device.
  * Synchronises the device; for tests and post-mortems, not for the hot path. No counterpart in the reference (its

@@ -20,6 +20,7 @@ EXPORTS = [
     "b2_cfg_combine", "b2_slg_correct", "b2_euler_update", "b2_ab2_update", "b2_guided_velocity_step",
     "b2_latent_to_tokens", "b2_tokens_to_latent", "b2_linear_fp32_row", "b2_rms_norm_modulate", "b2_time_sinusoid",
     "b2_time_vector_fp32", "b2_linear_bf16_workspace_bytes", "b2_linear_bf16", "b2_dit_forward_workspace_bytes", "b2_dit_forward",
+    "b2_dit_file_open", "b2_dit_file_get_info", "b2_dit_file_model", "b2_dit_file_time_embedding", "b2_dit_file_close",
 ]
 
 
@@ -95,6 +96,11 @@ class Forward(C.Structure):
                 ("tier", C.c_int), ("attention", AttentionOptions), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
+class DitFileInfo(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("num_blocks", C.c_int), ("F", C.c_int), ("tier", C.c_int), ("has_shell", C.c_int),
+                ("has_time_embedding", C.c_int), ("device_bytes", C.c_size_t)]
+
+
 class GuidedStep(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("x", C.c_void_p), ("v_cond", C.c_void_p), ("v_uncond", C.c_void_p),
                 ("v_skip", C.c_void_p), ("v_prev", C.c_void_p), ("v_out", C.c_void_p), ("cfg_scale", C.c_float),
@@ -123,6 +129,12 @@ def lib() -> C.CDLL:
                                                       C.c_int, C.c_int]
         l.b2_block_quant_workspace_bytes.restype = C.c_size_t
         l.b2_block_quant_workspace_bytes.argtypes = [C.POINTER(BlockRun)]
+        l.b2_dit_file_model.restype = C.POINTER(DitModel)
+        l.b2_dit_file_model.argtypes = [C.c_void_p]
+        l.b2_dit_file_time_embedding.restype = C.POINTER(TimeEmbedding)
+        l.b2_dit_file_time_embedding.argtypes = [C.c_void_p]
+        l.b2_dit_file_close.restype = None
+        l.b2_dit_file_close.argtypes = [C.c_void_p]
         l.b2_linear_bf16_workspace_bytes.restype = C.c_size_t
         l.b2_dit_forward_workspace_bytes.restype = C.c_size_t
         l.b2_dit_forward_workspace_bytes.argtypes = [C.POINTER(DitModel), C.POINTER(Forward)]

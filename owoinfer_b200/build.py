@@ -11,7 +11,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "csrc", "build")
 LIB = os.path.join(HERE, "libowoinfer_b200.so")
-SOURCES = ["api.cu", "rotate_quantize.cu", "int8_gemm.cu", "attention.cu", "block.cu", "sp_block.cu", "sampler_step.cu", "dit_shell.cu"]
+SOURCES = ["api.cu", "rotate_quantize.cu", "int8_gemm.cu", "attention.cu", "block.cu", "sp_block.cu", "sampler_step.cu", "dit_shell.cu", "dit_loader.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "-I", os.path.join(ROOT, "include"), "-I", CSRC]

@@ -559,3 +559,48 @@ def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, wor
     f.workspace, f.workspace_bytes = workspace.data_ptr(), workspace.numel()
     check(_lib.lib().b2_dit_forward(C.byref(model.struct), C.byref(f), _stream()))
     return outs, workspace
+
+
+# ------------------------------------------------------------------------------------------------ weight ingestion
+
+class _Loaded:
+    """A struct that lives in a loaded file (b2_block_weights or b2_dit_model): `.struct` for the calls that take one."""
+
+    def __init__(self, struct, owner):
+        self.struct, self.owner = struct, owner
+
+
+class DitFile:
+    """b2_dit_file: the quantized DiT of a ComfyUI-layout safetensors file, on the current device."""
+
+    def __init__(self, path: str):
+        self.handle = C.c_void_p()
+        check(_lib.lib().b2_dit_file_open(str(path).encode(), C.byref(self.handle)))
+        info = _lib.DitFileInfo()
+        info.struct_size = C.sizeof(_lib.DitFileInfo)
+        check(_lib.lib().b2_dit_file_get_info(self.handle, C.byref(info)))
+        self.num_blocks, self.F, self.tier = info.num_blocks, info.F, info.tier
+        self.has_shell, self.has_time_embedding, self.device_bytes = bool(info.has_shell), bool(info.has_time_embedding), info.device_bytes
+        model = _lib.lib().b2_dit_file_model(self.handle).contents
+        self.model = _Loaded(model, self)
+        self.blocks = [_Loaded(model.blocks[i], self) for i in range(self.num_blocks)]
+
+    def time_vector(self, timestep: float):
+        import numpy as np
+        te = _lib.lib().b2_dit_file_time_embedding(self.handle)
+        if not te:
+            raise ValueError("the file has no time embedding")
+        out = np.empty(te.contents.dim, np.float32)
+        check(_lib.lib().b2_time_vector_fp32(te, C.c_float(timestep), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def close(self):
+        if self.handle:
+            _lib.lib().b2_dit_file_close(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -126,3 +126,26 @@ def cu_seqlens(lengths, device="cuda") -> torch.Tensor:
     for n in lengths:
         out.append(out[-1] + int(n))
     return torch.tensor(out, dtype=torch.int32, device=device)
+
+
+def write_int8_dit_file(path, blocks: int, F: int, D: int = 3072, seed: int = 7) -> int:
+    """A ComfyUI-layout safetensors file of `blocks` INT8 ConvRot blocks under the official tensor names (random bytes,
+    per-module comfy_quant configs): what the loader reads. Returns the file's size in bytes."""
+    import json
+    import os
+    from safetensors.torch import save_file
+    g = torch.Generator().manual_seed(seed)
+    conf = torch.tensor(list(json.dumps({"format": "int8_tensorwise", "convrot": True, "convrot_groupsize": 256}).encode()),
+                        dtype=torch.uint8)
+    t = {}
+    for b in range(blocks):
+        p = f"layers.{b}."
+        for name, n in (("norm1", D), ("norm2", D), ("q_norm", 128), ("k_norm", 128)):
+            t[p + name + ".weight"] = (1 + 0.1 * torch.randn(n, generator=g)).to(torch.bfloat16)
+        for name, (n, k) in (("qkv", (3 * D, D)), ("o", (D, D)), ("ffn_up_gate", (2 * F, D)), ("ffn_down", (D, F))):
+            m = p + "proj." + name
+            t[m + ".weight"] = torch.randint(-127, 128, (n, k), dtype=torch.int8, generator=g)
+            t[m + ".weight_scale"] = torch.rand(n, generator=g) * 0.02 + 0.001
+            t[m + ".comfy_quant"] = conf.clone()
+    save_file(t, str(path))
+    return os.path.getsize(path)
