@@ -541,22 +541,52 @@ struct b2_dit_file {
 namespace b2 {
 namespace {
 
+// Two pinned host buffers and a copy stream: the file read of one chunk overlaps the device copy of the one before.
+struct Staging {
+  static constexpr std::size_t kChunk = std::size_t{32} << 20;
+  unsigned char* buf[2] = {nullptr, nullptr};
+  cudaEvent_t done[2] = {nullptr, nullptr};
+  cudaStream_t stream = nullptr;
+  int next = 0;
+  Staging() {
+    if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) fail("cannot create a copy stream");
+    for (int i = 0; i < 2; ++i) {
+      if (cudaHostAlloc(reinterpret_cast<void**>(&buf[i]), kChunk, cudaHostAllocDefault) != cudaSuccess ||
+          cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming) != cudaSuccess) {
+        fail("cannot allocate the pinned staging buffers");
+      }
+    }
+  }
+  ~Staging() {
+    if (stream != nullptr) cudaStreamSynchronize(stream);
+    for (int i = 0; i < 2; ++i) {
+      if (done[i] != nullptr) cudaEventDestroy(done[i]);
+      if (buf[i] != nullptr) cudaFreeHost(buf[i]);
+    }
+    if (stream != nullptr) cudaStreamDestroy(stream);
+  }
+  void drain() {
+    if (const cudaError_t err = cudaStreamSynchronize(stream); err != cudaSuccess) fail(std::string("copy to the device failed: ") + cudaGetErrorString(err));
+  }
+};
+
 struct Loader {
   const File& f;
   b2_dit_file& out;
-  std::vector<unsigned char> staging;
+  Staging staging;
 
-  // Tensor bytes -> device, in chunks through one host buffer.
+  // Tensor bytes -> device, in chunks through the pinned buffers.
   void upload(const Entry& e, void* dst, std::uint64_t first = 0, std::uint64_t bytes = ~std::uint64_t{0}) {
     if (bytes == ~std::uint64_t{0}) bytes = e.nbytes - first;
-    constexpr std::size_t kChunk = std::size_t{64} << 20;
-    if (staging.size() < std::min<std::uint64_t>(bytes, kChunk)) staging.resize(static_cast<std::size_t>(std::min<std::uint64_t>(bytes, kChunk)));
-    for (std::uint64_t at = 0; at < bytes; at += kChunk) {
-      const std::size_t n = static_cast<std::size_t>(std::min<std::uint64_t>(kChunk, bytes - at));
-      f.read(e.offset + first + at, staging.data(), n);
-      if (const cudaError_t err = cudaMemcpy(static_cast<unsigned char*>(dst) + at, staging.data(), n, cudaMemcpyHostToDevice); err != cudaSuccess) {
-        fail(std::string("copy to the device failed: ") + cudaGetErrorString(err));
-      }
+    for (std::uint64_t at = 0; at < bytes; at += Staging::kChunk) {
+      const std::size_t n = static_cast<std::size_t>(std::min<std::uint64_t>(Staging::kChunk, bytes - at));
+      const int b = staging.next;
+      staging.next ^= 1;
+      cudaEventSynchronize(staging.done[b]);  // the copy that last used this buffer
+      f.read(e.offset + first + at, staging.buf[b], n);
+      cudaError_t err = cudaMemcpyAsync(static_cast<unsigned char*>(dst) + at, staging.buf[b], n, cudaMemcpyHostToDevice, staging.stream);
+      if (err == cudaSuccess) err = cudaEventRecord(staging.done[b], staging.stream);
+      if (err != cudaSuccess) fail(std::string("copy to the device failed: ") + cudaGetErrorString(err));
     }
   }
   std::vector<float> floats(const Entry& e) {
@@ -743,7 +773,7 @@ int b2_dit_file_open(const char* path, b2_dit_file** out) {
       return fail_cuda(op, err);
     }
     file->arena.size = need;
-    Loader ld{f, *file, {}};
+    Loader ld{f, *file};
     file->blocks.resize(static_cast<std::size_t>(blocks));
     for (int b = 0; b < blocks; ++b) {
       const std::string p = "layers." + std::to_string(b) + ".";
@@ -782,6 +812,7 @@ int b2_dit_file_open(const char* path, b2_dit_file** out) {
       file->te_b2 = host("time_embedding.2.bias", {kDim});
       file->time = b2_time_embedding{sizeof(b2_time_embedding), kDim, file->te_w0.data(), file->te_b0.data(), file->te_w2.data(), file->te_b2.data()};
     }
+    ld.staging.drain();
     file->info = b2_dit_file_info{sizeof(b2_dit_file_info), blocks, static_cast<int>(F), tier, shell ? 1 : 0, has_time ? 1 : 0, file->arena.used};
     *out = file.release();
     return B2_OK;
