@@ -311,6 +311,21 @@ typedef struct b2_block_run {
   int tier;                  /* B2_TIER_* */
   b2_attention_options attention;
   int fused_norm_rope;       /* -1 auto (>= 3072 tokens, dit_block_quant.cpp:32-35), 0 separate kernel, 1 in the pre-pass */
+  /* Reference keys and reference prefill (BlockRun of src/models/moss_dit/dit_block_fused.h:131-147). A caller built
+   * against a header that ends at fused_norm_rope passes that struct_size and gets none of it. All zero / NULL: unused.
+   * slot_rows > 0: attention reads keys and values from the region [slot A | the run's tokens | slot B], slot_rows rows
+   * per slot; sequence i's keys are rows [k0 + cu_seqlens_k[i], k0 + cu_seqlens_k[i + 1]) of it, k0 <= k1 bound the rows
+   * the run reads, and max_seqlen covers the key lengths. slot_kv[s]: bf16 [slot_rows, 2 D], k | v per token as
+   * kv_tap wrote them (after QK-norm and RoPE), copied into slot s before attention; NULL for a slot the run does not
+   * read. QK-norm + RoPE then run as their own kernel on the run's own rows. */
+  int64_t slot_rows;
+  const void* slot_kv[2];
+  const int32_t* cu_seqlens_k; /* device int32 [batch + 1] */
+  int64_t k0, k1;
+  /* kv_tap != NULL: after QK-norm and RoPE the run's k and v rows are copied there as bf16 [tokens, 2 D]
+   * (tap_reference_kv, dit_block_fused.h:151); tap_only != 0: the block ends there, x untouched. */
+  void* kv_tap;
+  int tap_only;
 } b2_block_run;
 
 size_t b2_block_quant_workspace_bytes(const b2_block_run* run);

@@ -10,6 +10,8 @@
 // 590-599; W4A4-through-INT8 branch lines 352-355, 465-466, 520-525, 584-585).
 #include <algorithm>
 #include <cmath>
+#include <cstddef>
+#include <cstring>
 #include <string>
 
 #include "common.cuh"
@@ -27,9 +29,20 @@ struct Workspace {
   std::size_t attn_ws_bytes;
 };
 
-Workspace carve(const b2_block_run* run) {
+// The run as this file reads it: a caller's struct may end before the reference-key fields (an older header).
+constexpr std::size_t kRunCoreBytes = offsetof(b2_block_run, slot_rows);
+b2_block_run whole_run(const b2_block_run* run) {
+  b2_block_run r{};
+  std::memcpy(&r, run, std::min(run->struct_size, sizeof r));
+  return r;
+}
+
+Workspace carve(const b2_block_run* run_in) {
   Workspace w{};
+  const b2_block_run whole = whole_run(run_in);
+  const b2_block_run* run = &whole;
   const std::size_t L = static_cast<std::size_t>(run->tokens), D = static_cast<std::size_t>(run->D), F = static_cast<std::size_t>(run->F);
+  const std::size_t region = L + 2 * static_cast<std::size_t>(run->slot_rows);  // [slot A | tokens | slot B]
   const std::size_t kmax = std::max(D, F);
   std::size_t at = 0;
   const auto take = [&](std::size_t bytes) {
@@ -40,25 +53,35 @@ Workspace carve(const b2_block_run* run) {
   w.xq = take(L * kmax);
   w.x4 = take(run->tier == B2_TIER_W4A4_VIA_INT8 ? L * kmax / 2 : 0);
   w.scale = take(L * 4);
-  w.qkv = take(L * 3 * D * 2);
+  w.qkv = take(region * 3 * D * 2);
   w.attn = take(L * D * 2);
   w.ffn = take(L * F * 2);
   w.w_unpack = take(run->tier == B2_TIER_INT8 ? 0 : std::max({3 * D * D, 2 * F * D, D * F}));
-  w.attn_ws_bytes = b2_attention_q8_workspace_bytes(&run->attention, run->tokens, run->tokens, run->batch, run->max_seqlen,
-                                                    run->heads, run->heads);
+  w.attn_ws_bytes = b2_attention_q8_workspace_bytes(&run->attention, run->tokens, static_cast<std::int64_t>(region), run->batch,
+                                                    run->max_seqlen, run->heads, run->heads);
   w.attn_ws = take(w.attn_ws_bytes);
   w.total = at;
   return w;
 }
 
 int check_run(const char* op, const b2_block_run* run) {
-  if (run == nullptr || run->struct_size < sizeof(b2_block_run)) return fail_invalid(op, "run is null or from an older header");
+  if (run == nullptr || run->struct_size < kRunCoreBytes) return fail_invalid(op, "run is null or from an older header");
   if (run->tokens < 0 || run->D <= 0 || run->F <= 0 || run->heads <= 0 || run->D != run->heads * 128) {
     return fail_invalid(op, "needs D == heads * 128, F > 0, tokens >= 0");
   }
   if (run->D % 256 != 0 || run->F % 256 != 0) return fail_invalid(op, "D and F must be multiples of 256 (rotation groups)");
   if (run->tier < B2_TIER_INT8 || run->tier > B2_TIER_W4A8) return fail_invalid(op, "unknown tier");
   if (run->batch < 1 || run->max_seqlen < 1 || run->cu_seqlens == nullptr) return fail_invalid(op, "needs cu_seqlens, batch >= 1, max_seqlen >= 1");
+  const b2_block_run r = whole_run(run);
+  if (r.slot_rows < 0) return fail_invalid(op, "negative slot_rows");
+  if (r.slot_rows > 0) {
+    if (r.cu_seqlens_k == nullptr || r.k0 < 0 || r.k1 < r.k0 || r.k1 > r.tokens + 2 * r.slot_rows) {
+      return fail_invalid(op, "reference slots need cu_seqlens_k and 0 <= k0 <= k1 <= tokens + 2 * slot_rows");
+    }
+    if ((r.k0 < r.slot_rows && r.slot_kv[0] == nullptr) || (r.k1 > r.slot_rows + r.tokens && r.slot_kv[1] == nullptr)) {
+      return fail_invalid(op, "the key rows reach into a slot that has no slot_kv");
+    }
+  }
   return B2_OK;
 }
 
@@ -91,9 +114,11 @@ size_t b2_block_quant_workspace_bytes(const b2_block_run* run) {
   return carve(run).total;
 }
 
-int b2_run_block_quant(const b2_block_weights* w, const b2_block_buffers* a, const b2_block_run* run, void* stream) {
+int b2_run_block_quant(const b2_block_weights* w, const b2_block_buffers* a, const b2_block_run* run_in, void* stream) {
   constexpr const char* op = "run_block_quant";
-  if (const int rc = check_run(op, run)) return rc;
+  if (const int rc = check_run(op, run_in)) return rc;
+  const b2_block_run whole = whole_run(run_in);
+  const b2_block_run* run = &whole;
   if (w == nullptr || a == nullptr || w->struct_size < sizeof(b2_block_weights) || a->struct_size < sizeof(b2_block_buffers)) {
     return fail_invalid(op, "weights or buffers are null or from an older header");
   }
@@ -150,23 +175,50 @@ int b2_run_block_quant(const b2_block_weights* w, const b2_block_buffers* a, con
     return b2_int8_gemm_situ_glu(&o, out, ldo, st, B2_TILE_AUTO);
   };
 
-  // QKV projection.
+  // QKV projection, into the rows after slot A when the run reads reference keys.
+  const std::int64_t slot = run->slot_rows;
+  __nv_bfloat16* own = qkv + slot * 3 * D;
   if (const int rc = quant_norm(w->norm1, mod + 1 * D, mod + 0 * D)) return rc;
-  if (const int rc = site(w->qkv, 3 * D, D, 0, nullptr, qkv, 3 * D)) return rc;
+  if (const int rc = site(w->qkv, 3 * D, D, 0, nullptr, own, 3 * D)) return rc;
 
-  // Attention. QK-norm + RoPE inside the pre-pass from 3072 tokens on (same bits either way).
-  const bool fused = run->fused_norm_rope < 0 ? L >= kFusedNormRopeMinTokens : run->fused_norm_rope != 0;
+  // Attention. QK-norm + RoPE inside the pre-pass from 3072 tokens on (same bits either way); as their own kernel when
+  // the keys are not the run's own rows alone or the rows are tapped after them.
+  const bool plain = slot == 0 && run->kv_tap == nullptr;
+  const bool fused = plain && (run->fused_norm_rope < 0 ? L >= kFusedNormRopeMinTokens : run->fused_norm_rope != 0);
   if (!fused) {
-    if (const int rc = b2_qk_norm_rope_moss(qkv, 3 * D, L, run->heads, w->q_norm, w->k_norm, a->rope, 128, st)) return rc;
+    if (const int rc = b2_qk_norm_rope_moss(own, 3 * D, L, run->heads, w->q_norm, w->k_norm, a->rope, 128, st)) return rc;
   }
-  const b2_view3 vq{qkv, L, run->heads, 3 * D, 128}, vk{qkv + D, L, run->heads, 3 * D, 128}, vv{qkv + 2 * D, L, run->heads, 3 * D, 128};
+  const std::size_t kv_bytes = static_cast<std::size_t>(2 * D) * sizeof(__nv_bfloat16), row_bytes = static_cast<std::size_t>(3 * D) * sizeof(__nv_bfloat16);
+  if (run->kv_tap != nullptr) {
+    // tap_reference_kv: the k | v columns of every row, contiguous.
+    if (const cudaError_t e = cudaMemcpy2DAsync(run->kv_tap, kv_bytes, own + D, row_bytes, kv_bytes, static_cast<std::size_t>(L), cudaMemcpyDeviceToDevice, st); e != cudaSuccess) {
+      return fail_cuda(op, e);
+    }
+    if (run->tap_only != 0) return B2_OK;
+  }
+  std::int64_t k0 = 0, k_rows = L;
+  const std::int32_t* cu_k = run->cu_seqlens;
+  if (slot > 0) {
+    // The cached keys and values into the k | v columns of the slots the key rows reach (moss_dit.cpp:1441-1452).
+    for (int s2 = 0; s2 < 2; ++s2) {
+      const bool read = s2 == 0 ? run->k0 < slot : run->k1 > slot + L;
+      if (!read) continue;
+      __nv_bfloat16* dst = qkv + (s2 == 0 ? 0 : slot + L) * 3 * D + D;
+      if (const cudaError_t e = cudaMemcpy2DAsync(dst, row_bytes, run->slot_kv[s2], kv_bytes, kv_bytes, static_cast<std::size_t>(slot), cudaMemcpyDeviceToDevice, st); e != cudaSuccess) {
+        return fail_cuda(op, e);
+      }
+    }
+    k0 = run->k0, k_rows = run->k1 - run->k0, cu_k = run->cu_seqlens_k;
+  }
+  const b2_view3 vq{own, L, run->heads, 3 * D, 128};
+  const b2_view3 vk{qkv + k0 * 3 * D + D, k_rows, run->heads, 3 * D, 128}, vv{qkv + k0 * 3 * D + 2 * D, k_rows, run->heads, 3 * D, 128};
   const b2_view3 vo{attn, L, run->heads, D, 128};
   const b2_qk_norm_rope nr{w->q_norm, w->k_norm, a->rope, 128};
   b2_attention_options ao = run->attention;
   if (ao.variant == 0) ao.variant = B2_ATTENTION_Q8_FP8_F32ACC;
   const float sm_scale = static_cast<float>(1.0 / std::sqrt(128.0));
-  if (const int rc = b2_attention_q8(&ao, &vq, &vk, &vv, &vo, run->cu_seqlens, run->cu_seqlens, run->batch, run->max_seqlen,
-                                     sm_scale, base + ws.attn_ws, ws.attn_ws_bytes, st, fused ? &nr : nullptr)) {
+  if (const int rc = b2_attention_q8(&ao, &vq, &vk, &vv, &vo, run->cu_seqlens, cu_k, run->batch, run->max_seqlen, sm_scale,
+                                     base + ws.attn_ws, ws.attn_ws_bytes, st, fused ? &nr : nullptr)) {
     return rc;
   }
 
