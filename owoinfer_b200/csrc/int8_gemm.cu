@@ -156,15 +156,22 @@ __device__ __forceinline__ float situ_factor_full(const std::uint16_t* full, std
 // kCtas == 2: a CTA pair shares one 256 x 256 tile; each CTA stages its 128 rows of A and 128 of the 256 rows of B.
 // kW4: the stage also holds the packed 4-bit weight tile (half the bytes of the INT8 one) that the TMA warp brings and
 // the converter warps expand into the B operand.
-template <int kBN, int kCtas, bool kW4 = false>
+// kOutWarps > 0: the epilogue warps pass their output rows (and, gated residual, the residual rows) through a staging
+// tile of shared memory each, so that global memory sees whole 128-byte lines; the ring gives up a stage for it.
+constexpr int kOutRowBytes = 144;                       // 64 bf16 of a row + 16 bytes, which spreads the rows over the banks
+constexpr int kOutWarpBytes = 32 * kOutRowBytes;        // one epilogue warp's 32 rows x 64 columns
+template <int kBN, int kCtas, bool kW4 = false, int kOutWarps = 0>
 struct Shape {
-  static constexpr int kStages = kW4 ? 4 : (kBN == 256 && kCtas == 1) ? 4 : 6;
+  static constexpr int kStages = kW4 ? 4 : (kBN == 256 && kCtas == 1) ? (kOutWarps > 0 ? 3 : 4) : kOutWarps > 0 ? 5 : 6;
   static constexpr int kABytes = kBM * kBK;
   static constexpr int kBBytes = (kBN / kCtas) * kBK;
   static constexpr int kPBytes = kW4 ? kBBytes / 2 : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kPBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+  static constexpr int kOutBytes = kOutWarps * kOutWarpBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024;  // + alignment slack
 };
+// Which epilogues stage their rows: plain and gated residual (SiTU-GLU and the accumulator dump store as before).
+__host__ __device__ constexpr int out_warps(Epi e, int bn, bool w4) { return (e == Epi::kPlain || e == Epi::kGatedResidual) ? epi_warps(e, bn, w4) : 0; }
 
 // Eight 4-bit codes (nibble i = column i) -> eight INT8 values through the 16-entry table `t` of their (row, group):
 // two byte permutes pick among entries 0..7 and 8..15 by the low three bits of each code, a third takes the right one by
@@ -188,7 +195,7 @@ __global__ void __launch_bounds__(threads_of(kEpi, kBN, kW4), 1)
 int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   static_assert(kCtas == 1 || kBN == 256, "CTA pairs run 256 x 256 tiles");
   static_assert(!kW4 || kBN / kCtas == 128, "W4A8: one weight row of the stage per converter thread");
-  using S = Shape<kBN, kCtas, kW4>;
+  using S = Shape<kBN, kCtas, kW4, out_warps(kEpi, kBN, kW4)>;
   const std::uint32_t rank = kCtas == 2 ? cluster_ctarank() : 0u;   // CTA of the pair; rank 0 issues the MMAs
   const int tile0 = kCtas == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int tile_step = kCtas == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
@@ -212,6 +219,9 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const auto a_addr = [&](int s) { return tiles_base + static_cast<std::uint32_t>(s) * S::kStageBytes; };
   const auto b_addr = [&](int s) { return a_addr(s) + S::kABytes; };
   const auto p_addr = [&](int s) { return b_addr(s) + S::kBBytes; };
+  // The epilogue warps' staging tiles, after the ring (generic address of the same 1024-byte aligned base).
+  [[maybe_unused]] std::uint8_t* const out_stage =
+      smem_raw + (tiles_base - smem_u32(smem_raw)) + static_cast<std::uint32_t>(S::kStages) * S::kStageBytes;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -578,58 +588,91 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           tmem_ld_32x32(t_row + c0, *reinterpret_cast<std::uint32_t(*)[32]>(&r[0]));
           tmem_ld_32x32(t_row + c0 + 32, *reinterpret_cast<std::uint32_t(*)[32]>(&r[32]));
           tmem_ld_wait();
-          if (!row_ok) continue;
           if constexpr (kEpi == Epi::kAcc) {
+            if (!row_ok) continue;
             std::int32_t* arow = p.acc + static_cast<std::int64_t>(row) * p.ldacc;
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
               if (col0 + c0 + i < p.n) arow[col0 + c0 + i] = static_cast<std::int32_t>(r[i]);
             }
           } else {
-            __nv_bfloat16* orow = p.out + static_cast<std::int64_t>(row) * p.ldo;
-            uint4 resv[8];
+            // The warp's 32 rows x 64 columns pass through its staging tile: lane l moves the 16-byte piece l % 8 of rows
+            // l / 8, l / 8 + 4, ..., so that every global access of a quarter-warp is one whole 128-byte line, while
+            // thread r computes row r. (One thread per row straight to global memory made every request touch 32
+            // half-used sectors; at K = 3072 the stores and the residual loads, not the MMAs, set the pace of a tile.)
+            std::uint8_t* stage_tile = out_stage + (warp - 2) * kOutWarpBytes;
+            const int piece = lane & 7, sub = lane >> 3;
+            const int row_base = mt * (kBM * kCtas) + static_cast<int>(rank) * kBM + quarter * 32;
+            const int pcol = col0 + c0 + 8 * piece;  // first column of this lane's piece
+            // Where the piece of row r lives in global memory (plain: possibly in a column chunk of its own).
+            const auto global_piece = [&](int r) {
+              __nv_bfloat16* dst = p.out + static_cast<std::int64_t>(r) * p.ldo + pcol;
+              if constexpr (kEpi == Epi::kPlain) {
+                if (p.chunk_cols != 0) {  // chunk_cols % 8 == 0: a piece of 8 columns stays inside one chunk
+                  const int chunk = pcol / p.chunk_cols;
+                  dst = p.out + chunk * p.chunk_stride + static_cast<std::int64_t>(r) * p.ldo + (pcol - chunk * p.chunk_cols);
+                }
+              }
+              return dst;
+            };
             if constexpr (kEpi == Epi::kGatedResidual) {
+              __syncwarp();  // the tile's previous use (this warp's stores of the chunk before) is over
+              if (pcol < p.n) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const int r = row_base + sub + 4 * i;
+                  if (r < p.m) {
+                    *reinterpret_cast<uint4*>(stage_tile + (sub + 4 * i) * kOutRowBytes + 16 * piece) =
+                        *reinterpret_cast<const uint4*>(global_piece(r));
+                  }
+                }
+              }
+              __syncwarp();
+            }
+            if (row_ok) {
 #pragma unroll
               for (int v = 0; v < 8; ++v) {
-                if (col0 + c0 + 8 * v < p.n) resv[v] = *reinterpret_cast<const uint4*>(orow + col0 + c0 + 8 * v);
+                const int col = col0 + c0 + 8 * v;
+                if (col >= p.n) continue;  // n % 8 == 0: a vector of 8 columns is all in or all out
+                const int lc = c0 - col_half * kHalfCols + 8 * v;  // column inside this warp's half
+                const float4 w0 = *reinterpret_cast<const float4*>(vec + lc);
+                const float4 w1 = *reinterpret_cast<const float4*>(vec + lc + 4);
+                const float4 b0 = *reinterpret_cast<const float4*>(vec + 128 + lc);
+                const float4 b1 = *reinterpret_cast<const float4*>(vec + 128 + lc + 4);
+                const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                const float bias[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                float y[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  y[i] = fadd(fmul(fmul(__int2float_rn(static_cast<int>(r[8 * v + i])), xs), ws[i]), bias[i]);
+                }
+                uint4* mine = reinterpret_cast<uint4*>(stage_tile + lane * kOutRowBytes + 16 * v);
+                if constexpr (kEpi == Epi::kGatedResidual) {
+                  const float4 g0 = *reinterpret_cast<const float4*>(vec + 256 + lc);
+                  const float4 g1 = *reinterpret_cast<const float4*>(vec + 256 + lc + 4);
+                  const float gate[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                  float res[8];
+                  unpack8(*mine, res);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) y[i] = fadd(res[i], rbf(fmul(rbf(y[i]), gate[i])));
+                }
+                *mine = make_uint4(pack2(y[0], y[1]), pack2(y[2], y[3]), pack2(y[4], y[5]), pack2(y[6], y[7]));
               }
             }
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              const int col = col0 + c0 + 8 * v;
-              if (col >= p.n) continue;  // n % 8 == 0: a vector of 8 columns is all in or all out
-              const int lc = c0 - col_half * kHalfCols + 8 * v;  // column inside this warp's half
-              const float4 w0 = *reinterpret_cast<const float4*>(vec + lc);
-              const float4 w1 = *reinterpret_cast<const float4*>(vec + lc + 4);
-              const float4 b0 = *reinterpret_cast<const float4*>(vec + 128 + lc);
-              const float4 b1 = *reinterpret_cast<const float4*>(vec + 128 + lc + 4);
-              const float ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-              const float bias[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-              float y[8];
+            __syncwarp();
+            if (pcol < p.n) {
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                y[i] = fadd(fmul(fmul(__int2float_rn(static_cast<int>(r[8 * v + i])), xs), ws[i]), bias[i]);
-              }
-              if constexpr (kEpi == Epi::kGatedResidual) {
-                const float4 g0 = *reinterpret_cast<const float4*>(vec + 256 + lc);
-                const float4 g1 = *reinterpret_cast<const float4*>(vec + 256 + lc + 4);
-                const float gate[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-                float res[8];
-                unpack8(resv[v], res);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) y[i] = fadd(res[i], rbf(fmul(rbf(y[i]), gate[i])));
-              }
-              const uint4 packed = make_uint4(pack2(y[0], y[1]), pack2(y[2], y[3]), pack2(y[4], y[5]), pack2(y[6], y[7]));
-              if constexpr (kEpi == Epi::kPlain) {
-                __nv_bfloat16* dst = orow + col;
-                if (p.chunk_cols != 0) {  // chunk_cols % 8 == 0: a vector of 8 columns stays inside one chunk
-                  const int chunk = col / p.chunk_cols;
-                  dst = p.out + chunk * p.chunk_stride + static_cast<std::int64_t>(row) * p.ldo + (col - chunk * p.chunk_cols);
+                const int r = row_base + sub + 4 * i;
+                if (r < p.m) {
+                  const uint4 packed = *reinterpret_cast<const uint4*>(stage_tile + (sub + 4 * i) * kOutRowBytes + 16 * piece);
+                  // Plain: streaming, the output must not push the weight out of L2. Gated residual: in place, x stays.
+                  if constexpr (kEpi == Epi::kPlain) __stcs(reinterpret_cast<uint4*>(global_piece(r)), packed);
+                  else *reinterpret_cast<uint4*>(global_piece(r)) = packed;
                 }
-                __stcs(reinterpret_cast<uint4*>(dst), packed);  // streaming, as above
               }
-              else *reinterpret_cast<uint4*>(orow + col) = packed;
             }
+            if constexpr (kEpi == Epi::kPlain) __syncwarp();  // before the next chunk's rows overwrite the tile
           }
         }
       }
@@ -774,7 +817,7 @@ int check_output(const char* op, const char* name, const void* p, std::int64_t l
 // kW4: a->w points at the packed 4-bit codes [n, k / 2] (p.w4_* describe the rest of the weight).
 template <int kBN, Epi kEpi, int kCtas, bool kW4 = false>
 int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaStream_t stream) {
-  using S = Shape<kBN, kCtas, kW4>;
+  using S = Shape<kBN, kCtas, kW4, out_warps(kEpi, kBN, kW4)>;
   CUtensorMap map_a, map_b;
   if (!make_tensor_map_2d(&map_a, a->x_q, static_cast<std::uint64_t>(a->k), static_cast<std::uint64_t>(a->m),
                           static_cast<std::uint64_t>(a->ldx), kBK, 128, op)) {
@@ -806,13 +849,16 @@ int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaS
   if constexpr (kEpi == Epi::kSituGlu) p.n_tiles = (p.half + 127) / 128;
   else p.n_tiles = (p.n + kBN - 1) / kBN;
   const int total = p.m_tiles * p.n_tiles;
-  // M tiles per band: what one wave covers across all N tiles. A weight too large to stay in L2 beside the activations
-  // (above 32 MB) instead streams past a band of activation rows held to a fifth of L2 (band_m x tile rows x K bytes):
-  // it is then read from HBM once per band rather than once per M tile.
+  // M tiles per band. A weight that fits in L2 beside the activation rows in flight (up to 48 MB: every site of the block
+  // but up_gate) is swept by short bands of one or two M tiles, so that it is touched again every few microseconds and
+  // stays resident while the activations stream through once: at K = 12288 (down) bands of 8 M tiles read 687 MB from
+  // DRAM per launch, bands of 2 read 514 MB, the time the same or slightly better. A larger weight instead streams past
+  // a band of activation rows held to a fifth of L2 (band_m x tile rows x K bytes): it is then read from HBM once per
+  // band rather than once per M tile.
   {
-    p.band_m = std::max(1, (sm_count() / kCtas) / std::max(1, p.n_tiles));
+    p.band_m = std::min(2, std::max(1, (sm_count() / kCtas) / std::max(1, p.n_tiles)));
     const std::int64_t a_tile_bytes = static_cast<std::int64_t>(kBM * kCtas) * p.k;
-    if (static_cast<std::int64_t>(p.n) * p.k > (32 << 20)) {
+    if (static_cast<std::int64_t>(p.n) * p.k > (48 << 20)) {
       const std::int64_t resident = std::min<std::int64_t>(p.m_tiles, (25 << 20) / std::max<std::int64_t>(1, a_tile_bytes));
       p.band_m = std::max(p.band_m, static_cast<int>(resident));
     }
