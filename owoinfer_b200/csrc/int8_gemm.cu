@@ -68,6 +68,7 @@ struct GemmParams {
   int m, n, k;        // GEMM rows, GEMM columns (2F for SiTU-GLU), reduction length
   int m_tiles, n_tiles;
   int band_m;         // M tiles per band of the tile order (see tile_coords)
+  int situ_wide;      // SiTU-GLU: out, ldo and F allow 16-byte stores (else 8-byte stores straight from the threads)
   int half;           // SiTU-GLU: F
   const float* xs;
   const float* ws;
@@ -160,18 +161,20 @@ __device__ __forceinline__ float situ_factor_full(const std::uint16_t* full, std
 // tile of shared memory each, so that global memory sees whole 128-byte lines; the ring gives up a stage for it.
 constexpr int kOutRowBytes = 144;                       // 64 bf16 of a row + 16 bytes, which spreads the rows over the banks
 constexpr int kOutWarpBytes = 32 * kOutRowBytes;        // one epilogue warp's 32 rows x 64 columns
-template <int kBN, int kCtas, bool kW4 = false, int kOutWarps = 0>
+constexpr int kSituOutWarpBytes = 32 * 64;          // SiTU-GLU: one warp's 32 rows x 32 output columns, swizzled, no padding
+template <int kBN, int kCtas, bool kW4 = false, int kOutWarps = 0, int kOutWarpSize = kOutWarpBytes>
 struct Shape {
   static constexpr int kStages = kW4 ? 4 : (kBN == 256 && kCtas == 1) ? (kOutWarps > 0 ? 3 : 4) : kOutWarps > 0 ? 5 : 6;
   static constexpr int kABytes = kBM * kBK;
   static constexpr int kBBytes = (kBN / kCtas) * kBK;
   static constexpr int kPBytes = kW4 ? kBBytes / 2 : 0;
   static constexpr int kStageBytes = kABytes + kBBytes + kPBytes;
-  static constexpr int kOutBytes = kOutWarps * kOutWarpBytes;
+  static constexpr int kOutBytes = kOutWarps * kOutWarpSize;
   static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024;  // + alignment slack
 };
-// Which epilogues stage their rows: plain and gated residual (SiTU-GLU and the accumulator dump store as before).
-__host__ __device__ constexpr int out_warps(Epi e, int bn, bool w4) { return (e == Epi::kPlain || e == Epi::kGatedResidual) ? epi_warps(e, bn, w4) : 0; }
+// Which epilogues stage their rows: all but the accumulator dump.
+__host__ __device__ constexpr int out_warps(Epi e, int bn, bool w4) { return e == Epi::kAcc ? 0 : epi_warps(e, bn, w4); }
+__host__ __device__ constexpr int out_warp_bytes(Epi e) { return e == Epi::kSituGlu ? kSituOutWarpBytes : kOutWarpBytes; }
 
 // Eight 4-bit codes (nibble i = column i) -> eight INT8 values through the 16-entry table `t` of their (row, group):
 // two byte permutes pick among entries 0..7 and 8..15 by the low three bits of each code, a third takes the right one by
@@ -195,7 +198,7 @@ __global__ void __launch_bounds__(threads_of(kEpi, kBN, kW4), 1)
 int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   static_assert(kCtas == 1 || kBN == 256, "CTA pairs run 256 x 256 tiles");
   static_assert(!kW4 || kBN / kCtas == 128, "W4A8: one weight row of the stage per converter thread");
-  using S = Shape<kBN, kCtas, kW4, out_warps(kEpi, kBN, kW4)>;
+  using S = Shape<kBN, kCtas, kW4, out_warps(kEpi, kBN, kW4), out_warp_bytes(kEpi)>;
   const std::uint32_t rank = kCtas == 2 ? cluster_ctarank() : 0u;   // CTA of the pair; rank 0 issues the MMAs
   const int tile0 = kCtas == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int tile_step = kCtas == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
@@ -539,11 +542,19 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           tmem_ld_32x32(t_row + c0, rh);
           tmem_ld_32x32(t_row + 128 + c0, rg);
           tmem_ld_wait();
+          // The warp's 32 rows x 32 output columns pass through its staging tile (64 bytes per row, the 16-byte pieces of
+          // a row permuted by the row so that neither side has bank conflicts): thread r computes row r, lane l stores
+          // piece l % 4 of rows l / 4, l / 4 + 8, ..., so that global memory sees 64 contiguous bytes per row and whole
+          // sectors (one thread per row storing 8 bytes at a time made every request touch 32 quarter-used sectors).
+          std::uint8_t* stage_tile = out_stage + (warp - 2) * kSituOutWarpBytes;
+          const bool wide = p.situ_wide != 0;  // the same in every thread
+          __syncwarp();  // the stores of the part before have read the tile
           if (row_ok) {
-            __nv_bfloat16* orow = p.out + static_cast<std::int64_t>(row) * p.ldo;
+            uint2 even = make_uint2(0u, 0u);
 #pragma unroll
             for (int v = 0; v < 8; ++v) {
               const int col = col0 + c0 + 4 * v;
+              uint2 packed = make_uint2(0u, 0u);
               if (col < p.half) {
                 const float4 wh = *reinterpret_cast<const float4*>(pvec + 4 * v);
                 const float4 wg = *reinterpret_cast<const float4*>(pvec + 32 + 4 * v);
@@ -573,8 +584,33 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     o[i] = fmul(situ_factor_full(p.t_gate, both[i] >> 16), situ_factor_full(p.t_hidden, both[i] & 0xFFFFu));
                   }
                 }
-                // Streaming store: the output (4 x the weight's size) must not push the weight out of L2.
-                __stcs(reinterpret_cast<uint2*>(orow + col), make_uint2(pack2(o[0], o[1]), pack2(o[2], o[3])));
+                packed = make_uint2(pack2(o[0], o[1]), pack2(o[2], o[3]));
+              }
+              if (!wide) {
+                // An output whose rows or width only allow 8-byte accesses: straight from the thread, as before.
+                if (col < p.half) __stcs(reinterpret_cast<uint2*>(p.out + static_cast<std::int64_t>(row) * p.ldo + col), packed);
+              } else if ((v & 1) == 0) {
+                even = packed;
+              } else {
+                const int pc = (v >> 1) ^ ((lane >> 1) & 3);
+                *reinterpret_cast<uint4*>(stage_tile + lane * 64 + 16 * pc) = make_uint4(even.x, even.y, packed.x, packed.y);
+              }
+            }
+          }
+          __syncwarp();
+          if (wide) {
+            const int pc = lane & 3, sub = lane >> 2;
+            const int row_base = mt * (kBM * kCtas) + static_cast<int>(rank) * kBM + quarter * 32;
+            const int pcol = col0 + c0 + 8 * pc;
+            if (pcol < p.half) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int rr = sub + 8 * i, r = row_base + rr;
+                if (r < p.m) {
+                  const uint4 out16 = *reinterpret_cast<const uint4*>(stage_tile + rr * 64 + 16 * (pc ^ ((rr >> 1) & 3)));
+                  // Streaming store: the output (4 x the weight's size) must not push the weight out of L2.
+                  __stcs(reinterpret_cast<uint4*>(p.out + static_cast<std::int64_t>(r) * p.ldo + pcol), out16);
+                }
               }
             }
           }
@@ -817,7 +853,7 @@ int check_output(const char* op, const char* name, const void* p, std::int64_t l
 // kW4: a->w points at the packed 4-bit codes [n, k / 2] (p.w4_* describe the rest of the weight).
 template <int kBN, Epi kEpi, int kCtas, bool kW4 = false>
 int launch_kernel(const char* op, const b2_int8_operands* a, GemmParams p, cudaStream_t stream) {
-  using S = Shape<kBN, kCtas, kW4, out_warps(kEpi, kBN, kW4)>;
+  using S = Shape<kBN, kCtas, kW4, out_warps(kEpi, kBN, kW4), out_warp_bytes(kEpi)>;
   CUtensorMap map_a, map_b;
   if (!make_tensor_map_2d(&map_a, a->x_q, static_cast<std::uint64_t>(a->k), static_cast<std::uint64_t>(a->m),
                           static_cast<std::uint64_t>(a->ldx), kBK, 128, op)) {
@@ -1046,6 +1082,7 @@ int b2_int8_gemm_situ_glu(const b2_int8_operands* op_, void* out, int64_t ldo, v
   GemmParams p = base_params(op_);
   p.half = static_cast<int>(op_->n / 2);
   p.out = static_cast<__nv_bfloat16*>(out), p.ldo = ldo;
+  p.situ_wide = aligned_to(out, 16) && ldo % 8 == 0 && p.half % 8 == 0;
   p.t_gate = t.gate, p.t_hidden = t.hidden;
   return dispatch<Epi::kSituGlu>(op, op_, p, as_stream(stream), tile);
 }
@@ -1110,6 +1147,7 @@ int b2_w4a8_gemm(const int8_t* x_q, int64_t ldx, const float* x_scale, const b2_
     SituTables t;
     if (const int rc = situ_tables(as_stream(stream), &t)) return rc;
     p.half = static_cast<int>(n / 2), p.t_gate = t.gate, p.t_hidden = t.hidden;
+    p.situ_wide = aligned_to(out, 16) && ldo % 8 == 0 && p.half % 8 == 0;
     return dispatch_w4<Epi::kSituGlu>(op, &f, p, as_stream(stream));
   }
   if (const int rc = b2_decode_grouped_int8(w->packed, w->s_rel, w->scale_kind, w->codebook, n, k, w->group, scratch, nullptr, stream)) {
