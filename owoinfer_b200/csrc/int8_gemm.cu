@@ -123,14 +123,18 @@ __device__ __forceinline__ bool wait_bar(std::uint32_t bar, std::uint32_t parity
 
 __device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 
-// 8 consecutive bf16 (16 bytes) -> floats.
-__device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
-  const std::uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-  }
+// Packed bf16 pairs: a * b and a + b, each half rounded once to bf16. For bf16 operands that is the fp32 operation followed
+// by a rounding to bf16 (the fp32 product of two bf16 values is exact; the fp32 sum is exact unless the smaller operand is
+// below the larger one's bf16 half-step, where both forms return the larger).
+__device__ __forceinline__ std::uint32_t bmul2(std::uint32_t a, std::uint32_t b) {
+  std::uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ std::uint32_t badd2(std::uint32_t a, std::uint32_t b) {
+  std::uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
 __device__ __forceinline__ std::uint32_t pack2(float lo, float hi) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
@@ -511,15 +515,15 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               }
             }
             if constexpr (kEpi == Epi::kGatedResidual) {
+              // The gate stays packed bf16 (two words for these four columns): the epilogue multiplies packed pairs.
               const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.gate + col));
-              g = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
-                              __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u));
+              g = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), 0.f, 0.f);
             }
           }
           *reinterpret_cast<float4*>(vec + j) = w;
           if constexpr (kEpi != Epi::kSituGlu) {
             *reinterpret_cast<float4*>(vec + 128 + j) = b;
-            *reinterpret_cast<float4*>(vec + 256 + j) = g;
+            *reinterpret_cast<float2*>(vec + 256 + j / 2) = make_float2(g.x, g.y);  // word c / 2 = columns c, c + 1
           }
         }
       }
@@ -683,16 +687,15 @@ int8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                   y[i] = fadd(fmul(fmul(__int2float_rn(static_cast<int>(r[8 * v + i])), xs), ws[i]), bias[i]);
                 }
                 uint4* mine = reinterpret_cast<uint4*>(stage_tile + lane * kOutRowBytes + 16 * v);
+                uint4 out8 = make_uint4(pack2(y[0], y[1]), pack2(y[2], y[3]), pack2(y[4], y[5]), pack2(y[6], y[7]));
                 if constexpr (kEpi == Epi::kGatedResidual) {
-                  const float4 g0 = *reinterpret_cast<const float4*>(vec + 256 + lc);
-                  const float4 g1 = *reinterpret_cast<const float4*>(vec + 256 + lc + 4);
-                  const float gate[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-                  float res[8];
-                  unpack8(*mine, res);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) y[i] = fadd(res[i], rbf(fmul(rbf(y[i]), gate[i])));
+                  // res + bf16(bf16(y) * gate), rounded to bf16: every operand is a bf16 value after the first rounding,
+                  // so both steps run on packed pairs.
+                  const uint4 g = *reinterpret_cast<const uint4*>(vec + 256 + lc / 2), res = *mine;
+                  out8 = make_uint4(badd2(res.x, bmul2(out8.x, g.x)), badd2(res.y, bmul2(out8.y, g.y)),
+                                    badd2(res.z, bmul2(out8.z, g.z)), badd2(res.w, bmul2(out8.w, g.w)));
                 }
-                *mine = make_uint4(pack2(y[0], y[1]), pack2(y[2], y[3]), pack2(y[4], y[5]), pack2(y[6], y[7]));
+                *mine = out8;
               }
             }
             __syncwarp();
