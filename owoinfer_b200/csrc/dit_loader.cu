@@ -820,6 +820,8 @@ int b2_dit_file_open(const char* path, b2_dit_file** out) {
     return fail_invalid(op, std::string(path) + ": " + e.what);
   } catch (const std::bad_alloc&) {
     return fail_status(B2_ERR_INTERNAL, op, "out of host memory");
+  } catch (const std::exception& e) {  // nothing may cross the C boundary
+    return fail_status(B2_ERR_INTERNAL, op, std::string(path) + ": " + e.what());
   }
 }
 

@@ -374,7 +374,20 @@ size_t b2_dit_forward_workspace_bytes(const b2_dit_model* model, const b2_forwar
   return c.total;
 }
 
-int b2_dit_forward(const b2_dit_model* model, const b2_forward* forward, void* stream_) {
+namespace {
+int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void* stream_);
+}
+
+int b2_dit_forward(const b2_dit_model* model, const b2_forward* forward, void* stream) {
+  try {
+    return dit_forward_impl(model, forward, stream);
+  } catch (const std::exception& e) {  // host containers may throw; nothing may cross the C boundary
+    return fail_status(B2_ERR_INTERNAL, "dit_forward", e.what());
+  }
+}
+
+namespace {
+int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void* stream_) {
   constexpr const char* op = "dit_forward";
   std::vector<std::int64_t> off;
   Carve c{};
@@ -482,5 +495,6 @@ int b2_dit_forward(const b2_dit_model* model, const b2_forward* forward, void* s
   }
   return B2_OK;
 }
+}  // namespace
 
 }  // extern "C"
