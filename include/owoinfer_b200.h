@@ -189,6 +189,10 @@ int b2_qk_norm_rope_moss(void* qkv, int64_t ld, int64_t tokens, int heads, const
 
 /* kernels::moss_rope_table (src/kernels/basic/rope.h:37): out bf16 [height*width + text_length, 128] stride ld. */
 int b2_moss_rope_table(void* out, int64_t ld, int height, int width, int text_length, void* stream);
+/* kernels::moss_rope_table_reference (src/kernels/basic/rope.h:43; rope.cu:53-71, 169-180): the rows of reference image
+ * `index` (0-based) of the edit layout, bf16 [height * width, 128]: coordinates (index + 1, 0, centred row, centred
+ * column) with moss_rope_table's bands and arithmetic. */
+int b2_moss_rope_table_reference(void* out, int64_t ld, int height, int width, int index, void* stream);
 
 /* attention_q8::Variant / Options (src/kernels/attention_q8/attention_q8.h:75-88). Only the e4m3 P·V variant with fp32
  * accumulation (MI_ATTENTION_Q8_FP8_F32ACC, include/mossinfer/mossinfer.h:269) exists here: tcgen05 accumulates in
@@ -474,6 +478,11 @@ typedef struct b2_dit_model {
   const void* final_norm;       /* bf16 [D] */
   const void* final_w;          /* bf16 [128, D] */
   const void* final_bias;       /* bf16 [128] or NULL */
+  /* MossDit::InputExtension (moss_dit.h; set_input_extension, moss_dit.cpp:1120-1133): an embedder over the latent's 128
+   * channels followed by ext_channels more, used instead of video_w / video_bias when ext_w is not NULL. */
+  const void* ext_w;            /* bf16 [D, 128 + ext_channels] or NULL */
+  const void* ext_bias;         /* bf16 [D] */
+  int ext_channels;             /* > 0 and a multiple of 8 with ext_w */
 } b2_dit_model;
 
 /* MossDit::Row (moss_dit.h): one sequence of the forward = the video tokens of a latent followed by its text tokens. */
@@ -496,7 +505,36 @@ typedef struct b2_forward {
   b2_attention_options attention;
   void* workspace;           /* b2_dit_forward_workspace_bytes(), 256-byte aligned */
   size_t workspace_bytes;
+  /* With the model's input extension: device f32 [num_latents, ext_channels, height, width]. */
+  const float* extra;
+  /* Reference images (MossDit::set_references, moss_dit.cpp:1068-1090): the cache b2_dit_prefill_references filled,
+   * device bf16 [num_blocks, ref_tokens, 2 D]; NULL / 0 without. A forward with references takes one latent and at
+   * most two rows; every sequence then attends to its own keys plus the reference keys in a slot next to it
+   * (moss_dit.cpp:1283-1300). */
+  const void* ref_kv;
+  int64_t ref_tokens;
 } b2_forward;
+
+/* MossDit::prefill_references (moss_dit.cpp:1479-1580): the reference latents (each device f32 [128, h_i, w_i], their
+ * grids in heights / widths) run through every block as one sequence without text, under the modulation of
+ * time_vector (the time vector of timestep 0 there), each with its reference RoPE table; block b's k | v rows after
+ * QK-norm and RoPE land in kv_out[b] (device bf16 [num_blocks, sum h_i w_i, 2 D]). With the model's input extension
+ * the extra channels are zero. workspace: b2_dit_prefill_workspace_bytes(). */
+typedef struct b2_prefill {
+  size_t struct_size;
+  const float* const* latents; /* host array of num_refs device pointers */
+  const int* heights;
+  const int* widths;
+  int num_refs;
+  const float* time_vector;    /* host f32 [D] */
+  void* kv_out;
+  int tier;
+  b2_attention_options attention;
+  void* workspace;
+  size_t workspace_bytes;
+} b2_prefill;
+size_t b2_dit_prefill_workspace_bytes(const b2_dit_model* model, const b2_prefill* prefill);
+int b2_dit_prefill_references(const b2_dit_model* model, const b2_prefill* prefill, void* stream);
 
 size_t b2_dit_forward_workspace_bytes(const b2_dit_model* model, const b2_forward* forward);
 /* MossDit::forward (moss_dit.cpp:1181-1477) for the all-quantized block path, without reference slots, input extension,

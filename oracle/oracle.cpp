@@ -547,6 +547,24 @@ void orc_moss_rope_table(u16* out, i64 ld, int height, int width, int text_lengt
   }
 }
 
+// kernels::moss_rope_table_reference (src/kernels/basic/rope.cu:53-71): reference image `index` of the edit layout at
+// coordinates (index + 1, 0, centred row, centred column); no text rows.
+void orc_moss_rope_table_reference(u16* out, i64 ld, int height, int width, int index, const float* bands) {
+  const i64 hw = static_cast<i64>(height) * width;
+  const float h_mid = static_cast<float>((height - 1) / 2.0), w_mid = static_cast<float>((width - 1) / 2.0);
+  for (i64 r = 0; r < hw; ++r) {
+    for (int c = 0; c < 128; ++c) {
+      const int p = c & 63, axis = p >> 4, band = p & 15;
+      float coord = 0.0f;
+      if (axis == 0) coord = static_cast<float>(index + 1);
+      if (axis == 2) coord = static_cast<float>(r / width) - h_mid;
+      if (axis == 3) coord = static_cast<float>(r % width) - w_mid;
+      const float phase = coord * bands[band];
+      out[r * ld + c] = f2bf(c < 64 ? std::sin(phase) : std::cos(phase));
+    }
+  }
+}
+
 // Attention pre-pass (unfused form; with QK-norm + RoPE the reference's fused pass gives the same bits as
 // orc_qk_norm_rope followed by this). src/kernels/attention_q8/q8_preprocess.cu:67-385.
 //   k_mean[b,h,c]   = bf16(sum / len), the sum taken as: 16 row-threads each adding tokens row, row+16, ... of a 512-key

@@ -261,6 +261,13 @@ def moss_rope_table(height, width, text_length, bands=None):
     return out
 
 
+def moss_rope_table_reference(height, width, index, bands=None):
+    out = np.empty((height * width, 128), np.uint16)
+    b = _c(MOSS_ROPE_BANDS if bands is None else bands, np.float32)
+    lib().orc_moss_rope_table_reference(_p(out), i64(128), i32(height), i32(width), i32(index), _p(b))
+    return out
+
+
 def attention_prepass(qkv, cu, heads, max_seqlen, v_range=448.0):
     """qkv: uint16 [total, 3*heads*128] (q | k | v columns). Returns dict of natural-layout outputs."""
     qkv = _c(qkv, np.uint16)

@@ -20,6 +20,7 @@ EXPORTS = [
     "b2_cfg_combine", "b2_slg_correct", "b2_euler_update", "b2_ab2_update", "b2_guided_velocity_step",
     "b2_latent_to_tokens", "b2_tokens_to_latent", "b2_linear_fp32_row", "b2_rms_norm_modulate", "b2_time_sinusoid",
     "b2_time_vector_fp32", "b2_linear_bf16_workspace_bytes", "b2_linear_bf16", "b2_dit_forward_workspace_bytes", "b2_dit_forward",
+    "b2_moss_rope_table_reference", "b2_dit_prefill_workspace_bytes", "b2_dit_prefill_references",
     "b2_dit_file_open", "b2_dit_file_get_info", "b2_dit_file_model", "b2_dit_file_time_embedding", "b2_dit_file_close",
 ]
 
@@ -84,7 +85,7 @@ class DitModel(C.Structure):
                 ("F", C.c_int), ("heads", C.c_int), ("latent_channels", C.c_int), ("block_mod_w", C.c_void_p),
                 ("block_mod_bias", C.c_void_p), ("head_mod_w", C.c_void_p), ("head_mod_bias", C.c_void_p),
                 ("video_w", C.c_void_p), ("video_bias", C.c_void_p), ("final_norm", C.c_void_p), ("final_w", C.c_void_p),
-                ("final_bias", C.c_void_p)]
+                ("final_bias", C.c_void_p), ("ext_w", C.c_void_p), ("ext_bias", C.c_void_p), ("ext_channels", C.c_int)]
 
 
 class ForwardRow(C.Structure):
@@ -94,6 +95,13 @@ class ForwardRow(C.Structure):
 class Forward(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("latents", C.c_void_p), ("num_latents", C.c_int), ("height", C.c_int),
                 ("width", C.c_int), ("time_vector", C.c_void_p), ("rows", C.POINTER(ForwardRow)), ("num_rows", C.c_int),
+                ("tier", C.c_int), ("attention", AttentionOptions), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+                ("extra", C.c_void_p), ("ref_kv", C.c_void_p), ("ref_tokens", C.c_int64)]
+
+
+class Prefill(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("latents", C.POINTER(C.c_void_p)), ("heights", C.POINTER(C.c_int)),
+                ("widths", C.POINTER(C.c_int)), ("num_refs", C.c_int), ("time_vector", C.c_void_p), ("kv_out", C.c_void_p),
                 ("tier", C.c_int), ("attention", AttentionOptions), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
@@ -130,6 +138,8 @@ def lib() -> C.CDLL:
                                                       C.c_int, C.c_int]
         l.b2_block_quant_workspace_bytes.restype = C.c_size_t
         l.b2_block_quant_workspace_bytes.argtypes = [C.POINTER(BlockRun)]
+        l.b2_dit_prefill_workspace_bytes.restype = C.c_size_t
+        l.b2_dit_prefill_workspace_bytes.argtypes = [C.POINTER(DitModel), C.POINTER(Prefill)]
         l.b2_dit_file_model.restype = C.POINTER(DitModel)
         l.b2_dit_file_model.argtypes = [C.c_void_p]
         l.b2_dit_file_time_embedding.restype = C.POINTER(TimeEmbedding)

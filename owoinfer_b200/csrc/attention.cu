@@ -227,8 +227,9 @@ constexpr RopeBands kBands = {{1.f, 0.562341332f, 0.316227764f, 0.177827939f, 0.
 // One thread per table element: row r, column c; columns 0..63 hold sin, 64..127 cos, over (axis, band) = (c % 64 / 16,
 // c % 16); image tokens (r < height * width) have coordinates (0, text_length, row - (H-1)/2, col - (W-1)/2), text token i
 // has (0, i, 0, 0).
+// Reference tokens of the edit layout (image_r, image_f = reference index + 1, 0; no text rows) use the same arithmetic.
 __global__ void rope_table_kernel(__nv_bfloat16* out, std::int64_t ld, std::int64_t n, int height, int width,
-                                  int text_length, const RopeBands bands) {
+                                  float image_r, float image_f, const RopeBands bands) {
   const std::int64_t hw = static_cast<std::int64_t>(height) * width;
   const float h_mid = static_cast<float>((height - 1) / 2.0), w_mid = static_cast<float>((width - 1) / 2.0);
   const std::int64_t total = n * 128;
@@ -238,7 +239,8 @@ __global__ void rope_table_kernel(__nv_bfloat16* out, std::int64_t ld, std::int6
     const int c = static_cast<int>(i & 127), pz = c & 63, axis = pz >> 4, band = pz & 15;
     float coord = 0.f;
     if (r < hw) {
-      if (axis == 1) coord = static_cast<float>(text_length);
+      if (axis == 0) coord = image_r;
+      if (axis == 1) coord = image_f;
       if (axis == 2) coord = __fsub_rn(static_cast<float>(r / width), h_mid);
       if (axis == 3) coord = __fsub_rn(static_cast<float>(r % width), w_mid);
     } else if (axis == 1) {
@@ -1183,7 +1185,21 @@ int b2_moss_rope_table(void* out, int64_t ld, int height, int width, int text_le
   if (n == 0) return B2_OK;
   if (out == nullptr) return fail_invalid(op, "null table");
   const unsigned blocks = static_cast<unsigned>(std::min<std::int64_t>((n * 128 + 255) / 256, 148 * 32));
-  rope_table_kernel<<<blocks, 256, 0, as_stream(stream)>>>(static_cast<__nv_bfloat16*>(out), ld, n, height, width, text_length, kBands);
+  rope_table_kernel<<<blocks, 256, 0, as_stream(stream)>>>(static_cast<__nv_bfloat16*>(out), ld, n, height, width, 0.f,
+                                                           static_cast<float>(text_length), kBands);
+  return check_launch(op);
+}
+
+int b2_moss_rope_table_reference(void* out, int64_t ld, int height, int width, int index, void* stream) {
+  constexpr const char* op = "moss_rope_table_reference";
+  if (height < 1 || width < 1 || index < 0 || index >= (1 << 24) || ld < 128) {
+    return fail_invalid(op, "needs a grid of at least 1 x 1, 0 <= index < 2^24 and ld >= 128");
+  }
+  if (out == nullptr) return fail_invalid(op, "null table");
+  const std::int64_t n = static_cast<std::int64_t>(height) * width;
+  const unsigned blocks = static_cast<unsigned>(std::min<std::int64_t>((n * 128 + 255) / 256, 148 * 32));
+  rope_table_kernel<<<blocks, 256, 0, as_stream(stream)>>>(static_cast<__nv_bfloat16*>(out), ld, n, height, width,
+                                                           static_cast<float>(index + 1), 0.f, kBands);
   return check_launch(op);
 }
 

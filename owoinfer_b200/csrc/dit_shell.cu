@@ -178,8 +178,9 @@ int lt_handle(cublasLtHandle_t* out) {
 struct Run {
   int r0, r1;        // rows [r0, r1)
   std::int64_t t0, t1;
-  int cu_at;         // index of its first entry in the cu_seqlens array
+  int cu_at;         // index of its first entry in the cu_seqlens array (and in the cu_seqlens_k array)
   int max_len;
+  bool slot_a = false, slot_b = false;  // with reference images: which slots its key rows reach
 };
 
 std::size_t align_up(std::size_t v) { return (v + 255) & ~static_cast<std::size_t>(255); }
@@ -187,6 +188,35 @@ std::size_t align_up(std::size_t v) { return (v + 255) & ~static_cast<std::size_
 struct Carve {
   std::size_t x, rope, mod, head, time, tokens, y, cu, lt, block, total;
 };
+
+int check_extension(const char* op, const b2_dit_model* m) {
+  if (m->ext_w == nullptr) return B2_OK;
+  if (m->ext_bias == nullptr || m->ext_channels <= 0 || m->ext_channels % 8 != 0 || m->ext_channels > 4096) {
+    return fail_invalid(op, "an input extension needs a bias and 8, 16, ... extra channels");
+  }
+  return B2_OK;
+}
+
+// embed_video (moss_dit.cpp:1100-1118): latent plane [128, hw] (+ the extension's plane [c, hw], or zeros for it when
+// `extra` is null) -> tokens -> linear -> rows of x.
+int embed_video(const b2_dit_model& m, const float* plane, const float* extra, std::int64_t hw, __nv_bfloat16* tokens,
+                __nv_bfloat16* dst, void* lt_ws, cudaStream_t stream) {
+  const char* op = "dit_forward";
+  const std::int64_t D = m.D;
+  if (m.ext_w == nullptr) {
+    if (const int rc = b2_latent_to_tokens(plane, 128, hw, tokens, 128, stream)) return rc;
+    return b2_linear_bf16(tokens, 128, m.video_w, m.video_bias, dst, D, hw, static_cast<int>(D), 128, lt_ws, kLtWorkspaceBytes, stream);
+  }
+  const int cin = 128 + m.ext_channels;
+  if (const int rc = b2_latent_to_tokens(plane, 128, hw, tokens, cin, stream)) return rc;
+  if (extra != nullptr) {
+    if (const int rc = b2_latent_to_tokens(extra, m.ext_channels, hw, tokens + 128, cin, stream)) return rc;
+  } else if (const cudaError_t e = cudaMemset2DAsync(tokens + 128, static_cast<std::size_t>(cin) * 2, 0, static_cast<std::size_t>(m.ext_channels) * 2,
+                                                     static_cast<std::size_t>(hw), stream); e != cudaSuccess) {
+    return fail_cuda(op, e);
+  }
+  return b2_linear_bf16(tokens, cin, m.ext_w, m.ext_bias, dst, D, hw, static_cast<int>(D), cin, lt_ws, kLtWorkspaceBytes, stream);
+}
 
 int plan_forward(const char* op, const b2_dit_model* m, const b2_forward* f, std::vector<std::int64_t>* off, Carve* c,
                  b2_block_run* widest) {
@@ -199,6 +229,13 @@ int plan_forward(const char* op, const b2_dit_model* m, const b2_forward* f, std
   }
   if (f->height < 1 || f->width < 1 || f->num_latents < 1 || f->num_rows < 1 || f->num_rows > 8 || f->rows == nullptr) {
     return fail_invalid(op, "needs a latent grid, 1..8 rows and at least one latent");
+  }
+  if (const int rc = check_extension(op, m)) return rc;
+  if (m->ext_w != nullptr && f->extra == nullptr) return fail_invalid(op, "the model's input extension needs the forward's extra latents");
+  const std::int64_t R = f->ref_tokens;
+  if (R < 0 || (R > 0) != (f->ref_kv != nullptr)) return fail_invalid(op, "ref_kv and ref_tokens go together");
+  if (R > 0 && (f->num_latents != 1 || f->num_rows > 2)) {
+    return fail_invalid(op, "a forward with reference images takes one latent and at most 2 rows");
   }
   const std::int64_t hw = static_cast<std::int64_t>(f->height) * f->width;
   off->assign(1, 0);
@@ -218,6 +255,10 @@ int plan_forward(const char* op, const b2_dit_model* m, const b2_forward* f, std
   widest->max_seqlen = max_len, widest->tier = f->tier, widest->attention = f->attention, widest->fused_norm_rope = -1;
   static const std::int32_t placeholder = 0;  // sizing reads no offsets; every run of the forward brings its own
   widest->cu_seqlens = &placeholder;
+  if (R > 0) {
+    widest->slot_rows = R, widest->slot_kv[0] = widest->slot_kv[1] = &placeholder, widest->cu_seqlens_k = &placeholder;
+    widest->k0 = 0, widest->k1 = total + 2 * R, widest->max_seqlen = static_cast<int>(max_len + R);
+  }
   const std::size_t block_bytes = b2_block_quant_workspace_bytes(widest);
   if (block_bytes == 0) return B2_ERR_INVALID_ARGUMENT;  // the block's own message stands
   const std::size_t D = static_cast<std::size_t>(m->D);
@@ -232,9 +273,9 @@ int plan_forward(const char* op, const b2_dit_model* m, const b2_forward* f, std
   c->mod = take(6 * D * 2);
   c->head = take(2 * D * 2);
   c->time = take(D * 4);
-  c->tokens = take(static_cast<std::size_t>(hw) * 128 * 2);
+  c->tokens = take(static_cast<std::size_t>(hw) * static_cast<std::size_t>(128 + (m->ext_w != nullptr ? m->ext_channels : 0)) * 2);
   c->y = take(static_cast<std::size_t>(hw) * D * 2);
-  c->cu = take(static_cast<std::size_t>(f->num_rows + 1) * (f->num_rows * (f->num_rows + 1) / 2) * 4);
+  c->cu = take(static_cast<std::size_t>(f->num_rows + 1) * (f->num_rows * (f->num_rows + 1) / 2) * 4 * 2);  // cu_seqlens and cu_seqlens_k
   c->lt = take(kLtWorkspaceBytes);
   c->block = take(block_bytes);
   c->total = at;
@@ -397,7 +438,7 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
   const b2_forward& f = *forward;
   if (f.latents == nullptr || f.time_vector == nullptr) return fail_invalid(op, "needs latents and the host time vector");
   if (m.block_mod_w == nullptr || m.block_mod_bias == nullptr || m.head_mod_w == nullptr || m.head_mod_bias == nullptr ||
-      m.video_w == nullptr || m.final_norm == nullptr || m.final_w == nullptr) {
+      (m.video_w == nullptr && m.ext_w == nullptr) || m.final_norm == nullptr || m.final_w == nullptr) {
     return fail_invalid(op, "the model lacks a modulation, embedder or head tensor");
   }
   if (f.workspace == nullptr || !aligned_to(f.workspace, 256) || f.workspace_bytes < c.total) {
@@ -417,7 +458,8 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
 
   // The runs of contiguous rows that execute each block, one varlen batch each with zero-based cu_seqlens; a run that
   // recurs (the usual case: no skips, one run over all rows) is described once.
-  std::vector<std::int32_t> cu;
+  std::vector<std::int32_t> cu, cu_k;
+  const std::int64_t R = f.ref_tokens;
   std::map<std::pair<int, int>, Run> unique;
   std::vector<std::vector<Run>> block_runs(static_cast<std::size_t>(m.num_blocks));
   for (int bi = 0; bi < m.num_blocks; ++bi) {
@@ -434,7 +476,15 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
         Run run{r0, r1, off[static_cast<std::size_t>(r0)], off[static_cast<std::size_t>(r1)], static_cast<int>(cu.size()), 0};
         for (int r = r0; r <= r1; ++r) {
           cu.push_back(static_cast<std::int32_t>(off[static_cast<std::size_t>(r)] - off[static_cast<std::size_t>(r0)]));
+          // With reference images sequence j of the run also has j slots of R rows before its keys begin: the first
+          // sequence takes slot A when the run starts at row 0, every other one slot B (moss_dit.cpp:1283-1300).
+          cu_k.push_back(static_cast<std::int32_t>(cu.back() + static_cast<std::int64_t>(r - r0) * R));
           if (r < r1) run.max_len = std::max<int>(run.max_len, static_cast<int>(off[static_cast<std::size_t>(r) + 1] - off[static_cast<std::size_t>(r)]));
+        }
+        if (R > 0) {
+          run.slot_a = r0 == 0;
+          run.slot_b = r1 - r0 == 2 || !run.slot_a;
+          run.max_len += static_cast<int>(R);
         }
         it = unique.emplace(std::make_pair(r0, r1), run).first;
       }
@@ -443,6 +493,10 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
     }
   }
   if (const int rc = write_words(op, cu_dev, cu.data(), cu.size(), stream)) return rc;
+  std::int32_t* cu_k_dev = cu_dev + cu.size();
+  if (R > 0) {
+    if (const int rc = write_words(op, cu_k_dev, cu_k.data(), cu_k.size(), stream)) return rc;
+  }
   // time_modulation: the time vector (host, fp32) through the two modulation linears.
   if (const int rc = write_words(op, time, f.time_vector, static_cast<std::size_t>(D), stream)) return rc;
   if (const int rc = b2_linear_fp32_row(m.block_mod_w, time, m.block_mod_bias, mod, static_cast<int>(6 * D), static_cast<int>(D), stream)) return rc;
@@ -461,9 +515,10 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
     }
     __nv_bfloat16* xr = x + off[static_cast<std::size_t>(r)] * D;
     if (src == r) {
-      const float* plane = f.latents + static_cast<std::size_t>(f.rows[r].latent) * 128 * static_cast<std::size_t>(hw);
-      if (const int rc = b2_latent_to_tokens(plane, 128, hw, tokens, 128, stream)) return rc;
-      if (const int rc = b2_linear_bf16(tokens, 128, m.video_w, m.video_bias, xr, D, hw, static_cast<int>(D), 128, base + c.lt, kLtWorkspaceBytes, stream)) return rc;
+      const std::size_t l = static_cast<std::size_t>(f.rows[r].latent), plane_size = static_cast<std::size_t>(hw);
+      const float* plane = f.latents + l * 128 * plane_size;
+      const float* extra = m.ext_w != nullptr ? f.extra + l * static_cast<std::size_t>(m.ext_channels) * plane_size : nullptr;
+      if (const int rc = embed_video(m, plane, extra, hw, tokens, xr, base + c.lt, stream)) return rc;
     } else if (const cudaError_t e = cudaMemcpyAsync(xr, x + off[static_cast<std::size_t>(src)] * D, static_cast<std::size_t>(hw) * row_bytes, cudaMemcpyDeviceToDevice, stream); e != cudaSuccess) {
       return fail_cuda(op, e);
     }
@@ -478,6 +533,14 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
     for (const Run& run : block_runs[static_cast<std::size_t>(bi)]) {
       b2_block_run br = widest;
       br.tokens = run.t1 - run.t0, br.batch = run.r1 - run.r0, br.max_seqlen = run.max_len, br.cu_seqlens = cu_dev + run.cu_at;
+      br.slot_rows = 0, br.slot_kv[0] = br.slot_kv[1] = nullptr, br.cu_seqlens_k = nullptr, br.k0 = br.k1 = 0;
+      if (R > 0) {
+        // Block bi's cached reference keys and values, the same rows for both slots.
+        const __nv_bfloat16* cached = static_cast<const __nv_bfloat16*>(f.ref_kv) + static_cast<std::size_t>(bi) * static_cast<std::size_t>(R) * 2 * static_cast<std::size_t>(D);
+        br.slot_rows = R, br.cu_seqlens_k = cu_k_dev + run.cu_at;
+        br.slot_kv[0] = run.slot_a ? cached : nullptr, br.slot_kv[1] = run.slot_b ? cached : nullptr;
+        br.k0 = run.slot_a ? 0 : R, br.k1 = R + br.tokens + (run.slot_b ? R : 0);
+      }
       b2_block_buffers bb{};
       bb.struct_size = sizeof bb;
       bb.x = x + run.t0 * D, bb.mod = mod, bb.rope = rope + run.t0 * 128, bb.workspace = base + c.block;
@@ -496,5 +559,119 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
   return B2_OK;
 }
 }  // namespace
+
+namespace {
+struct PrefillCarve {
+  std::size_t x, rope, mod, time, tokens, cu, lt, block, total;
+};
+int plan_prefill(const char* op, const b2_dit_model* m, const b2_prefill* f, std::int64_t* total, PrefillCarve* c, b2_block_run* run) {
+  if (m == nullptr || f == nullptr || m->struct_size < sizeof(b2_dit_model) || f->struct_size < sizeof(b2_prefill)) {
+    return fail_invalid(op, "null model or prefill, or one from an older header");
+  }
+  if (m->blocks == nullptr || m->num_blocks < 1 || m->D != 3072 || m->heads != 24 || m->latent_channels != 128) {
+    return fail_invalid(op, "needs the blocks of the MOSS-Image DiT");
+  }
+  if (const int rc = check_extension(op, m)) return rc;
+  if (f->num_refs < 1 || f->latents == nullptr || f->heights == nullptr || f->widths == nullptr) {
+    return fail_invalid(op, "prefill needs at least one reference latent with its grid");
+  }
+  std::int64_t n = 0, widest = 0;
+  for (int i = 0; i < f->num_refs; ++i) {
+    if (f->latents[i] == nullptr || f->heights[i] < 1 || f->widths[i] < 1) return fail_invalid(op, "a reference latent must be [128, h, w]");
+    const std::int64_t hw = static_cast<std::int64_t>(f->heights[i]) * f->widths[i];
+    n += hw, widest = std::max(widest, hw);
+    if (n > (1 << 20)) return fail_invalid(op, "the reference images hold too many tokens");
+  }
+  *total = n;
+  *run = b2_block_run{};
+  run->struct_size = sizeof(b2_block_run);
+  run->tokens = n, run->D = m->D, run->F = m->F, run->heads = m->heads, run->batch = 1, run->max_seqlen = static_cast<int>(n);
+  run->tier = f->tier, run->attention = f->attention, run->fused_norm_rope = -1;
+  static const std::int32_t placeholder = 0;
+  run->cu_seqlens = &placeholder;
+  const std::size_t block_bytes = b2_block_quant_workspace_bytes(run);
+  if (block_bytes == 0) return B2_ERR_INVALID_ARGUMENT;
+  const std::size_t D = static_cast<std::size_t>(m->D);
+  std::size_t at = 0;
+  const auto take = [&](std::size_t bytes) {
+    const std::size_t here = at;
+    at += align_up(bytes);
+    return here;
+  };
+  c->x = take(static_cast<std::size_t>(n) * D * 2);
+  c->rope = take(static_cast<std::size_t>(n) * 128 * 2);
+  c->mod = take(6 * D * 2);
+  c->time = take(D * 4);
+  c->tokens = take(static_cast<std::size_t>(widest) * static_cast<std::size_t>(128 + (m->ext_w != nullptr ? m->ext_channels : 0)) * 2);
+  c->cu = take(256);
+  c->lt = take(kLtWorkspaceBytes);
+  c->block = take(block_bytes);
+  c->total = at;
+  return B2_OK;
+}
+
+int prefill_impl(const b2_dit_model* model, const b2_prefill* prefill, void* stream_) {
+  constexpr const char* op = "dit_prefill_references";
+  std::int64_t total = 0;
+  PrefillCarve c{};
+  b2_block_run run{};
+  if (const int rc = plan_prefill(op, model, prefill, &total, &c, &run)) return rc;
+  const b2_dit_model& m = *model;
+  const b2_prefill& f = *prefill;
+  if (f.time_vector == nullptr || f.kv_out == nullptr) return fail_invalid(op, "needs the host time vector and the cache to fill");
+  if (m.block_mod_w == nullptr || m.block_mod_bias == nullptr || (m.video_w == nullptr && m.ext_w == nullptr)) {
+    return fail_invalid(op, "the model lacks the modulation linear or the embedder");
+  }
+  if (f.workspace == nullptr || !aligned_to(f.workspace, 256) || f.workspace_bytes < c.total) {
+    return fail_invalid(op, "workspace must be 256-byte aligned and hold b2_dit_prefill_workspace_bytes() = " + std::to_string(c.total));
+  }
+  cudaStream_t stream = as_stream(stream_);
+  const std::int64_t D = m.D;
+  unsigned char* base = static_cast<unsigned char*>(f.workspace);
+  __nv_bfloat16* x = reinterpret_cast<__nv_bfloat16*>(base + c.x);
+  __nv_bfloat16* rope = reinterpret_cast<__nv_bfloat16*>(base + c.rope);
+  __nv_bfloat16* mod = reinterpret_cast<__nv_bfloat16*>(base + c.mod);
+  float* time = reinterpret_cast<float*>(base + c.time);
+  __nv_bfloat16* tokens = reinterpret_cast<__nv_bfloat16*>(base + c.tokens);
+  std::int32_t* cu_dev = reinterpret_cast<std::int32_t*>(base + c.cu);
+  const std::int32_t cu[2] = {0, static_cast<std::int32_t>(total)};
+  if (const int rc = write_words(op, cu_dev, cu, 2, stream)) return rc;
+  if (const int rc = write_words(op, time, f.time_vector, static_cast<std::size_t>(D), stream)) return rc;
+  if (const int rc = b2_linear_fp32_row(m.block_mod_w, time, m.block_mod_bias, mod, static_cast<int>(6 * D), static_cast<int>(D), stream)) return rc;
+  std::int64_t at = 0;
+  for (int i = 0; i < f.num_refs; ++i) {
+    const std::int64_t hw = static_cast<std::int64_t>(f.heights[i]) * f.widths[i];
+    if (const int rc = b2_moss_rope_table_reference(rope + at * 128, 128, f.heights[i], f.widths[i], i, stream)) return rc;
+    if (const int rc = embed_video(m, f.latents[i], nullptr, hw, tokens, x + at * D, base + c.lt, stream)) return rc;
+    at += hw;
+  }
+  run.cu_seqlens = cu_dev;
+  for (int bi = 0; bi < m.num_blocks; ++bi) {
+    b2_block_run tap = run;
+    tap.kv_tap = static_cast<__nv_bfloat16*>(f.kv_out) + static_cast<std::size_t>(bi) * static_cast<std::size_t>(total) * 2 * static_cast<std::size_t>(D);
+    b2_block_buffers bb{};
+    bb.struct_size = sizeof bb;
+    bb.x = x, bb.mod = mod, bb.rope = rope, bb.workspace = base + c.block, bb.workspace_bytes = c.total - c.block;
+    if (const int rc = b2_run_block_quant(&m.blocks[bi], &bb, &tap, stream)) return rc;
+  }
+  return B2_OK;
+}
+}  // namespace
+
+size_t b2_dit_prefill_workspace_bytes(const b2_dit_model* model, const b2_prefill* prefill) {
+  std::int64_t total = 0;
+  PrefillCarve c{};
+  b2_block_run run{};
+  if (plan_prefill("dit_prefill_workspace_bytes", model, prefill, &total, &c, &run) != B2_OK) return 0;
+  return c.total;
+}
+
+int b2_dit_prefill_references(const b2_dit_model* model, const b2_prefill* prefill, void* stream) {
+  try {
+    return prefill_impl(model, prefill, stream);
+  } catch (const std::exception& e) {  // nothing may cross the C boundary
+    return fail_status(B2_ERR_INTERNAL, "dit_prefill_references", e.what());
+  }
+}
 
 }  // extern "C"

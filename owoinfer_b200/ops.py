@@ -201,6 +201,13 @@ def moss_rope_table(height, width, text_length, device="cuda"):
     return out
 
 
+def moss_rope_table_reference(height, width, index, device="cuda"):
+    out = torch.empty((height * width, 128), dtype=torch.bfloat16, device=device)
+    check(_lib.lib().b2_moss_rope_table_reference(_ptr(out), C.c_int64(128), C.c_int(height), C.c_int(width), C.c_int(index),
+                                                  _stream()))
+    return out
+
+
 def _view3(t):
     return _lib.View3(t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), t.stride(1))
 
@@ -528,9 +535,9 @@ class DitModel:
     """b2_dit_model over torch tensors: `blocks` a list of BlockWeights, the rest device tensors (kept alive here)."""
 
     def __init__(self, blocks, F, block_mod_w, block_mod_bias, head_mod_w, head_mod_bias, video_w, video_bias, final_norm,
-                 final_w, final_bias, D=3072, heads=24):
+                 final_w, final_bias, D=3072, heads=24, ext_w=None, ext_bias=None):
         self.keep = (blocks, block_mod_w, block_mod_bias, head_mod_w, head_mod_bias, video_w, video_bias, final_norm, final_w,
-                     final_bias)
+                     final_bias, ext_w, ext_bias)
         self.arr = (_lib.BlockWeights * max(1, len(blocks)))(*[b.struct for b in blocks])
         m = _lib.DitModel()
         m.struct_size, m.blocks, m.num_blocks = C.sizeof(_lib.DitModel), self.arr, len(blocks)
@@ -538,10 +545,11 @@ class DitModel:
         p = lambda t: None if t is None else t.data_ptr()
         m.block_mod_w, m.block_mod_bias, m.head_mod_w, m.head_mod_bias = p(block_mod_w), p(block_mod_bias), p(head_mod_w), p(head_mod_bias)
         m.video_w, m.video_bias, m.final_norm, m.final_w, m.final_bias = p(video_w), p(video_bias), p(final_norm), p(final_w), p(final_bias)
+        m.ext_w, m.ext_bias, m.ext_channels = p(ext_w), p(ext_bias), 0 if ext_w is None else ext_w.shape[1] - 128
         self.struct = m
 
 
-def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, workspace=None):
+def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, workspace=None, extra=None, ref_kv=None):
     """rows: list of (text bf16 [S, D], skip mask int, latent index). latents f32 [n, 128, h, w]; time_vector numpy f32 [D].
     Returns the per-row outputs f32 [128, h, w] (and the workspace, for reuse)."""
     import numpy as np
@@ -555,6 +563,8 @@ def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, wor
     f.struct_size, f.latents, f.num_latents, f.height, f.width = C.sizeof(_lib.Forward), latents.data_ptr(), n, h, w
     f.time_vector, f.rows, f.num_rows, f.tier = tv.ctypes.data, arr, len(rows), tier
     f.attention = _lib.AttentionOptions(ATTENTION_Q8_FP8_F32ACC, 0.0, 0.0)
+    f.extra = None if extra is None else extra.data_ptr()
+    f.ref_kv, f.ref_tokens = (None, 0) if ref_kv is None else (ref_kv.data_ptr(), ref_kv.shape[1])
     need = _lib.lib().b2_dit_forward_workspace_bytes(C.byref(model.struct), C.byref(f))
     if need == 0:
         check(-1)
@@ -563,6 +573,29 @@ def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, wor
     f.workspace, f.workspace_bytes = workspace.data_ptr(), workspace.numel()
     check(_lib.lib().b2_dit_forward(C.byref(model.struct), C.byref(f), _stream()))
     return outs, workspace
+
+
+def dit_prefill_references(model, latents, time_vector, tier=TIER_INT8):
+    """latents: list of f32 [128, h, w] reference latents. Returns the cache bf16 [num_blocks, sum h w, 2 D]."""
+    import numpy as np
+    n = len(latents)
+    ptrs = (C.c_void_p * n)(*[t.data_ptr() for t in latents])
+    hs, ws = (C.c_int * n)(*[t.shape[1] for t in latents]), (C.c_int * n)(*[t.shape[2] for t in latents])
+    total = sum(t.shape[1] * t.shape[2] for t in latents)
+    m = model.struct
+    kv = torch.empty((m.num_blocks, total, 2 * m.D), dtype=torch.bfloat16, device=latents[0].device)
+    tv = np.ascontiguousarray(time_vector, np.float32)
+    f = _lib.Prefill()
+    f.struct_size, f.latents, f.heights, f.widths, f.num_refs = C.sizeof(_lib.Prefill), ptrs, hs, ws, n
+    f.time_vector, f.kv_out, f.tier = tv.ctypes.data, kv.data_ptr(), tier
+    f.attention = _lib.AttentionOptions(ATTENTION_Q8_FP8_F32ACC, 0.0, 0.0)
+    need = _lib.lib().b2_dit_prefill_workspace_bytes(C.byref(m), C.byref(f))
+    if need == 0:
+        check(-1)
+    ws_buf = torch.empty(need, dtype=torch.uint8, device=latents[0].device)
+    f.workspace, f.workspace_bytes = ws_buf.data_ptr(), need
+    check(_lib.lib().b2_dit_prefill_references(C.byref(m), C.byref(f), _stream()))
+    return kv
 
 
 # ------------------------------------------------------------------------------------------------ weight ingestion

@@ -211,3 +211,124 @@ def test_dit_forward_rejects_bad_arguments(ops):
     small = torch.empty(1024, dtype=torch.uint8, device="cuda")
     outs, ws = ops.dit_forward(model, lat, tv, [(text, 0, 0)], workspace=small)   # too small a workspace is replaced
     assert ws.numel() > small.numel() and torch.isfinite(outs[0]).all()
+
+
+@pytest.mark.parametrize("h,w,index", [(16, 24, 0), (5, 3, 2), (1, 1, 7)])
+def test_reference_rope_table(ops, h, w, index):
+    got = bits(ops.moss_rope_table_reference(h, w, index))
+    want = orc.moss_rope_table_reference(h, w, index)
+    # sinf / cosf of the device against libm: equal except for rare last-place differences before the bf16 rounding
+    assert (got == want).mean() >= 0.9995
+    assert np.abs(bf_to_f64(got) - bf_to_f64(want)).max() <= 2.0 ** -7
+    # axis r carries index + 1 at every row; the centred coordinates are the image table's
+    img = bits(ops.moss_rope_table(h, w, 0))
+    assert np.array_equal(got[:, 32:64], img[:h * w, 32:64]) and np.array_equal(got[:, 96:128], img[:h * w, 96:128])
+
+
+def test_reference_images_prefill_then_forward(ops):
+    """prefill_references, then a forward that reads the cache through its slots (moss_dit.cpp:1479-1580, 1283-1300,
+    1441-1452), against the same work spelt out call by call with the block-level slots and tap (which
+    tests/test_gpu_reference_slots.py holds to plain runs over the longer sequences)."""
+    D, F, h, w = 3072, 8192, 16, 16
+    hw = h * w
+    model, bws, p, _ = _model(ops, 2, F, 5)
+    rng = np.random.default_rng(21)
+    refs = [torch.from_numpy(rng.normal(0, 1, (128, 8, 16)).astype(np.float32)).cuda(),
+            torch.from_numpy(rng.normal(0, 1, (128, 16, 8)).astype(np.float32)).cuda()]
+    R = 256
+    tv0, tv = rng.normal(0, 1, D).astype(np.float32), rng.normal(0, 1, D).astype(np.float32)
+    kv = ops.dit_prefill_references(model, refs, tv0)
+    torch.cuda.synchronize()
+    assert kv.shape == (2, R, 2 * D) and torch.isfinite(kv.float()).all()
+
+    # The prefill call by call: one sequence of the references' tokens, every block tapped.
+    mod0 = ops.linear_fp32_row(p["block_mod_w"], torch.from_numpy(tv0).cuda(), p["block_mod_bias"])
+    x = torch.cat([ops.linear_bf16(ops.latent_to_tokens(r), p["video_w"], p["video_bias"]) for r in refs]).contiguous()
+    rope = torch.cat([ops.moss_rope_table_reference(8, 16, 0), ops.moss_rope_table_reference(16, 8, 1)]).contiguous()
+    cu = synth.cu_seqlens([R])
+    for bi in range(2):
+        tap = torch.empty((R, 2 * D), dtype=torch.bfloat16, device="cuda")
+        run = ops.block_run(R, cu, R, D=D, F=F, kv_tap=tap)
+        ws = torch.empty(ops.block_quant_workspace_bytes(run), dtype=torch.uint8, device="cuda")
+        ops.run_block_quant(bws[bi], ops.block_buffers(x, mod0, rope, ws), run)
+        assert torch.equal(kv[bi].view(torch.int16), tap.view(torch.int16)), f"block {bi}"
+
+    # The forward with references: two rows of one latent; row 0 reads slot A, row 1 slot B.
+    latents = torch.from_numpy(rng.normal(0, 1, (1, 128, h, w)).astype(np.float32)).cuda()
+    texts = [bfdev(to_bf16(rng.normal(0, 1, (s, D)))) for s in (32, 64)]
+    for skips in ((0, 0), (0, 0b01), (0b10, 0)):
+        outs, _ = ops.dit_forward(model, latents, tv, [(texts[r], skips[r], 0) for r in range(2)], ref_kv=kv)
+        dtv = torch.from_numpy(tv).cuda()
+        mod = ops.linear_fp32_row(p["block_mod_w"], dtv, p["block_mod_bias"])
+        head = ops.linear_fp32_row(p["head_mod_w"], dtv, p["head_mod_bias"])
+        off = [0, hw + 32, 2 * hw + 96]
+        xs = torch.empty((off[-1], D), dtype=torch.bfloat16, device="cuda")
+        rp = torch.empty((off[-1], 128), dtype=torch.bfloat16, device="cuda")
+        emb = ops.linear_bf16(ops.latent_to_tokens(latents[0]), p["video_w"], p["video_bias"])
+        for r in range(2):
+            xs[off[r]:off[r] + hw] = emb
+            xs[off[r] + hw:off[r + 1]] = texts[r]
+            rp[off[r]:off[r + 1]] = ops.moss_rope_table(h, w, texts[r].shape[0])
+        for bi in range(2):
+            rows = [r for r in range(2) if not (skips[r] >> bi) & 1]
+            if rows == [0, 1]:
+                lens = [off[1] - off[0], off[2] - off[1]]
+                run = ops.block_run(off[2], synth.cu_seqlens(lens), max(lens) + R, D=D, F=F, slot_rows=R, slot_kv=(kv[bi], kv[bi]),
+                                    cu_seqlens_k=synth.cu_seqlens([lens[0] + R, lens[1] + R]), k0=0, k1=off[2] + 2 * R)
+                view = xs
+                rview = rp
+            elif rows == [1]:   # row 1 alone: not at row 0, so its keys are [own | slot B]
+                n = off[2] - off[1]
+                run = ops.block_run(n, synth.cu_seqlens([n]), n + R, D=D, F=F, slot_rows=R, slot_kv=(None, kv[bi]),
+                                    cu_seqlens_k=synth.cu_seqlens([n + R]), k0=R, k1=R + n + R)
+                view, rview = xs[off[1]:], rp[off[1]:]
+            else:               # row 0 alone: its keys are [slot A | own]
+                n = off[1]
+                run = ops.block_run(n, synth.cu_seqlens([n]), n + R, D=D, F=F, slot_rows=R, slot_kv=(kv[bi], None),
+                                    cu_seqlens_k=synth.cu_seqlens([n + R]), k0=0, k1=R + n)
+                view, rview = xs[:off[1]], rp[:off[1]]
+            ws = torch.empty(ops.block_quant_workspace_bytes(run), dtype=torch.uint8, device="cuda")
+            ops.run_block_quant(bws[bi], ops.block_buffers(view, mod, rview, ws), run)
+        for r in range(2):
+            y = ops.rms_norm_modulate(xs[off[r]:off[r] + hw], p["final_norm"], head[D:], head[:D])
+            want = ops.tokens_to_latent(ops.linear_bf16(y, p["final_w"], p["final_bias"])).reshape(128, h, w)
+            assert torch.equal(outs[r].view(torch.int32), want.view(torch.int32)), f"skips {skips} row {r}"
+    # the references matter: without them the outputs differ
+    plain, _ = ops.dit_forward(model, latents, tv, [(texts[r], 0, 0) for r in range(2)])
+    with_refs, _ = ops.dit_forward(model, latents, tv, [(texts[r], 0, 0) for r in range(2)], ref_kv=kv)
+    assert not torch.equal(plain[0], with_refs[0])
+    with pytest.raises(ValueError, match="one latent and at most 2 rows"):
+        ops.dit_forward(model, latents, tv, [(texts[0], 0, 0)] * 3, ref_kv=kv)
+
+
+def test_input_extension(ops):
+    """set_input_extension (moss_dit.cpp:1120-1133): the embedder reads [latent | extra] channels."""
+    D, F, h, w, c = 3072, 8192, 8, 8, 16
+    rng = np.random.default_rng(31)
+    _, bws, p, _ = _model(ops, 1, F, 6)
+    ext_w, ext_b = bfdev(to_bf16(rng.normal(0, 0.08, (D, 128 + c)))), bfdev(to_bf16(rng.normal(0, 0.1, D)))
+    model = ops.DitModel(bws, F, p["block_mod_w"], p["block_mod_bias"], p["head_mod_w"], p["head_mod_bias"], None, None,
+                         p["final_norm"], p["final_w"], p["final_bias"], ext_w=ext_w, ext_bias=ext_b)
+    latents = torch.from_numpy(rng.normal(0, 1, (1, 128, h, w)).astype(np.float32)).cuda()
+    extra = torch.from_numpy(rng.normal(0, 1, (1, c, h, w)).astype(np.float32)).cuda()
+    text = bfdev(to_bf16(rng.normal(0, 1, (9, D))))
+    tv = rng.normal(0, 1, D).astype(np.float32)
+    got, _ = ops.dit_forward(model, latents, tv, [(text, 0, 0)], extra=extra)
+    # the same with a plain embedder over the concatenated channels folded by hand
+    tok = torch.empty((h * w, 128 + c), dtype=torch.bfloat16, device="cuda")
+    ops.latent_to_tokens(latents[0], tokens=tok)
+    ops.latent_to_tokens(extra[0], tokens=tok, col0=128)
+    emb = ops.linear_bf16(tok, ext_w, ext_b)
+    dtv = torch.from_numpy(tv).cuda()
+    mod = ops.linear_fp32_row(p["block_mod_w"], dtv, p["block_mod_bias"])
+    head = ops.linear_fp32_row(p["head_mod_w"], dtv, p["head_mod_bias"])
+    x = torch.cat([emb, text]).contiguous()
+    n = x.shape[0]
+    run = ops.block_run(n, synth.cu_seqlens([n]), n, D=D, F=F)
+    ws = torch.empty(ops.block_quant_workspace_bytes(run), dtype=torch.uint8, device="cuda")
+    ops.run_block_quant(bws[0], ops.block_buffers(x, mod, ops.moss_rope_table(h, w, 9), ws), run)
+    y = ops.rms_norm_modulate(x[:h * w], p["final_norm"], head[D:], head[:D])
+    want = ops.tokens_to_latent(ops.linear_bf16(y, p["final_w"], p["final_bias"])).reshape(128, h, w)
+    assert torch.equal(got[0].view(torch.int32), want.view(torch.int32))
+    with pytest.raises(ValueError, match="extra latents"):
+        ops.dit_forward(model, latents, tv, [(text, 0, 0)])
