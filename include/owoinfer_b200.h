@@ -315,7 +315,7 @@ typedef struct b2_block_run {
   int tier;                  /* B2_TIER_* */
   b2_attention_options attention;
   int fused_norm_rope;       /* -1 auto (>= 3072 tokens, dit_block_quant.cpp:32-35), 0 separate kernel, 1 in the pre-pass */
-  /* Reference keys and reference prefill (BlockRun of src/models/moss_dit/dit_block_fused.h:131-147). A caller built
+  /* Reference keys and reference prefill (BlockRun of src/models/moss_dit/dit_block_fused.h:132-147). A caller built
    * against a header that ends at fused_norm_rope passes that struct_size and gets none of it. All zero / NULL: unused.
    * slot_rows > 0: attention reads keys and values from the region [slot A | the run's tokens | slot B], slot_rows rows
    * per slot; sequence i's keys are rows [k0 + cu_seqlens_k[i], k0 + cu_seqlens_k[i + 1]) of it, k0 <= k1 bound the rows
@@ -327,7 +327,7 @@ typedef struct b2_block_run {
   const int32_t* cu_seqlens_k; /* device int32 [batch + 1] */
   int64_t k0, k1;
   /* kv_tap != NULL: after QK-norm and RoPE the run's k and v rows are copied there as bf16 [tokens, 2 D]
-   * (tap_reference_kv, dit_block_fused.h:151); tap_only != 0: the block ends there, x untouched. */
+   * (tap_reference_kv, dit_block_fused.h:158); tap_only != 0: the block ends there, x untouched. */
   void* kv_tap;
   int tap_only;
 } b2_block_run;
@@ -395,9 +395,9 @@ int b2_cfg_combine(const float* cond, const float* uncond, float g, float* out, 
 /* pipeline::slg_correct (sampler_driver.h:189; kernel sampler_kernels.cu:308): out = pred + scale * (cond - skipped). */
 int b2_slg_correct(const float* pred, const float* cond, const float* skipped, float scale, float* out, int64_t n,
                    void* stream);
-/* pipeline::euler_update (sampler_driver.h:201; kernel sampler_kernels.cu:209): x += h * v. */
+/* pipeline::euler_update (sampler_driver.h:202; kernel sampler_kernels.cu:209): x += h * v. */
 int b2_euler_update(float* x, const float* v, float h, int64_t n, void* stream);
-/* pipeline::ab2_update (sampler_driver.h:202; kernel sampler_kernels.cu:213): x += h * (a * v - b * v_prev). */
+/* pipeline::ab2_update (sampler_driver.h:203; kernel sampler_kernels.cu:213): x += h * (a * v - b * v_prev). */
 int b2_ab2_update(float* x, const float* v, const float* v_prev, float h, float a, float b, int64_t n, void* stream);
 
 /* pipeline::guide_prediction in velocity space (src/pipeline/samplers/sampler_driver.cpp:565-577) followed by the
@@ -423,7 +423,7 @@ int b2_guided_velocity_step(const b2_guided_step* step, void* stream);
  * The shell of MossDit::forward around the block loop (src/models/moss_dit/moss_dit.cpp:1181-1477).
  * ------------------------------------------------------------------------------------------------------------- */
 
-/* moss_dit::latent_to_tokens (src/models/moss_dit/dit_kernels.h:18; dit_kernels.cu:137-158): f32 [channels, hw] ->
+/* moss_dit::latent_to_tokens (src/models/moss_dit/dit_kernels.h:16-19; dit_kernels.cu:137-158): f32 [channels, hw] ->
  * bf16 tokens [hw, channels] (row stride ld >= channels, so a wider token matrix can be filled at a column offset). */
 int b2_latent_to_tokens(const float* latents, int channels, int64_t hw, void* tokens, int64_t ld, void* stream);
 /* moss_dit::tokens_to_latent (dit_kernels.h:22): contiguous bf16 [hw, channels] -> f32 [channels, hw]. */
@@ -432,7 +432,7 @@ int b2_tokens_to_latent(const void* tokens, float* latents, int channels, int64_
  * weights [n, k], fp32 x [k] and bias [n], the dot product in the reference kernel's order (one warp per row, 8 weights
  * per lane and step, one fma per weight, butterfly of adds): same bits. k % 8 == 0; w and x 16-byte aligned. */
 int b2_linear_fp32_row(const void* w, const float* x, const float* bias, void* out, int n, int k, void* stream);
-/* kernels::rms_norm_modulate_moss (src/kernels/basic/norm.h; bits of basic/norm.cu:67-128, the prologue of
+/* kernels::rms_norm_modulate_moss (src/kernels/basic/norm.h:29; bits of basic/norm.cu:67-128, the prologue of
  * b2_rms_norm_modulate_rotate_quantize without the quantiser): y = bf16(bf16(bf16(bf16(x * r) * w) * bf16(1 + scale)) +
  * shift), r from the mean of squares in torch's order for an [m, k] input. k % 256 == 0, k <= 4096. */
 int b2_rms_norm_modulate(const void* x, int64_t ldx, const void* norm_weight, const void* mod_scale, const void* mod_shift,
@@ -478,14 +478,14 @@ typedef struct b2_dit_model {
   const void* final_norm;       /* bf16 [D] */
   const void* final_w;          /* bf16 [128, D] */
   const void* final_bias;       /* bf16 [128] or NULL */
-  /* MossDit::InputExtension (moss_dit.h; set_input_extension, moss_dit.cpp:1120-1133): an embedder over the latent's 128
+  /* MossDit::InputExtension (moss_dit.h:215; set_input_extension, moss_dit.cpp:1118-1133): an embedder over the latent's 128
    * channels followed by ext_channels more, used instead of video_w / video_bias when ext_w is not NULL. */
   const void* ext_w;            /* bf16 [D, 128 + ext_channels] or NULL */
   const void* ext_bias;         /* bf16 [D] */
   int ext_channels;             /* > 0 and a multiple of 8 with ext_w */
 } b2_dit_model;
 
-/* MossDit::Row (moss_dit.h): one sequence of the forward = the video tokens of a latent followed by its text tokens. */
+/* MossDit::Row (src/models/moss_dit/moss_dit.h:99): one sequence of the forward = the video tokens of a latent followed by its text tokens. */
 typedef struct b2_forward_row {
   const void* text;  /* device bf16 [text_len, D] */
   int64_t text_len;  /* >= 1 */
@@ -507,7 +507,7 @@ typedef struct b2_forward {
   size_t workspace_bytes;
   /* With the model's input extension: device f32 [num_latents, ext_channels, height, width]. */
   const float* extra;
-  /* Reference images (MossDit::set_references, moss_dit.cpp:1068-1090): the cache b2_dit_prefill_references filled,
+  /* Reference images (MossDit::set_references, moss_dit.h:383, moss_dit.cpp:1080-1090; RefKv, moss_dit.h:227): the cache b2_dit_prefill_references filled,
    * device bf16 [num_blocks, ref_tokens, 2 D]; NULL / 0 without. A forward with references takes one latent and at
    * most two rows; every sequence then attends to its own keys plus the reference keys in a slot next to it
    * (moss_dit.cpp:1283-1300). */

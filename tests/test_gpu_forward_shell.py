@@ -302,7 +302,7 @@ def test_reference_images_prefill_then_forward(ops):
 
 
 def test_input_extension(ops):
-    """set_input_extension (moss_dit.cpp:1120-1133): the embedder reads [latent | extra] channels."""
+    """set_input_extension (moss_dit.cpp:1118-1133): the embedder reads [latent | extra] channels."""
     D, F, h, w, c = 3072, 8192, 8, 8, 16
     rng = np.random.default_rng(31)
     _, bws, p, _ = _model(ops, 1, F, 6)

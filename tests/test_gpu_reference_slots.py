@@ -1,5 +1,5 @@
 """Reference keys ("slots") and the reference prefill tap of a block run (BlockRun of
-src/models/moss_dit/dit_block_fused.h:131-147; MossDit::forward, moss_dit.cpp:1283-1300, 1441-1452).
+src/models/moss_dit/dit_block_fused.h:132-147; MossDit::forward, moss_dit.cpp:1283-1300, 1441-1452).
 
 Attention whose keys are [slot A | own] or [own | slot B] is, for the sequence's own queries, the same arithmetic as
 self-attention over the longer sequence that starts with the slot rows (when the slot is a whole number of 128-row query
