@@ -324,6 +324,7 @@ typedef struct b2_block_run {
    * read. QK-norm + RoPE then run as their own kernel on the run's own rows. */
   int64_t slot_rows;
   const void* slot_kv[2];
+  int64_t slot_kv_ld;          /* elements between rows of slot_kv; 0 = 2 D (contiguous, as kv_tap writes them) */
   const int32_t* cu_seqlens_k; /* device int32 [batch + 1] */
   int64_t k0, k1;
   /* kv_tap != NULL: after QK-norm and RoPE the run's k and v rows are copied there as bf16 [tokens, 2 D]

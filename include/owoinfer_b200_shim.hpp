@@ -31,16 +31,17 @@ inline void b200_check(int status) {
 }
 
 // The blocks this library runs: all four linears INT8 ConvRot and fused (dit_weights.h:106-111), attention in the e4m3
-// P.V variant with fp32 accumulation, no LoRA side branch, no reference slots, no K/V tap. Everything else stays on the
-// reference's own path.
-inline bool b200_can_run(const BlockTensors& w, const QuantBlockBuffers& a, const BlockRun& run, AttentionMode attention) {
+// P.V variant with fp32 accumulation, no LoRA side branch; reference slots and the K/V tap included. Everything else
+// stays on the reference's own path.
+inline bool b200_can_run(const BlockTensors& w, const QuantBlockBuffers& a, const BlockRun& /*run*/, AttentionMode attention) {
   return !w.qkv_split && !w.qkv8.empty() && !w.o8.empty() && !w.up_gate8.empty() && !w.down8.empty() && !w.int4() &&
-         !w.nvfp4() && attention == AttentionMode::kQ8Fp8F32Acc && a.lora == nullptr && run.slot_rows == 0 &&
-         run.kv_tap == nullptr && !run.tap_only;
+         !w.nvfp4() && attention == AttentionMode::kQ8Fp8F32Acc && a.lora == nullptr;
 }
 
-// The b2_block_run of a run of the reference: D and F from the weights' shapes, heads = D / 128.
-inline b2_block_run b200_block_run(const BlockTensors& w, const BlockRun& run) {
+// The b2_block_run of a run of the reference: D and F from the weights' shapes, heads = D / 128. With reference slots the
+// cached k | v rows are read where MossDit::forward put them, in the k | v columns of the slot rows of `big` (slot A
+// before all tokens, slot B after them: dit_block_fused.h:136-141); this library copies them next to its own QKV rows.
+inline b2_block_run b200_block_run(const BlockTensors& w, const BlockRun& run, const QuantBlockBuffers* a = nullptr) {
   b2_block_run br{};
   br.struct_size = sizeof(b2_block_run);
   br.tokens = run.t1 - run.t0;
@@ -53,6 +54,21 @@ inline b2_block_run b200_block_run(const BlockTensors& w, const BlockRun& run) {
   br.tier = B2_TIER_INT8;
   br.attention = b2_attention_options{B2_ATTENTION_Q8_FP8_F32ACC, 0.f, 0.f};
   br.fused_norm_rope = -1;
+  br.kv_tap = run.kv_tap;
+  br.tap_only = run.tap_only ? 1 : 0;
+  if (run.slot_rows > 0) {
+    br.slot_rows = run.slot_rows;
+    br.cu_seqlens_k = static_cast<const std::int32_t*>(run.cu_seqlens_k.data);
+    br.k0 = run.k0 - run.t0;  // rows of [slot A | the run's tokens | slot B]
+    br.k1 = run.k1 - run.t0;
+    if (a != nullptr) {
+      const std::int64_t qkv_dim = 3 * static_cast<std::int64_t>(br.D), total = a->f.x.dim(0);
+      const auto* big = static_cast<const std::uint16_t*>(a->f.big.data);
+      br.slot_kv[0] = big + br.D;
+      br.slot_kv[1] = big + (run.slot_rows + total) * qkv_dim + br.D;
+      br.slot_kv_ld = qkv_dim;
+    }
+  }
   return br;
 }
 
@@ -70,7 +86,7 @@ inline void run_block_quant_b200(const BlockTensors& w, const QuantBlockBuffers&
                                  const QkvGemm& /*qkv_gemm*/, const FusedRouteSnapshot& /*route*/, AttentionMode attention,
                                  cudaStream_t stream, int /*block*/, void* workspace, std::size_t workspace_bytes) {
   if (!b200_can_run(w, a, run, attention)) {
-    throw std::invalid_argument("run_block_quant_b200: not an all-INT8 block with q8_fp8_f32acc attention, or it uses LoRA, reference slots or the K/V tap");
+    throw std::invalid_argument("run_block_quant_b200: not an all-INT8 block with q8_fp8_f32acc attention, or it uses LoRA");
   }
   const auto lin = [](const Int8Linear& l) {
     return b2_linear{static_cast<const std::int8_t*>(l.w.data), static_cast<const float*>(l.scale.data), nullptr};
@@ -79,7 +95,7 @@ inline void run_block_quant_b200(const BlockTensors& w, const QuantBlockBuffers&
   bw.struct_size = sizeof(b2_block_weights);
   bw.norm1 = w.norm1.data, bw.norm2 = w.norm2.data, bw.q_norm = w.q_norm.data, bw.k_norm = w.k_norm.data;
   bw.qkv = lin(w.qkv8), bw.o = lin(w.o8), bw.up_gate = lin(w.up_gate8), bw.down = lin(w.down8);
-  const b2_block_run br = b200_block_run(w, run);
+  const b2_block_run br = b200_block_run(w, run, &a);
   b2_block_buffers bb{};
   bb.struct_size = sizeof(b2_block_buffers);
   bb.x = static_cast<char*>(a.f.x.data) + run.t0 * a.f.x.stride[0] * 2;          // rows [t0, t1) of the residual stream

@@ -71,7 +71,7 @@ class BlockBuffers(C.Structure):
 class BlockRun(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("tokens", C.c_int64), ("D", C.c_int), ("F", C.c_int), ("heads", C.c_int),
                 ("cu_seqlens", C.c_void_p), ("batch", C.c_int), ("max_seqlen", C.c_int), ("tier", C.c_int),
-                ("attention", AttentionOptions), ("fused_norm_rope", C.c_int), ("slot_rows", C.c_int64), ("slot_kv", C.c_void_p * 2),
+                ("attention", AttentionOptions), ("fused_norm_rope", C.c_int), ("slot_rows", C.c_int64), ("slot_kv", C.c_void_p * 2), ("slot_kv_ld", C.c_int64),
                 ("cu_seqlens_k", C.c_void_p), ("k0", C.c_int64), ("k1", C.c_int64), ("kv_tap", C.c_void_p), ("tap_only", C.c_int)]
 
 

@@ -73,7 +73,7 @@ int check_run(const char* op, const b2_block_run* run) {
   if (run->tier < B2_TIER_INT8 || run->tier > B2_TIER_W4A8) return fail_invalid(op, "unknown tier");
   if (run->batch < 1 || run->max_seqlen < 1 || run->cu_seqlens == nullptr) return fail_invalid(op, "needs cu_seqlens, batch >= 1, max_seqlen >= 1");
   const b2_block_run r = whole_run(run);
-  if (r.slot_rows < 0) return fail_invalid(op, "negative slot_rows");
+  if (r.slot_rows < 0 || r.slot_kv_ld < 0 || (r.slot_kv_ld > 0 && r.slot_kv_ld < 2 * r.D)) return fail_invalid(op, "negative slot_rows, or slot_kv_ld below 2 D");
   if (r.slot_rows > 0) {
     if (r.cu_seqlens_k == nullptr || r.k0 < 0 || r.k1 < r.k0 || r.k1 > r.tokens + 2 * r.slot_rows) {
       return fail_invalid(op, "reference slots need cu_seqlens_k and 0 <= k0 <= k1 <= tokens + 2 * slot_rows");
@@ -204,7 +204,8 @@ int b2_run_block_quant(const b2_block_weights* w, const b2_block_buffers* a, con
       const bool read = s2 == 0 ? run->k0 < slot : run->k1 > slot + L;
       if (!read) continue;
       __nv_bfloat16* dst = qkv + (s2 == 0 ? 0 : slot + L) * 3 * D + D;
-      if (const cudaError_t e = cudaMemcpy2DAsync(dst, row_bytes, run->slot_kv[s2], kv_bytes, kv_bytes, static_cast<std::size_t>(slot), cudaMemcpyDeviceToDevice, st); e != cudaSuccess) {
+      const std::size_t src_pitch = run->slot_kv_ld > 0 ? static_cast<std::size_t>(run->slot_kv_ld) * sizeof(__nv_bfloat16) : kv_bytes;
+      if (const cudaError_t e = cudaMemcpy2DAsync(dst, row_bytes, run->slot_kv[s2], src_pitch, kv_bytes, static_cast<std::size_t>(slot), cudaMemcpyDeviceToDevice, st); e != cudaSuccess) {
         return fail_cuda(op, e);
       }
     }

@@ -112,6 +112,16 @@ def test_tap_then_slots_round_trip(ops):
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
     assert torch.isfinite(got.float()).all()
 
+    # The slot rows read in place from a QKV-shaped buffer (row stride 3 D, k | v columns), as the reference keeps them.
+    wide = torch.zeros((slot, 3 * D), dtype=torch.bfloat16, device="cuda")
+    wide[:, D:] = tap
+    runw = ops.block_run(n0 + n1, cu, max(slot + n0, n1 + slot), D=D, F=F, slot_rows=slot, slot_kv=(wide[:, D:], wide[:, D:]),
+                         cu_seqlens_k=cu_k, k0=0, k1=n0 + n1 + 2 * slot, slot_kv_ld=3 * D)
+    gotw = x.clone()
+    ops.run_block_quant(bw, ops.block_buffers(gotw, mod, rope, ws), runw)
+    torch.cuda.synchronize()
+    assert torch.equal(gotw.view(torch.int16), got.view(torch.int16))
+
     # Only one slot read: the second sequence attends to its own keys alone.
     cu_k1 = synth.cu_seqlens([slot + n0, n1])
     run1 = ops.block_run(n0 + n1, cu, max(slot + n0, n1), D=D, F=F, slot_rows=slot, slot_kv=(tap, None), cu_seqlens_k=cu_k1,
@@ -131,5 +141,8 @@ def test_slot_arguments_are_checked(ops):
     with pytest.raises(ValueError, match="cu_seqlens_k"):
         ops.block_quant_workspace_bytes(ops.block_run(64, cu, 64, F=512, slot_rows=16))
     tap = torch.zeros((16, 2 * D), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="slot_kv_ld"):
+        ops.block_quant_workspace_bytes(ops.block_run(64, cu, 96, F=512, slot_rows=32, slot_kv=(tap, None), cu_seqlens_k=cu, k0=0, k1=96,
+                                                      slot_kv_ld=D))
     with pytest.raises(ValueError, match="no slot_kv"):
         ops.block_quant_workspace_bytes(ops.block_run(64, cu, 96, F=512, slot_rows=16, slot_kv=(tap, None), cu_seqlens_k=cu, k0=0, k1=96))
