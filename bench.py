@@ -372,6 +372,28 @@ def forward_shell_ms(torch, ops, synth, grid, text_len, rows, blocks, F, steps):
         e1.record()
         torch.cuda.synchronize()
         out[name] = e0.elapsed_time(e1) / steps
+        if name == "forward":
+            # A launch-bound shape (a 256 x 256 image: 256 video + 64 text tokens per row) eagerly and through the step-graph
+            # cache (b2_dit_forward_graphed), both on a stream of their own.
+            small = torch.randn(1, 128, 16, 16, device="cuda", generator=g)
+            rows_small = [(x[:64], 0, 0) for x in texts]
+            side = torch.cuda.Stream()
+            graphs = ops.DitGraphs(capacity=2)
+            with torch.cuda.stream(side):
+                for key, cache in (("forward256_eager_ms", None), ("forward256_graph_ms", graphs)):
+                    outs_s = ws_s = None
+                    for _ in range(3):
+                        outs_s, ws_s = ops.dit_forward(model, small, tv, rows_small, workspace=ws_s, outs=outs_s, graphs=cache)
+                    side.synchronize()
+                    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s0.record(side)
+                    for _ in range(10):
+                        ops.dit_forward(model, small, tv, rows_small, workspace=ws_s, outs=outs_s, graphs=cache)
+                    s1.record(side)
+                    side.synchronize()
+                    out[key] = s0.elapsed_time(s1) / 10
+            out["forward256_graph_stats"] = graphs.stats()
+            graphs.close()
     return out
 
 
@@ -613,6 +635,7 @@ def main():
                 fw = forward_shell_ms(torch, ops, synth, 64, seq_len - 64 * 64, seqs, n_blocks, F, min(args.steps, 3))
                 line["extra"]["forward1024_ms"] = fw["forward"]
                 line["extra"]["forward1024_shell_only_ms"] = fw["shell_only"]
+                line["extra"].update({k: v for k, v in fw.items() if k.startswith("forward256_")})
                 line["extra"]["load_file"] = load_file_record(torch, ops, synth, F)
     if world > 1 and args.workload == "step1024" and not args.no_ulysses and tier == ops.TIER_INT8:
         # The headline above is image data parallel (no collective). The sequence-parallel configuration, the one with an

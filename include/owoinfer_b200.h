@@ -516,6 +516,28 @@ typedef struct b2_forward {
   int64_t ref_tokens;
 } b2_forward;
 
+/* moss_dit::StepGraphs (src/models/moss_dit/dit_graph.h:14-66; runtime::GraphCache, src/runtime/graph_cache.h:20-58):
+ * CUDA graphs of whole forwards, least recently used first out. b2_dit_forward_graphed enqueues what b2_dit_forward
+ * would, through the graph of the call's key: replayed when cached (*replayed = 1), otherwise captured from one run of
+ * the forward and launched. The key is everything but device memory contents and the time vector: the model structure
+ * and its block table, grid, rows (text address and length, skip set, latent, output address), tier, attention
+ * options, workspace, reference cache. The time vector is written to a buffer of the cache ahead of the graph, so
+ * steps of one shape replay one graph. A key whose hash meets another cached key's runs eagerly (collisions), as does
+ * a forward whose capture cannot be made (eager) or a cache of capacity 0. stream: not the default stream. Not
+ * thread-safe (one cache per model and thread); the model, block table, rows' buffers and workspace of a cached
+ * graph must stay where they are while it can be replayed (b2_dit_graphs_clear otherwise). */
+typedef struct b2_dit_graphs b2_dit_graphs;
+typedef struct b2_dit_graph_stats {
+  uint64_t replays, captures, collisions, eager, evictions;
+  size_t size; /* graphs cached now */
+} b2_dit_graph_stats;
+int b2_dit_graphs_create(size_t capacity, b2_dit_graphs** out);
+int b2_dit_graphs_clear(b2_dit_graphs* graphs);
+int b2_dit_graphs_destroy(b2_dit_graphs* graphs);
+int b2_dit_graphs_stats(const b2_dit_graphs* graphs, b2_dit_graph_stats* stats);
+int b2_dit_forward_graphed(b2_dit_graphs* graphs, const b2_dit_model* model, const b2_forward* forward, void* stream,
+                           int* replayed);
+
 /* MossDit::prefill_references (moss_dit.cpp:1479-1580): the reference latents (each device f32 [128, h_i, w_i], their
  * grids in heights / widths) run through every block as one sequence without text, under the modulation of
  * time_vector (the time vector of timestep 0 there), each with its reference RoPE table; block b's k | v rows after

@@ -21,6 +21,7 @@ EXPORTS = [
     "b2_latent_to_tokens", "b2_tokens_to_latent", "b2_linear_fp32_row", "b2_rms_norm_modulate", "b2_time_sinusoid",
     "b2_time_vector_fp32", "b2_linear_bf16_workspace_bytes", "b2_linear_bf16", "b2_dit_forward_workspace_bytes", "b2_dit_forward",
     "b2_moss_rope_table_reference", "b2_dit_prefill_workspace_bytes", "b2_dit_prefill_references",
+    "b2_dit_graphs_create", "b2_dit_graphs_clear", "b2_dit_graphs_destroy", "b2_dit_graphs_stats", "b2_dit_forward_graphed",
     "b2_dit_file_open", "b2_dit_file_get_info", "b2_dit_file_model", "b2_dit_file_time_embedding", "b2_dit_file_close",
 ]
 
@@ -99,6 +100,11 @@ class Forward(C.Structure):
                 ("extra", C.c_void_p), ("ref_kv", C.c_void_p), ("ref_tokens", C.c_int64)]
 
 
+class DitGraphStats(C.Structure):
+    _fields_ = [("replays", C.c_uint64), ("captures", C.c_uint64), ("collisions", C.c_uint64), ("eager", C.c_uint64),
+                ("evictions", C.c_uint64), ("size", C.c_size_t)]
+
+
 class Prefill(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("latents", C.POINTER(C.c_void_p)), ("heights", C.POINTER(C.c_int)),
                 ("widths", C.POINTER(C.c_int)), ("num_refs", C.c_int), ("time_vector", C.c_void_p), ("kv_out", C.c_void_p),
@@ -148,6 +154,11 @@ def lib() -> C.CDLL:
         l.b2_dit_file_close.argtypes = [C.c_void_p]
         l.b2_linear_bf16_workspace_bytes.restype = C.c_size_t
         l.b2_dit_forward_workspace_bytes.restype = C.c_size_t
+        l.b2_dit_graphs_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
+        l.b2_dit_graphs_clear.argtypes = [C.c_void_p]
+        l.b2_dit_graphs_destroy.argtypes = [C.c_void_p]
+        l.b2_dit_graphs_stats.argtypes = [C.c_void_p, C.POINTER(DitGraphStats)]
+        l.b2_dit_forward_graphed.argtypes = [C.c_void_p, C.POINTER(DitModel), C.POINTER(Forward), C.c_void_p, C.POINTER(C.c_int)]
         l.b2_dit_forward_workspace_bytes.argtypes = [C.POINTER(DitModel), C.POINTER(Forward)]
         l.b2_block_quant_sp_workspace_bytes.restype = C.c_size_t
         l.b2_block_quant_sp_workspace_bytes.argtypes = [C.POINTER(SpRun), C.c_int]

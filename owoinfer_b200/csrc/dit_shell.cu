@@ -12,7 +12,9 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <list>
 #include <map>
+#include <new>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -416,19 +418,21 @@ size_t b2_dit_forward_workspace_bytes(const b2_dit_model* model, const b2_forwar
 }
 
 namespace {
-int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void* stream_);
+int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, const float* time_device, void* stream_);
 }
 
 int b2_dit_forward(const b2_dit_model* model, const b2_forward* forward, void* stream) {
   try {
-    return dit_forward_impl(model, forward, stream);
+    return dit_forward_impl(model, forward, nullptr, stream);
   } catch (const std::exception& e) {  // host containers may throw; nothing may cross the C boundary
     return fail_status(B2_ERR_INTERNAL, "dit_forward", e.what());
   }
 }
 
 namespace {
-int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void* stream_) {
+// time_device: the time vector already on the device (fp32 [D]), read in place of forward->time_vector; a captured
+// forward takes it so that its graph does not freeze one step's time vector.
+int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, const float* time_device, void* stream_) {
   constexpr const char* op = "dit_forward";
   std::vector<std::int64_t> off;
   Carve c{};
@@ -436,7 +440,7 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
   if (const int rc = plan_forward(op, model, forward, &off, &c, &widest)) return rc;
   const b2_dit_model& m = *model;
   const b2_forward& f = *forward;
-  if (f.latents == nullptr || f.time_vector == nullptr) return fail_invalid(op, "needs latents and the host time vector");
+  if (f.latents == nullptr || (f.time_vector == nullptr && time_device == nullptr)) return fail_invalid(op, "needs latents and the host time vector");
   if (m.block_mod_w == nullptr || m.block_mod_bias == nullptr || m.head_mod_w == nullptr || m.head_mod_bias == nullptr ||
       (m.video_w == nullptr && m.ext_w == nullptr) || m.final_norm == nullptr || m.final_w == nullptr) {
     return fail_invalid(op, "the model lacks a modulation, embedder or head tensor");
@@ -451,7 +455,7 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
   __nv_bfloat16* rope = reinterpret_cast<__nv_bfloat16*>(base + c.rope);
   __nv_bfloat16* mod = reinterpret_cast<__nv_bfloat16*>(base + c.mod);
   __nv_bfloat16* head = reinterpret_cast<__nv_bfloat16*>(base + c.head);
-  float* time = reinterpret_cast<float*>(base + c.time);
+  const float* time = time_device != nullptr ? time_device : reinterpret_cast<const float*>(base + c.time);
   __nv_bfloat16* tokens = reinterpret_cast<__nv_bfloat16*>(base + c.tokens);
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(base + c.y);
   std::int32_t* cu_dev = reinterpret_cast<std::int32_t*>(base + c.cu);
@@ -498,7 +502,9 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
     if (const int rc = write_words(op, cu_k_dev, cu_k.data(), cu_k.size(), stream)) return rc;
   }
   // time_modulation: the time vector (host, fp32) through the two modulation linears.
-  if (const int rc = write_words(op, time, f.time_vector, static_cast<std::size_t>(D), stream)) return rc;
+  if (time_device == nullptr) {
+    if (const int rc = write_words(op, base + c.time, f.time_vector, static_cast<std::size_t>(D), stream)) return rc;
+  }
   if (const int rc = b2_linear_fp32_row(m.block_mod_w, time, m.block_mod_bias, mod, static_cast<int>(6 * D), static_cast<int>(D), stream)) return rc;
   if (const int rc = b2_linear_fp32_row(m.head_mod_w, time, m.head_mod_bias, head, static_cast<int>(2 * D), static_cast<int>(D), stream)) return rc;
 
@@ -559,6 +565,219 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, void*
   return B2_OK;
 }
 }  // namespace
+
+}  // extern "C"
+
+namespace b2 {
+// ------------------------------------------------------------------------------------------------ step graphs
+// CUDA graphs of whole forwards (moss_dit::StepGraphs, src/models/moss_dit/dit_graph.h:14-66, over runtime::GraphCache,
+// src/runtime/graph_cache.h:20-58). A graph freezes kernel arguments and addresses, so an entry's key is everything the
+// enqueued work depends on except device memory contents: the model structure and its block table (weight addresses
+// and shapes), the latent grid, every row (text address and length, skip set, latent index, output address), the
+// tier and attention options, the workspace, the reference cache and the device. The step's time vector is the one
+// host array that changes between steps of the same shape: it is written to a buffer of the cache ahead of the graph
+// and the captured forward reads it from there. Entries are found by a 64-bit hash and the whole key is compared on a
+// hit, so two keys with one hash run the second one eagerly rather than replaying the wrong graph.
+namespace {
+
+struct GraphEntry {
+  std::uint64_t hash = 0;
+  std::vector<unsigned char> key;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+};
+
+void destroy_entry(GraphEntry& e) {
+  if (e.exec != nullptr) cudaGraphExecDestroy(e.exec);
+  if (e.graph != nullptr) cudaGraphDestroy(e.graph);
+  e.exec = nullptr, e.graph = nullptr;
+}
+
+template <typename T>
+void put(std::vector<unsigned char>* key, const T& v) {
+  static_assert(std::is_trivially_copyable_v<T>, "keys are raw bytes");
+  const auto* p = reinterpret_cast<const unsigned char*>(&v);
+  key->insert(key->end(), p, p + sizeof(T));
+}
+
+std::uint64_t fnv1a(const std::vector<unsigned char>& key) {
+  std::uint64_t h = 1469598103934665603ull;
+  for (const unsigned char c : key) h = (h ^ c) * 1099511628211ull;
+  return h;
+}
+
+}  // namespace
+}  // namespace b2
+
+struct b2_dit_graphs {
+  std::size_t capacity = 0;
+  std::list<b2::GraphEntry> lru;  // front = most recently used
+  std::map<std::uint64_t, std::list<b2::GraphEntry>::iterator> by_hash;
+  b2_dit_graph_stats stats{};
+  float* time = nullptr;  // device fp32 [D]: the time vector of the step being enqueued
+  int device = -1;
+};
+
+namespace b2 {
+namespace {
+
+// Field by field (struct padding is not part of a key).
+void forward_key(const b2_dit_model& m, const b2_forward& f, int device, std::vector<unsigned char>* key) {
+  key->clear();
+  put(key, device);
+  put(key, m.blocks), put(key, m.num_blocks), put(key, m.D), put(key, m.F), put(key, m.heads), put(key, m.latent_channels);
+  put(key, m.block_mod_w), put(key, m.block_mod_bias), put(key, m.head_mod_w), put(key, m.head_mod_bias);
+  put(key, m.video_w), put(key, m.video_bias), put(key, m.final_norm), put(key, m.final_w), put(key, m.final_bias);
+  put(key, m.ext_w), put(key, m.ext_bias), put(key, m.ext_channels);
+  for (int b = 0; b < m.num_blocks; ++b) {
+    const b2_block_weights& w = m.blocks[b];
+    put(key, w.norm1), put(key, w.norm2), put(key, w.q_norm), put(key, w.k_norm);
+    for (const b2_linear* l : {&w.qkv, &w.o, &w.up_gate, &w.down}) {
+      put(key, l->w), put(key, l->scale), put(key, l->w4);
+      if (l->w4 != nullptr) {
+        const b2_w4_weight& q = *l->w4;
+        put(key, q.packed), put(key, q.s_rel), put(key, q.scale_kind), put(key, q.group), put(key, q.codebook), put(key, q.s_channel);
+      }
+    }
+  }
+  put(key, f.latents), put(key, f.num_latents), put(key, f.height), put(key, f.width), put(key, f.num_rows), put(key, f.tier);
+  put(key, f.attention.variant), put(key, f.attention.p_range), put(key, f.attention.v_range);
+  put(key, f.workspace), put(key, f.workspace_bytes), put(key, f.extra), put(key, f.ref_kv), put(key, f.ref_tokens);
+  for (int r = 0; r < f.num_rows; ++r) {
+    const b2_forward_row& row = f.rows[r];
+    put(key, row.text), put(key, row.text_len), put(key, row.skip), put(key, row.latent), put(key, row.out);
+  }
+}
+
+int graphed_impl(b2_dit_graphs* g, const b2_dit_model* model, const b2_forward* forward, void* stream_, int* replayed) {
+  constexpr const char* op = "dit_forward_graphed";
+  if (replayed != nullptr) *replayed = 0;
+  if (g == nullptr) return fail_invalid(op, "null cache");
+  if (stream_ == nullptr) return fail_invalid(op, "capture needs a stream of its own, not the default stream");
+  // Everything a caller can get wrong is refused before anything is enqueued.
+  std::vector<std::int64_t> off;
+  Carve c{};
+  b2_block_run widest{};
+  if (const int rc = plan_forward(op, model, forward, &off, &c, &widest)) return rc;
+  if (forward->time_vector == nullptr) return fail_invalid(op, "needs the host time vector");
+  cudaStream_t stream = as_stream(stream_);
+  int device = 0;
+  if (const cudaError_t e = cudaGetDevice(&device); e != cudaSuccess) return fail_cuda(op, e);
+  if (g->time == nullptr) {
+    if (const cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&g->time), static_cast<std::size_t>(model->D) * sizeof(float)); e != cudaSuccess) {
+      return fail_cuda(op, e);
+    }
+    g->device = device;
+  }
+  if (g->device != device) return fail_invalid(op, "a cache belongs to the device of its first forward");
+  if (const int rc = write_words(op, g->time, forward->time_vector, static_cast<std::size_t>(model->D), stream)) return rc;
+
+  std::vector<unsigned char> key;
+  forward_key(*model, *forward, device, &key);
+  const std::uint64_t hash = fnv1a(key);
+  const auto hit = g->by_hash.find(hash);
+  if (hit != g->by_hash.end()) {
+    if (hit->second->key != key) {
+      ++g->stats.collisions;
+      return dit_forward_impl(model, forward, g->time, stream_);
+    }
+    g->lru.splice(g->lru.begin(), g->lru, hit->second);
+    if (const cudaError_t e = cudaGraphLaunch(hit->second->exec, stream); e != cudaSuccess) return fail_cuda(op, e);
+    ++g->stats.replays;
+    if (replayed != nullptr) *replayed = 1;
+    return B2_OK;
+  }
+  if (g->capacity == 0) {
+    ++g->stats.eager;
+    return dit_forward_impl(model, forward, g->time, stream_);
+  }
+  // What the library sets up once per device and cannot do inside a capture.
+  cublasLtHandle_t handle = nullptr;
+  if (const int rc = lt_handle(&handle)) return rc;
+
+  GraphEntry entry;
+  entry.hash = hash, entry.key = std::move(key);
+  if (const cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal); e != cudaSuccess) return fail_cuda(op, e);
+  const int rc = dit_forward_impl(model, forward, g->time, stream_);
+  const cudaError_t ended = cudaStreamEndCapture(stream, &entry.graph);
+  cudaError_t made = cudaSuccess;
+  if (rc == B2_OK && ended == cudaSuccess && entry.graph != nullptr) made = cudaGraphInstantiate(&entry.exec, entry.graph, 0);
+  if (rc != B2_OK || ended != cudaSuccess || entry.graph == nullptr || made != cudaSuccess) {
+    // Nothing of a failed capture ran. Run the forward as it is; the next call with this key tries again.
+    destroy_entry(entry);
+    cudaGetLastError();
+    ++g->stats.eager;
+    return dit_forward_impl(model, forward, g->time, stream_);
+  }
+  if (const cudaError_t e = cudaGraphLaunch(entry.exec, stream); e != cudaSuccess) {
+    destroy_entry(entry);
+    return fail_cuda(op, e);
+  }
+  g->lru.push_front(std::move(entry));
+  g->by_hash[hash] = g->lru.begin();
+  ++g->stats.captures;
+  while (g->lru.size() > g->capacity) {
+    g->by_hash.erase(g->lru.back().hash);
+    destroy_entry(g->lru.back());
+    g->lru.pop_back();
+    ++g->stats.evictions;
+  }
+  return B2_OK;
+}
+
+void clear_graphs(b2_dit_graphs* g) {
+  for (GraphEntry& e : g->lru) destroy_entry(e);
+  g->lru.clear();
+  g->by_hash.clear();
+}
+
+}  // namespace
+}  // namespace b2
+
+extern "C" {
+
+int b2_dit_graphs_create(size_t capacity, b2_dit_graphs** out) {
+  if (out == nullptr) return fail_invalid("dit_graphs_create", "null output");
+  *out = nullptr;
+  b2_dit_graphs* g = new (std::nothrow) b2_dit_graphs;
+  if (g == nullptr) return fail_status(B2_ERR_INTERNAL, "dit_graphs_create", "out of host memory");
+  g->capacity = capacity;
+  *out = g;
+  return B2_OK;
+}
+
+int b2_dit_graphs_clear(b2_dit_graphs* graphs) {
+  if (graphs == nullptr) return fail_invalid("dit_graphs_clear", "null cache");
+  clear_graphs(graphs);
+  return B2_OK;
+}
+
+int b2_dit_graphs_destroy(b2_dit_graphs* graphs) {
+  if (graphs == nullptr) return B2_OK;
+  clear_graphs(graphs);
+  if (graphs->time != nullptr) cudaFree(graphs->time);
+  delete graphs;
+  return B2_OK;
+}
+
+int b2_dit_graphs_stats(const b2_dit_graphs* graphs, b2_dit_graph_stats* stats) {
+  if (graphs == nullptr || stats == nullptr) return fail_invalid("dit_graphs_stats", "null argument");
+  *stats = graphs->stats;
+  stats->size = graphs->lru.size();
+  return B2_OK;
+}
+
+int b2_dit_forward_graphed(b2_dit_graphs* graphs, const b2_dit_model* model, const b2_forward* forward, void* stream, int* replayed) {
+  try {
+    return graphed_impl(graphs, model, forward, stream, replayed);
+  } catch (const std::exception& e) {  // nothing may cross the C boundary
+    return fail_status(B2_ERR_INTERNAL, "dit_forward_graphed", e.what());
+  }
+}
+
+}  // extern "C"
+
+extern "C" {
 
 namespace {
 struct PrefillCarve {

@@ -550,12 +550,44 @@ class DitModel:
         self.struct = m
 
 
-def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, workspace=None, extra=None, ref_kv=None):
+class DitGraphs:
+    """b2_dit_graphs: CUDA graphs of whole forwards, least recently used first out. Creating one touches no device."""
+
+    def __init__(self, capacity=8):
+        self.handle = C.c_void_p()
+        check(_lib.lib().b2_dit_graphs_create(capacity, C.byref(self.handle)))
+        self.last_replayed = False
+
+    def stats(self):
+        st = _lib.DitGraphStats()
+        check(_lib.lib().b2_dit_graphs_stats(self.handle, C.byref(st)))
+        return {name: int(getattr(st, name)) for name, _ in st._fields_}
+
+    def clear(self):
+        check(_lib.lib().b2_dit_graphs_clear(self.handle))
+
+    def close(self):
+        if self.handle:
+            _lib.lib().b2_dit_graphs_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, workspace=None, extra=None, ref_kv=None,
+                graphs=None, outs=None):
     """rows: list of (text bf16 [S, D], skip mask int, latent index). latents f32 [n, 128, h, w]; time_vector numpy f32 [D].
-    Returns the per-row outputs f32 [128, h, w] (and the workspace, for reuse)."""
+    Returns the per-row outputs f32 [128, h, w] (and the workspace, for reuse). With `graphs` (a DitGraphs) the forward
+    goes through b2_dit_forward_graphed on the current (non-default) stream; pass the same `outs` and `workspace` again for
+    the call to find its graph."""
     import numpy as np
     n, _, h, w = latents.shape
-    outs = [torch.empty((128, h, w), dtype=torch.float32, device=latents.device) for _ in rows]
+    if outs is None:
+        outs = [torch.empty((128, h, w), dtype=torch.float32, device=latents.device) for _ in rows]
     arr = (_lib.ForwardRow * len(rows))()
     for i, (text, skip, latent) in enumerate(rows):
         arr[i].text, arr[i].text_len, arr[i].skip, arr[i].latent, arr[i].out = text.data_ptr(), text.shape[0], skip, latent, outs[i].data_ptr()
@@ -572,7 +604,12 @@ def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, wor
     if workspace is None or workspace.numel() < need:
         workspace = torch.empty(need, dtype=torch.uint8, device=latents.device)
     f.workspace, f.workspace_bytes = workspace.data_ptr(), workspace.numel()
-    check(_lib.lib().b2_dit_forward(C.byref(model.struct), C.byref(f), _stream()))
+    if graphs is None:
+        check(_lib.lib().b2_dit_forward(C.byref(model.struct), C.byref(f), _stream()))
+    else:
+        replayed = C.c_int(0)
+        check(_lib.lib().b2_dit_forward_graphed(graphs.handle, C.byref(model.struct), C.byref(f), _stream(), C.byref(replayed)))
+        graphs.last_replayed = bool(replayed.value)
     return outs, workspace
 
 

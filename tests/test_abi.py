@@ -220,6 +220,24 @@ def test_block_rejects_mismatched_buffers():
     assert _status(lib.b2_run_block_quant(C.byref(w), C.byref(b), C.byref(run), None))[0] == -1
 
 
+def test_step_graph_cache_handle_and_checks():
+    """A cache is host state until its first forward; a graphed forward is refused on the default stream and on a bad
+    forward before anything is enqueued (dit_graph.h:49-52: the stream of a capture is not the default stream)."""
+    lib = _lib.lib()
+    g = C.c_void_p()
+    assert lib.b2_dit_graphs_create(4, C.byref(g)) == 0 and g.value
+    st = _lib.DitGraphStats()
+    assert lib.b2_dit_graphs_stats(g, C.byref(st)) == 0
+    assert (st.replays, st.captures, st.collisions, st.eager, st.evictions, st.size) == (0, 0, 0, 0, 0, 0)
+    m, f, replayed = _lib.DitModel(), _lib.Forward(), C.c_int(7)
+    rc, msg = _status(lib.b2_dit_forward_graphed(g, C.byref(m), C.byref(f), None, C.byref(replayed)))
+    assert rc == -1 and "default stream" in msg and replayed.value == 0
+    rc, msg = _status(lib.b2_dit_forward_graphed(g, C.byref(m), C.byref(f), C.c_void_p(0x1000), C.byref(replayed)))
+    assert rc == -1 and "older header" in msg
+    assert _status(lib.b2_dit_forward_graphed(None, C.byref(m), C.byref(f), C.c_void_p(0x1000), None))[0] == -1
+    assert lib.b2_dit_graphs_clear(g) == 0 and lib.b2_dit_graphs_destroy(g) == 0 and lib.b2_dit_graphs_destroy(None) == 0
+
+
 def test_cpp_shim_compiles_against_the_reference_headers():
     """include/owoinfer_b200_shim.hpp takes moss_dit::run_block_quant's parameters in its order
     (src/models/moss_dit/dit_block_quant.h:145-146): checked by the compiler against the reference's own headers."""

@@ -332,3 +332,61 @@ def test_input_extension(ops):
     assert torch.equal(got[0].view(torch.int32), want.view(torch.int32))
     with pytest.raises(ValueError, match="extra latents"):
         ops.dit_forward(model, latents, tv, [(text, 0, 0)])
+
+
+def test_step_graphs_replay_the_forward(ops):
+    """b2_dit_forward_graphed: the first call of a key captures (or, when a capture cannot be made, runs eagerly), later
+    calls replay; the time vector is not part of the graph; a new shape is a new graph; the oldest graph leaves a full
+    cache. Every output equals the eager forward's bit for bit."""
+    D, F, h, w = 3072, 8192, 8, 12
+    model, _, _, _ = _model(ops, 2, F, 5)
+    rng = np.random.default_rng(17)
+    latents = torch.from_numpy(rng.normal(0, 1, (1, 128, h, w)).astype(np.float32)).cuda()
+    texts = [bfdev(to_bf16(rng.normal(0, 1, (s, D)))) for s in (19, 40)]
+    tvs = [rng.normal(0, 1, D).astype(np.float32) for _ in range(3)]
+    rows = [(texts[0], 0, 0), (texts[1], 0b10, 0)]
+    want = [[o.clone() for o in ops.dit_forward(model, latents, tv, rows)[0]] for tv in tvs]
+    torch.cuda.synchronize()
+    assert not torch.equal(want[0][0], want[1][0])
+
+    graphs = ops.DitGraphs(capacity=1)
+    assert graphs.stats() == dict(replays=0, captures=0, collisions=0, eager=0, evictions=0, size=0)
+    side = torch.cuda.Stream()
+    outs = ws = None
+    with torch.cuda.stream(side):
+        for i, tv in enumerate(tvs + tvs[:1]):
+            outs, ws = ops.dit_forward(model, latents, tv, rows, graphs=graphs, outs=outs, workspace=ws)
+            side.synchronize()
+            for r in range(2):
+                assert torch.equal(outs[r].view(torch.int32), want[i % 3][r].view(torch.int32)), (i, r)
+        st = graphs.stats()
+        # A cold process may run the first forward eagerly (one-time set-up cannot be captured); it captures on the next call.
+        assert st["captures"] == 1 and st["size"] == 1 and st["captures"] + st["eager"] + st["replays"] == 4
+        assert st["replays"] >= 2 and graphs.last_replayed and st["collisions"] == 0
+
+        # Another text length: another key. Capacity 1: the first graph leaves.
+        rows2 = [(texts[1], 0, 0)]
+        want2 = ops.dit_forward(model, latents, tvs[0], rows2)[0][0].clone()
+        outs2, ws2 = ops.dit_forward(model, latents, tvs[0], rows2, graphs=graphs)
+        side.synchronize()
+        assert torch.equal(outs2[0].view(torch.int32), want2.view(torch.int32))
+        st2 = graphs.stats()
+        assert st2["captures"] == 2 and st2["evictions"] == 1 and st2["size"] == 1 and not graphs.last_replayed
+        outs2, ws2 = ops.dit_forward(model, latents, tvs[1], rows2, graphs=graphs, outs=outs2, workspace=ws2)
+        side.synchronize()
+        assert graphs.last_replayed
+        graphs.clear()
+        assert graphs.stats()["size"] == 0
+
+    # The default stream cannot be captured: refused before anything runs.
+    with pytest.raises(ValueError, match="default stream"):
+        ops.dit_forward(model, latents, tvs[0], rows, graphs=graphs)
+    # Capacity 0: always eager.
+    none = ops.DitGraphs(capacity=0)
+    with torch.cuda.stream(side):
+        o, _ = ops.dit_forward(model, latents, tvs[2], rows, graphs=none)
+        side.synchronize()
+    assert torch.equal(o[0].view(torch.int32), want[2][0].view(torch.int32)) and none.stats()["eager"] == 1
+    graphs.close()
+    none.close()
+    assert ops.kernel_status() == (0, 0)
