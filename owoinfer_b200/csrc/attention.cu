@@ -698,6 +698,15 @@ constexpr std::uint32_t kTmemCols = 256;  // S(u % 2): columns [64 (u % 2), +64)
 // nothing measurable.
 constexpr float kHeadroom = 3.0f, kRaise = 1.0f;
 
+// 1 = the CTAs that start on an SM alternate which of warps 0 and 1 loads and which issues the MMAs, so that the two CTAs
+// resident on an SM do not both put their MMA warp on the same warp scheduler.
+#ifndef B2_ATTN_ROLE_SWAP
+#define B2_ATTN_ROLE_SWAP 0
+#endif
+#if B2_ATTN_ROLE_SWAP
+__device__ unsigned g_attn_sm_launches[1024];
+#endif
+
 struct AttnArgs {
   const float* q_scale;
   const float* k_scale;
@@ -775,6 +784,9 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       s_v_empty[kKvStages], s_step[2], s_p_full[2], s_s_ready;
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
+#if B2_ATTN_ROLE_SWAP
+  __shared__ int s_swap;
+#endif
   const std::uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const std::uint32_t q_smem = base;
   const auto k_smem = [&](int s) { return base + kTileBytes * (1 + s); };
@@ -797,6 +809,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     mbar_init(smem_u32(&s_s_ready), 4);
     s_abort = 0;
+#if B2_ATTN_ROLE_SWAP
+    unsigned smid;
+    asm("mov.u32 %0, %%smid;" : "=r"(smid));
+    s_swap = static_cast<int>(atomicAdd(&g_attn_sm_launches[smid & 1023u], 1u) & 1u);
+#endif
     fence_mbar_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
@@ -813,8 +830,13 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   volatile int* abort_word = &s_abort;
   const int n_tiles = (kv_len + kTileK - 1) / kTileK;  // 128-key K/V tiles
   const int n_sub = (kv_len + kSubK - 1) / kSubK;      // 64-key sub-tiles
+#if B2_ATTN_ROLE_SWAP
+  const int tma_warp = s_swap, mma_warp = s_swap ^ 1;
+#else
+  constexpr int tma_warp = 0, mma_warp = 1;
+#endif
 
-  if (warp == 0) {
+  if (warp == tma_warp) {
     if (lane == 0) {
       mbar_expect_tx(smem_u32(&s_q_full), kTileBytes);
       tma_load_2d(q_smem, &map_q, smem_u32(&s_q_full), h * kHeadDim, q_start + q0);
@@ -830,7 +852,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == mma_warp) {
     // The whole warp walks the loop (uniform control flow, every lane takes the waits); one elected lane issues.
 #ifdef B2_ATTN_TRACE
     const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
@@ -877,7 +899,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       bool got = true;
       if ((u & 1) == 0) got = wait_bar(smem_u32(&s_v_full[s]), ((u >> 1) / kKvStages) & 1u, abort_word);
       // The softmax warps have consumed S(u) and written P(u).
-      got = got && wait_bar_relaxed<B2_MMA_SLEEP_NS>(smem_u32(&s_p_full[u & 1]), (u >> 1) & 1u, abort_word);
+      if constexpr (B2_MMA_SLEEP_NS == 0) got = got && wait_bar(smem_u32(&s_p_full[u & 1]), (u >> 1) & 1u, abort_word);
+      else got = got && wait_bar_relaxed<B2_MMA_SLEEP_NS>(smem_u32(&s_p_full[u & 1]), (u >> 1) & 1u, abort_word);
       if (__any_sync(0xffffffffu, !got)) break;
       tc_fence_after();
       TRACE(5);
