@@ -698,15 +698,6 @@ constexpr std::uint32_t kTmemCols = 256;  // S(u % 2): columns [64 (u % 2), +64)
 // nothing measurable.
 constexpr float kHeadroom = 3.0f, kRaise = 1.0f;
 
-// 1 = the CTAs that start on an SM alternate which of warps 0 and 1 loads and which issues the MMAs, so that the two CTAs
-// resident on an SM do not both put their MMA warp on the same warp scheduler.
-#ifndef B2_ATTN_ROLE_SWAP
-#define B2_ATTN_ROLE_SWAP 0
-#endif
-#if B2_ATTN_ROLE_SWAP
-__device__ unsigned g_attn_sm_launches[1024];
-#endif
-
 struct AttnArgs {
   const float* q_scale;
   const float* k_scale;
@@ -784,9 +775,6 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       s_v_empty[kKvStages], s_step[2], s_p_full[2], s_s_ready;
   __shared__ std::uint32_t s_tmem_base;
   __shared__ int s_abort;
-#if B2_ATTN_ROLE_SWAP
-  __shared__ int s_swap;
-#endif
   const std::uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const std::uint32_t q_smem = base;
   const auto k_smem = [&](int s) { return base + kTileBytes * (1 + s); };
@@ -809,11 +797,6 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     mbar_init(smem_u32(&s_s_ready), 4);
     s_abort = 0;
-#if B2_ATTN_ROLE_SWAP
-    unsigned smid;
-    asm("mov.u32 %0, %%smid;" : "=r"(smid));
-    s_swap = static_cast<int>(atomicAdd(&g_attn_sm_launches[smid & 1023u], 1u) & 1u);
-#endif
     fence_mbar_init();
     prefetch_tensormap(&map_q);
     prefetch_tensormap(&map_k);
@@ -830,13 +813,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   volatile int* abort_word = &s_abort;
   const int n_tiles = (kv_len + kTileK - 1) / kTileK;  // 128-key K/V tiles
   const int n_sub = (kv_len + kSubK - 1) / kSubK;      // 64-key sub-tiles
-#if B2_ATTN_ROLE_SWAP
-  const int tma_warp = s_swap, mma_warp = s_swap ^ 1;
-#else
-  constexpr int tma_warp = 0, mma_warp = 1;
-#endif
 
-  if (warp == tma_warp) {
+  if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(smem_u32(&s_q_full), kTileBytes);
       tma_load_2d(q_smem, &map_q, smem_u32(&s_q_full), h * kHeadDim, q_start + q0);
@@ -852,7 +830,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
     }
     __syncwarp();
-  } else if (warp == mma_warp) {
+  } else if (warp == 1) {
     // The whole warp walks the loop (uniform control flow, every lane takes the waits); one elected lane issues.
 #ifdef B2_ATTN_TRACE
     const bool tracing = a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
@@ -899,8 +877,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       bool got = true;
       if ((u & 1) == 0) got = wait_bar(smem_u32(&s_v_full[s]), ((u >> 1) / kKvStages) & 1u, abort_word);
       // The softmax warps have consumed S(u) and written P(u).
-      if constexpr (B2_MMA_SLEEP_NS == 0) got = got && wait_bar(smem_u32(&s_p_full[u & 1]), (u >> 1) & 1u, abort_word);
-      else got = got && wait_bar_relaxed<B2_MMA_SLEEP_NS>(smem_u32(&s_p_full[u & 1]), (u >> 1) & 1u, abort_word);
+      got = got && wait_bar_relaxed<B2_MMA_SLEEP_NS>(smem_u32(&s_p_full[u & 1]), (u >> 1) & 1u, abort_word);
       if (__any_sync(0xffffffffu, !got)) break;
       tc_fence_after();
       TRACE(5);
@@ -941,6 +918,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const bool dumping = kDump && b == a.dump_seq && h == a.dump_head && bq == a.dump_tile;
     constexpr float kNone = -5000000.0f;  // "no score": below every scaled score
     float m_run = kNone, d_run = 0.f;
+    float mx_run = kNone;  // the row's largest scaled score so far
+    // Rows past the sequence's end hold whatever the tile load brought (the next sequence's queries, or zeros): they follow
+    // the warp's raises but never ask for one, so a sequence's output does not depend on its neighbours in the batch.
+    const bool row_live = q0 + r_local < qo_len;
     float o_scale = 1.0f;  // factor O still has to be multiplied by (applied once the P·V before it have landed)
     // Bounded wait with one answer for the whole warp (the TMEM accesses that follow are warp-wide).
     const auto warp_wait = [&](std::uint32_t bar, std::uint32_t parity) {
@@ -1069,12 +1050,18 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         TRACE(13);
         // Less than kRaise binades of headroom left: raise the reference for the sub-tiles to come. P·V of this one was
         // computed against the old reference, so O is rescaled after it lands (at the end of the next pass).
-        if (mx - m_run > a.p_offset - kRaise) {
-          const float m_new = mx - (a.p_offset - kHeadroom);
-          const float grow = ex2(m_run - m_new);
-          m_run = m_new;
-          d_run *= grow;
-          o_scale = grow;
+        // One row short of headroom raises the reference of every row of the warp whose scores have grown since its last
+        // raise: the rescale that follows is the whole warp's anyway (it stalls the CTA's pipeline for about a pass), and
+        // rows raised together do not ask for one each later.
+        mx_run = fmaxf(mx_run, mx);
+        if (__any_sync(0xffffffffu, row_live && mx - m_run > a.p_offset - kRaise)) {
+          const float m_new = mx_run - (a.p_offset - kHeadroom);
+          if (m_new > m_run) {
+            const float grow = ex2(m_run - m_new);
+            m_run = m_new;
+            d_run *= grow;
+            o_scale = grow;
+          }
         }
         ks_cur = ks_next;
       }
