@@ -110,12 +110,7 @@ __device__ __forceinline__ std::uint32_t pack_i8x4(float a, float b, float c, fl
   return (static_cast<std::uint32_t>(f2i8(a)) & 0xFF) | ((static_cast<std::uint32_t>(f2i8(b)) & 0xFF) << 8) |
          ((static_cast<std::uint32_t>(f2i8(c)) & 0xFF) << 16) | ((static_cast<std::uint32_t>(f2i8(d)) & 0xFF) << 24);
 }
-// Two floats -> two e4m3 bytes (round to nearest even, saturate to +-448): `lo` in the low byte.
-__device__ __forceinline__ std::uint32_t e4m3x2(float lo, float hi) {
-  std::uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
+// Four floats -> four e4m3 bytes (round to nearest even, saturate to +-448): `a` in the low byte.
 __device__ __forceinline__ std::uint32_t e4m3x4(float a, float b, float c, float d) {
   std::uint32_t w;
   asm("{\n\t.reg .b16 lo, hi;\n\t"
@@ -898,6 +893,14 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (elect_one()) tc_commit(smem_u32(&s_step[u & 1]));
       __syncwarp();
       TRACE(7);
+#ifdef B2_ATTN_TRACE
+      // Tracing only: when the step's MMAs have completed (the warp has nothing else to do until P(u + 1) arrives).
+      if (tracing) {
+        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(smem_u32(&s_step[u & 1]), ((u >> 1) + 1) & 1u); ++spin) {
+        }
+        TRACE(15);
+      }
+#endif
     }
   } else {
     // Softmax: 4 warps, one thread per query row; warp w may touch TMEM lanes [32 (w % 4), +32). One pass per sub-tile:
