@@ -194,9 +194,13 @@ int b2_moss_rope_table(void* out, int64_t ld, int height, int width, int text_le
  * column) with moss_rope_table's bands and arithmetic. */
 int b2_moss_rope_table_reference(void* out, int64_t ld, int height, int width, int index, void* stream);
 
-/* attention_q8::Variant / Options (src/kernels/attention_q8/attention_q8.h:75-88). Only the e4m3 P·V variant with fp32
- * accumulation (MI_ATTENTION_Q8_FP8_F32ACC, include/mossinfer/mossinfer.h:269) exists here: tcgen05 accumulates in
- * fp32. p_range / v_range <= 0 pick 448 / 448. */
+/* attention_q8::Variant / Options (src/kernels/attention_q8/attention_q8.h:75-88), the two e4m3 P·V variants
+ * (MI_ATTENTION_Q8_FP8, MI_ATTENTION_Q8_FP8_F32ACC, include/mossinfer/mossinfer.h:268-269). p_range / v_range <= 0 pick
+ * the variant's defaults: 448 / 448 for int8_fp8_f32acc, 112 / 4.5 for int8_fp8. tcgen05 accumulates in fp32, so
+ * int8_fp8 runs the same kernel with its own ranges: where the reference adds a 64-key tile in fp16 before flushing it
+ * into fp32, this library adds in fp32 throughout (at least as close to exact attention); ranges are accepted and
+ * refused by the reference's rule for fp16 accumulation all the same. The fp16 P·V variants (0, 1) are not built. */
+#define B2_ATTENTION_Q8_FP8 2
 #define B2_ATTENTION_Q8_FP8_F32ACC 3
 typedef struct b2_attention_options {
   int variant;

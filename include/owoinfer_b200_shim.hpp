@@ -30,12 +30,13 @@ inline void b200_check(int status) {
   throw std::runtime_error(what);
 }
 
-// The blocks this library runs: all four linears INT8 ConvRot and fused (dit_weights.h:106-111), attention in the e4m3
-// P.V variant with fp32 accumulation, no LoRA side branch; reference slots and the K/V tap included. Everything else
-// stays on the reference's own path.
+// The blocks this library runs: all four linears INT8 ConvRot and fused (dit_weights.h:106-111), attention in one of the
+// e4m3 P.V variants (q8_fp8, the High tier's default, with its 112 / 4.5 ranges and fp32 in place of its fp16 tile
+// accumulation; q8_fp8_f32acc), no LoRA side branch; reference slots and the K/V tap included. Everything else stays on
+// the reference's own path.
 inline bool b200_can_run(const BlockTensors& w, const QuantBlockBuffers& a, const BlockRun& /*run*/, AttentionMode attention) {
   return !w.qkv_split && !w.qkv8.empty() && !w.o8.empty() && !w.up_gate8.empty() && !w.down8.empty() && !w.int4() &&
-         !w.nvfp4() && attention == AttentionMode::kQ8Fp8F32Acc && a.lora == nullptr;
+         !w.nvfp4() && (attention == AttentionMode::kQ8Fp8F32Acc || attention == AttentionMode::kQ8Fp8) && a.lora == nullptr;
 }
 
 // The b2_block_run of a run of the reference: D and F from the weights' shapes, heads = D / 128. With reference slots the
@@ -86,7 +87,7 @@ inline void run_block_quant_b200(const BlockTensors& w, const QuantBlockBuffers&
                                  const QkvGemm& /*qkv_gemm*/, const FusedRouteSnapshot& /*route*/, AttentionMode attention,
                                  cudaStream_t stream, int /*block*/, void* workspace, std::size_t workspace_bytes) {
   if (!b200_can_run(w, a, run, attention)) {
-    throw std::invalid_argument("run_block_quant_b200: not an all-INT8 block with q8_fp8_f32acc attention, or it uses LoRA");
+    throw std::invalid_argument("run_block_quant_b200: not an all-INT8 block with q8_fp8 or q8_fp8_f32acc attention, or it uses LoRA");
   }
   const auto lin = [](const Int8Linear& l) {
     return b2_linear{static_cast<const std::int8_t*>(l.w.data), static_cast<const float*>(l.scale.data), nullptr};
@@ -95,7 +96,8 @@ inline void run_block_quant_b200(const BlockTensors& w, const QuantBlockBuffers&
   bw.struct_size = sizeof(b2_block_weights);
   bw.norm1 = w.norm1.data, bw.norm2 = w.norm2.data, bw.q_norm = w.q_norm.data, bw.k_norm = w.k_norm.data;
   bw.qkv = lin(w.qkv8), bw.o = lin(w.o8), bw.up_gate = lin(w.up_gate8), bw.down = lin(w.down8);
-  const b2_block_run br = b200_block_run(w, run, &a);
+  b2_block_run br = b200_block_run(w, run, &a);
+  if (attention == AttentionMode::kQ8Fp8) br.attention.variant = B2_ATTENTION_Q8_FP8;
   b2_block_buffers bb{};
   bb.struct_size = sizeof(b2_block_buffers);
   bb.x = static_cast<char*>(a.f.x.data) + run.t0 * a.f.x.stride[0] * 2;          // rows [t0, t1) of the residual stream

@@ -33,6 +33,8 @@ def lib():
         l.ref_attention_q8_workspace_bytes.restype = sz
         l.ref_attention_q8_workspace_bytes.argtypes = [i64, i32, i32, i32]
         l.ref_attention_q8.argtypes = [vp, i64, i64, i32, vp, i64, vp, i32, i32, f32, vp, sz, i32, vp, vp, vp, vp]
+        if hasattr(l, "ref_attention_q8_variant"):
+            l.ref_attention_q8_variant.argtypes = [i32, f32, f32, vp, i64, i64, i32, vp, i64, vp, i32, i32, f32, vp, sz, i32, vp, vp, vp, vp]
         if hasattr(l, "ref_cfg_velocity"):
             l.ref_cfg_velocity.argtypes = [vp, vp, f32, vp, i64, vp]
             l.ref_slg_velocity.argtypes = [vp, vp, vp, f32, vp, i64, vp]
@@ -98,10 +100,20 @@ def attention_workspace_bytes(total, batch, max_seqlen, heads) -> int:
     return int(lib().ref_attention_q8_workspace_bytes(total, batch, max_seqlen, heads))
 
 
-def attention_q8(qkv, heads, out, cu, max_seqlen, scale, workspace, norm_rope=None):
+def has_attention_variants() -> bool:
+    return hasattr(lib(), "ref_attention_q8_variant")
+
+
+def attention_q8(qkv, heads, out, cu, max_seqlen, scale, workspace, norm_rope=None, variant=3, p_range=0.0, v_range=0.0):
     """Self-attention over a fused [total, 3 * heads * 128] buffer; norm_rope = (q_norm, k_norm, table) fuses QK-norm +
-    RoPE into the pre-pass (the buffer itself is then left as it was)."""
+    RoPE into the pre-pass (the buffer itself is then left as it was). variant 2 = int8_fp8 (fp16 tile accumulation,
+    ranges 112 / 4.5 by default), 3 = int8_fp8_f32acc."""
     nr = norm_rope or (None, None, None)
+    if variant != 3 or p_range or v_range:
+        _ok(lib().ref_attention_q8_variant(variant, p_range, v_range, _p(qkv), qkv.stride(0), qkv.shape[0], heads, _p(out),
+                                           out.stride(0), _p(cu), cu.numel() - 1, max_seqlen, scale, _p(workspace),
+                                           workspace.numel(), 1 if norm_rope else 0, _p(nr[0]), _p(nr[1]), _p(nr[2]), _stream()))
+        return
     _ok(lib().ref_attention_q8(_p(qkv), qkv.stride(0), qkv.shape[0], heads, _p(out), out.stride(0), _p(cu),
                                cu.numel() - 1, max_seqlen, scale, _p(workspace), workspace.numel(),
                                1 if norm_rope else 0, _p(nr[0]), _p(nr[1]), _p(nr[2]), _stream()))

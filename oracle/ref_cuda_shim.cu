@@ -135,18 +135,21 @@ std::size_t ref_attention_q8_workspace_bytes(std::int64_t total, int batch, int 
   return mi::attention_q8::attention_q8_workspace_bytes(o, total, total, batch, max_seqlen, heads, heads);
 }
 
-// Self-attention over a fused qkv buffer [total, 3 * heads * 128] (row stride ld), variant int8_fp8_f32acc; norm_rope != 0
-// runs the fused QK-norm + RoPE pre-pass.
-int ref_attention_q8(void* qkv, std::int64_t ld, std::int64_t total, int heads, void* out, std::int64_t out_ld, int* cu,
-                     int batch, int max_seqlen, float scale, void* workspace, std::size_t workspace_bytes, int norm_rope,
-                     void* q_norm, void* k_norm, void* table, void* stream) {
+// Self-attention over a fused qkv buffer [total, 3 * heads * 128] (row stride ld); variant 2 = int8_fp8 (fp16 tile
+// accumulation), 3 = int8_fp8_f32acc; p_range / v_range <= 0 pick the variant's defaults; norm_rope != 0 runs the fused
+// QK-norm + RoPE pre-pass.
+int ref_attention_q8_variant(int variant, float p_range, float v_range, void* qkv, std::int64_t ld, std::int64_t total,
+                             int heads, void* out, std::int64_t out_ld, int* cu, int batch, int max_seqlen, float scale,
+                             void* workspace, std::size_t workspace_bytes, int norm_rope, void* q_norm, void* k_norm,
+                             void* table, void* stream) {
   return guarded([&] {
     auto* base = static_cast<__nv_bfloat16*>(qkv);
     const Tensor q = view3(base, total, heads, ld, 128), k = view3(base + heads * 128, total, heads, ld, 128);
     const Tensor v = view3(base + 2 * heads * 128, total, heads, ld, 128), o = view3(out, total, heads, out_ld, 128);
     const Tensor cuq = Tensor::view(cu, DType::kI32, mi::Device::kCUDA, {batch + 1});
     mi::attention_q8::Options opt;
-    opt.variant = mi::attention_q8::Variant::kInt8Fp8F32Acc;
+    opt.variant = variant == 2 ? mi::attention_q8::Variant::kInt8Fp8 : mi::attention_q8::Variant::kInt8Fp8F32Acc;
+    opt.p_range = p_range, opt.v_range = v_range;
     mi::attention_q8::QkNormRope nr;
     if (norm_rope) {
       nr.q_norm = Tensor::view(q_norm, DType::kBF16, mi::Device::kCUDA, {128});
@@ -158,10 +161,18 @@ int ref_attention_q8(void* qkv, std::int64_t ld, std::int64_t total, int heads, 
   });
 }
 
+int ref_attention_q8(void* qkv, std::int64_t ld, std::int64_t total, int heads, void* out, std::int64_t out_ld, int* cu,
+                     int batch, int max_seqlen, float scale, void* workspace, std::size_t workspace_bytes, int norm_rope,
+                     void* q_norm, void* k_norm, void* table, void* stream) {
+  return ref_attention_q8_variant(3, 0.f, 0.f, qkv, ld, total, heads, out, out_ld, cu, batch, max_seqlen, scale, workspace,
+                                  workspace_bytes, norm_rope, q_norm, k_norm, table, stream);
+}
+
 // The guidance and velocity-update kernels of the sampler driver (src/pipeline/samplers/sampler_kernels.cu).
 int ref_cfg_velocity(const float* c, const float* u, float g, float* out, std::int64_t n, cudaStream_t st) {
   return guarded([&] { mi::pipeline::sampler_kernels::cfg_velocity(c, u, g, out, n, st); });
 }
+
 int ref_slg_velocity(const float* p, const float* c, const float* k, float s, float* out, std::int64_t n, cudaStream_t st) {
   return guarded([&] { mi::pipeline::sampler_kernels::slg_velocity(p, c, k, s, out, n, st); });
 }

@@ -1150,7 +1150,19 @@ int check_view(const char* op, const b2_view3* t, const char* name) {
   return B2_OK;
 }
 
-float resolve(float v) { return v > 0 ? v : 448.f; }
+// attention_q8::effective_p_range / effective_v_range (attention_q8.cu:184-194): <= 0 picks the variant's default.
+float resolve_p(const b2_attention_options& o) { return o.p_range > 0 ? o.p_range : o.variant == B2_ATTENTION_Q8_FP8 ? 112.f : 448.f; }
+float resolve_v(const b2_attention_options& o) { return o.v_range > 0 ? o.v_range : o.variant == B2_ATTENTION_Q8_FP8 ? 4.5f : 448.f; }
+float p_offset_of(float p_range) { return static_cast<float>(std::floor(std::log2(static_cast<double>(p_range)) * 1000.0) / 1000.0); }
+// The nearest e4m3 value (ties to even) of a positive number up to 448.
+double e4m3_nearest(double v) {
+  if (v <= 0) return 0;
+  int e = 0;
+  std::frexp(v, &e);                                   // v = f * 2^e, f in [0.5, 1)
+  const int exp = std::max(e - 1, -6);                 // normal exponents -6 .. 8; below: subnormal steps of 2^-9
+  const double step = std::ldexp(1.0, exp - 3);
+  return std::min(448.0, std::nearbyint(v / step) * step);
+}
 
 }  // namespace
 
@@ -1248,8 +1260,8 @@ int attention_impl(const char* op, const b2_attention_options* o, const b2_view3
   if (!prepass_only) {
     if (const int rc = check_view(op, out, "out")) return rc;
   }
-  if (o->variant != B2_ATTENTION_Q8_FP8_F32ACC) {
-    return fail_status(B2_ERR_NOT_SUPPORTED, op, "only the e4m3 P·V variant with fp32 accumulation (int8_fp8_f32acc) is built for sm_100a");
+  if (o->variant != B2_ATTENTION_Q8_FP8_F32ACC && o->variant != B2_ATTENTION_Q8_FP8) {
+    return fail_status(B2_ERR_NOT_SUPPORTED, op, "only the e4m3 P·V variants (int8_fp8, int8_fp8_f32acc) are built for sm_100a");
   }
   const std::int64_t total_q = q->tokens, heads = q->heads, total_k = k->tokens, kv_heads = k->heads;
   if (v->tokens != total_k || v->heads != kv_heads) return fail_invalid(op, "k and v must both be [total_k, num_kv_heads, 128]");
@@ -1259,9 +1271,17 @@ int attention_impl(const char* op, const b2_attention_options* o, const b2_view3
   if (cu_seqlens_q == nullptr || cu_seqlens_k == nullptr) return fail_invalid(op, "null cu_seqlens");
   if (max_seqlen <= 0) return fail_invalid(op, "max_seqlen must be positive");
   if (!(std::isfinite(scale) && scale > 0)) return fail_invalid(op, "scale must be finite and positive");
-  const float p_range = resolve(o->p_range), v_range = resolve(o->v_range);
+  const float p_range = resolve_p(*o), v_range = resolve_v(*o);
   if (!(std::isfinite(p_range) && p_range <= 448.f && std::isfinite(v_range) && v_range <= 448.f)) {
     return fail_invalid(op, "p_range and v_range must be in (0, 448] (e4m3 max)");
+  }
+  if (o->variant == B2_ATTENTION_Q8_FP8) {
+    // The variant's own rule (attention_q8.cu:255-261): a 64-key partial sum of the largest P and V must stay finite in
+    // fp16. Accumulation here is fp32, but a caller's ranges are accepted and refused exactly as the reference does.
+    const double p_max = e4m3_nearest(std::exp2(static_cast<double>(p_offset_of(p_range)))), v_max = e4m3_nearest(v_range);
+    if (64.0 * p_max * v_max > 65504.0) {
+      return fail_invalid(op, "int8_fp8: 64 * e4m3(2^p_offset) * e4m3(v_range) must be <= 65504 with fp16 accumulation");
+    }
   }
   if (norm_rope != nullptr) {
     if (norm_rope->q_norm == nullptr || norm_rope->k_norm == nullptr || norm_rope->table == nullptr ||
@@ -1338,7 +1358,7 @@ int attention_impl(const char* op, const b2_attention_options* o, const b2_view3
   a.out = static_cast<__nv_bfloat16*>(out->data), a.out_row = out->row_stride, a.out_head = out->head_stride;
   a.heads = static_cast<int>(heads), a.q_blocks = l.q_blocks, a.k_blocks = l.k_blocks;
   a.scale_log2 = scale * 1.44269504088896340736f;
-  a.p_offset = static_cast<float>(std::floor(std::log2(static_cast<double>(p_range)) * 1000.0) / 1000.0);
+  a.p_offset = p_offset_of(p_range);
   if (dump != nullptr) {
     a.dump = dump->scores, a.dump_ld = dump->ld;
     a.dump_seq = dump->seq, a.dump_head = dump->head, a.dump_tile = dump->tile;

@@ -17,6 +17,7 @@ from ._lib import check
 
 TILE_AUTO, TILE_128x256, TILE_128x128, TILE_2CTA_256x256 = 0, 1, 2, 3
 TIER_INT8, TIER_W4A4_VIA_INT8, TIER_W4A8 = 0, 1, 2
+ATTENTION_Q8_FP8 = 2          # e4m3 P.V with the ranges of the fp16-accumulating variant (112 / 4.5); accumulated in fp32 here
 ATTENTION_Q8_FP8_F32ACC = 3
 
 
@@ -212,8 +213,8 @@ def _view3(t):
     return _lib.View3(t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), t.stride(1))
 
 
-def attention_options(p_range=0.0, v_range=0.0):
-    return _lib.AttentionOptions(ATTENTION_Q8_FP8_F32ACC, p_range, v_range)
+def attention_options(p_range=0.0, v_range=0.0, variant=ATTENTION_Q8_FP8_F32ACC):
+    return _lib.AttentionOptions(variant, p_range, v_range)
 
 
 def attention_q8_workspace_bytes(total_q, total_k, batch, max_seqlen, heads, kv_heads=None, options=None):

@@ -193,6 +193,24 @@ def test_attention_rejects_bad_arguments():
     assert lay.q_i8 % 256 == 0 and lay.k_i8 % 256 == 0 and lay.v8 % 256 == 0
 
 
+def test_attention_int8_fp8_ranges_follow_the_reference_rule():
+    """attention_q8.h:79-88, attention_q8.cu:255-261: int8_fp8 defaults to 112 / 4.5 and refuses ranges whose 64-key
+    partial sum could overflow fp16 (117 / 8.74: 64 * 120 * 9 = 69120), before anything is launched."""
+    lib = _lib.lib()
+    v = _lib.View3(A16.value, 64, 2, 768, 128)
+    cu = A16
+    call = lambda o: _status(lib.b2_attention_q8(C.byref(o), C.byref(v), C.byref(v), C.byref(v), C.byref(v), cu, cu, 1, 64,
+                                                 C.c_float(0.0883883), None, 0, None, None))
+    rc, msg = call(_lib.AttentionOptions(2, 117.0, 8.74))
+    assert rc == -1 and "65504" in msg
+    rc, msg = call(_lib.AttentionOptions(2, 0.0, 0.0))     # defaults pass the rule; the call then stops at the workspace
+    assert rc == -1 and "workspace" in msg
+    rc, msg = call(_lib.AttentionOptions(2, 112.0, 9.0))   # 64 * 112 * 9 = 64512: allowed
+    assert rc == -1 and "workspace" in msg
+    rc, msg = call(_lib.AttentionOptions(1, 0.0, 0.0))     # the fp16 P.V variants are not built
+    assert rc == -3 and "only the e4m3" in msg
+
+
 def test_block_rejects_mismatched_buffers():
     lib = _lib.lib()
     run = _lib.BlockRun()

@@ -105,7 +105,7 @@ def _exact_attention(src, lens, heads, scale):
     return exact
 
 
-def _attention_three_way(ops, qkv, lens, heads, fused):
+def _attention_three_way(ops, qkv, lens, heads, fused, variant=3):
     """This library's attention, the reference's kernel and exact fp32 attention on the same inputs. Returns the L2 and
     worst-element errors of both kernels against exact attention and their mutual L2 distance."""
     from owoinfer_b200 import synth
@@ -116,11 +116,12 @@ def _attention_three_way(ops, qkv, lens, heads, fused):
     v = qkv.clone().view(total, 3, heads, 128)  # the fused pre-pass writes the normalised, rotated k back in place
     out = torch.zeros((total, heads, 128), dtype=torch.bfloat16, device="cuda")
     nr = (qn, kn, table) if fused else None
-    ops.attention_q8(v[:, 0], v[:, 1], v[:, 2], out, cu, cu, max(lens), ops.SM_SCALE, norm_rope=nr)
+    ops.attention_q8(v[:, 0], v[:, 1], v[:, 2], out, cu, cu, max(lens), ops.SM_SCALE, norm_rope=nr,
+                     options=ops.attention_options(variant=variant))
     rout = torch.zeros((total, heads * 128), dtype=torch.bfloat16, device="cuda")
     ws = torch.empty(max(256, ref.attention_workspace_bytes(total, len(lens), max(lens), heads)), dtype=torch.uint8,
                      device="cuda")
-    ref.attention_q8(qkv.clone(), heads, rout, cu, max(lens), ops.SM_SCALE, ws, nr)
+    ref.attention_q8(qkv.clone(), heads, rout, cu, max(lens), ops.SM_SCALE, ws, nr, variant=variant)
     src = qkv.clone()
     if fused:
         ops.qk_norm_rope_moss(src, heads, qn, kn, table)
@@ -148,6 +149,24 @@ def test_attention_close_to_reference_kernel(ops, lens, fused):
     heads, total = 4, sum(lens)
     qkv = synth.activations(total, 3 * heads * 128, 71 + total)
     _check_three_way(_attention_three_way(ops, qkv, lens, heads, fused))
+
+
+@pytest.mark.parametrize("lens,fused", [([1280], 0), ([700, 333], 1), ([8192], 1)])
+def test_attention_int8_fp8_variant_close_to_reference_kernel(ops, lens, fused):
+    """Variant int8_fp8 (the High tier's default: P in [0, 112], V in [-4.5, 4.5]; attention_q8.h:79-88). The reference adds
+    each 64-key tile in fp16 and flushes it into fp32; this library adds in fp32 throughout with the variant's ranges, and
+    has to be as close to exact attention as the reference's kernel."""
+    if not ref.has_attention_variants():
+        pytest.skip("the reference shim predates the variant entry")
+    from owoinfer_b200 import synth
+    total = sum(lens)
+    heads = 24 if total >= 8192 else 4
+    qkv = synth.activations(total, 3 * heads * 128, 171 + total)
+    r = _attention_three_way(ops, qkv, lens, heads, fused, variant=ops.ATTENTION_Q8_FP8)
+    print("int8_fp8", lens, r)
+    _check_three_way(r)
+    r3 = _attention_three_way(ops, qkv, lens, heads, fused)
+    assert abs(r["ours"] - r3["ours"]) <= 0.5 * r3["ours"] + 1e-4, (r, r3)   # the narrower ranges cost little
 
 
 @pytest.mark.parametrize("lens", [[8192], [20480]])
