@@ -162,10 +162,11 @@ class RefBlock:
     (src/models/moss_dit/dit_block_quant.cpp: norm+quantize, qkv GEMM, 8-bit attention with the fused norm+RoPE pre-pass,
     rotate, o-proj GEMM with gated residual, norm+quantize, up_gate GEMM with SiTU-GLU, rotate, down GEMM with residual)."""
 
-    def __init__(self, tokens, cu, max_seqlen, D, F, heads):
+    def __init__(self, tokens, cu, max_seqlen, D, F, heads, attention_variant=3):
         import torch
         dev = "cuda"
         self.D, self.F, self.heads, self.cu, self.max_seqlen = D, F, heads, cu, max_seqlen
+        self.attention_variant = attention_variant
         self.xq = torch.empty((tokens, max(D, F)), dtype=torch.int8, device=dev)
         self.scale = torch.empty(tokens, dtype=torch.float32, device=dev)
         self.qkv = torch.empty((tokens, 3 * D), dtype=torch.bfloat16, device=dev)
@@ -181,7 +182,7 @@ class RefBlock:
         rms_norm_modulate_rotate_quantize(x, w["norm1"], m[1], m[0], xq_d, self.scale)
         int8_gemm(xq_d, self.scale, w["qkv"][0], w["qkv"][1], self.qkv)
         attention_q8(self.qkv, self.heads, self.attn, self.cu, self.max_seqlen, sm_scale, self.ws,
-                     (w["q_norm"], w["k_norm"], rope))
+                     (w["q_norm"], w["k_norm"], rope), variant=self.attention_variant)
         rotate_quantize(self.attn, xq_d, self.scale)
         int8_gemm_gated_residual(xq_d, self.scale, w["o"][0], w["o"][1], m[2], x)
         rms_norm_modulate_rotate_quantize(x, w["norm2"], m[4], m[3], xq_d, self.scale)

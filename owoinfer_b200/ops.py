@@ -330,13 +330,13 @@ class BlockWeights:
 
 def block_run(tokens, cu_seqlens, max_seqlen, D=3072, F=12288, heads=24, tier=TIER_INT8, p_range=0.0, v_range=0.0,
               fused_norm_rope=-1, slot_rows=0, slot_kv=(None, None), cu_seqlens_k=None, k0=0, k1=0, kv_tap=None, tap_only=False,
-              slot_kv_ld=0):
+              slot_kv_ld=0, attention_variant=ATTENTION_Q8_FP8_F32ACC):
     r = _lib.BlockRun()
     r.struct_size = C.sizeof(_lib.BlockRun)
     r.tokens, r.D, r.F, r.heads = tokens, D, F, heads
     r.cu_seqlens = cu_seqlens.data_ptr()
     r.batch, r.max_seqlen, r.tier = cu_seqlens.shape[0] - 1, max_seqlen, tier
-    r.attention = attention_options(p_range, v_range)
+    r.attention = attention_options(p_range, v_range, attention_variant)
     r.fused_norm_rope = fused_norm_rope
     r.slot_rows, r.k0, r.k1, r.tap_only, r.slot_kv_ld = slot_rows, k0, k1, int(tap_only), slot_kv_ld
     r.slot_kv[0], r.slot_kv[1] = (None if t is None else t.data_ptr() for t in slot_kv)

@@ -215,7 +215,7 @@ def _block_metrics(got, want):
     return cos, max_rel, per_elem, rel_l2
 
 
-def _ours_vs_ref_block(ops, lens, F, grid, seed, tier=0):
+def _ours_vs_ref_block(ops, lens, F, grid, seed, tier=0, attention_variant=3):
     from owoinfer_b200 import synth
     D, heads = 3072, 24
     L = sum(lens)
@@ -245,6 +245,16 @@ def _ours_vs_ref_block(ops, lens, F, grid, seed, tier=0):
 
 def test_block_close_to_reference_kernels(ops):
     cos, max_rel, per_elem, rel_l2 = _ours_vs_ref_block(ops, [1280], 12288, 32, 7)
+    assert cos >= 0.9995 and max_rel <= 1e-2, (cos, max_rel, per_elem, rel_l2)
+
+
+def test_block_with_the_high_tier_default_attention(ops):
+    """AttentionMode::kQ8Fp8 (dit_block_quant.h:60-68), the High tier's default: this library's block with variant int8_fp8
+    against the reference's kernels with theirs, one 8192-token sequence at full width."""
+    if not ref.has_attention_variants():
+        pytest.skip("the reference shim predates the variant entry")
+    cos, max_rel, per_elem, rel_l2 = _ours_vs_ref_block(ops, [8192], 12288, 64, 19, attention_variant=ops.ATTENTION_Q8_FP8)
+    print("block int8_fp8", dict(cos=cos, max_rel=max_rel, per_elem=per_elem, rel_l2=rel_l2))
     assert cos >= 0.9995 and max_rel <= 1e-2, (cos, max_rel, per_elem, rel_l2)
 
 
