@@ -586,6 +586,7 @@ typedef struct b2_dit_file_info {
   int has_shell;          /* the tensors outside the blocks are there: b2_dit_file_model() can run b2_dit_forward */
   int has_time_embedding; /* time_embedding.0 / .2 are there: b2_dit_file_time_embedding() is not NULL */
   size_t device_bytes;
+  int stored_tier;        /* the tier of the file's bytes; differs from `tier` after b2_dit_file_open_expanded */
 } b2_dit_file_info;
 
 /* Reads the header, checks every tensor the model needs (names, dtypes, shapes, per-module comfy_quant configs or the
@@ -595,6 +596,15 @@ typedef struct b2_dit_file_info {
  * stored apart are stacked into the fused QKV matrix. Everything else in the file (text embedder, other models'
  * tensors) is ignored. Errors: B2_ERR_INVALID_ARGUMENT with a message that names the file and the tensor. */
 int b2_dit_file_open(const char* path, b2_dit_file** out);
+/* The same, for a part with memory to spare: grouped 4-bit linears (asym_w4a8_int8) are expanded to the INT8 grid
+ * once, on the device, behind their upload (quant::decode_grouped_int8, a NaN or negative group scale raising the
+ * library's b2_w4_invalid_scales word), and the blocks run the INT8 tier with s_channel as the weight scale
+ * (info.tier == B2_TIER_INT8, info.stored_tier == B2_TIER_W4A8). The W4A8 tier does that expansion into a scratch on
+ * every step, so the outputs are bit-identical and the per-step decode is gone; the price is n * k more bytes per
+ * linear (a 42-block model: 6.3 GB more). The reference keeps 4-bit weights packed because its GPUs have 16-24 GB
+ * (src/models/moss_dit/dit_weights.h:106-136). INT8 files, and convrot_w4a4 files (whose tier also quantises the
+ * activations to 4 bits), load as with b2_dit_file_open. */
+int b2_dit_file_open_expanded(const char* path, b2_dit_file** out);
 int b2_dit_file_get_info(const b2_dit_file* file, b2_dit_file_info* info);
 /* The loaded model; blocks[] always, the shell tensors when has_shell. Valid until b2_dit_file_close. */
 const b2_dit_model* b2_dit_file_model(const b2_dit_file* file);

@@ -21,7 +21,7 @@ EXPORTS = [
     "b2_latent_to_tokens", "b2_tokens_to_latent", "b2_linear_fp32_row", "b2_rms_norm_modulate", "b2_time_sinusoid",
     "b2_time_vector_fp32", "b2_linear_bf16_workspace_bytes", "b2_linear_bf16", "b2_dit_forward_workspace_bytes", "b2_dit_forward",
     "b2_moss_rope_table_reference", "b2_dit_prefill_workspace_bytes", "b2_dit_prefill_references",
-    "b2_dit_graphs_create", "b2_dit_graphs_clear", "b2_dit_graphs_destroy", "b2_dit_graphs_stats", "b2_dit_forward_graphed",
+    "b2_dit_file_open_expanded", "b2_dit_graphs_create", "b2_dit_graphs_clear", "b2_dit_graphs_destroy", "b2_dit_graphs_stats", "b2_dit_forward_graphed",
     "b2_dit_file_open", "b2_dit_file_get_info", "b2_dit_file_model", "b2_dit_file_time_embedding", "b2_dit_file_close",
 ]
 
@@ -113,7 +113,7 @@ class Prefill(C.Structure):
 
 class DitFileInfo(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("num_blocks", C.c_int), ("F", C.c_int), ("tier", C.c_int), ("has_shell", C.c_int),
-                ("has_time_embedding", C.c_int), ("device_bytes", C.c_size_t)]
+                ("has_time_embedding", C.c_int), ("device_bytes", C.c_size_t), ("stored_tier", C.c_int)]
 
 
 class GuidedStep(C.Structure):

@@ -573,6 +573,7 @@ struct Staging {
 struct Loader {
   const File& f;
   b2_dit_file& out;
+  bool expand = false;  // grouped 4-bit weights (W4A8) are expanded to the INT8 grid once, here, and the blocks run the INT8 tier
   Staging staging;
 
   // Tensor bytes -> device, in chunks through the pinned buffers.
@@ -681,6 +682,16 @@ struct Loader {
           if (p.codebook != nullptr) fail("'" + a.module + "': q, k and v need one codebook to run as one GEMM");
         }
       }
+      if (expand) {
+        // quant::decode_grouped_int8 on the copy stream, behind the uploads it reads: the INT8 GEMM over these values with
+        // s_channel as the weight scale is what the W4A8 tier computes on every step.
+        std::int8_t* dec = static_cast<std::int8_t*>(out.arena.take(static_cast<std::size_t>(n * a.k)));
+        if (b2_decode_grouped_int8(packed, s_rel, 0, w4->codebook, n, a.k, a.group, dec, nullptr, staging.stream) != B2_OK) {
+          fail("'" + a.module + "': " + b2_last_error_message());
+        }
+        lin.w = dec, lin.scale = s_channel;
+        return lin;
+      }
       lin.w4 = w4.get();
       out.w4.push_back(std::move(w4));
       return lin;
@@ -699,11 +710,12 @@ struct Loader {
   }
 };
 
-std::size_t linear_bytes(const std::vector<Stored>& parts) {
+std::size_t linear_bytes(const std::vector<Stored>& parts, bool expand) {
   std::size_t total = 0;
   for (const Stored& p : parts) {
     total += padded(p.weight->nbytes) + padded(static_cast<std::uint64_t>(p.n) * 4) + 512;
     if (p.s_rel != nullptr) total += padded(p.s_rel->nbytes) + 512;
+    if (expand && p.enc == Enc::kW4A8) total += padded(static_cast<std::uint64_t>(p.n) * static_cast<std::uint64_t>(p.k)) + 512;
   }
   return total + 1024;
 }
@@ -711,10 +723,9 @@ std::size_t linear_bytes(const std::vector<Stored>& parts) {
 }  // namespace
 }  // namespace b2
 
-extern "C" {
-
-int b2_dit_file_open(const char* path, b2_dit_file** out) {
-  constexpr const char* op = "dit_file_open";
+namespace b2 {
+namespace {
+int open_impl(const char* op, const char* path, bool expand, b2_dit_file** out) {
   if (path == nullptr || out == nullptr) return fail_invalid(op, "null argument");
   *out = nullptr;
   try {
@@ -761,7 +772,7 @@ int b2_dit_file_open(const char* path, b2_dit_file** out) {
         const int t = tier_of(parts[0].enc);
         if (tier >= 0 && t != tier) fail("'" + parts[0].module + "' is of another tier than the linears before it: a block run has one tier");
         tier = t;
-        need += linear_bytes(parts);
+        need += linear_bytes(parts, expand);
       }
     }
     const bool shell = f.find("shared_block_modulation.weight") != nullptr;
@@ -773,7 +784,7 @@ int b2_dit_file_open(const char* path, b2_dit_file** out) {
       return fail_cuda(op, err);
     }
     file->arena.size = need;
-    Loader ld{f, *file};
+    Loader ld{f, *file, expand};
     file->blocks.resize(static_cast<std::size_t>(blocks));
     for (int b = 0; b < blocks; ++b) {
       const std::string p = "layers." + std::to_string(b) + ".";
@@ -813,7 +824,7 @@ int b2_dit_file_open(const char* path, b2_dit_file** out) {
       file->time = b2_time_embedding{sizeof(b2_time_embedding), kDim, file->te_w0.data(), file->te_b0.data(), file->te_w2.data(), file->te_b2.data()};
     }
     ld.staging.drain();
-    file->info = b2_dit_file_info{sizeof(b2_dit_file_info), blocks, static_cast<int>(F), tier, shell ? 1 : 0, has_time ? 1 : 0, file->arena.used};
+    file->info = b2_dit_file_info{sizeof(b2_dit_file_info), blocks, static_cast<int>(F), expand && tier == B2_TIER_W4A8 ? B2_TIER_INT8 : tier, shell ? 1 : 0, has_time ? 1 : 0, file->arena.used, tier};
     *out = file.release();
     return B2_OK;
   } catch (const LoadError& e) {
@@ -825,9 +836,21 @@ int b2_dit_file_open(const char* path, b2_dit_file** out) {
   }
 }
 
+}  // namespace
+}  // namespace b2
+
+extern "C" {
+
+int b2_dit_file_open(const char* path, b2_dit_file** out) { return open_impl("dit_file_open", path, false, out); }
+
+int b2_dit_file_open_expanded(const char* path, b2_dit_file** out) { return open_impl("dit_file_open_expanded", path, true, out); }
+
 int b2_dit_file_get_info(const b2_dit_file* file, b2_dit_file_info* info) {
-  if (file == nullptr || info == nullptr || info->struct_size < sizeof(b2_dit_file_info)) return fail_invalid("dit_file_get_info", "null argument or an older header");
-  *info = file->info;
+  constexpr std::size_t kFirst = offsetof(b2_dit_file_info, stored_tier);  // the struct before stored_tier was added
+  if (file == nullptr || info == nullptr || info->struct_size < kFirst) return fail_invalid("dit_file_get_info", "null argument or an older header");
+  const std::size_t theirs = info->struct_size;
+  std::memcpy(info, &file->info, std::min(theirs, sizeof(b2_dit_file_info)));
+  info->struct_size = theirs;
   return B2_OK;
 }
 

@@ -649,13 +649,15 @@ class _Loaded:
 class DitFile:
     """b2_dit_file: the quantized DiT of a ComfyUI-layout safetensors file, on the current device."""
 
-    def __init__(self, path: str):
+    def __init__(self, path: str, expanded: bool = False):
+        """expanded: grouped 4-bit (W4A8) weights are expanded to the INT8 grid once at load (b2_dit_file_open_expanded)."""
         self.handle = C.c_void_p()
-        check(_lib.lib().b2_dit_file_open(str(path).encode(), C.byref(self.handle)))
+        opener = _lib.lib().b2_dit_file_open_expanded if expanded else _lib.lib().b2_dit_file_open
+        check(opener(str(path).encode(), C.byref(self.handle)))
         info = _lib.DitFileInfo()
         info.struct_size = C.sizeof(_lib.DitFileInfo)
         check(_lib.lib().b2_dit_file_get_info(self.handle, C.byref(info)))
-        self.num_blocks, self.F, self.tier = info.num_blocks, info.F, info.tier
+        self.num_blocks, self.F, self.tier, self.stored_tier = info.num_blocks, info.F, info.tier, info.stored_tier
         self.has_shell, self.has_time_embedding, self.device_bytes = bool(info.has_shell), bool(info.has_time_embedding), info.device_bytes
         model = _lib.lib().b2_dit_file_model(self.handle).contents
         self.model = _Loaded(model, self)

@@ -115,3 +115,25 @@ def test_w4a8_file(ops, tmp_path, codebook):
     want = _step(ops, [_direct_block(ops, t, 0, f.tier)], F, f.tier)
     assert torch.equal(got.view(torch.int16), want.view(torch.int16)) and torch.isfinite(got.float()).all()
     assert ops.w4_invalid_scales(clear=True) == 0
+
+
+@pytest.mark.parametrize("maker,tier", [("w4a4", 1), ("w4a8", 2), ("w4a8_codebook", 2), ("int8", 0)])
+def test_expanded_open_runs_the_int8_tier_with_the_same_bits(ops, tmp_path, maker, tier):
+    """b2_dit_file_open_expanded: grouped 4-bit weights expanded once at load, the blocks then run the INT8 tier. What the
+    W4A8 tier computes is that expansion followed by the INT8 GEMM, so the step's output does not change by a bit. Other
+    files (INT8; W4A4, whose tier quantises the activations to 4 bits as well) load unchanged."""
+    F = 256
+    make = {"w4a4": lf.w4a4_linear, "w4a8": lf.w4a8_linear, "int8": lf.int8_linear,
+            "w4a8_codebook": lambda n, r, k, s: lf.w4a8_linear(n, r, k, s, codebook=True)}[maker]
+    t = {}
+    for b in range(2):
+        t.update(lf.block(b, F, make, 70 + 10 * b))
+    path = lf.save(tmp_path / "model.safetensors", t)
+    packed, wide = ops.DitFile(path), ops.DitFile(path, expanded=True)
+    assert packed.tier == tier and packed.stored_tier == tier
+    assert wide.tier == (ops.TIER_INT8 if tier == 2 else tier) and wide.stored_tier == tier and wide.num_blocks == 2
+    assert (wide.device_bytes > packed.device_bytes) == (tier == 2)
+    want = _step(ops, packed.blocks, F, packed.tier)
+    got = _step(ops, wide.blocks, F, wide.tier)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16)) and torch.isfinite(got.float()).all()
+    assert ops.w4_invalid_scales(clear=True) == 0

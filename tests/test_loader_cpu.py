@@ -27,6 +27,8 @@ def base():
 def refused(ops, path, match):
     with pytest.raises(ValueError, match=match):
         ops.DitFile(path)
+    with pytest.raises(ValueError, match=match):   # the expanding open checks the same things before it allocates
+        ops.DitFile(path, expanded=True)
 
 
 def test_container_errors(ops, tmp_path):
