@@ -56,7 +56,9 @@ def main() -> None:
     fn = C.CDLL(path).b2_attention_trace
     if fn(buf, 4096) != 0:
         raise RuntimeError("the trace could not be read")
-    a = np.array(buf[:4096], dtype=np.int64).reshape(-1, 16)[:128]
+    full = np.array(buf[:4096], dtype=np.int64).reshape(-1, 16)
+    print("start-up issues with idle softmax warps: Q.K^T(0) incl. the wait for K", int(full[200, 1] - full[200, 0]), "clocks, Q.K^T(1)", int(full[200, 2] - full[200, 1]), "clocks")
+    a = full[:128]
     u = np.arange(9, 120)
     med = lambda x: float(np.median(x))
     print("| from -> to (softmax warp %d, sub-tile u) | clocks |" % 2)

@@ -865,8 +865,18 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     bool ok = wait_bar(smem_u32(&s_q_full), 0, abort_word) && wait_bar(smem_u32(&s_s_ready), 0, abort_word);
     ok = !__any_sync(0xffffffffu, !ok);
     tc_fence_after();
+#ifdef B2_ATTN_TRACE
+    // Tracing only: wait for both K halves' tile first, then time the two start-up issues (the softmax warps are idle).
+    if (tracing) a.trace[200 * 16 + 0] = clock64();
+#endif
     ok = ok && issue_qk(0);
+#ifdef B2_ATTN_TRACE
+    if (tracing) a.trace[200 * 16 + 1] = clock64();
+#endif
     if (ok && n_sub > 1) ok = issue_qk(1);
+#ifdef B2_ATTN_TRACE
+    if (tracing) a.trace[200 * 16 + 2] = clock64();
+#endif
     for (int u = 0; ok && u < n_sub; ++u) {
       const int s = (u >> 1) % kKvStages;
       bool got = true;
