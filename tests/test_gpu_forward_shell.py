@@ -390,3 +390,36 @@ def test_step_graphs_replay_the_forward(ops):
     graphs.close()
     none.close()
     assert ops.kernel_status() == (0, 0)
+
+
+def test_step_graphs_with_reference_images(ops):
+    """A captured forward with a reference cache (slot copies inside the blocks) equals the eager one; the reference
+    cache's address is part of the key."""
+    D, F, h, w = 3072, 8192, 16, 16
+    model, _, _, _ = _model(ops, 2, F, 8)
+    rng = np.random.default_rng(33)
+    refs = [torch.from_numpy(rng.normal(0, 1, (128, 8, 16)).astype(np.float32)).cuda()]
+    tv0, tv = rng.normal(0, 1, D).astype(np.float32), rng.normal(0, 1, D).astype(np.float32)
+    kv = ops.dit_prefill_references(model, refs, tv0)
+    latents = torch.from_numpy(rng.normal(0, 1, (1, 128, h, w)).astype(np.float32)).cuda()
+    texts = [bfdev(to_bf16(rng.normal(0, 1, (s, D)))) for s in (32, 64)]
+    rows = [(texts[0], 0, 0), (texts[1], 0b01, 0)]
+    want = [o.clone() for o in ops.dit_forward(model, latents, tv, rows, ref_kv=kv)[0]]
+    torch.cuda.synchronize()
+    graphs = ops.DitGraphs(capacity=4)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        outs = ws = None
+        for _ in range(3):
+            outs, ws = ops.dit_forward(model, latents, tv, rows, ref_kv=kv, graphs=graphs, outs=outs, workspace=ws)
+            side.synchronize()
+            for r in range(2):
+                assert torch.equal(outs[r].view(torch.int32), want[r].view(torch.int32)), r
+        assert graphs.last_replayed and graphs.stats()["captures"] == 1
+        kv2 = kv.clone()
+        ops.dit_forward(model, latents, tv, rows, ref_kv=kv2, graphs=graphs, outs=outs, workspace=ws)
+        side.synchronize()
+        assert not graphs.last_replayed and graphs.stats()["captures"] == 2      # another cache address: another graph
+        assert torch.equal(outs[0].view(torch.int32), want[0].view(torch.int32))
+    graphs.close()
+    assert ops.kernel_status() == (0, 0)
