@@ -456,7 +456,8 @@ typedef struct b2_time_embedding {
   const float* b2;  /* [dim] */
 } b2_time_embedding;
 /* moss_dit::time_vector_fp32 (distill.cpp:126-150): sinusoid -> linear -> SiLU -> linear on the host, each dot product
- * accumulated in double from the bias on. About 10 ms of one core for dim 3072: cache it per timestep as the reference
+ * accumulated in double from the bias on. About 10 ms of one core for dim 3072; the rows are split over up to eight
+ * host threads (each row summed in the same order, so no bit changes: 2-3 ms). Cache it per timestep as the reference
  * does (moss_dit.cpp:954-960). time: host [dim]. */
 int b2_time_vector_fp32(const b2_time_embedding* te, float timestep, float* time);
 
