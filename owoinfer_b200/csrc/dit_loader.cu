@@ -29,6 +29,8 @@
 #include <memory>
 #include <optional>
 #include <string>
+#include <system_error>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -255,12 +257,44 @@ struct File {
   ~File() {
     if (fd >= 0) ::close(fd);
   }
-  void read(std::uint64_t offset, void* dst, std::size_t n) const {
-    char* out = static_cast<char*>(dst);
+  // false (and *bad = the offset) on a short read.
+  bool read_piece(std::uint64_t offset, char* out, std::size_t n, std::uint64_t* bad) const {
     while (n > 0) {
       const ssize_t got = ::pread(fd, out, n, static_cast<off_t>(offset));
-      if (got <= 0) fail("short read at byte " + std::to_string(offset));
+      if (got <= 0) {
+        *bad = offset;
+        return false;
+      }
       out += got, offset += static_cast<std::uint64_t>(got), n -= static_cast<std::size_t>(got);
+    }
+    return true;
+  }
+  // A large read is split over four threads: one thread copying out of the page cache moves 4-5 GB/s, far below what the
+  // copy to the device behind it takes.
+  void read(std::uint64_t offset, void* dst, std::size_t n) const {
+    char* out = static_cast<char*>(dst);
+    constexpr int kPieces = 4;
+    bool ok[kPieces] = {true, true, true, true};
+    std::uint64_t bad[kPieces] = {0, 0, 0, 0};
+    if (n < (std::size_t{8} << 20)) {
+      ok[0] = read_piece(offset, out, n, &bad[0]);
+    } else {
+      const std::size_t per = (n / kPieces + 4095) & ~std::size_t{4095};
+      std::vector<std::thread> workers;
+      for (int i = 1; i < kPieces; ++i) {
+        const std::size_t at = std::min(n, per * static_cast<std::size_t>(i)), len = std::min(n, per * static_cast<std::size_t>(i + 1)) - at;
+        if (len == 0) continue;
+        try {
+          workers.emplace_back([=, &ok, &bad] { ok[i] = read_piece(offset + at, out + at, len, &bad[i]); });
+        } catch (const std::system_error&) {
+          ok[i] = read_piece(offset + at, out + at, len, &bad[i]);
+        }
+      }
+      ok[0] = read_piece(offset, out, std::min(n, per), &bad[0]);
+      for (std::thread& w : workers) w.join();
+    }
+    for (int i = 0; i < kPieces; ++i) {
+      if (!ok[i]) fail("short read at byte " + std::to_string(bad[i]));
     }
   }
   const Entry* find(const std::string& name) const {
