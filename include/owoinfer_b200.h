@@ -461,6 +461,30 @@ typedef struct b2_time_embedding {
  * does (moss_dit.cpp:954-960). time: host [dim]. */
 int b2_time_vector_fp32(const b2_time_embedding* te, float timestep, float* time);
 
+/* kernels::silu (src/kernels/basic/elementwise.cu:92-100): out = bf16(x / (1 + expf(-x))), bf16 in and out, in place allowed. */
+int b2_silu_bf16(const void* x, void* out, int64_t n, void* stream);
+
+/* MossDit::time_modulation in its bf16 form (moss_dit.cpp:970-990, the path a model without a fp32 timestep MLP takes):
+ * the sinusoid in double -> bf16 [256], linear -> SiLU -> linear (the timestep MLP), then the block and head modulation
+ * linears, all bf16 with fp32 accumulation through cuBLASLt as in the reference (summation order the library's).
+ * Weights and biases bf16 on the device (a bias may be NULL). mod: device bf16 [6 dim], head: [2 dim], for
+ * b2_forward::mod / head. workspace: 256-byte aligned, b2_time_modulation_bf16_workspace_bytes(). */
+typedef struct b2_time_mlp_bf16 {
+  size_t struct_size;
+  int64_t dim;                 /* 3072 */
+  const void* in_w;            /* [dim, 256] */
+  const void* in_bias;         /* [dim] */
+  const void* out_w;           /* [dim, dim] */
+  const void* out_bias;        /* [dim] */
+  const void* block_mod_w;     /* [6 dim, dim] */
+  const void* block_mod_bias;  /* [6 dim] */
+  const void* head_mod_w;      /* [2 dim, dim] */
+  const void* head_mod_bias;   /* [2 dim] */
+} b2_time_mlp_bf16;
+size_t b2_time_modulation_bf16_workspace_bytes(const b2_time_mlp_bf16* m);
+int b2_time_modulation_bf16(const b2_time_mlp_bf16* m, float timestep, void* mod, void* head, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
 /* kernels::Gemm::linear for the two bf16 linears of the shell (src/kernels/basic/gemm.h:20-63): out [m, n] = x [m, k] *
  * w [n, k]^T (+ bias [n]), bf16 in and out, fp32 accumulation, through cuBLASLt bound at run time (libcublasLt.so.12,
  * preferring a copy the process has already loaded; B2_ERR_NOT_SUPPORTED when none is found). As in the reference the
@@ -519,6 +543,11 @@ typedef struct b2_forward {
    * (moss_dit.cpp:1283-1300). */
   const void* ref_kv;
   int64_t ref_tokens;
+  /* The modulation vectors already computed (device bf16 [6 D] and [2 D]: b2_time_modulation_bf16, or a caller's own):
+   * both or neither; with them time_vector is not read and the model's modulation linears are not needed. A caller
+   * compiled against the struct without these two fields still works. */
+  const void* mod;
+  const void* head;
 } b2_forward;
 
 /* moss_dit::StepGraphs (src/models/moss_dit/dit_graph.h:14-66; runtime::GraphCache, src/runtime/graph_cache.h:20-58):

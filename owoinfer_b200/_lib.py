@@ -21,7 +21,8 @@ EXPORTS = [
     "b2_latent_to_tokens", "b2_tokens_to_latent", "b2_linear_fp32_row", "b2_rms_norm_modulate", "b2_time_sinusoid",
     "b2_time_vector_fp32", "b2_linear_bf16_workspace_bytes", "b2_linear_bf16", "b2_dit_forward_workspace_bytes", "b2_dit_forward",
     "b2_moss_rope_table_reference", "b2_dit_prefill_workspace_bytes", "b2_dit_prefill_references",
-    "b2_dit_file_open_expanded", "b2_dit_graphs_create", "b2_dit_graphs_clear", "b2_dit_graphs_destroy", "b2_dit_graphs_stats", "b2_dit_forward_graphed",
+    "b2_dit_file_open_expanded", "b2_silu_bf16", "b2_time_modulation_bf16_workspace_bytes", "b2_time_modulation_bf16",
+    "b2_dit_graphs_create", "b2_dit_graphs_clear", "b2_dit_graphs_destroy", "b2_dit_graphs_stats", "b2_dit_forward_graphed",
     "b2_dit_file_open", "b2_dit_file_get_info", "b2_dit_file_model", "b2_dit_file_time_embedding", "b2_dit_file_close",
 ]
 
@@ -97,7 +98,13 @@ class Forward(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("latents", C.c_void_p), ("num_latents", C.c_int), ("height", C.c_int),
                 ("width", C.c_int), ("time_vector", C.c_void_p), ("rows", C.POINTER(ForwardRow)), ("num_rows", C.c_int),
                 ("tier", C.c_int), ("attention", AttentionOptions), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("extra", C.c_void_p), ("ref_kv", C.c_void_p), ("ref_tokens", C.c_int64)]
+                ("extra", C.c_void_p), ("ref_kv", C.c_void_p), ("ref_tokens", C.c_int64), ("mod", C.c_void_p), ("head", C.c_void_p)]
+
+
+class TimeMlpBf16(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("dim", C.c_int64), ("in_w", C.c_void_p), ("in_bias", C.c_void_p), ("out_w", C.c_void_p),
+                ("out_bias", C.c_void_p), ("block_mod_w", C.c_void_p), ("block_mod_bias", C.c_void_p), ("head_mod_w", C.c_void_p),
+                ("head_mod_bias", C.c_void_p)]
 
 
 class DitGraphStats(C.Structure):
@@ -154,6 +161,10 @@ def lib() -> C.CDLL:
         l.b2_dit_file_close.argtypes = [C.c_void_p]
         l.b2_linear_bf16_workspace_bytes.restype = C.c_size_t
         l.b2_dit_forward_workspace_bytes.restype = C.c_size_t
+        l.b2_time_modulation_bf16_workspace_bytes.restype = C.c_size_t
+        l.b2_time_modulation_bf16_workspace_bytes.argtypes = [C.POINTER(TimeMlpBf16)]
+        l.b2_time_modulation_bf16.argtypes = [C.POINTER(TimeMlpBf16), C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+        l.b2_silu_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         l.b2_dit_graphs_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
         l.b2_dit_graphs_clear.argtypes = [C.c_void_p]
         l.b2_dit_graphs_destroy.argtypes = [C.c_void_p]

@@ -51,6 +51,16 @@ int write_words(const char* op, void* dst, const void* src, std::size_t words, c
   return B2_OK;
 }
 
+// kernels::silu (src/kernels/basic/elementwise.cu:92-100, detail.h:100): bf16(x / (1 + expf(-x))), the division and the
+// addition each rounded once.
+__global__ void silu_bf16_kernel(const __nv_bfloat16* x, __nv_bfloat16* out, std::int64_t n) {
+  for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<std::int64_t>(gridDim.x) * blockDim.x) {
+    const float v = __bfloat162float(x[i]);
+    out[i] = __float2bfloat16_rn(__fdiv_rn(v, __fadd_rn(1.0f, expf(-v))));
+  }
+}
+
 // out[c * ld + r] = convert(in[r * cols + c]): a [rows, cols] row-major matrix transposed through a padded shared tile,
 // f32 -> bf16 (round to nearest even) or bf16 -> f32.
 template <typename In, typename Out>
@@ -245,7 +255,7 @@ int embed_video(const b2_dit_model& m, const float* plane, const float* extra, s
 
 int plan_forward(const char* op, const b2_dit_model* m, const b2_forward* f, std::vector<std::int64_t>* off, Carve* c,
                  b2_block_run* widest) {
-  if (m == nullptr || f == nullptr || m->struct_size < sizeof(b2_dit_model) || f->struct_size < sizeof(b2_forward)) {
+  if (m == nullptr || f == nullptr || m->struct_size < sizeof(b2_dit_model) || f->struct_size < offsetof(b2_forward, mod)) {
     return fail_invalid(op, "null model or forward, or one from an older header");
   }
   if (m->blocks == nullptr || m->num_blocks < 0 || m->num_blocks > 64) return fail_invalid(op, "0..64 blocks (skip masks are 64 bits)");
@@ -390,6 +400,55 @@ int b2_time_vector_fp32(const b2_time_embedding* te, float timestep, float* time
 
 size_t b2_linear_bf16_workspace_bytes(void) { return kLtWorkspaceBytes; }
 
+int b2_silu_bf16(const void* x, void* out, int64_t n, void* stream) {
+  constexpr const char* op = "silu_bf16";
+  if (n < 0 || (n > 0 && (x == nullptr || out == nullptr))) return fail_invalid(op, "needs bf16 x and out of n values");
+  if (n == 0) return B2_OK;
+  const unsigned blocks = static_cast<unsigned>(std::min<std::int64_t>((n + 255) / 256, 4096));
+  silu_bf16_kernel<<<blocks, 256, 0, as_stream(stream)>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), n);
+  return check_launch(op);
+}
+
+size_t b2_time_modulation_bf16_workspace_bytes(const b2_time_mlp_bf16* m) {
+  if (m == nullptr || m->dim < 8) return 0;
+  return 1024 + 2 * align_up(static_cast<std::size_t>(m->dim) * 2) + kLtWorkspaceBytes;
+}
+
+int b2_time_modulation_bf16(const b2_time_mlp_bf16* m, float timestep, void* mod, void* head, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  constexpr const char* op = "time_modulation_bf16";
+  if (m == nullptr || m->struct_size < sizeof(b2_time_mlp_bf16) || mod == nullptr || head == nullptr) return fail_invalid(op, "null argument");
+  if (m->dim < 8 || m->dim % 8 != 0 || m->dim > (1 << 16) || m->in_w == nullptr || m->out_w == nullptr || m->block_mod_w == nullptr ||
+      m->head_mod_w == nullptr) {
+    return fail_invalid(op, "needs the four bf16 weights of the timestep MLP and the modulation linears, dim a multiple of 8");
+  }
+  if (workspace == nullptr || !aligned_to(workspace, 256) || workspace_bytes < b2_time_modulation_bf16_workspace_bytes(m)) {
+    return fail_invalid(op, "workspace must be 256-byte aligned and hold b2_time_modulation_bf16_workspace_bytes()");
+  }
+  // The sinusoid in double, rounded to fp32 and then to bf16 (moss_dit.cpp:979-985).
+  float emb[kFreq];
+  b2_time_sinusoid(timestep, emb);
+  std::uint32_t packed[kFreq / 2];
+  for (int i = 0; i < kFreq; i += 2) {
+    const auto bits = [](float v) {
+      std::uint32_t u;
+      std::memcpy(&u, &v, 4);
+      return (u + 0x7FFFu + ((u >> 16) & 1u)) >> 16;
+    };
+    packed[i / 2] = bits(emb[i]) | (bits(emb[i + 1]) << 16);
+  }
+  unsigned char* base = static_cast<unsigned char*>(workspace);
+  const std::size_t row = align_up(static_cast<std::size_t>(m->dim) * 2);
+  void *t_in = base, *hidden = base + 1024, *time = base + 1024 + row, *lt_ws = base + 1024 + 2 * row;
+  const int D = static_cast<int>(m->dim);
+  if (const int rc = write_words(op, t_in, packed, kFreq / 2, as_stream(stream))) return rc;
+  if (const int rc = b2_linear_bf16(t_in, kFreq, m->in_w, m->in_bias, hidden, D, 1, D, kFreq, lt_ws, kLtWorkspaceBytes, stream)) return rc;
+  if (const int rc = b2_silu_bf16(hidden, hidden, D, stream)) return rc;
+  if (const int rc = b2_linear_bf16(hidden, D, m->out_w, m->out_bias, time, D, 1, D, D, lt_ws, kLtWorkspaceBytes, stream)) return rc;
+  if (const int rc = b2_linear_bf16(time, D, m->block_mod_w, m->block_mod_bias, mod, 6 * D, 1, 6 * D, D, lt_ws, kLtWorkspaceBytes, stream)) return rc;
+  return b2_linear_bf16(time, D, m->head_mod_w, m->head_mod_bias, head, 2 * D, 1, 2 * D, D, lt_ws, kLtWorkspaceBytes, stream);
+}
+
 int b2_linear_bf16(const void* x, int64_t ldx, const void* w, const void* bias, void* out, int64_t ldo, int64_t m, int n,
                    int k, void* workspace, size_t workspace_bytes, void* stream) {
   constexpr const char* op = "linear_bf16";
@@ -473,8 +532,13 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, const
   if (const int rc = plan_forward(op, model, forward, &off, &c, &widest)) return rc;
   const b2_dit_model& m = *model;
   const b2_forward& f = *forward;
-  if (f.latents == nullptr || (f.time_vector == nullptr && time_device == nullptr)) return fail_invalid(op, "needs latents and the host time vector");
-  if (m.block_mod_w == nullptr || m.block_mod_bias == nullptr || m.head_mod_w == nullptr || m.head_mod_bias == nullptr ||
+  // The modulation vectors computed by the caller (b2_time_modulation_bf16, or anything else), when the struct has them.
+  const bool given = f.struct_size >= sizeof(b2_forward) && f.mod != nullptr && f.head != nullptr;
+  if (f.struct_size >= sizeof(b2_forward) && (f.mod != nullptr) != (f.head != nullptr)) return fail_invalid(op, "mod and head go together");
+  if (f.latents == nullptr || (!given && f.time_vector == nullptr && time_device == nullptr)) {
+    return fail_invalid(op, "needs latents and the host time vector (or mod and head)");
+  }
+  if ((!given && (m.block_mod_w == nullptr || m.block_mod_bias == nullptr || m.head_mod_w == nullptr || m.head_mod_bias == nullptr)) ||
       (m.video_w == nullptr && m.ext_w == nullptr) || m.final_norm == nullptr || m.final_w == nullptr) {
     return fail_invalid(op, "the model lacks a modulation, embedder or head tensor");
   }
@@ -486,8 +550,8 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, const
   unsigned char* base = static_cast<unsigned char*>(f.workspace);
   __nv_bfloat16* x = reinterpret_cast<__nv_bfloat16*>(base + c.x);
   __nv_bfloat16* rope = reinterpret_cast<__nv_bfloat16*>(base + c.rope);
-  __nv_bfloat16* mod = reinterpret_cast<__nv_bfloat16*>(base + c.mod);
-  __nv_bfloat16* head = reinterpret_cast<__nv_bfloat16*>(base + c.head);
+  __nv_bfloat16* mod = given ? static_cast<__nv_bfloat16*>(const_cast<void*>(f.mod)) : reinterpret_cast<__nv_bfloat16*>(base + c.mod);
+  __nv_bfloat16* head = given ? static_cast<__nv_bfloat16*>(const_cast<void*>(f.head)) : reinterpret_cast<__nv_bfloat16*>(base + c.head);
   const float* time = time_device != nullptr ? time_device : reinterpret_cast<const float*>(base + c.time);
   __nv_bfloat16* tokens = reinterpret_cast<__nv_bfloat16*>(base + c.tokens);
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(base + c.y);
@@ -535,11 +599,13 @@ int dit_forward_impl(const b2_dit_model* model, const b2_forward* forward, const
     if (const int rc = write_words(op, cu_k_dev, cu_k.data(), cu_k.size(), stream)) return rc;
   }
   // time_modulation: the time vector (host, fp32) through the two modulation linears.
-  if (time_device == nullptr) {
-    if (const int rc = write_words(op, base + c.time, f.time_vector, static_cast<std::size_t>(D), stream)) return rc;
+  if (!given) {
+    if (time_device == nullptr) {
+      if (const int rc = write_words(op, base + c.time, f.time_vector, static_cast<std::size_t>(D), stream)) return rc;
+    }
+    if (const int rc = b2_linear_fp32_row(m.block_mod_w, time, m.block_mod_bias, mod, static_cast<int>(6 * D), static_cast<int>(D), stream)) return rc;
+    if (const int rc = b2_linear_fp32_row(m.head_mod_w, time, m.head_mod_bias, head, static_cast<int>(2 * D), static_cast<int>(D), stream)) return rc;
   }
-  if (const int rc = b2_linear_fp32_row(m.block_mod_w, time, m.block_mod_bias, mod, static_cast<int>(6 * D), static_cast<int>(D), stream)) return rc;
-  if (const int rc = b2_linear_fp32_row(m.head_mod_w, time, m.head_mod_bias, head, static_cast<int>(2 * D), static_cast<int>(D), stream)) return rc;
 
   // Joint inputs [video_r | text_r] and per-row RoPE tables. The video embedding is the same for every row of a latent:
   // computed once, into the first row that reads the latent, and copied to its other rows.
@@ -676,6 +742,7 @@ void forward_key(const b2_dit_model& m, const b2_forward& f, int device, std::ve
   put(key, f.latents), put(key, f.num_latents), put(key, f.height), put(key, f.width), put(key, f.num_rows), put(key, f.tier);
   put(key, f.attention.variant), put(key, f.attention.p_range), put(key, f.attention.v_range);
   put(key, f.workspace), put(key, f.workspace_bytes), put(key, f.extra), put(key, f.ref_kv), put(key, f.ref_tokens);
+  if (f.struct_size >= sizeof(b2_forward)) put(key, f.mod), put(key, f.head);
   for (int r = 0; r < f.num_rows; ++r) {
     const b2_forward_row& row = f.rows[r];
     put(key, row.text), put(key, row.text_len), put(key, row.skip), put(key, row.latent), put(key, row.out);
@@ -692,7 +759,8 @@ int graphed_impl(b2_dit_graphs* g, const b2_dit_model* model, const b2_forward* 
   Carve c{};
   b2_block_run widest{};
   if (const int rc = plan_forward(op, model, forward, &off, &c, &widest)) return rc;
-  if (forward->time_vector == nullptr) return fail_invalid(op, "needs the host time vector");
+  const bool given = forward->struct_size >= sizeof(b2_forward) && forward->mod != nullptr && forward->head != nullptr;
+  if (!given && forward->time_vector == nullptr) return fail_invalid(op, "needs the host time vector (or mod and head)");
   cudaStream_t stream = as_stream(stream_);
   int device = 0;
   if (const cudaError_t e = cudaGetDevice(&device); e != cudaSuccess) return fail_cuda(op, e);
@@ -703,7 +771,9 @@ int graphed_impl(b2_dit_graphs* g, const b2_dit_model* model, const b2_forward* 
     g->device = device;
   }
   if (g->device != device) return fail_invalid(op, "a cache belongs to the device of its first forward");
-  if (const int rc = write_words(op, g->time, forward->time_vector, static_cast<std::size_t>(model->D), stream)) return rc;
+  if (!given) {
+    if (const int rc = write_words(op, g->time, forward->time_vector, static_cast<std::size_t>(model->D), stream)) return rc;
+  }
 
   std::vector<unsigned char> key;
   forward_key(*model, *forward, device, &key);

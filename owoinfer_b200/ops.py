@@ -551,6 +551,29 @@ class DitModel:
         self.struct = m
 
 
+def silu_bf16(x, out=None):
+    """kernels::silu: bf16(x / (1 + expf(-x)))."""
+    out = torch.empty_like(x) if out is None else out
+    check(_lib.lib().b2_silu_bf16(_ptr(x), _ptr(out), x.numel(), _stream()))
+    return out
+
+
+def time_modulation_bf16(in_w, in_bias, out_w, out_bias, block_mod_w, block_mod_bias, head_mod_w, head_mod_bias, timestep):
+    """MossDit::time_modulation in its bf16 form: (mod bf16 [6 D], head bf16 [2 D]) on the device. All arguments bf16 device tensors
+    (a bias may be None)."""
+    m = _lib.TimeMlpBf16()
+    m.struct_size, m.dim = C.sizeof(_lib.TimeMlpBf16), out_w.shape[0]
+    for name, t in (("in_w", in_w), ("in_bias", in_bias), ("out_w", out_w), ("out_bias", out_bias), ("block_mod_w", block_mod_w),
+                    ("block_mod_bias", block_mod_bias), ("head_mod_w", head_mod_w), ("head_mod_bias", head_mod_bias)):
+        setattr(m, name, None if t is None else t.data_ptr())
+    D = out_w.shape[0]
+    mod = torch.empty(6 * D, dtype=torch.bfloat16, device=out_w.device)
+    head = torch.empty(2 * D, dtype=torch.bfloat16, device=out_w.device)
+    ws = torch.empty(_lib.lib().b2_time_modulation_bf16_workspace_bytes(C.byref(m)), dtype=torch.uint8, device=out_w.device)
+    check(_lib.lib().b2_time_modulation_bf16(C.byref(m), C.c_float(timestep), _ptr(mod), _ptr(head), _ptr(ws), ws.numel(), _stream()))
+    return mod, head
+
+
 class DitGraphs:
     """b2_dit_graphs: CUDA graphs of whole forwards, least recently used first out. Creating one touches no device."""
 
@@ -580,7 +603,7 @@ class DitGraphs:
 
 
 def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, workspace=None, extra=None, ref_kv=None,
-                graphs=None, outs=None):
+                graphs=None, outs=None, mod=None, head=None):
     """rows: list of (text bf16 [S, D], skip mask int, latent index). latents f32 [n, 128, h, w]; time_vector numpy f32 [D].
     Returns the per-row outputs f32 [128, h, w] (and the workspace, for reuse). With `graphs` (a DitGraphs) the forward
     goes through b2_dit_forward_graphed on the current (non-default) stream; pass the same `outs` and `workspace` again for
@@ -592,10 +615,11 @@ def dit_forward(model: DitModel, latents, time_vector, rows, tier=TIER_INT8, wor
     arr = (_lib.ForwardRow * len(rows))()
     for i, (text, skip, latent) in enumerate(rows):
         arr[i].text, arr[i].text_len, arr[i].skip, arr[i].latent, arr[i].out = text.data_ptr(), text.shape[0], skip, latent, outs[i].data_ptr()
-    tv = np.ascontiguousarray(time_vector, np.float32)
+    tv = None if time_vector is None else np.ascontiguousarray(time_vector, np.float32)
     f = _lib.Forward()
     f.struct_size, f.latents, f.num_latents, f.height, f.width = C.sizeof(_lib.Forward), latents.data_ptr(), n, h, w
-    f.time_vector, f.rows, f.num_rows, f.tier = tv.ctypes.data, arr, len(rows), tier
+    f.time_vector, f.rows, f.num_rows, f.tier = (None if tv is None else tv.ctypes.data), arr, len(rows), tier
+    f.mod, f.head = (None if mod is None else mod.data_ptr()), (None if head is None else head.data_ptr())
     f.attention = _lib.AttentionOptions(ATTENTION_Q8_FP8_F32ACC, 0.0, 0.0)
     f.extra = None if extra is None else extra.data_ptr()
     f.ref_kv, f.ref_tokens = (None, 0) if ref_kv is None else (ref_kv.data_ptr(), ref_kv.shape[1])

@@ -423,3 +423,68 @@ def test_step_graphs_with_reference_images(ops):
         assert torch.equal(outs[0].view(torch.int32), want[0].view(torch.int32))
     graphs.close()
     assert ops.kernel_status() == (0, 0)
+
+
+def test_silu_and_the_bf16_time_modulation(ops):
+    """kernels::silu within one bf16 step of the float64 value (expf differs from libm by an ulp at most), and
+    MossDit::time_modulation's bf16 form (moss_dit.cpp:970-990) against float64 on the same bf16 weights: the linears are
+    the library's (cuBLASLt, as in the reference), so the bar is bf16 rounding of a 3072-term sum, not bits."""
+    rng = np.random.default_rng(41)
+    x = bfdev(to_bf16(rng.normal(0, 3, 4099)))
+    got = ops.silu_bf16(x).float().cpu().numpy().astype(np.float64)
+    xv = x.float().cpu().numpy().astype(np.float64)
+    want = xv / (1.0 + np.exp(-xv))
+    assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -7 + 1e-30)
+
+    D = 3072
+    t = lambda a: bfdev(to_bf16(a))
+    w = dict(in_w=t(rng.normal(0, 0.06, (D, 256))), in_bias=t(rng.normal(0, 0.1, D)), out_w=t(rng.normal(0, 0.02, (D, D))),
+             out_bias=t(rng.normal(0, 0.1, D)), block_mod_w=t(rng.normal(0, 0.02, (6 * D, D))), block_mod_bias=t(rng.normal(0, 0.3, 6 * D)),
+             head_mod_w=t(rng.normal(0, 0.02, (2 * D, D))), head_mod_bias=t(rng.normal(0, 0.3, 2 * D)))
+    f64 = {k: v.float().cpu().numpy().astype(np.float64) for k, v in w.items()}
+    rb = lambda a: to_bf16(a).view(np.uint16).astype(np.uint32).__lshift__(16).view(np.float32).astype(np.float64)
+    for timestep in (0.0, 0.731, 640.0):
+        mod, head = ops.time_modulation_bf16(**w, timestep=timestep)
+        phase = np.float64(np.float32(timestep)) * 10000.0 ** (-np.arange(128, dtype=np.float64) / 128)
+        emb = rb(np.concatenate([np.cos(phase), np.sin(phase)]).astype(np.float32).astype(np.float64))
+        hid = rb(f64["in_w"] @ emb + f64["in_bias"])
+        hid = rb(hid / (1.0 + np.exp(-hid)))
+        tim = rb(f64["out_w"] @ hid + f64["out_bias"])
+        for got_t, wt, bias in ((mod, "block_mod_w", "block_mod_bias"), (head, "head_mod_w", "head_mod_bias")):
+            want = f64[wt] @ tim + f64[bias]
+            g = got_t.float().cpu().numpy().astype(np.float64)
+            assert np.abs(g - want).max() <= 0.02 * np.abs(want).max(), (timestep, wt, np.abs(g - want).max(), np.abs(want).max())
+            assert np.corrcoef(g, want)[0, 1] >= 0.9999
+
+
+def test_dit_forward_with_given_modulation_vectors(ops):
+    """b2_forward::mod / head: a forward handed the vectors it would have computed from the time vector gives the same
+    bits, eagerly and through the step graphs (where the two buffers are inputs like any other)."""
+    D, F, h, w = 3072, 8192, 8, 8
+    model, _, p, _ = _model(ops, 2, F, 12)
+    rng = np.random.default_rng(43)
+    latents = torch.from_numpy(rng.normal(0, 1, (1, 128, h, w)).astype(np.float32)).cuda()
+    rows = [(bfdev(to_bf16(rng.normal(0, 1, (24, D)))), 0, 0)]
+    tv = rng.normal(0, 1, D).astype(np.float32)
+    want = ops.dit_forward(model, latents, tv, rows)[0][0].clone()
+    dtv = torch.from_numpy(tv).cuda()
+    mod = ops.linear_fp32_row(p["block_mod_w"], dtv, p["block_mod_bias"])
+    head = ops.linear_fp32_row(p["head_mod_w"], dtv, p["head_mod_bias"])
+    got = ops.dit_forward(model, latents, None, rows, mod=mod, head=head)[0][0]
+    assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+    with pytest.raises(ValueError, match="go together"):
+        ops.dit_forward(model, latents, tv, rows, mod=mod)
+    graphs = ops.DitGraphs(capacity=2)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        outs = ws = None
+        for _ in range(2):
+            outs, ws = ops.dit_forward(model, latents, None, rows, mod=mod, head=head, graphs=graphs, outs=outs, workspace=ws)
+            side.synchronize()
+            assert torch.equal(outs[0].view(torch.int32), want.view(torch.int32))
+        assert graphs.last_replayed
+        mod.mul_(0.5)                                   # other contents, same buffers: the same graph, another result
+        outs, ws = ops.dit_forward(model, latents, None, rows, mod=mod, head=head, graphs=graphs, outs=outs, workspace=ws)
+        side.synchronize()
+        assert graphs.last_replayed and not torch.equal(outs[0].view(torch.int32), want.view(torch.int32))
+    graphs.close()
