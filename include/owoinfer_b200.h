@@ -642,6 +642,9 @@ const b2_dit_model* b2_dit_file_model(const b2_dit_file* file);
  * reference runs this MLP in bf16 through cuBLASLt (moss_dit.cpp:970-990) unless a fp32 replacement is installed
  * (distill.h), so results agree with its fp32 form, not bit for bit with its bf16 form. */
 const b2_time_embedding* b2_dit_file_time_embedding(const b2_dit_file* file);
+/* The same MLP and the two modulation linears as bf16 device tensors for b2_time_modulation_bf16 (the reference's default
+ * form, moss_dit.cpp:970-990), or NULL when the file lacks the shell or the time embedding. */
+const b2_time_mlp_bf16* b2_dit_file_time_mlp_bf16(const b2_dit_file* file);
 void b2_dit_file_close(b2_dit_file* file);
 
 /* Every mbarrier wait inside the tensor-core kernels is bounded (200 ms); a CTA whose wait expired raises a device word,

@@ -23,7 +23,7 @@ EXPORTS = [
     "b2_moss_rope_table_reference", "b2_dit_prefill_workspace_bytes", "b2_dit_prefill_references",
     "b2_dit_file_open_expanded", "b2_silu_bf16", "b2_time_modulation_bf16_workspace_bytes", "b2_time_modulation_bf16",
     "b2_dit_graphs_create", "b2_dit_graphs_clear", "b2_dit_graphs_destroy", "b2_dit_graphs_stats", "b2_dit_forward_graphed",
-    "b2_dit_file_open", "b2_dit_file_get_info", "b2_dit_file_model", "b2_dit_file_time_embedding", "b2_dit_file_close",
+    "b2_dit_file_open", "b2_dit_file_get_info", "b2_dit_file_model", "b2_dit_file_time_embedding", "b2_dit_file_time_mlp_bf16", "b2_dit_file_close",
 ]
 
 
@@ -161,6 +161,8 @@ def lib() -> C.CDLL:
         l.b2_dit_file_close.argtypes = [C.c_void_p]
         l.b2_linear_bf16_workspace_bytes.restype = C.c_size_t
         l.b2_dit_forward_workspace_bytes.restype = C.c_size_t
+        l.b2_dit_file_time_mlp_bf16.restype = C.POINTER(TimeMlpBf16)
+        l.b2_dit_file_time_mlp_bf16.argtypes = [C.c_void_p]
         l.b2_time_modulation_bf16_workspace_bytes.restype = C.c_size_t
         l.b2_time_modulation_bf16_workspace_bytes.argtypes = [C.POINTER(TimeMlpBf16)]
         l.b2_time_modulation_bf16.argtypes = [C.POINTER(TimeMlpBf16), C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]

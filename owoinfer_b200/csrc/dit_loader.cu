@@ -568,6 +568,7 @@ struct b2_dit_file {
   std::vector<std::unique_ptr<b2_w4_weight>> w4;  // stable addresses for b2_linear::w4
   b2_dit_model model{};
   b2_time_embedding time{};
+  b2_time_mlp_bf16 time_bf16{};  // the same MLP and the modulation linears as bf16 device tensors (struct_size 0: absent)
   std::vector<float> te_w0, te_b0, te_w2, te_b2;
   b2_dit_file_info info{};
 };
@@ -812,6 +813,8 @@ int open_impl(const char* op, const char* path, bool expand, b2_dit_file** out) 
     const bool shell = f.find("shared_block_modulation.weight") != nullptr;
     const bool has_time = f.find("time_embedding.0.weight") != nullptr;
     if (shell) need += padded(6 * kDim * kDim * 2) + padded(2 * kDim * kDim * 2) + padded(kDim * kLatent * 2) * 2 + padded(8 * kDim * 4) + padded(kDim * 2) * 3 + 8192;
+    // The bf16 form of the time modulation: the timestep MLP and bf16 copies of the two modulation biases.
+    if (shell && has_time) need += padded(kDim * kFreq * 2) + padded(kDim * kDim * 2) + padded(kDim * 2) * 2 + padded(8 * kDim * 2) + 4096;
 
     auto file = std::make_unique<b2_dit_file>();
     if (const cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&file->arena.base), need); err != cudaSuccess) {
@@ -856,6 +859,19 @@ int open_impl(const char* op, const char* path, bool expand, b2_dit_file** out) 
       file->te_w2 = host("time_embedding.2.weight", {kDim, kDim});
       file->te_b2 = host("time_embedding.2.bias", {kDim});
       file->time = b2_time_embedding{sizeof(b2_time_embedding), kDim, file->te_w0.data(), file->te_b0.data(), file->te_w2.data(), file->te_b2.data()};
+      if (shell) {
+        b2_time_mlp_bf16& t = file->time_bf16;
+        t.dim = kDim;
+        t.in_w = ld.upload_bf16("time_embedding.0.weight", {kDim, kFreq});
+        t.in_bias = ld.upload_bf16("time_embedding.0.bias", {kDim});
+        t.out_w = ld.upload_bf16("time_embedding.2.weight", {kDim, kDim});
+        t.out_bias = ld.upload_bf16("time_embedding.2.bias", {kDim});
+        t.block_mod_w = m.block_mod_w;
+        t.block_mod_bias = ld.upload_bf16("shared_block_modulation.bias", {6 * kDim});
+        t.head_mod_w = m.head_mod_w;
+        t.head_mod_bias = ld.upload_bf16("video_head_modulation.bias", {2 * kDim});
+        t.struct_size = sizeof(b2_time_mlp_bf16);
+      }
     }
     ld.staging.drain();
     file->info = b2_dit_file_info{sizeof(b2_dit_file_info), blocks, static_cast<int>(F), expand && tier == B2_TIER_W4A8 ? B2_TIER_INT8 : tier, shell ? 1 : 0, has_time ? 1 : 0, file->arena.used, tier};
@@ -892,6 +908,10 @@ const b2_dit_model* b2_dit_file_model(const b2_dit_file* file) { return file == 
 
 const b2_time_embedding* b2_dit_file_time_embedding(const b2_dit_file* file) {
   return file == nullptr || file->info.has_time_embedding == 0 ? nullptr : &file->time;
+}
+
+const b2_time_mlp_bf16* b2_dit_file_time_mlp_bf16(const b2_dit_file* file) {
+  return file == nullptr || file->time_bf16.struct_size == 0 ? nullptr : &file->time_bf16;
 }
 
 void b2_dit_file_close(b2_dit_file* file) { delete file; }

@@ -696,6 +696,18 @@ class DitFile:
         check(_lib.lib().b2_time_vector_fp32(te, C.c_float(timestep), out.ctypes.data_as(C.c_void_p)))
         return out
 
+    def time_modulation_bf16(self, timestep: float):
+        """(mod bf16 [6 D], head bf16 [2 D]) through the bf16 form of the file's timestep MLP and modulation linears."""
+        m = _lib.lib().b2_dit_file_time_mlp_bf16(self.handle)
+        if not m:
+            raise ValueError("the file lacks the shell or the time embedding")
+        D = m.contents.dim
+        mod = torch.empty(6 * D, dtype=torch.bfloat16, device="cuda")
+        head = torch.empty(2 * D, dtype=torch.bfloat16, device="cuda")
+        ws = torch.empty(_lib.lib().b2_time_modulation_bf16_workspace_bytes(m), dtype=torch.uint8, device="cuda")
+        check(_lib.lib().b2_time_modulation_bf16(m, C.c_float(timestep), _ptr(mod), _ptr(head), _ptr(ws), ws.numel(), _stream()))
+        return mod, head
+
     def close(self):
         if self.handle:
             _lib.lib().b2_dit_file_close(self.handle)

@@ -82,6 +82,20 @@ def test_int8_file_with_shell(ops, tmp_path):
     want, _ = ops.dit_forward(model, latents, tv, rows)
     for a, b in zip(got, want):
         assert torch.equal(a.view(torch.int32), b.view(torch.int32)) and torch.isfinite(a).all() and a.abs().max() > 0
+    # The bf16 form of the time modulation from the file's tensors: the same as the same tensors handed over directly, and
+    # the same function as the fp32 form up to bf16 rounding.
+    mod, head = f.time_modulation_bf16(0.481)
+    b16 = lambda n: t[n].cuda().to(torch.bfloat16)
+    mod2, head2 = ops.time_modulation_bf16(b16("time_embedding.0.weight"), b16("time_embedding.0.bias"), b16("time_embedding.2.weight"),
+                                           b16("time_embedding.2.bias"), b16("shared_block_modulation.weight"),
+                                           b16("shared_block_modulation.bias"), b16("video_head_modulation.weight"),
+                                           b16("video_head_modulation.bias"), 0.481)
+    assert torch.equal(mod.view(torch.int16), mod2.view(torch.int16)) and torch.equal(head.view(torch.int16), head2.view(torch.int16))
+    dtv = torch.from_numpy(tv).cuda()
+    mod32 = ops.linear_fp32_row(c("shared_block_modulation.weight"), dtv, c("shared_block_modulation.bias").float())
+    assert (mod.float() - mod32.float()).abs().max() <= 0.03 * mod32.float().abs().max()
+    outs16, _ = ops.dit_forward(f.model, latents, None, rows, mod=mod, head=head)
+    assert torch.isfinite(outs16[0]).all()
     f.close()
 
 
