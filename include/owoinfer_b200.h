@@ -318,7 +318,9 @@ typedef struct b2_block_run {
   int max_seqlen;
   int tier;                  /* B2_TIER_* */
   b2_attention_options attention;
-  int fused_norm_rope;       /* -1 auto (>= 3072 tokens, dit_block_quant.cpp:32-35), 0 separate kernel, 1 in the pre-pass */
+  int fused_norm_rope;       /* -1 auto (in the pre-pass whenever the run has no slots or tap; same bits either way, and
+                              * faster here at every size: the reference's 3072-row switch, dit_block_quant.cpp:32-35, is an
+                              * sm_89 measurement), 0 separate kernel, 1 in the pre-pass */
   /* Reference keys and reference prefill (BlockRun of src/models/moss_dit/dit_block_fused.h:132-147). A caller built
    * against a header that ends at fused_norm_rope passes that struct_size and gets none of it. All zero / NULL: unused.
    * slot_rows > 0: attention reads keys and values from the region [slot A | the run's tokens | slot B], slot_rows rows

@@ -48,7 +48,6 @@ namespace b2 {
 namespace {
 
 constexpr std::size_t kAlign = 256;
-constexpr int kFusedNormRopeMinTokens = 3072;  // as the single-GPU block
 std::size_t align_up(std::size_t n) { return (n + kAlign - 1) / kAlign * kAlign; }
 
 struct Nccl {
@@ -343,7 +342,7 @@ int b2_run_block_quant_sp(const b2_block_weights* w, const b2_block_buffers* a, 
 
   // Attention over the full sequences, this rank's heads, half by half; QK-norm + RoPE in its pre-pass from 3072 tokens
   // on. The return exchange of a half starts as soon as its attention is done.
-  const bool fused = r.fused_norm_rope < 0 ? T >= kFusedNormRopeMinTokens : r.fused_norm_rope != 0;
+  const bool fused = r.fused_norm_rope != 0;  // automatic (< 0) = in the pre-pass, as in the single-GPU block
   const b2_qk_norm_rope nr{w->q_norm, w->k_norm, a->rope, 128};
   b2_attention_options ao = r.attention;
   if (ao.variant == 0) ao.variant = B2_ATTENTION_Q8_FP8_F32ACC;
